@@ -1,0 +1,157 @@
+/*
+ * tvb200: C ABI of the B200 runtime and kernels behind torch-vulkan's
+ * quantised matrix products.
+ *
+ * This is the boundary a host runtime binds (cgo / Rust FFI / ctypes / the
+ * C++ ATen layer in torch_vulkan_b200/csrc/aten): plain pointers and sizes, no
+ * torch types. It takes the place of the reference's C ABI between its C++
+ * ATen layer and its Rust runtime (crates/pyvk/csrc/vk.h:49-69, implemented in
+ * crates/pyvk/src/ffi.rs), with two changes: every call names a device (the
+ * reference has one), and the stringly-typed vkt_dispatch(name, spec, push,
+ * grid) is replaced by one typed launcher per kernel family.
+ *
+ * Conventions (as ffi.rs:1-4): functions return 0 on success and -1 on
+ * failure, with the message available from tvb_last_error() on the same
+ * thread. Kernels are queued on the device's stream (tvb_stream) and run
+ * asynchronously; tvb_synchronize waits. All pointers passed to the kernel
+ * launchers are device pointers unless said otherwise. There is no CPU
+ * fallback anywhere: without a usable GPU every call fails with a message.
+ */
+#ifndef TVB200_H
+#define TVB200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define TVB_API __attribute__((visibility("default")))
+#else
+#define TVB_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Element types (the kernel-name suffixes of the reference: "f32", "f16", "bf16", ...). */
+enum TvbDtype {
+  TVB_F32 = 0,
+  TVB_F16 = 1,
+  TVB_BF16 = 2,
+  TVB_E4M3 = 3, /* float8_e4m3fn */
+  TVB_E5M2 = 4, /* float8_e5m2 */
+  TVB_I8 = 5,
+  TVB_U8 = 6,
+  TVB_I32 = 7,
+  TVB_I64 = 8,
+  TVB_F64 = 9,
+  TVB_BOOL = 10,
+  TVB_I16 = 11
+};
+
+/* An allocation as seen by the host (replaces VktAlloc, vk.h:50-55: on CUDA
+ * the data pointer is the device address, so `host`/`address` collapse). */
+typedef struct TvbAlloc {
+  void* handle;   /* pass back to tvb_free */
+  void* ptr;      /* device pointer, 256-byte aligned */
+  uint64_t size;  /* bytes reserved (>= requested) */
+  int32_t device;
+  int32_t pad;
+} TvbAlloc;
+
+/* ---- runtime (replaces vkt_last_error / vkt_alloc / vkt_free / vkt_synchronize /
+ *      vkt_empty_cache / vkt_memory_stats / vkt_capabilities, vk.h:56-68) ---- */
+
+TVB_API const char* tvb_last_error(void);
+/* Number of usable sm_100 devices; -1 (with a message) if CUDA cannot start. */
+TVB_API int tvb_device_count(void);
+TVB_API int tvb_set_device(int device);
+TVB_API int tvb_current_device(void);
+TVB_API int tvb_device_name(int device, char* buf, size_t n);
+/* Feature bits in the reference's layout (vk.h:97-106): always
+ * float64|int16|float16|int8|bf16-matrices|shared32K = 1|2|4|8|16|32|64 on a B200. */
+TVB_API uint32_t tvb_capabilities(int device);
+TVB_API int tvb_alloc(int device, uint64_t nbytes, TvbAlloc* out);
+/* Returns the block to the device's pool (stream-ordered). Safe after tvb_shutdown. */
+TVB_API void tvb_free(void* handle);
+TVB_API int tvb_synchronize(int device);
+TVB_API int tvb_empty_cache(int device);
+TVB_API void tvb_memory_stats(int device, uint64_t* allocated, uint64_t* reserved, uint64_t* blocks);
+/* The CUDA stream (cudaStream_t) that every launcher queues on for `device`. */
+TVB_API void* tvb_stream(int device);
+/* Replaces the device's stream with a caller-owned one (NULL restores the runtime's own). */
+TVB_API int tvb_set_stream(int device, void* stream);
+/* Kernels launched so far (the reference's dispatch_count, crates/pyvk/src/lib.rs:112-116). */
+TVB_API uint64_t tvb_dispatch_count(void);
+/* Waits for queued work and releases every pool and stream. */
+TVB_API void tvb_shutdown(void);
+
+/* Copies: host<->device wait for completion when the host buffer is pageable
+ * (cudaMemcpyAsync semantics otherwise); device->device is stream-ordered. */
+TVB_API int tvb_memcpy_h2d(int device, void* dst, const void* src, uint64_t nbytes);
+TVB_API int tvb_memcpy_d2h(int device, void* dst, const void* src, uint64_t nbytes);
+TVB_API int tvb_memcpy_d2d(int device, void* dst, const void* src, uint64_t nbytes);
+
+/* ---- data movement kernels (the slice of the reference's cast / move / fill
+ *      kernels that the four ops and their tests need: cast.slang, move.slang) */
+
+/* dst[i...] = convert(src[i...]) over `ndim` (<= 8) dimensions with element strides. */
+TVB_API int tvb_copy_strided(int device, void* dst, int dst_dtype, const int64_t* dst_strides, const void* src, int src_dtype,
+                     const int64_t* src_strides, const int64_t* sizes, int ndim);
+/* Every element of a strided tensor of `itemsize`-byte elements set to the low bytes of `bits`. */
+TVB_API int tvb_fill_strided(int device, void* dst, int itemsize, uint64_t bits, const int64_t* strides, const int64_t* sizes,
+                     int ndim);
+
+/* ---- aten::_weight_int8pack_mm (replaces vkt_dispatch("qmm8_<f32|f16|bf16>", ...),
+ *      crates/pyvk/csrc/quant.cpp:86-117; parameters as Q8Params, quant.cpp:31-37) ----
+ * C[m, n] = A[m, k] @ (int8 B[n, k] * scales[n]).T, float32 accumulation, rounded once
+ * to `dtype`. a_sm: A's row stride in elements (column stride 1). scales and C have A's
+ * dtype; B and C are contiguous. variant: 0 automatic, 1 the plain CUDA-core kernel,
+ * 2 the TMA-fed skinny kernel (m <= 64, 16-bit A, k % 128 == 0), 3 the tcgen05 kernel. */
+TVB_API int tvb_qmm8(int device, const void* a, int dtype, int64_t a_sm, const int8_t* b, const void* scales, void* c,
+             int64_t m, int64_t n, int64_t k, int variant);
+
+/* ---- aten::_dyn_quant_pack_4bit_weight (replaces the cat of three casts,
+ *      quant.cpp:139-143) ----
+ * packed[0..nw) = float(weights bytes), then float(scales) [ns], then float(bias) [nbias]. */
+TVB_API int tvb_qmm4_pack(int device, const uint8_t* weights, int64_t nw, const void* scales, int scales_dtype, int64_t ns,
+                  const void* bias, int bias_dtype, int64_t nbias, float* packed);
+
+/* ---- aten::_dyn_quant_matmul_4bit (replaces the two vkt_dispatch("qmm4_*") phases,
+ *      quant.cpp:187-202; parameters as Q4Params, quant.cpp:39-43) ---- */
+
+/* PHASE 0 (qmm4.slang:132-181): per-row asymmetric int8 quantisation of inp [m, k]
+ * (float32 or bfloat16, contiguous). q: int8 [m, k]; recip: float [m] (1 / scale);
+ * neg_zp: int32 [m] (-zero point). groupwise selects the zero point's association. */
+TVB_API int tvb_qmm4_quantize(int device, const void* inp, int dtype, int64_t m, int64_t k, int groupwise, int8_t* q,
+                      float* recip, int32_t* neg_zp);
+/* PHASE 1 (qmm4.slang:183-247): out[m, n] from q, the rows' recip / -zp and the packed
+ * float32 vector (weights' bytes as floats, scales, optional bias). iacc_out (optional,
+ * int32 [m, n, k / bs]) receives every block's integer sum. */
+TVB_API int tvb_qmm4_matmul(int device, const int8_t* q, const float* recip, const int32_t* neg_zp, const float* packed,
+                    int has_bias, void* out, int dtype, int64_t m, int64_t n, int64_t k, int64_t bs,
+                    int32_t* iacc_out);
+/* Bytes of scratch tvb_qmm4 needs for an [m, k] input. */
+TVB_API uint64_t tvb_qmm4_workspace_bytes(int64_t m, int64_t k);
+/* Both phases; workspace: device scratch of at least tvb_qmm4_workspace_bytes(m, k). */
+TVB_API int tvb_qmm4(int device, const void* inp, int dtype, const float* packed, int has_bias, void* out, int64_t m,
+             int64_t n, int64_t k, int64_t bs, void* workspace, uint64_t workspace_bytes);
+
+/* ---- aten::_scaled_mm (replaces the chain of cast / mul / matmul / add / cast
+ *      dispatches, quant.cpp:283-299) ----
+ * out[m, n] = cast((a * scale_a) @ (b * scale_b) + bias) (float8 outputs: times
+ * 1 / *scale_result). a: float8 [m, k], element (i, kk) at a[i * a_s0 + kk * a_s1];
+ * b: float8 [k, n], element (kk, j) at b[kk * b_s0 + j * b_s1] (strides in elements).
+ * a_dtype / b_dtype: TVB_E4M3 or TVB_E5M2. scale_a / scale_b: device float32, one element
+ * (rowwise 0) or m / n elements (rowwise 1). bias: n elements of bias_dtype, or NULL.
+ * scale_result: device float32 or NULL. out: contiguous [m, n] of out_dtype (F32, F16,
+ * BF16, E4M3, E5M2). variant: 0 automatic, 1 the plain kernel, 2 the tcgen05 kernel. */
+TVB_API int tvb_scaled_mm(int device, const void* a, int a_dtype, int64_t a_s0, int64_t a_s1, const void* b, int b_dtype,
+                  int64_t b_s0, int64_t b_s1, const float* scale_a, const float* scale_b, int rowwise,
+                  const void* bias, int bias_dtype, const float* scale_result, void* out, int out_dtype, int64_t m,
+                  int64_t n, int64_t k, int variant);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TVB200_H */

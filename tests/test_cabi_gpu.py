@@ -1,0 +1,157 @@
+"""GPU parity of the CUDA kernels, called through the C ABI (include/tvb200.h) with
+device pointers, against the CPU oracle on the same seeded inputs. The cases are the
+reference's own (tests/python/test_quant.py) plus shapes around the kernels' tile
+sizes. Bit-exact where the op is integer / defined bit for bit (dyn-int4), within
+the reference's error bound elsewhere."""
+
+import pytest
+import torch
+
+import _cases as C
+from oracle import oracle as O
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def abi():
+    from torch_vulkan_b200 import cabi
+
+    assert cabi.lib().tvb_device_count() >= 1, cabi.lib().tvb_last_error()
+    return cabi
+
+
+def dev(t):
+    return None if t is None else t.cuda()
+
+
+# ---------------------------------------------------------------- int8 weight-only
+
+@pytest.mark.parametrize("dtype", C.INT8_DTYPES)
+@pytest.mark.parametrize("m,k,n", C.INT8_SHAPES)
+def test_qmm8_reference_cases(abi, dtype, m, k, n):
+    a, b, s = C.int8_case(dtype, m, k, n)
+    want, tol = C.int8_want(a, b, s)
+    got = abi.qmm8(dev(a), dev(b), dev(s))
+    sliced = abi.qmm8(dev(a)[::2], dev(b), dev(s))
+    abi.synchronize()
+    assert ((got.cpu().float() - want.float()).abs() <= tol).all()
+    assert ((sliced.cpu().float() - want[::2].float()).abs() <= tol[::2]).all()
+    oracle = O.weight_int8pack_mm(a, b, s)
+    assert ((got.cpu().float() - oracle.float()).abs() <= 2 * tol).all()
+
+
+@pytest.mark.parametrize("variant", [1, 2])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("m,k,n", [(1, 128, 8), (1, 256, 257), (3, 1024, 255), (8, 4096, 300), (9, 512, 1000), (16, 2048, 4099),
+                                   (13, 8192, 520), (33, 256, 77), (64, 384, 513)])
+def test_qmm8_kernel_variants(abi, variant, dtype, m, k, n):
+    a, b, s = C.config_int8(m, k, n, dtype, seed=m + n)
+    want, tol = C.int8_want(a, b, s)
+    got = abi.qmm8(dev(a), dev(b), dev(s), variant=variant)
+    abi.synchronize()
+    err = (got.cpu().float() - want.float()).abs()
+    assert (err <= tol).all(), f"max excess {(err - tol).max()}"
+
+
+def test_qmm8_skinny_is_deterministic_and_repeatable(abi):
+    a, b, s = C.config_int8(16, 1024, 3000, torch.bfloat16)
+    da, db, ds = dev(a), dev(b), dev(s)
+    first = abi.qmm8(da, db, ds, variant=2)
+    for _ in range(3):
+        again = abi.qmm8(da, db, ds, variant=2)
+        abi.synchronize()
+        assert torch.equal(first, again)
+
+
+def test_qmm8_decode_shape_sample(abi):
+    # the decode benchmark's k with a slice of its n: every SM's unit range crosses tiles
+    a, b, s = C.config_int8(4, 8192, 3584, torch.bfloat16)
+    want, tol = C.int8_want(a, b, s)
+    got = abi.qmm8(dev(a), dev(b), dev(s))
+    abi.synchronize()
+    assert ((got.cpu().float() - want.float()).abs() <= tol).all()
+
+
+def test_qmm8_fp32_config1(abi):
+    a, b, s = C.config_int8(32, 4096, 4096, torch.float32)
+    want, tol = C.int8_want(a, b, s)
+    got = abi.qmm8(dev(a), dev(b), dev(s))
+    abi.synchronize()
+    assert ((got.cpu() - want).abs() <= tol).all()
+
+
+# ---------------------------------------------------------------- dyn-int4
+
+@pytest.mark.parametrize("m,k,n,bs,bias", C.DYN4_CASES + [(33, 512, 130, 128, True), (70, 1024, 257, 32, True),
+                                                             (2, 4096, 512, 32, True)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_qmm4_bit_exact(abi, m, k, n, bs, bias, dtype):
+    if dtype == torch.bfloat16 and bs != k:
+        pytest.skip("bfloat16 inputs are channelwise only (the CPU's check)")
+    x, w, sc, bvec = C.dyn4_case(m, k, n, bs, bias, dtype)
+    packed = O.dyn_quant_pack_4bit_weight(w, sc, bvec, bs, k, n)
+    want, want_iacc = O.dyn_quant_matmul_4bit(x, packed, bs, k, n, return_iacc=True)
+    wq, wrecip, wzp, _ = O.dyn_quant_quantize(x, bs != k)
+
+    packed_dev = abi.qmm4_pack(dev(w), dev(sc), dev(bvec))
+    q, recip, neg_zp = abi.qmm4_quantize(dev(x), bs != k)
+    got, iacc = abi.qmm4_matmul(q, recip, neg_zp, packed_dev, n, k, bs, dtype, return_iacc=True)
+    fused = abi.qmm4(dev(x), dev(packed), bs, k, n)
+    abi.synchronize()
+    assert torch.equal(packed_dev.cpu(), packed)
+    assert torch.equal(q.cpu().int(), wq)
+    assert torch.equal(recip.cpu().view(torch.int32), wrecip.view(torch.int32))
+    assert torch.equal(neg_zp.cpu(), wzp)
+    assert torch.equal(iacc.cpu(), want_iacc)
+    assert torch.equal(got.cpu().view(torch.int16 if dtype == torch.bfloat16 else torch.int32),
+                       want.view(torch.int16 if dtype == torch.bfloat16 else torch.int32))
+    assert torch.equal(fused.cpu(), want)
+
+
+# ---------------------------------------------------------------- float8
+
+@pytest.mark.parametrize("variant", [0, 1])
+@pytest.mark.parametrize("fa,fb", [(C.FLOAT8[0], C.FLOAT8[0]), (C.FLOAT8[1], C.FLOAT8[0]), (C.FLOAT8[0], C.FLOAT8[1])])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32, torch.float16, torch.float8_e4m3fn, None])
+@pytest.mark.parametrize("rowwise", [False, True])
+def test_scaled_mm_reference_cases(abi, variant, fa, fb, out_dtype, rowwise):
+    a, b, sa, sb, bias, sr = C.scaled_case(fa, fb, out_dtype, rowwise)
+    want, tol = C.scaled_want(a, b, sa, sb, bias, sr, out_dtype)
+    got = abi.scaled_mm(dev(a), dev(b), dev(sa), dev(sb), dev(bias), dev(sr), out_dtype, variant=variant)
+    abi.synchronize()
+    assert got.dtype == want.dtype and got.shape == want.shape
+    assert ((got.cpu().float() - want.float()).abs() <= tol).all()
+
+
+@pytest.mark.parametrize("fa,fb", [(C.FLOAT8[0], C.FLOAT8[0]), (C.FLOAT8[1], C.FLOAT8[0]), (C.FLOAT8[0], C.FLOAT8[1])])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32, torch.float16, torch.float8_e4m3fn])
+@pytest.mark.parametrize("rowwise", [False, True])
+@pytest.mark.parametrize("m,k,n", [(128, 128, 256), (130, 144, 264), (1, 16, 8), (257, 1024, 511), (384, 4096 + 32, 768)])
+def test_scaled_mm_tcgen05(abi, fa, fb, out_dtype, rowwise, m, k, n):
+    a, b, sa, sb, bias, sr = C.scaled_case(fa, fb, out_dtype, rowwise, m=m, k=k, n=n)
+    want, tol = C.scaled_want(a, b, sa, sb, bias, sr, out_dtype)
+    got = abi.scaled_mm(dev(a), dev(b), dev(sa), dev(sb), dev(bias), dev(sr), out_dtype, variant=2)
+    abi.synchronize()
+    err = (got.cpu().float() - want.float()).abs()
+    ok = err <= tol
+    # float8 outputs: a value within float32 rounding of a rounding boundary may land on either neighbour
+    if out_dtype in C.FLOAT8:
+        assert ok.float().mean() > 0.999
+        up = (want.float().abs() * 2**-2).clamp_min(2**-9)
+        assert (err <= up + tol).all()
+    else:
+        assert ok.all(), f"max excess {(err - tol).max()} at {(err - tol).argmax()}"
+
+
+def test_scaled_mm_config4_sample(abi):
+    for rowwise in (False, True):
+        a, b, sa, sb = C.config_fp8(512, 8192, 1024, rowwise)
+        want, tol = C.scaled_want(a, b, sa, sb, None, None, torch.bfloat16)
+        got = abi.scaled_mm(dev(a), dev(b), dev(sa), dev(sb), None, None, torch.bfloat16)
+        abi.synchronize()
+        assert ((got.cpu().float() - want.float()).abs() <= tol).all()
+        # the benchmark's stated bound: within 2 bfloat16 ulp of the float64-accumulated product
+        ref64 = (a.double() * sa.double()) @ (b.double() * sb.double())
+        ulp = torch.finfo(torch.bfloat16).eps * ref64.abs().clamp_min(2.0**-8 * ref64.abs().max())
+        assert ((got.cpu().double() - ref64).abs() <= 2 * ulp).all()

@@ -1,0 +1,177 @@
+// The tcgen05 GEMM main loop shared by the large-m kernels of this library:
+// D[m, n] = A[m, k] . B[n, k]^T with both operands K-major in global memory.
+//
+// One persistent CTA per SM walks 128 x BN output tiles. Warp roles:
+//   warp 4, one lane: TMA producer. Fills a ring of shared-memory stages, each holding a
+//            128-row slice of A and a BN-row slice of B, 128 bytes of k wide, written by
+//            cp.async.bulk.tensor with the 128-byte swizzle (no cluster multicast).
+//   warp 5, one lane: issues tcgen05.mma (four per stage, 32 bytes of k each) into one of two
+//            TMEM accumulator buffers (2 x BN columns of float32 / int32), and
+//            tcgen05.commit's each stage back to the producer and each finished tile to the
+//            epilogue. The warp also owns the TMEM allocation.
+//   warps 0-3: epilogue. Each warp reads its 32 TMEM lanes (one output row per thread)
+//            32 columns at a time with tcgen05.ld and hands them to the Epilogue policy,
+//            while the MMA warp already works on the next tile in the other buffer.
+// All mbarrier waits are bounded (ptx::mbar_wait); a wait that runs out makes every role
+// leave its loop, the TMEM allocation is released, and the status word tells the host.
+#pragma once
+
+#include <cuda.h>
+
+#include "ptx.cuh"
+
+namespace tvb {
+
+struct GemmTcShape {
+  int m, n;
+  int kblocks;       // ceil(k bytes / 128)
+  int k_elems_per_block;  // 128 for 8-bit operands, 64 for 16-bit
+  int tiles_m, tiles_n;
+};
+
+template <int BN, int EPI_SMEM>
+struct GemmTcCfg {
+  static constexpr int kBM = 128;
+  static constexpr int kStageA = kBM * 128, kStageB = BN * 128, kStage = kStageA + kStageB;
+  static constexpr int kStages = (200 * 1024 - EPI_SMEM) / kStage;
+  static constexpr int kThreads = 192;
+  static constexpr int kTmemCols = 2 * BN <= 32 ? 32 : (2 * BN <= 64 ? 64 : (2 * BN <= 128 ? 128 : (2 * BN <= 256 ? 256 : 512)));
+  static constexpr int kBarBytes = 256;
+  static constexpr int kSmemBytes = kStages * kStage + 1024 + kBarBytes + EPI_SMEM;
+};
+
+// Epilogue policy interface:
+//   struct Params;                       kernel parameters of the epilogue
+//   static constexpr int kSmemBytes;     per-CTA shared memory of the epilogue
+//   __device__ static void begin_tile(const Params&, uint8_t* smem, int row0, int col0, int m, int n, int tid);
+//       called by all 128 epilogue threads before a tile's loads (they synchronise inside as needed)
+//   __device__ static void store(const Params&, const uint8_t* smem, int row, int col_tile0, int col_off,
+//                                const uint32_t (&acc)[32], int m, int n);
+//       thread `row`'s 32 accumulators for columns col_tile0 + col_off ... + 31
+template <int KIND, int BN, class Epi>
+__global__ void __launch_bounds__(192, 1)
+    gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmTcShape sh,
+                   const uint32_t idesc, const typename Epi::Params ep, int* status) {
+  using Cfg = GemmTcCfg<BN, Epi::kSmemBytes>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* base_ptr = smem_raw + (base - ptx::smem_u32(smem_raw));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(base_ptr + Cfg::kStages * Cfg::kStage);
+  const uint32_t full0 = ptx::smem_u32(bars), empty0 = full0 + 8 * Cfg::kStages;
+  const uint32_t tfull0 = empty0 + 8 * Cfg::kStages, tempty0 = tfull0 + 16;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * Cfg::kStages + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  uint8_t* epi_smem = base_ptr + Cfg::kStages * Cfg::kStage + Cfg::kBarBytes;
+  static_assert((2 * 8 + 4) * 8 + 8 <= Cfg::kBarBytes, "barrier area too small");
+  static_assert(Cfg::kStages >= 2 && Cfg::kStages <= 8, "stage count out of range");
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < Cfg::kStages; s++) {
+      ptx::mbar_init(full0 + 8 * s, 1);
+      ptx::mbar_init(empty0 + 8 * s, 1);
+    }
+    for (int a = 0; a < 2; a++) {
+      ptx::mbar_init(tfull0 + 8 * a, 1);
+      ptx::mbar_init(tempty0 + 8 * a, 128);
+    }
+    *abort_flag = 0;
+    ptx::fence_mbar_init();
+  }
+  if (warp == 5) ptx::tmem_alloc(ptx::smem_u32(tmem_slot), Cfg::kTmemCols);
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const int tiles = sh.tiles_m * sh.tiles_n;
+
+  if (warp == 4) {
+    if (lane == 0) {
+      ptx::prefetch_tensormap(&map_a);
+      ptx::prefetch_tensormap(&map_b);
+      long long it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
+        const int tm = tile % sh.tiles_m, tn = tile / sh.tiles_m;
+        for (int kb = 0; kb < sh.kblocks; kb++, it++) {
+          const int s = static_cast<int>(it % Cfg::kStages);
+          const uint32_t ph = static_cast<uint32_t>((it / Cfg::kStages) & 1);
+          ok = ptx::mbar_wait(empty0 + 8 * s, ph ^ 1u, abort_flag);
+          if (!ok) break;
+          const uint32_t dst = base + s * Cfg::kStage;
+          ptx::mbar_expect_tx(full0 + 8 * s, Cfg::kStage);
+          ptx::tma_load_2d(dst, &map_a, kb * sh.k_elems_per_block, tm * Cfg::kBM, full0 + 8 * s);
+          ptx::tma_load_2d(dst + Cfg::kStageA, &map_b, kb * sh.k_elems_per_block, tn * BN, full0 + 8 * s);
+        }
+      }
+      // no copy may still be in flight when the CTA's shared memory is released
+      const long long first = it > Cfg::kStages ? it - Cfg::kStages : 0;
+      for (long long j = first; j < it; j++) {
+        volatile int never = 0;
+        ptx::mbar_wait(full0 + 8 * static_cast<int>(j % Cfg::kStages), static_cast<uint32_t>((j / Cfg::kStages) & 1), &never);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 5) {
+    if (lane == 0) {
+      long long it = 0;
+      int titer = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, titer++) {
+        const int acc = titer & 1;
+        const uint32_t aph = static_cast<uint32_t>((titer >> 1) & 1);
+        ok = ptx::mbar_wait(tempty0 + 8 * acc, aph ^ 1u, abort_flag);  // the epilogue has drained this buffer
+        if (!ok) break;
+        ptx::tc_fence_after();
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
+        for (int kb = 0; kb < sh.kblocks; kb++, it++) {
+          const int s = static_cast<int>(it % Cfg::kStages);
+          const uint32_t ph = static_cast<uint32_t>((it / Cfg::kStages) & 1);
+          ok = ptx::mbar_wait(full0 + 8 * s, ph, abort_flag);
+          if (!ok) break;
+          ptx::tc_fence_after();
+          const uint64_t a_desc = ptx::tc_smem_desc_sw128(base + s * Cfg::kStage);
+          const uint64_t b_desc = ptx::tc_smem_desc_sw128(base + s * Cfg::kStage + Cfg::kStageA);
+#pragma unroll
+          for (int j = 0; j < 4; j++)  // 32 bytes of k per instruction: +2 in the descriptor's 16-byte units
+            ptx::tc_mma<KIND>(d_tmem, a_desc + 2 * j, b_desc + 2 * j, idesc, (kb | j) != 0 ? 1u : 0u);
+          ptx::tc_commit(empty0 + 8 * s);
+        }
+        if (ok) ptx::tc_commit(tfull0 + 8 * acc);
+      }
+    }
+    __syncwarp();
+  } else {
+    int titer = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, titer++) {
+      const int tm = tile % sh.tiles_m, tn = tile / sh.tiles_m;
+      const int acc = titer & 1;
+      const uint32_t aph = static_cast<uint32_t>((titer >> 1) & 1);
+      Epi::begin_tile(ep, epi_smem, tm * Cfg::kBM, tn * BN, sh.m, sh.n, threadIdx.x);
+      ok = ptx::mbar_wait(tfull0 + 8 * acc, aph, abort_flag);
+      if (!ok) break;
+      ptx::tc_fence_after();
+      const int row = tm * Cfg::kBM + warp * 32 + lane;
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + static_cast<uint32_t>(acc * BN);
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; c++) {
+        uint32_t r[32];
+        ptx::tmem_ld_32x32(taddr + c * 32, r);
+        ptx::tmem_ld_wait();
+        Epi::store(ep, epi_smem, row, tn * BN, c * 32, r, sh.m, sh.n);
+      }
+      ptx::tc_fence_before();
+      ptx::mbar_arrive(tempty0 + 8 * acc);
+    }
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (threadIdx.x == 0 && *abort_flag != 0) atomicExch(status, 2);
+  if (warp == 5) {
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc(tmem_base, Cfg::kTmemCols);
+  }
+}
+
+}  // namespace tvb

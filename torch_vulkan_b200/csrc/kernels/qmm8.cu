@@ -1,0 +1,415 @@
+// aten::_weight_int8pack_mm on sm_100a: C[m, n] = A[m, k] @ (int8 B[n, k] * scales[n]).T
+//
+// What it computes is the reference's qmm8 shader (crates/vkcore/shaders/qmm8.slang:
+// float32 accumulation of A times the dequantised weights, rounded once to A's dtype;
+// launched from crates/pyvk/csrc/quant.cpp:86-117). How it computes it is not:
+//
+//  * qmm8_skinny_kernel (m <= 16 per pass, 16-bit A): the decode path, bound by
+//    streaming B from HBM once. Persistent CTAs, one per SM. One producer lane feeds
+//    a ring of shared-memory stages with TMA (128-byte-swizzled boxes of 256 weight
+//    rows x 128 k, plus the matching slice of A); eight consumer warps read 16 bytes
+//    per lane, widen int8 to bf16 / f16 exactly in registers (two byte permutes and a
+//    packed subtract per pair) and multiply with mma.sync m16n8k16 (weights as the
+//    16-row operand, tokens as the 8-column operand), float32 accumulators.
+//    Work is the list of (256-row tile, 128-k chunk) units cut into equal contiguous
+//    ranges, one per CTA, so every SM streams the same number of bytes whatever n is;
+//    a tile shared by several CTAs is finished by the last of them to arrive, which adds
+//    the partial sums in CTA order (deterministic), from scratch memory. The scale
+//    multiplies the finished sum: (sum a*b) * s instead of sum a*(b*s); both are within
+//    the float32 rounding the reference's tests allow (tests/python/test_quant.py:36-40).
+//  * qmm8_plain_kernel: any shape, stride and dtype (float32 A included), one warp per
+//    output column, as the shader's matrix-vector path (qmm8.slang:78-111).
+#include <cuda.h>
+
+#include "../core/common.h"
+#include "../core/tensormap.h"
+#include "numerics.cuh"
+#include "ptx.cuh"
+
+namespace tvb {
+namespace {
+
+// ------------------------------------------------------------------ plain kernel
+
+constexpr int kPlainRows = 8;
+
+template <int DT>
+__global__ void __launch_bounds__(256) qmm8_plain_kernel(const void* __restrict__ a, int64_t a_sm,
+                                                         const int8_t* __restrict__ b, const void* __restrict__ scales,
+                                                         void* __restrict__ c, int m, int n, int k) {
+  int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  int col = blockIdx.x * 8 + warp;
+  if (col >= n) return;
+  float scale = load_float<DT>(scales, col);
+  const int8_t* brow = b + static_cast<int64_t>(col) * k;
+  for (int r0 = blockIdx.y * kPlainRows; r0 < m; r0 += gridDim.y * kPlainRows) {
+    float acc[kPlainRows];
+#pragma unroll
+    for (int r = 0; r < kPlainRows; r++) acc[r] = 0.0f;
+    int rows = min(kPlainRows, m - r0);
+    for (int kk = lane; kk < k; kk += 32) {
+      float w = static_cast<float>(static_cast<int>(brow[kk])) * scale;
+#pragma unroll
+      for (int r = 0; r < kPlainRows; r++)
+        if (r < rows) acc[r] = fmaf(load_float<DT>(a, static_cast<int64_t>(r0 + r) * a_sm + kk), w, acc[r]);
+    }
+#pragma unroll
+    for (int r = 0; r < kPlainRows; r++) {
+      float v = acc[r];
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+      if (lane == 0 && r < rows) store_float<DT>(c, static_cast<int64_t>(r0 + r) * n + col, v);
+    }
+  }
+}
+
+// ------------------------------------------------------------------ skinny kernel
+
+constexpr int kChunkK = 128;  // k values (= bytes of a weight row) per pipeline stage
+
+template <int NT, int RW, int NWARPS>
+struct SkinnyCfg {
+  static constexpr int kRowsPerTile = NWARPS * RW * 16;
+  static constexpr int kTokens = NT * 8;
+  static constexpr int kWeightBytes = kRowsPerTile * kChunkK;   // one TMA box
+  static constexpr int kTokenBoxBytes = kTokens * 128;          // 64 k of 16-bit values per row: two boxes per stage
+  static constexpr int kStageBytes = kWeightBytes + 2 * kTokenBoxBytes;
+  static constexpr int kStages = (220 * 1024) / kStageBytes < 8 ? (220 * 1024) / kStageBytes : 8;
+  static constexpr int kThreads = (NWARPS + 1) * 32;
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /* alignment slack */ + 256 /* barriers */;
+  static constexpr int kPartialFloats = NWARPS * RW * NT * 32 * 4;  // one CTA's accumulators
+};
+
+// int8 x 4 (one 32-bit word, k ascending) -> two packed pairs of 16-bit floats, exactly.
+// bf16: the low 7 bits ride a 2^7 exponent (0x4300 | l = 128 + l); the same exponent with
+// the sign bit as its top mantissa bit is 128 or 256; their difference is the int8 value.
+// f16: 0x6400 | (x + 128) = 1024 + 128 + x; subtract 1152.
+template <int DT>
+__device__ __forceinline__ void widen_int8x4(uint32_t w, uint32_t& lo, uint32_t& hi) {
+  if (DT == TVB_BF16) {
+    uint32_t l = w & 0x7f7f7f7fu, s = w & 0x80808080u;
+    lo = ptx::sub_bf16x2(ptx::prmt(l, 0x43434343u, 0x4140u), ptx::prmt(s, 0x43434343u, 0x4140u));
+    hi = ptx::sub_bf16x2(ptx::prmt(l, 0x43434343u, 0x4342u), ptx::prmt(s, 0x43434343u, 0x4342u));
+  } else {
+    uint32_t u = w ^ 0x80808080u;
+    lo = ptx::sub_f16x2(ptx::prmt(u, 0x64646464u, 0x4140u), 0x64806480u);
+    hi = ptx::sub_f16x2(ptx::prmt(u, 0x64646464u, 0x4342u), 0x64806480u);
+  }
+}
+
+template <int DT>
+__device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                          uint32_t b1) {
+  if (DT == TVB_BF16) ptx::mma_bf16_16816(d, a0, a1, a2, a3, b0, b1);
+  else ptx::mma_f16_16816(d, a0, a1, a2, a3, b0, b1);
+}
+
+struct SkinnyParams {
+  const void* scales;
+  void* c;
+  float* partials;   // [grid][2][kPartialFloats]
+  int* counters;     // [tiles], zero between launches
+  int* status;
+  int m, n, k;
+  int m0;            // first token row of this pass
+  int tiles, chunks; // tiles = ceil(n / rows per tile), chunks = k / 128
+};
+
+// First unit of CTA c when `units` units are cut into `grid` contiguous ranges.
+__device__ __forceinline__ long long range_start(long long c, long long units, long long grid) { return c * units / grid; }
+// The CTA whose range holds unit x.
+__device__ __forceinline__ int range_owner(long long x, long long units, long long grid) {
+  return static_cast<int>(((x + 1) * grid + units - 1) / units - 1);
+}
+
+template <int DT, int NT, int RW, int NWARPS>
+__global__ void __launch_bounds__((NWARPS + 1) * 32, 1)
+    qmm8_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
+                       const SkinnyParams p) {
+  using Cfg = SkinnyCfg<NT, RW, NWARPS>;
+  extern __shared__ uint8_t smem_raw[];
+  // stages need 1024-byte alignment for the 128-byte swizzle pattern
+  uint32_t base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* base_ptr = smem_raw + (base - ptx::smem_u32(smem_raw));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(base_ptr + Cfg::kStages * Cfg::kStageBytes);
+  const uint32_t full0 = ptx::smem_u32(bars), empty0 = full0 + 8 * Cfg::kStages;
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 2 * Cfg::kStages);
+  int* last_flag = const_cast<int*>(abort_flag) + 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < Cfg::kStages; s++) {
+      ptx::mbar_init(full0 + 8 * s, 1);
+      ptx::mbar_init(empty0 + 8 * s, NWARPS);
+    }
+    *abort_flag = 0;
+    *last_flag = 0;
+    ptx::fence_mbar_init();
+  }
+  __syncthreads();
+
+  const long long units = static_cast<long long>(p.tiles) * p.chunks;
+  const long long grid = gridDim.x;
+  const long long u0 = range_start(blockIdx.x, units, grid), u1 = range_start(blockIdx.x + 1, units, grid);
+
+  if (warp == NWARPS) {
+    // ---------------- producer: one lane issues every TMA copy
+    if (lane == 0) {
+      ptx::prefetch_tensormap(&map_w);
+      ptx::prefetch_tensormap(&map_a);
+      const uint64_t stream_policy = ptx::policy_evict_first();  // weights are read once
+      const uint64_t keep_policy = ptx::policy_evict_last();     // every CTA re-reads A
+      long long it = 0;
+      bool ok = true;
+      for (long long u = u0; u < u1 && ok; u++, it++) {
+        int tile = static_cast<int>(u / p.chunks), chunk = static_cast<int>(u % p.chunks);
+        int s = static_cast<int>(it % Cfg::kStages);
+        uint32_t ph = static_cast<uint32_t>((it / Cfg::kStages) & 1);
+        ok = ptx::mbar_wait(empty0 + 8 * s, ph ^ 1u, abort_flag);
+        if (!ok) break;
+        uint32_t dst = base + s * Cfg::kStageBytes;
+        ptx::mbar_expect_tx(full0 + 8 * s, Cfg::kStageBytes);
+        ptx::tma_load_2d_hint(dst, &map_w, chunk * kChunkK, tile * Cfg::kRowsPerTile, full0 + 8 * s, stream_policy);
+        ptx::tma_load_2d_hint(dst + Cfg::kWeightBytes, &map_a, chunk * kChunkK, p.m0, full0 + 8 * s, keep_policy);
+        ptx::tma_load_2d_hint(dst + Cfg::kWeightBytes + Cfg::kTokenBoxBytes, &map_a, chunk * kChunkK + 64, p.m0,
+                              full0 + 8 * s, keep_policy);
+      }
+      // Leave no copy in flight behind: every stage that was armed has landed before the CTA ends.
+      long long first = it > Cfg::kStages ? it - Cfg::kStages : 0;
+      for (long long j = first; j < it; j++) {
+        int s = static_cast<int>(j % Cfg::kStages);
+        uint32_t ph = static_cast<uint32_t>((j / Cfg::kStages) & 1);
+        volatile int never = 0;
+        ptx::mbar_wait(full0 + 8 * s, ph, &never);
+      }
+      if (*abort_flag != 0) atomicExch(p.status, 1);
+    }
+    return;
+  }
+
+  // ---------------- consumers
+  const int g = lane >> 2, t = lane & 3;
+  float acc[RW][NT][4];
+  long long it = 0;
+  bool ok = true;
+  long long u = u0;
+  while (u < u1 && ok) {
+    const int tile = static_cast<int>(u / p.chunks), c0 = static_cast<int>(u % p.chunks);
+    const int c1 = static_cast<int>(min(static_cast<long long>(p.chunks), c0 + (u1 - u)));
+    const bool first_segment = (u == u0);
+#pragma unroll
+    for (int rb = 0; rb < RW; rb++)
+#pragma unroll
+      for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+        for (int i = 0; i < 4; i++) acc[rb][nt][i] = 0.0f;
+
+    for (int chunk = c0; chunk < c1; chunk++, it++) {
+      const int s = static_cast<int>(it % Cfg::kStages);
+      const uint32_t ph = static_cast<uint32_t>((it / Cfg::kStages) & 1);
+      ok = ptx::mbar_wait(full0 + 8 * s, ph, abort_flag);
+      if (!ok) break;
+      const uint32_t wbase = base + s * Cfg::kStageBytes;
+      const uint32_t tbase = wbase + Cfg::kWeightBytes;
+#pragma unroll
+      for (int h = 0; h < 2; h++) {
+        // this lane's 16 k of every token row: 32 bytes = swizzled 16-byte chunks 2t and 2t+1 of row nt*8+g
+        uint32_t tok[NT][8];
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++) {
+          uint32_t row = tbase + h * Cfg::kTokenBoxBytes + (nt * 8 + g) * 128;
+          uint4 x = ptx::lds128(row + (((2 * t) ^ g) << 4));
+          uint4 y = ptx::lds128(row + (((2 * t + 1) ^ g) << 4));
+          tok[nt][0] = x.x; tok[nt][1] = x.y; tok[nt][2] = x.z; tok[nt][3] = x.w;
+          tok[nt][4] = y.x; tok[nt][5] = y.y; tok[nt][6] = y.z; tok[nt][7] = y.w;
+        }
+#pragma unroll
+        for (int rb = 0; rb < RW; rb++) {
+          // rows g and g+8 of this warp's 16-row block; both have (row & 7) == g
+          uint32_t r0 = wbase + ((warp * RW + rb) * 16 + g) * 128 + (((4 * h + t) ^ g) << 4);
+          uint4 w0 = ptx::lds128(r0);
+          uint4 w1 = ptx::lds128(r0 + 8 * 128);
+          const uint32_t w0v[4] = {w0.x, w0.y, w0.z, w0.w};
+          const uint32_t w1v[4] = {w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+          for (int j = 0; j < 4; j++) {
+            uint32_t a0, a1, a2, a3;
+            widen_int8x4<DT>(w0v[j], a0, a2);
+            widen_int8x4<DT>(w1v[j], a1, a3);
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++) mma_16816<DT>(acc[rb][nt], a0, a1, a2, a3, tok[nt][2 * j], tok[nt][2 * j + 1]);
+          }
+        }
+      }
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(empty0 + 8 * s);
+    }
+    if (!ok) break;
+
+    // ---- the segment's sums are complete: finish the tile, alone or with the other CTAs that share it
+    bool finish = true;
+    if (!(c0 == 0 && c1 == p.chunks)) {
+      float4* mine = reinterpret_cast<float4*>(p.partials + (static_cast<size_t>(blockIdx.x) * 2 + (first_segment ? 0 : 1)) *
+                                                                Cfg::kPartialFloats);
+#pragma unroll
+      for (int rb = 0; rb < RW; rb++)
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++)
+          __stcg(&mine[((warp * RW + rb) * NT + nt) * 32 + lane],
+                 make_float4(acc[rb][nt][0], acc[rb][nt][1], acc[rb][nt][2], acc[rb][nt][3]));
+      const long long tile_first_unit = static_cast<long long>(tile) * p.chunks;
+      const int cta_first = range_owner(tile_first_unit, units, grid);
+      const int cta_last = range_owner(tile_first_unit + p.chunks - 1, units, grid);
+      __threadfence();
+      ptx::named_bar_sync(1, NWARPS * 32);
+      if (threadIdx.x == 0) {
+        int arrived = atomicAdd(&p.counters[tile], 1);
+        int last = arrived == cta_last - cta_first;
+        if (last) atomicExch(&p.counters[tile], 0);  // zero again for the next launch
+        *last_flag = last;
+      }
+      ptx::named_bar_sync(1, NWARPS * 32);
+      finish = *last_flag != 0;
+      ptx::named_bar_sync(1, NWARPS * 32);  // (everyone has read the flag before it is rewritten)
+      if (finish) {
+        __threadfence();
+#pragma unroll
+        for (int rb = 0; rb < RW; rb++)
+#pragma unroll
+          for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+            for (int i = 0; i < 4; i++) acc[rb][nt][i] = 0.0f;
+        for (int cta = cta_first; cta <= cta_last; cta++) {  // fixed order: the sum does not depend on who came last
+          const bool cta_first_segment = range_start(cta, units, grid) / p.chunks == tile;
+          const float4* theirs = reinterpret_cast<const float4*>(
+              p.partials + (static_cast<size_t>(cta) * 2 + (cta_first_segment ? 0 : 1)) * Cfg::kPartialFloats);
+#pragma unroll
+          for (int rb = 0; rb < RW; rb++)
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++) {
+              float4 v = __ldcg(&theirs[((warp * RW + rb) * NT + nt) * 32 + lane]);
+              acc[rb][nt][0] += v.x; acc[rb][nt][1] += v.y; acc[rb][nt][2] += v.z; acc[rb][nt][3] += v.w;
+            }
+        }
+      }
+    }
+    if (finish) {
+#pragma unroll
+      for (int rb = 0; rb < RW; rb++) {
+        const int row0 = tile * Cfg::kRowsPerTile + (warp * RW + rb) * 16 + g;
+#pragma unroll
+        for (int half = 0; half < 2; half++) {
+          const int col = row0 + 8 * half;  // weight row = output column
+          if (col >= p.n) continue;
+          const float scale = load_float<DT>(p.scales, col);
+#pragma unroll
+          for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+            for (int i = 0; i < 2; i++) {
+              const int token = p.m0 + nt * 8 + 2 * t + i;
+              if (token < p.m) store_float<DT>(p.c, static_cast<int64_t>(token) * p.n + col, acc[rb][nt][2 * half + i] * scale);
+            }
+        }
+      }
+    }
+    u += c1 - c0;
+  }
+}
+
+// ------------------------------------------------------------------ host side
+
+template <int DT>
+int launch_plain(cudaStream_t stream, const void* a, int64_t a_sm, const int8_t* b, const void* scales, void* c, int m, int n,
+                 int k) {
+  dim3 grid(static_cast<unsigned>(ceil_div(n, 8)), static_cast<unsigned>(std::min<int64_t>(ceil_div(m, kPlainRows), 64)));
+  qmm8_plain_kernel<DT><<<grid, 256, 0, stream>>>(a, a_sm, b, scales, c, m, n, k);
+  return launched("qmm8_plain", grid, dim3(256), 0, stream);
+}
+
+template <int DT, int NT>
+int launch_skinny(int device, cudaStream_t stream, const void* a, int64_t a_sm, const int8_t* b, const void* scales, void* c,
+                  int m, int n, int k, int m0) {
+  constexpr int RW = 2, NWARPS = 8;
+  using Cfg = SkinnyCfg<NT, RW, NWARPS>;
+  auto kernel = qmm8_skinny_kernel<DT, NT, RW, NWARPS>;
+  static bool configured[64] = {};
+  if (!configured[device & 63]) {
+    TVB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+    configured[device & 63] = true;
+  }
+  CUtensorMap map_w, map_a;
+  if (make_tensor_map_2d(&map_w, b, CU_TENSOR_MAP_DATA_TYPE_UINT8, k, n, k, kChunkK, Cfg::kRowsPerTile,
+                         CU_TENSOR_MAP_SWIZZLE_128B) != 0)
+    return -1;
+  if (make_tensor_map_2d(&map_a, a, DT == TVB_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, k, m,
+                         a_sm * 2, 64, Cfg::kTokens, CU_TENSOR_MAP_SWIZZLE_128B) != 0)
+    return -1;
+  SkinnyParams p{};
+  p.tiles = static_cast<int>(ceil_div(n, Cfg::kRowsPerTile));
+  p.chunks = k / kChunkK;
+  long long units = static_cast<long long>(p.tiles) * p.chunks;
+  int grid = static_cast<int>(std::min<long long>(sm_count(device), units));
+  size_t partial_bytes = static_cast<size_t>(grid) * 2 * Cfg::kPartialFloats * sizeof(float);
+  size_t counter_bytes = (static_cast<size_t>(p.tiles) * sizeof(int) + 255) & ~size_t(255);
+  void* ws = nullptr;
+  if (workspace(device, 0, counter_bytes + partial_bytes, &ws) != 0) return -1;
+  p.counters = static_cast<int*>(ws);
+  p.partials = reinterpret_cast<float*>(static_cast<uint8_t*>(ws) + counter_bytes);
+  if (status_word(device, &p.status) != 0) return -1;
+  p.scales = scales;
+  p.c = c;
+  p.m = m;
+  p.n = n;
+  p.k = k;
+  p.m0 = m0;
+  kernel<<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(map_w, map_a, p);
+  return launched("qmm8_skinny", dim3(grid), dim3(Cfg::kThreads), Cfg::kSmemBytes, stream);
+}
+
+bool skinny_ok(const void* a, int dtype, int64_t a_sm, const int8_t* b, int64_t m, int64_t n, int64_t k) {
+  return (dtype == TVB_BF16 || dtype == TVB_F16) && m <= 64 && k % kChunkK == 0 && k >= kChunkK &&
+         (a_sm % 8 == 0 || m == 1) && (reinterpret_cast<uintptr_t>(a) & 15u) == 0 && (reinterpret_cast<uintptr_t>(b) & 15u) == 0 &&
+         n >= 1;
+}
+
+}  // namespace
+}  // namespace tvb
+
+using namespace tvb;
+
+extern "C" int tvb_qmm8(int device, const void* a, int dtype, int64_t a_sm, const int8_t* b, const void* scales, void* c,
+                        int64_t m, int64_t n, int64_t k, int variant) {
+  TVB_REQUIRE(dtype == TVB_F32 || dtype == TVB_F16 || dtype == TVB_BF16, "tvb_qmm8: A must be float32, float16 or bfloat16");
+  TVB_REQUIRE(m >= 0 && n >= 0 && k >= 0, "tvb_qmm8: negative size");
+  TVB_REQUIRE(m < (int64_t(1) << 31) && n < (int64_t(1) << 31) && k < (int64_t(1) << 31) && n * k < (int64_t(1) << 40),
+              "tvb_qmm8: sizes beyond 32 bits");
+  if (m == 0 || n == 0) return 0;
+  TVB_REQUIRE(c != nullptr && scales != nullptr && (k == 0 || (a != nullptr && b != nullptr)), "tvb_qmm8: NULL pointer");
+  cudaStream_t stream;
+  if (enter(device, &stream) != 0) return -1;
+  int mi = static_cast<int>(m), ni = static_cast<int>(n), ki = static_cast<int>(k);
+  bool can_skinny = skinny_ok(a, dtype, a_sm, b, m, n, k);
+  TVB_REQUIRE(variant != 2 || can_skinny,
+              "tvb_qmm8: the skinny kernel needs 16-bit A, m <= 64, k a multiple of 128, 16-byte aligned rows");
+  TVB_REQUIRE(variant >= 0 && variant <= 2, "tvb_qmm8: unknown kernel variant");
+  if (variant == 2 || (variant == 0 && can_skinny)) {
+    int64_t stride = m == 1 ? k : a_sm;  // (one row: any stride will do for the map)
+    for (int m0 = 0; m0 < mi; m0 += 16) {
+      int rows = mi - m0;
+      int rc;
+      if (dtype == TVB_BF16)
+        rc = rows <= 8 ? launch_skinny<TVB_BF16, 1>(device, stream, a, stride, b, scales, c, mi, ni, ki, m0)
+                       : launch_skinny<TVB_BF16, 2>(device, stream, a, stride, b, scales, c, mi, ni, ki, m0);
+      else
+        rc = rows <= 8 ? launch_skinny<TVB_F16, 1>(device, stream, a, stride, b, scales, c, mi, ni, ki, m0)
+                       : launch_skinny<TVB_F16, 2>(device, stream, a, stride, b, scales, c, mi, ni, ki, m0);
+      if (rc != 0) return rc;
+    }
+    return 0;
+  }
+  switch (dtype) {
+    case TVB_F32: return launch_plain<TVB_F32>(stream, a, a_sm, b, scales, c, mi, ni, ki);
+    case TVB_F16: return launch_plain<TVB_F16>(stream, a, a_sm, b, scales, c, mi, ni, ki);
+    default: return launch_plain<TVB_BF16>(stream, a, a_sm, b, scales, c, mi, ni, ki);
+  }
+}

@@ -1,0 +1,29 @@
+// Parameters shared by the two aten::_scaled_mm kernels (plain and tcgen05).
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+namespace tvb {
+
+struct ScaledMmParams {
+  const void* a;         // float8 [m, k]: element (i, kk) at a[i * a_s0 + kk * a_s1]
+  const void* b;         // float8 [k, n]: element (kk, j) at b[kk * b_s0 + j * b_s1]
+  const float* scale_a;  // 1 or m values
+  const float* scale_b;  // 1 or n values
+  const void* bias;      // n values of bias_dtype, or NULL
+  const float* scale_result;  // 1 value or NULL (float8 outputs only)
+  void* out;             // contiguous [m, n] of out_dtype
+  int64_t m, n, k;
+  int64_t a_s0, a_s1, b_s0, b_s1;
+  int a_dtype, b_dtype, bias_dtype, out_dtype, rowwise;
+};
+
+int scaled_mm_plain(cudaStream_t stream, const ScaledMmParams& p);
+// The tcgen05 kernel; `usable` tells whether the layout qualifies (K-major operands,
+// 16-byte aligned rows).
+bool scaled_mm_tc_usable(const ScaledMmParams& p);
+int scaled_mm_tc(int device, cudaStream_t stream, const ScaledMmParams& p);
+
+}  // namespace tvb

@@ -1,0 +1,177 @@
+// aten::_scaled_mm on the fifth-generation tensor cores: float8 operands straight into
+// tcgen05.mma kind::f8f6f4, float32 accumulation in tensor memory, and the scales, bias,
+// 1 / scale_result and the cast to the output type applied as the accumulators are read back.
+//
+// The reference emulates the op (crates/pyvk/csrc/quant.cpp:283-299): two float8 -> float32
+// casts, two multiplications by the scales, a float32 GEMM (linalg.cpp:285-321), a bias add and
+// a cast, seven dispatches in all. Float8 products are exact in float32, so
+// (sum a*b) * scale_a[i] * scale_b[j] differs from sum (a*scale_a)(b*scale_b) only by
+// float32 roundings, inside the bound the reference's test uses (tests/python/test_quant.py:124-128).
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "../core/common.h"
+#include "../core/tensormap.h"
+#include "gemm_tc.cuh"
+#include "numerics.cuh"
+#include "scaled_mm.h"
+
+namespace tvb {
+namespace {
+
+constexpr int kBN = 256;
+
+struct ScaledEpilogue {
+  struct Params {
+    const float* scale_a;
+    const float* scale_b;
+    const void* bias;
+    const float* scale_result;
+    void* out;
+    int bias_dtype, out_dtype, rowwise, vector_ok;
+  };
+  static constexpr int kSmemBytes = 4 * kBN * 2 * 4;  // per epilogue warp: column scales and biases of the tile
+
+  __device__ static void begin_tile(const Params& p, uint8_t* smem, int row0, int col0, int m, int n, int tid) {
+    const int warp = tid >> 5, lane = tid & 31;
+    float* cs = reinterpret_cast<float*>(smem) + warp * 2 * kBN;
+    float* cb = cs + kBN;
+    __syncwarp();  // (the previous tile's reads are done)
+    for (int i = lane; i < kBN; i += 32) {
+      const int col = col0 + i;
+      float s = 1.0f, b = 0.0f;
+      if (col < n) {
+        s = p.rowwise ? p.scale_b[col] : p.scale_b[0];
+        if (p.bias != nullptr) b = load_float_rt(p.bias, col, p.bias_dtype);
+      }
+      cs[i] = s;
+      cb[i] = b;
+    }
+    __syncwarp();
+  }
+
+  __device__ static void store(const Params& p, const uint8_t* smem, int row, int col_tile0, int col_off,
+                               const uint32_t (&acc)[32], int m, int n) {
+    if (row >= m) return;
+    const int warp = (threadIdx.x >> 5) & 3;
+    const float* cs = reinterpret_cast<const float*>(smem) + warp * 2 * kBN + col_off;
+    const float* cb = cs + kBN;
+    const float sa = p.rowwise ? p.scale_a[row] : p.scale_a[0];
+    const bool f8_out = p.out_dtype == TVB_E4M3 || p.out_dtype == TVB_E5M2;
+    const float inv = f8_out && p.scale_result != nullptr ? 1.0f / p.scale_result[0] : 1.0f;
+    float v[32];
+#pragma unroll
+    for (int i = 0; i < 32; i++) {
+      float x = __uint_as_float(acc[i]) * sa * cs[i] + cb[i];
+      v[i] = f8_out ? x * inv : x;
+    }
+    const int col = col_tile0 + col_off;
+    const int64_t o = static_cast<int64_t>(row) * n + col;
+    if (p.vector_ok && col + 32 <= n) {
+      if (p.out_dtype == TVB_BF16) {
+        uint4* dst = reinterpret_cast<uint4*>(static_cast<uint16_t*>(p.out) + o);
+#pragma unroll
+        for (int q = 0; q < 4; q++) {
+          uint32_t w[4];
+#pragma unroll
+          for (int j = 0; j < 4; j++) {
+            __nv_bfloat162 h = __floats2bfloat162_rn(v[q * 8 + 2 * j], v[q * 8 + 2 * j + 1]);
+            w[j] = *reinterpret_cast<uint32_t*>(&h);
+          }
+          dst[q] = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+        return;
+      }
+      if (p.out_dtype == TVB_F32) {
+        float4* dst = reinterpret_cast<float4*>(static_cast<float*>(p.out) + o);
+#pragma unroll
+        for (int q = 0; q < 8; q++) dst[q] = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+        return;
+      }
+    }
+    for (int i = 0; i < 32; i++)
+      if (col + i < n) store_float_rt(p.out, o + i, p.out_dtype, v[i]);
+  }
+};
+
+}  // namespace
+
+bool scaled_mm_tc_usable(const ScaledMmParams& p) {
+  auto aligned = [](const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15u) == 0; };
+  return p.m >= 1 && p.n >= 1 && p.k >= 16 && p.a_s1 == 1 && p.b_s0 == 1 && p.a_s0 % 16 == 0 && p.b_s1 % 16 == 0 &&
+         p.a_s0 >= p.k && p.b_s1 >= p.k && aligned(p.a) && aligned(p.b) && p.m < (int64_t(1) << 31) && p.n < (int64_t(1) << 31) &&
+         p.k < (int64_t(1) << 31);
+}
+
+int scaled_mm_tc(int device, cudaStream_t stream, const ScaledMmParams& p) {
+  using Cfg = GemmTcCfg<kBN, ScaledEpilogue::kSmemBytes>;
+  auto kernel = gemm_tc_kernel<0, kBN, ScaledEpilogue>;
+  static bool configured[64] = {};
+  if (!configured[device & 63]) {
+    TVB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+    configured[device & 63] = true;
+  }
+  CUtensorMap map_a, map_b;
+  if (make_tensor_map_2d(&map_a, p.a, CU_TENSOR_MAP_DATA_TYPE_UINT8, p.k, p.m, p.a_s0, 128, Cfg::kBM,
+                         CU_TENSOR_MAP_SWIZZLE_128B) != 0)
+    return -1;
+  if (make_tensor_map_2d(&map_b, p.b, CU_TENSOR_MAP_DATA_TYPE_UINT8, p.k, p.n, p.b_s1, 128, kBN, CU_TENSOR_MAP_SWIZZLE_128B) != 0)
+    return -1;
+  GemmTcShape sh{};
+  sh.m = static_cast<int>(p.m);
+  sh.n = static_cast<int>(p.n);
+  sh.kblocks = static_cast<int>(ceil_div(p.k, 128));
+  sh.k_elems_per_block = 128;
+  sh.tiles_m = static_cast<int>(ceil_div(p.m, Cfg::kBM));
+  sh.tiles_n = static_cast<int>(ceil_div(p.n, kBN));
+  ScaledEpilogue::Params ep{};
+  ep.scale_a = p.scale_a;
+  ep.scale_b = p.scale_b;
+  ep.bias = p.bias;
+  ep.scale_result = p.scale_result;
+  ep.out = p.out;
+  ep.bias_dtype = p.bias_dtype;
+  ep.out_dtype = p.out_dtype;
+  ep.rowwise = p.rowwise;
+  ep.vector_ok = (reinterpret_cast<uintptr_t>(p.out) & 15u) == 0 && (p.n * dtype_size(p.out_dtype)) % 16 == 0;
+  // float8 formats of kind::f8f6f4: 0 = e4m3, 1 = e5m2; float32 accumulators
+  const uint32_t idesc = ptx::tc_instr_desc(1, p.a_dtype == TVB_E4M3 ? 0 : 1, p.b_dtype == TVB_E4M3 ? 0 : 1, Cfg::kBM, kBN);
+  int* status = nullptr;
+  if (status_word(device, &status) != 0) return -1;
+  const int grid = static_cast<int>(std::min<int64_t>(sm_count(device), static_cast<int64_t>(sh.tiles_m) * sh.tiles_n));
+  kernel<<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(map_a, map_b, sh, idesc, ep, status);
+  return launched("scaled_mm_tc", dim3(grid), dim3(Cfg::kThreads), Cfg::kSmemBytes, stream);
+}
+
+}  // namespace tvb
+
+using namespace tvb;
+
+extern "C" int tvb_scaled_mm(int device, const void* a, int a_dtype, int64_t a_s0, int64_t a_s1, const void* b, int b_dtype,
+                             int64_t b_s0, int64_t b_s1, const float* scale_a, const float* scale_b, int rowwise,
+                             const void* bias, int bias_dtype, const float* scale_result, void* out, int out_dtype, int64_t m,
+                             int64_t n, int64_t k, int variant) {
+  TVB_REQUIRE((a_dtype == TVB_E4M3 || a_dtype == TVB_E5M2) && (b_dtype == TVB_E4M3 || b_dtype == TVB_E5M2),
+              "tvb_scaled_mm: operands must be float8_e4m3fn or float8_e5m2");
+  TVB_REQUIRE(out_dtype == TVB_F32 || out_dtype == TVB_F16 || out_dtype == TVB_BF16 || out_dtype == TVB_E4M3 ||
+                  out_dtype == TVB_E5M2,
+              "tvb_scaled_mm: unsupported output dtype");
+  TVB_REQUIRE(m >= 0 && n >= 0 && k >= 0, "tvb_scaled_mm: negative size");
+  TVB_REQUIRE(variant >= 0 && variant <= 2, "tvb_scaled_mm: unknown kernel variant");
+  if (m == 0 || n == 0) return 0;
+  TVB_REQUIRE(out != nullptr && scale_a != nullptr && scale_b != nullptr && (k == 0 || (a != nullptr && b != nullptr)),
+              "tvb_scaled_mm: NULL pointer");
+  cudaStream_t stream;
+  if (enter(device, &stream) != 0) return -1;
+  ScaledMmParams p{};
+  p.a = a; p.b = b; p.scale_a = scale_a; p.scale_b = scale_b; p.bias = bias; p.scale_result = scale_result; p.out = out;
+  p.m = m; p.n = n; p.k = k;
+  p.a_s0 = a_s0; p.a_s1 = a_s1; p.b_s0 = b_s0; p.b_s1 = b_s1;
+  p.a_dtype = a_dtype; p.b_dtype = b_dtype; p.bias_dtype = bias_dtype; p.out_dtype = out_dtype; p.rowwise = rowwise;
+  const bool usable = scaled_mm_tc_usable(p);
+  TVB_REQUIRE(variant != 2 || usable, "tvb_scaled_mm: the tcgen05 kernel needs K-major operands with 16-byte aligned rows");
+  // small problems do not fill one wave of 128 x 256 tiles: the plain kernel's 64 x 64 tiles spread them wider
+  const bool big = m * n >= int64_t(128) * 256 * 8 && k >= 128;
+  if (variant == 2 || (variant == 0 && usable && big)) return scaled_mm_tc(device, stream, p);
+  return scaled_mm_plain(stream, p);
+}
