@@ -1,0 +1,230 @@
+// The four quantised matrix products as aten kernels of device "vk":
+//
+//   _weight_int8pack_mm                    -> tvb_qmm8
+//   _dyn_quant_pack_4bit_weight            -> tvb_qmm4_pack
+//   _dyn_quant_matmul_4bit                 -> tvb_qmm4 (quantise + multiply)
+//   _scaled_mm, _scaled_mm.out             -> tvb_scaled_mm
+//
+// Same schemas, argument checks and error messages as the reference's entry points
+// (crates/pyvk/csrc/quant.cpp:59-119, :127-144, :146-204, :234-310), which are in turn
+// the CPU kernels' (ATen/native/LinearAlgebra.cpp, ScaledBlas.cpp); registered the same
+// way (quant.cpp:315-322). Where the reference would hand an unsupported case to the CPU
+// (operands elsewhere, sizes past 2^31: quant.cpp:75-78, :134-138, :159-164, :238-241)
+// this layer raises: strict semantics are the only mode.
+#include <ATen/native/Resize.h>
+#include <torch/library.h>
+
+#include <sstream>
+
+#include "backend.h"
+
+namespace vkb {
+namespace {
+
+void require_vk(const char* op, std::initializer_list<const at::Tensor*> tensors) {
+  for (const at::Tensor* t : tensors) {
+    if (t != nullptr && t->defined() && !is_vk(*t)) {
+      std::ostringstream why;
+      why << "an operand is on " << t->device() << ", not on \"vk\"";
+      no_fallback(op, why.str());
+    }
+  }
+}
+
+// ------------------------------------------------------------------ int8 weight-only
+
+at::Tensor weight_int8pack_mm(const at::Tensor& A, const at::Tensor& B, const at::Tensor& scales) {
+  constexpr const char* fn = "_weight_int8pack_mm_cpu";  // (the messages name the CPU kernel, as the reference's do)
+  const int64_t M = A.size(0), N = B.size(0), K = A.size(1);
+  TORCH_CHECK(A.dtype() == at::kBFloat16 || A.dtype() == at::kHalf || A.dtype() == at::kFloat, fn,
+              " : expect A to be either 32-bit or 16-bit float tensor.");
+  TORCH_CHECK(A.dim() == 2, fn, " : expect A to be 2D tensor.");
+  TORCH_CHECK(A.stride(1) == 1, fn, " : A must be contiguous on the last dimension.");
+  TORCH_CHECK(B.dtype() == at::kChar, fn, " : expect B to be int8 tensor.");
+  TORCH_CHECK(B.is_contiguous(), fn, " : expect B to be contiguous.");
+  TORCH_CHECK(B.size(1) == K, fn, " : expect B.size(1) == ", K);
+  TORCH_CHECK(scales.dim() == 1 && scales.size(0) == N, fn, " : expect scales to be 1d tensor with size ", N);
+  require_vk("aten::_weight_int8pack_mm", {&A, &B, &scales});
+
+  at::Tensor C = at::empty({M, N}, A.options());
+  if (C.numel() == 0) return C;
+  at::Tensor s = scales.to(A.scalar_type()).contiguous();  // (the CPU reads the scales in A's dtype)
+  const int dev = enter_device(A);
+  check(tvb_qmm8(dev, gpu_address(A), dtype_code(A.scalar_type()), A.stride(0), static_cast<const int8_t*>(gpu_address(B)),
+                 gpu_address(s), gpu_address_out(C), M, N, K, 0));
+  return C;
+}
+
+// ------------------------------------------------------------------ dynamic int8 x int4
+
+void check_group_size(const char* fn, int64_t block_size, int64_t in_features) {
+  TORCH_CHECK(block_size == in_features || (!(block_size % 32) && !(in_features % block_size)), fn,
+              ": Group size should be multiple of 32, in_features [", in_features, "]. Provided ", block_size);
+}
+
+at::Tensor dyn_quant_pack_4bit_weight(const at::Tensor& weights, const at::Tensor& scales_zeros,
+                                      const std::optional<at::Tensor>& bias, int64_t block_size, int64_t in_features,
+                                      int64_t out_features) {
+  TORCH_CHECK(weights.dtype() == at::kByte, "_dyn_quant_pack_4bit_weight_cpu", " : expect weight to be kByte.");
+  check_group_size("_dyn_quant_pack_4bit_weight_cpu", block_size, in_features);
+  const at::Tensor* b = bias.has_value() && bias->defined() ? &*bias : nullptr;
+  require_vk("aten::_dyn_quant_pack_4bit_weight", {&weights, &scales_zeros, b});
+  // One float32 vector: the weights' bytes, the scales, the bias (the CPU's layout, so that packing on
+  // either device serves either device's product). One kernel writes all three parts.
+  at::Tensor w = weights.contiguous(), s = scales_zeros.contiguous();
+  at::Tensor bv = b != nullptr ? b->contiguous() : at::Tensor();
+  const int sd = dtype_code(s.scalar_type());
+  TORCH_CHECK(sd == TVB_F32 || sd == TVB_BF16 || sd == TVB_F16 || sd == TVB_F64,
+              "_dyn_quant_pack_4bit_weight: scales must be a floating point tensor, got ", s.scalar_type());
+  const int64_t nb = bv.defined() ? bv.numel() : 0;
+  at::Tensor packed = at::empty({w.numel() + s.numel() + nb}, weights.options().dtype(at::kFloat));
+  if (packed.numel() == 0) return packed;
+  const int dev = enter_device(weights);
+  check(tvb_qmm4_pack(dev, static_cast<const uint8_t*>(gpu_address(w)), w.numel(), gpu_address(s), sd, s.numel(),
+                      nb ? gpu_address(bv) : nullptr, nb ? dtype_code(bv.scalar_type()) : TVB_F32, nb,
+                      static_cast<float*>(gpu_address_out(packed))));
+  return packed;
+}
+
+at::Tensor dyn_quant_matmul_4bit(const at::Tensor& inp, const at::Tensor& packed_weights, int64_t block_size,
+                                 int64_t in_features, int64_t out_features) {
+  constexpr const char* fn = "_dyn_quant_matmul_4bit_cpu";
+  TORCH_CHECK(inp.dtype() == at::kFloat || (inp.dtype() == at::kBFloat16 && block_size == in_features), fn,
+              " : expect input to be float32 or bfloat16 tensor.");
+  check_group_size(fn, block_size, in_features);
+  TORCH_CHECK(inp.dim() == 2 && inp.size(1) == in_features, "_dyn_quant_matmul_4bit: expected input of shape [M, ", in_features,
+              "], got ", inp.sizes());
+  require_vk("aten::_dyn_quant_matmul_4bit", {&inp, &packed_weights});
+  const int64_t M = inp.size(0), N = out_features, K = in_features;
+  if (M * std::max(K, N) >= (int64_t(1) << 31) || packed_weights.numel() >= (int64_t(1) << 32))
+    no_fallback("aten::_dyn_quant_matmul_4bit", "sizes beyond 32-bit offsets");
+  at::Tensor out = at::empty({M, N}, inp.options());
+  const int64_t weight_elements = N * K / 2, scale_elements = N * (K / block_size);
+  TORCH_CHECK(packed_weights.numel() >= weight_elements + scale_elements, "Invalid packed weight tensor size");
+  const int64_t bias_elements = packed_weights.numel() - (weight_elements + scale_elements);
+  if (bias_elements != 0) TORCH_CHECK(bias_elements == N, "Expected bias length to match output dimension");
+  if (out.numel() == 0) return out;
+  at::Tensor x = inp.contiguous();
+  at::Tensor packed = packed_weights.to(at::kFloat).contiguous();
+  const uint64_t ws_bytes = tvb_qmm4_workspace_bytes(M, K);
+  at::Tensor ws = at::empty({static_cast<int64_t>(ws_bytes)}, inp.options().dtype(at::kByte));
+  const int dev = enter_device(inp);
+  check(tvb_qmm4(dev, gpu_address(x), dtype_code(x.scalar_type()), static_cast<const float*>(gpu_address(packed)),
+                 bias_elements != 0 ? 1 : 0, gpu_address_out(out), M, N, K, block_size, gpu_address_out(ws), ws_bytes));
+  return out;
+}
+
+// ------------------------------------------------------------------ float8
+
+bool tensorwise_scale(const at::Tensor& t, const at::Tensor& scale) {
+  return at::isFloat8Type(t.scalar_type()) && scale.scalar_type() == at::kFloat && scale.numel() == 1;
+}
+
+bool rowwise_scale(const at::Tensor& t, const at::Tensor& scale) {
+  return at::isFloat8Type(t.scalar_type()) && scale.scalar_type() == at::kFloat && scale.dim() == 2 &&
+         scale.size(0) == t.size(0) && scale.size(1) == 1 && scale.is_contiguous();
+}
+
+// (ScaledBlas.cpp's message for a scale layout that is neither tensor-wise nor row-wise)
+[[noreturn]] void bad_scaling(const at::Tensor& a, const at::Tensor& b, const at::Tensor& sa, const at::Tensor& sb) {
+  std::ostringstream msg;
+  msg << "Invalid scaling configuration.\n"
+      << "- For TensorWise scaling, a and b should be float8, scales should be float and singletons.\n"
+      << "- For RowWise scaling, a and b should be float8, scales should be float, scale_a should be (" << a.size(0)
+      << ", 1) and scale_b should be (1, " << b.size(1) << "), and both should be contiguous.\n"
+      << "Got mat_a.dtype()=" << a.scalar_type() << ", scale_a.dtype()=" << sa.scalar_type()
+      << ", scale_a.size()=" << sa.sizes() << ", scale_a.stride()=" << sa.strides() << ", mat_b.dtype()=" << b.scalar_type()
+      << ", scale_b.dtype()=" << sb.scalar_type() << ", scale_b.size()=" << sb.sizes()
+      << " and scale_b.stride()=" << sb.strides();
+  TORCH_CHECK_VALUE(false, msg.str());
+}
+
+at::Tensor& scaled_mm_out(const at::Tensor& mat1, const at::Tensor& mat2, const at::Tensor& scale_a, const at::Tensor& scale_b,
+                          const std::optional<at::Tensor>& bias, const std::optional<at::Tensor>& scale_result,
+                          std::optional<c10::ScalarType> out_dtype, bool use_fast_accum, at::Tensor& out) {
+  const at::Tensor* bias_t = bias.has_value() && bias->defined() ? &*bias : nullptr;
+  const at::Tensor* result_t = scale_result.has_value() && scale_result->defined() ? &*scale_result : nullptr;
+  require_vk("aten::_scaled_mm", {&mat1, &mat2, &out});
+  TORCH_CHECK_VALUE(!out_dtype || *out_dtype == out.scalar_type(), "out_dtype must match output matrix type");
+  bool rowwise = false;
+  if (!(tensorwise_scale(mat1, scale_a) && tensorwise_scale(mat2.t(), scale_b.t()))) {
+    if (!(rowwise_scale(mat1, scale_a) && rowwise_scale(mat2.t(), scale_b.t()))) bad_scaling(mat1, mat2, scale_a, scale_b);
+    rowwise = true;
+  }
+  TORCH_CHECK(mat1.dim() == 2, "mat1 must be a matrix");
+  TORCH_CHECK(mat2.dim() == 2, "mat2 must be a matrix");
+  TORCH_CHECK(mat1.sizes()[1] == mat2.sizes()[0], "mat_a and mat_b shapes cannot be multiplied (", mat1.sizes()[0], "x",
+              mat1.sizes()[1], " and ", mat2.sizes()[0], "x", mat2.sizes()[1], ")");
+  const bool both_f8 = at::isFloat8Type(mat1.scalar_type()) && at::isFloat8Type(mat2.scalar_type());
+  if (!rowwise) {
+    TORCH_CHECK_VALUE(both_f8, "mat1 and mat2 must be fp8 types, got: ", mat1.scalar_type(), mat2.scalar_type());
+    TORCH_CHECK_VALUE(scale_a.numel() == 1 && scale_a.scalar_type() == at::kFloat, "scale_a must have 1 Float element");
+    TORCH_CHECK_VALUE(scale_b.numel() == 1 && scale_b.scalar_type() == at::kFloat, "scale_b must have 1 Float element");
+  } else {
+    TORCH_CHECK_VALUE(both_f8, "mat1 and mat_b must be fp8 types, got: ", mat1.scalar_type(), mat2.scalar_type());
+    TORCH_CHECK_VALUE(scale_a.size(0) == mat1.size(0) && scale_a.size(1) == 1, "scale_a must have shape [", mat1.size(0),
+                      ", 1], got [", scale_a.sizes(), "]");
+    TORCH_CHECK_VALUE(scale_a.numel() == mat1.size(0) && scale_a.scalar_type() == at::kFloat, "scale_a must have ",
+                      mat1.size(0), " Float elements, got ", scale_a.numel());
+    TORCH_CHECK_VALUE(scale_b.numel() == mat2.size(1) && scale_b.scalar_type() == at::kFloat, "scale_b must have ",
+                      mat2.size(1), " Float elements, got ", scale_b.numel());
+    TORCH_CHECK_VALUE(scale_a.stride(1) == 1, "expected scale_a.stride(1) to be 1, but got ", scale_a.stride(1));
+    TORCH_CHECK_VALUE(scale_b.stride(1) == 1, "expected scale_b.stride(1) to be 1, but got ", scale_b.stride(1));
+  }
+  TORCH_CHECK(result_t == nullptr || (result_t->numel() == 1 && result_t->scalar_type() == at::kFloat),
+              "scale_result must be a float scalar");
+  TORCH_CHECK(bias_t == nullptr || bias_t->numel() == mat2.sizes()[1], "Bias must be size ", mat2.sizes()[1], " but got ",
+              bias_t == nullptr ? 0 : bias_t->numel());
+  TORCH_CHECK(at::isFloat8Type(mat1.scalar_type()), "Expected mat1 to be Float8 matrix got ", mat1.scalar_type());
+  TORCH_CHECK(at::isFloat8Type(mat2.scalar_type()), "Expected mat2 to be Float8 matrix got ", mat2.scalar_type());
+  require_vk("aten::_scaled_mm", {&scale_a, &scale_b, bias_t, result_t});
+
+  const int64_t M = mat1.size(0), K = mat1.size(1), N = mat2.size(1);
+  at::native::resize_output(out, {M, N});
+  if (out.numel() == 0) return out;
+  const int ad = dtype_code(mat1.scalar_type()), bd = dtype_code(mat2.scalar_type()), od = dtype_code(out.scalar_type());
+  if ((ad != TVB_E4M3 && ad != TVB_E5M2) || (bd != TVB_E4M3 && bd != TVB_E5M2))
+    no_fallback("aten::_scaled_mm", "only float8_e4m3fn and float8_e5m2 operands have kernels");
+  if (od != TVB_F32 && od != TVB_F16 && od != TVB_BF16 && od != TVB_E4M3 && od != TVB_E5M2)
+    no_fallback("aten::_scaled_mm", std::string("no kernel writes ") + c10::toString(out.scalar_type()));
+  // The kernels write a contiguous [M, N]; any other `out` receives a copy of one.
+  at::Tensor dst = out.is_contiguous() ? out : at::empty({M, N}, out.options());
+  at::Tensor sa = scale_a.contiguous(), sb = scale_b.contiguous();
+  at::Tensor bv;
+  int bias_dtype = TVB_F32;
+  if (bias_t != nullptr) {
+    bv = bias_t->contiguous();
+    bias_dtype = dtype_code(bv.scalar_type());
+    if (bias_dtype != TVB_F32 && bias_dtype != TVB_F16 && bias_dtype != TVB_BF16) {
+      bv = bv.to(at::kFloat);
+      bias_dtype = TVB_F32;
+    }
+  }
+  const int dev = enter_device(mat1);
+  check(tvb_scaled_mm(dev, gpu_address(mat1), ad, mat1.stride(0), mat1.stride(1), gpu_address(mat2), bd, mat2.stride(0),
+                      mat2.stride(1), static_cast<const float*>(gpu_address(sa)), static_cast<const float*>(gpu_address(sb)),
+                      rowwise ? 1 : 0, bias_t != nullptr ? gpu_address(bv) : nullptr, bias_dtype,
+                      result_t != nullptr ? static_cast<const float*>(gpu_address(*result_t)) : nullptr, gpu_address_out(dst),
+                      od, M, N, K, 0));
+  if (!dst.is_same(out)) out.copy_(dst);
+  return out;
+}
+
+at::Tensor scaled_mm(const at::Tensor& mat_a, const at::Tensor& mat_b, const at::Tensor& scale_a, const at::Tensor& scale_b,
+                     const std::optional<at::Tensor>& bias, const std::optional<at::Tensor>& scale_result,
+                     std::optional<c10::ScalarType> out_dtype, bool use_fast_accum) {
+  at::Tensor out = at::empty({0}, mat_a.options().dtype(out_dtype.value_or(mat_a.scalar_type())));
+  return scaled_mm_out(mat_a, mat_b, scale_a, scale_b, bias, scale_result, out_dtype, use_fast_accum, out);
+}
+
+}  // namespace
+}  // namespace vkb
+
+TORCH_LIBRARY_IMPL(aten, PrivateUse1, m) {
+  using namespace vkb;
+  m.impl("_weight_int8pack_mm", &weight_int8pack_mm);
+  m.impl("_dyn_quant_pack_4bit_weight", &dyn_quant_pack_4bit_weight);
+  m.impl("_dyn_quant_matmul_4bit", &dyn_quant_matmul_4bit);
+  m.impl("_scaled_mm", &scaled_mm);
+  m.impl("_scaled_mm.out", &scaled_mm_out);
+}
