@@ -1,0 +1,393 @@
+"""Benchmark of the quantised matrix-product path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--no-extra]
+
+Headline workload (`config.workload`): the decode configuration of the int8
+weight-only product, `aten::_weight_int8pack_mm` with bf16 A[M, 8192] for M in
+{1, 4, 16} against int8 W[28672, 8192] and bf16 per-channel scales. One step is
+the three products (one per M). The metric is weight-streaming bandwidth: the
+algorithmic bytes of the three launches (weights + scales + A + C) per second.
+With N GPUs the weight rows (output columns) are sharded N ways, every rank runs
+its slice and the outputs are assembled with an NCCL all-gather (strong scaling).
+
+One JSON line is printed by rank 0. `value` is timed on the device with the
+inputs resident in HBM; `e2e` runs the same step through the public API from
+pinned host memory (copy of A up, copy of C down, every call); `roofline` is the
+decode kernel against the measured HBM copy bandwidth; `cpu_baseline` is
+PyTorch's CPU kernel for the same op (the kernel the reference falls back to and
+is validated against) timed on this host's cores; `extra` holds the large-m
+configurations (dyn-int4 and float8) in TFLOP/s.
+
+`--impl reference` times that CPU kernel alone, on the same workload and metric.
+"""
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+N_OUT, K_IN = 28672, 8192
+MS = (1, 4, 16)
+METRIC = "int8_weight_only_decode_weight_bandwidth"
+UNIT = "GB/s"
+WORKLOAD = "config2: _weight_int8pack_mm bf16 A[M,8192] M in {1,4,16} x int8 W[28672,8192] + bf16 scales[28672]"
+
+
+def algorithmic_bytes(m, n, k):
+    """Weights + scales + A + C of one product (bf16 activations, int8 weights)."""
+    return n * k + 2 * n + 2 * m * k + 2 * m * n
+
+
+def gen(seed):
+    return torch.Generator().manual_seed(seed)
+
+
+def make_inputs(n_rows, rank_seed=0):
+    w = torch.randint(-127, 128, (n_rows, K_IN), dtype=torch.int8, generator=gen(2 + rank_seed))
+    s = (torch.rand(n_rows, generator=gen(3 + rank_seed)) * (2e-2 - 1e-3) + 1e-3).to(torch.bfloat16)
+    a = {m: torch.randn(m, K_IN, generator=gen(1 + m)).to(torch.bfloat16) for m in MS}
+    return a, w, s
+
+
+def config_fp8(m, k, n, rowwise):
+    """float8 config: values ~ N(0,1)*64 clamped to +-448; scales 1/64 or uniform in [1/128, 1/32]."""
+    a = (torch.randn(m, k, generator=gen(1)) * 64).clamp(-448, 448).to(torch.float8_e4m3fn)
+    b = (torch.randn(n, k, generator=gen(2)) * 64).clamp(-448, 448).to(torch.float8_e4m3fn).t()
+    if rowwise:
+        sa = torch.rand(m, 1, generator=gen(3)) * (1 / 32 - 1 / 128) + 1 / 128
+        sb = torch.rand(1, n, generator=gen(4)) * (1 / 32 - 1 / 128) + 1 / 128
+    else:
+        sa, sb = torch.tensor(1 / 64), torch.tensor(1 / 64)
+    return a, b, sa, sb
+
+
+def config_dyn4_weights(k=4096, n=14336, bs=32):
+    """dyn-int4 config: uniform nibbles; bf16 group scales uniform in [5e-3, 5e-2]; bias ~ N(0, 0.1)."""
+    w = torch.randint(0, 256, (n, k // 2), dtype=torch.uint8, generator=gen(7))
+    sc = (torch.rand(n, k // bs, generator=gen(8)) * (5e-2 - 5e-3) + 5e-3).to(torch.bfloat16)
+    bias = torch.randn(n, generator=gen(9)) * 0.1
+    return w, sc, bias
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return {"hbm_gbs": p["hbm_gbs"], "bf16_tflops": p["bf16_tflops"], "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons of one GPU with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device_index):
+        self.proc, self.path = None, None
+        try:
+            uuid = str(torch.cuda.get_device_properties(device_index).uuid)
+            if not uuid.startswith("GPU-"):
+                uuid = "GPU-" + uuid
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", uuid, f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                                          "-lms", "100"], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        rows = []
+        with open(self.path) as f:
+            for line in f:
+                parts = [x.strip() for x in line.split(",")]
+                if len(parts) >= 7 and parts[0].replace(".", "").isdigit():
+                    rows.append(parts)
+        os.unlink(self.path)
+        if not rows:
+            return out
+        busiest = sorted(float(r[2]) if r[2].replace(".", "").isdigit() else 0.0 for r in rows)
+        load_cut = busiest[len(busiest) // 2]
+        under_load = [r for r in rows if (float(r[2]) if r[2].replace(".", "").isdigit() else 0.0) >= load_cut] or rows
+        out["sm_mhz"] = statistics.median(float(r[0]) for r in under_load)
+        out["sm_max_mhz"] = float(rows[0][1])
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        out["reasons"] = [n for i, n in enumerate(names) if any(r[3 + i].lower().startswith("active") for r in rows)]
+        out["samples"] = len(rows)
+        return out
+
+
+def cpu_reference_time(a, w, s, budget_s):
+    """Seconds per step of PyTorch's CPU _weight_int8pack_mm on the full workload (all host threads)."""
+    for m in MS:
+        torch._weight_int8pack_mm(a[m], w, s)  # warm call
+    times = []
+    t_end = time.perf_counter() + budget_s
+    while len(times) < 3 or (time.perf_counter() < t_end and len(times) < 50):
+        t0 = time.perf_counter()
+        for m in MS:
+            torch._weight_int8pack_mm(a[m], w, s)
+        times.append(time.perf_counter() - t0)
+    return statistics.median(times), len(times)
+
+
+def run_reference(args, rank):
+    """The reference arm: the CPU kernel the reference falls back to (crates/pyvk/csrc/quant.cpp:77), all host threads."""
+    if rank != 0:
+        return
+    a, w, s = make_inputs(N_OUT)
+    step_bytes = sum(algorithmic_bytes(m, N_OUT, K_IN) for m in MS)
+    for _ in range(max(args.warmup, 1)):
+        for m in MS:
+            torch._weight_int8pack_mm(a[m], w, s)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        for m in MS:
+            torch._weight_int8pack_mm(a[m], w, s)
+    dt = (time.perf_counter() - t0) / args.steps
+    value = step_bytes / dt / 1e9
+    cores = torch.get_num_threads()
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "bf16 activations, int8 weights, float32 accumulation", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "device": "host CPU", "torch": torch.__version__, "os_cpu_count": os.cpu_count()},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "reference",
+                         "sample": "the full workload, every step: torch._weight_int8pack_mm on CPU tensors, the kernel the "
+                                   "reference hands this op to without a GPU and checks its shader against"},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def time_steps(fn, steps, stream):
+    """Runs fn(step) `steps` times between two events on `stream`; returns the events."""
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record(stream)
+    for i in range(steps):
+        fn(i)
+    end.record(stream)
+    return start, end
+
+
+def extra_configs(tv, stream, peaks, quick):
+    """Large-m configurations, one GPU: float8 _scaled_mm 8192^3 and dyn-int4 [M,4096]x[14336,4096]."""
+    out = {}
+
+    def timed(fn, iters):
+        for _ in range(3):
+            fn()
+        tv.synchronize()
+        evs = []
+        for _ in range(iters):
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record(stream)
+            fn()
+            e.record(stream)
+            evs.append((s, e))
+        tv.synchronize()
+        return statistics.median(s.elapsed_time(e) for s, e in evs)
+
+    m = n = k = 8192
+    for rowwise in (False, True):
+        a, b, sa, sb = config_fp8(m, k, n, rowwise)
+        av, bv, sav, sbv = a.to("vk"), b.t().to("vk").t(), sa.to("vk"), sb.to("vk")
+        ms = timed(lambda: torch._scaled_mm(av, bv, sav, sbv, out_dtype=torch.bfloat16), 5 if quick else 10)
+        tf = 2.0 * m * n * k / ms / 1e9
+        out["fp8_scaled_mm_8192_" + ("rowwise" if rowwise else "tensorwise")] = {
+            "tflops": tf, "ms": ms, "frac_of_2x_measured_bf16": tf / (2 * peaks["bf16_tflops"]), "frac_of_nominal_fp8": tf / 4500.0}
+        del av, bv
+    w, sc, bias = config_dyn4_weights()
+    packed = torch._dyn_quant_pack_4bit_weight(w.to("vk"), sc.to("vk"), bias.to("vk"), 32, 4096, 14336)
+    for mm in ((128,) if quick else (128, 512, 2048)):
+        xv = torch.randn(mm, 4096, generator=gen(11)).to("vk")
+        ms = timed(lambda: torch._dyn_quant_matmul_4bit(xv, packed, 32, 4096, 14336), 3)
+        tops = 2.0 * mm * 14336 * 4096 / ms / 1e9
+        out[f"dyn_int4_m{mm}"] = {"tops": tops, "ms": ms, "frac_of_2x_measured_bf16": tops / (2 * peaks["bf16_tflops"])}
+    tv.empty_cache()
+    return out
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-extra", action="store_true", help="skip the large-m configurations")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+
+    import torch_vulkan_b200 as tv  # raises if the extension is missing: there is no fallback
+
+    if not tv.is_available():
+        raise SystemExit("bench.py: no B200 available to torch_vulkan_b200 (and there is no CPU path)")
+    torch.cuda.set_device(local_rank)
+    tv.set_device(local_rank)
+    dev = f"vk:{local_rank}"
+    stream = tv.cuda_stream(local_rank)
+    if world > 1:
+        import torch.distributed as dist
+
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    peaks = measured_peaks()
+
+    # ---- inputs: this rank's slice of the weight rows (output columns); A replicated
+    rows = N_OUT // world
+    a_host, w_full, s_full = make_inputs(N_OUT)
+    w = w_full[rank * rows:(rank + 1) * rows].contiguous().to(dev)
+    s = s_full[rank * rows:(rank + 1) * rows].contiguous().to(dev)
+    a_dev = {m: a_host[m].to(dev) for m in MS}
+    a_pinned = {m: a_host[m].pin_memory() for m in MS}
+    gathered = {m: torch.empty(world, m, rows, dtype=torch.bfloat16, device=dev) for m in MS} if world > 1 else None
+
+    def product(m, a):
+        c = torch._weight_int8pack_mm(a, w, s)
+        if world > 1:
+            # all ranks' column slices, [world, m, rows]; queued on the backend's stream after the product
+            import torch.distributed as dist
+
+            with torch.cuda.stream(stream):
+                dist.all_gather_into_tensor(tv.as_cuda(gathered[m]), tv.as_cuda(c))
+            return gathered[m]
+        return c
+
+    def step_plain(i, _):
+        for m in MS:
+            product(m, a_dev[m])
+
+    def barrier():
+        tv.synchronize(local_rank)
+        torch.cuda.synchronize()
+        if world > 1:
+            import torch.distributed as dist
+
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    # ---- device-resident timing
+    for i in range(args.warmup):
+        step_plain(i)
+    barrier()
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    launches_before = tv.dispatch_count()
+    start, end = time_steps(step_plain, args.steps, stream)
+    barrier()
+    launches = tv.dispatch_count() - launches_before
+    total_ms = start.elapsed_time(end)
+
+    # ---- per-launch duration of the decode kernel (the roofline's numerator), same loop with an event pair per launch
+    pairs = []
+    for i in range(args.steps):
+        for m in MS:
+            s0, e0 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s0.record(stream)
+            torch._weight_int8pack_mm(a_dev[m], w, s)
+            e0.record(stream)
+            pairs.append((m, s0, e0))
+    barrier()
+    clocks = sampler.stop() if sampler is not None else None
+    launch_ms = {m: statistics.mean(s0.elapsed_time(e0) for mm, s0, e0 in pairs if mm == m) for m in MS}
+    avg_launch_ms = statistics.mean(launch_ms.values())
+
+    # ---- end to end through the public API: A from pinned host memory, C back to the host, every call
+    def step_e2e():
+        for m in MS:
+            a = a_pinned[m].to(dev, non_blocking=True)
+            product(m, a).cpu()
+
+    for _ in range(3):
+        step_e2e()
+    barrier()
+    e2e_steps = max(5, min(args.steps, 30))
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        step_e2e()
+    barrier()
+    e2e_s = (time.perf_counter() - t0) / e2e_steps
+
+    # ---- max over ranks
+    if world > 1:
+        import torch.distributed as dist
+
+        t = torch.tensor([total_ms, e2e_s, avg_launch_ms], dtype=torch.float64, device=torch.device("cuda", local_rank))
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        total_ms, e2e_s, avg_launch_ms = t.tolist()
+
+    if rank == 0:
+        step_bytes = sum(algorithmic_bytes(m, N_OUT, K_IN) for m in MS)  # whole job, all ranks
+        ms_per_step = total_ms / args.steps
+        value = step_bytes / (ms_per_step * 1e-3) / 1e9
+        launch_bytes = statistics.mean(algorithmic_bytes(m, rows, K_IN) for m in MS)  # one launch, this rank's slice
+        achieved = launch_bytes / (avg_launch_ms * 1e-3) / 1e9
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "bf16 activations, int8 weights, float32 accumulation", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "sharding": f"weight rows / {world}" + (" + NCCL all-gather of C" if world > 1 else ""),
+                       "l2": "no flush: each launch streams %.0f MB of weights, larger than the 126 MB L2" % (rows * K_IN / 1e6)
+                       if rows * K_IN > 126e6 else "weight slice of %.0f MB fits the 126 MB L2: launches after the first read it from L2" % (rows * K_IN / 1e6),
+                       "launches_per_step": len(MS)},
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                         "frac": achieved / peaks["hbm_gbs"], "traffic": None, "peak_source": peaks["source"],
+                         "kernel": "qmm8_skinny_kernel", "avg_launch_us": avg_launch_ms * 1e3,
+                         "launch_us_by_m": {str(m): launch_ms[m] * 1e3 for m in MS}},
+            "e2e": {"value": step_bytes / e2e_s / 1e9, "unit": UNIT,
+                    "h2d_bytes_per_step": sum(2 * m * K_IN for m in MS), "d2h_bytes_per_step": sum(2 * m * N_OUT for m in MS),
+                    "ms_per_step": e2e_s * 1e3},
+            "gpu_launches": int(launches),
+            "clocks": clocks,
+        }
+        traffic_path = os.path.join(ROOT, "profiles", "qmm8_skinny_traffic.json")
+        if os.path.exists(traffic_path):
+            with open(traffic_path) as f:
+                line["roofline"]["traffic"] = json.load(f).get("dram_bytes_per_launch_config2")
+        if not args.no_cpu and world == 1:
+            cpu_s, reps = cpu_reference_time(a_host, w_full, s_full, 8.0)
+            line["cpu_baseline"] = {"value": step_bytes / cpu_s / 1e9, "unit": UNIT, "cores": torch.get_num_threads(),
+                                    "kind": "reference",
+                                    "sample": f"{reps} full steps (median): torch._weight_int8pack_mm on CPU tensors, the kernel "
+                                              "the reference hands this op to without a GPU and checks its shader against",
+                                    "ms_per_step": cpu_s * 1e3}
+        if not args.no_extra and world == 1:
+            del w_full
+            line["extra"] = extra_configs(tv, stream, peaks, quick=False)
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
