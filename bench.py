@@ -281,7 +281,7 @@ def main():
             return gathered[m]
         return c
 
-    def step_plain(i, _):
+    def step_plain(i):
         for m in MS:
             product(m, a_dev[m])
 

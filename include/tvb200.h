@@ -92,6 +92,12 @@ TVB_API int tvb_memcpy_h2d(int device, void* dst, const void* src, uint64_t nbyt
 TVB_API int tvb_memcpy_d2h(int device, void* dst, const void* src, uint64_t nbytes);
 TVB_API int tvb_memcpy_d2d(int device, void* dst, const void* src, uint64_t nbytes);
 
+/* Page-locked host memory (replaces the reference's pinned allocator, crates/pyvk/csrc/backend.cpp:313-340):
+ * copies from and to it are asynchronous. tvb_host_is_pinned: 1 if `ptr` lies in page-locked memory, else 0. */
+TVB_API int tvb_host_alloc(uint64_t nbytes, void** out);
+TVB_API void tvb_host_free(void* ptr);
+TVB_API int tvb_host_is_pinned(const void* ptr);
+
 /* ---- data movement kernels (the slice of the reference's cast / move / fill
  *      kernels that the four ops and their tests need: cast.slang, move.slang) */
 

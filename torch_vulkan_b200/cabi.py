@@ -39,6 +39,9 @@ SIGNATURES = {
     "tvb_set_stream": (_i, [_i, _vp]),
     "tvb_dispatch_count": (_u64, []),
     "tvb_shutdown": (None, []),
+    "tvb_host_alloc": (_i, [_u64, _c.POINTER(_vp)]),
+    "tvb_host_free": (None, [_vp]),
+    "tvb_host_is_pinned": (_i, [_vp]),
     "tvb_memcpy_h2d": (_i, [_i, _vp, _vp, _u64]),
     "tvb_memcpy_d2h": (_i, [_i, _vp, _vp, _u64]),
     "tvb_memcpy_d2d": (_i, [_i, _vp, _vp, _u64]),

@@ -83,6 +83,21 @@ struct VkAllocator final : c10::Allocator {
 
 VkAllocator g_allocator;
 
+// Page-locked host memory for tensor.pin_memory() (the reference's pinned allocator, backend.cpp:313-340).
+void delete_pinned(void* ptr) { tvb_host_free(ptr); }
+
+struct PinnedAllocator final : c10::Allocator {
+  c10::DataPtr allocate(size_t nbytes) override {
+    void* ptr = nullptr;
+    if (nbytes != 0) check(tvb_host_alloc(nbytes, &ptr));
+    return {ptr, ptr, &delete_pinned, c10::Device(c10::DeviceType::CPU)};
+  }
+  c10::DeleterFnPtr raw_deleter() const override { return &delete_pinned; }
+  void copy_data(void* dest, const void* src, std::size_t count) const override { std::memcpy(dest, src, count); }
+};
+
+PinnedAllocator g_pinned;
+
 // ---------------------------------------------------------------- device guard
 
 struct VkGuardImpl final : c10::impl::DeviceGuardImplInterface {
@@ -121,7 +136,8 @@ struct VkHooks final : at::PrivateUse1HooksInterface {
   bool isAvailable() const override { return device_count() > 0; }
   bool hasPrimaryContext(c10::DeviceIndex) const override { return true; }
   at::Device getDeviceFromPtr(void*) const override { return at::Device(kDevice, g_current); }
-  bool isPinnedPtr(const void*) const override { return false; }
+  bool isPinnedPtr(const void* data) const override { return tvb_host_is_pinned(data) != 0; }
+  c10::Allocator* getPinnedMemoryAllocator() const override { return &g_pinned; }
   void resizePrivateUse1Bytes(const c10::Storage& storage, size_t newsize) const override {
     c10::StorageImpl* impl = storage.unsafeGetStorageImpl();
     TORCH_CHECK(impl->resizable(), "Trying to resize storage that is not resizable");

@@ -384,6 +384,36 @@ void tvb_shutdown(void) {
   cudaGetLastError();
 }
 
+int tvb_host_alloc(uint64_t nbytes, void** out) {
+  TVB_REQUIRE(out != nullptr, "tvb_host_alloc: out is NULL");
+  *out = nullptr;
+  if (nbytes == 0) return 0;
+  {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    if (count_devices_locked() <= 0) return fail("no CUDA device: cannot page-lock host memory");
+  }
+  TVB_CUDA(cudaHostAlloc(out, nbytes, cudaHostAllocPortable));
+  return 0;
+}
+
+void tvb_host_free(void* ptr) {
+  if (ptr != nullptr && cudaFreeHost(ptr) != cudaSuccess) cudaGetLastError();
+}
+
+int tvb_host_is_pinned(const void* ptr) {
+  if (ptr == nullptr) return 0;
+  {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    if (!g_counted || g_count <= 0) return 0;  // (never starts CUDA just to answer)
+  }
+  cudaPointerAttributes attr{};
+  if (cudaPointerGetAttributes(&attr, ptr) != cudaSuccess) {
+    cudaGetLastError();
+    return 0;
+  }
+  return attr.type == cudaMemoryTypeHost ? 1 : 0;
+}
+
 int tvb_memcpy_h2d(int device, void* dst, const void* src, uint64_t nbytes) {
   cudaStream_t s;
   if (enter(device, &s) != 0) return -1;

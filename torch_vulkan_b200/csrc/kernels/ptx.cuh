@@ -96,6 +96,11 @@ __device__ __forceinline__ uint64_t policy_evict_last() {
   return p;
 }
 
+// Programmatic dependent launch: lets the next kernel in the stream begin (its CTAs take SMs as ours retire), and
+// waits until every earlier kernel in the stream has completed and its writes are visible.
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 __device__ __forceinline__ void named_bar_sync(int id, int threads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }

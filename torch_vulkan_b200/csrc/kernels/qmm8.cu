@@ -21,6 +21,8 @@
 //    output column, as the shader's matrix-vector path (qmm8.slang:78-111).
 #include <cuda.h>
 
+#include <cstdlib>
+
 #include "../core/common.h"
 #include "../core/tensormap.h"
 #include "numerics.cuh"
@@ -110,6 +112,7 @@ struct SkinnyParams {
   float* partials;   // [grid][2][kPartialFloats]
   int* counters;     // [tiles], zero between launches
   int* status;
+  long long* times;  // optional [grid][3]: SM id, first and last globaltimer ns of each CTA (diagnostics), or NULL
   int m, n, k;
   int m0;            // first token row of this pass
   int tiles, chunks; // tiles = ceil(n / rows per tile), chunks = k / 128
@@ -134,19 +137,28 @@ __global__ void __launch_bounds__((NWARPS + 1) * 32, 1)
   uint64_t* bars = reinterpret_cast<uint64_t*>(base_ptr + Cfg::kStages * Cfg::kStageBytes);
   const uint32_t full0 = ptx::smem_u32(bars), empty0 = full0 + 8 * Cfg::kStages;
   volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 2 * Cfg::kStages);
-  int* last_flag = const_cast<int*>(abort_flag) + 1;
+  int* last_flag = const_cast<int*>(abort_flag) + 1;  // two slots
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
+    if (p.times != nullptr) {
+      unsigned smid;
+      long long now;
+      asm volatile("mov.u32 %0, %smid;" : "=r"(smid));
+      asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
+      p.times[blockIdx.x * 3] = smid;
+      p.times[blockIdx.x * 3 + 1] = now;
+    }
     for (int s = 0; s < Cfg::kStages; s++) {
       ptx::mbar_init(full0 + 8 * s, 1);
       ptx::mbar_init(empty0 + 8 * s, NWARPS);
     }
     *abort_flag = 0;
-    *last_flag = 0;
+    last_flag[0] = last_flag[1] = 0;
     ptx::fence_mbar_init();
   }
   __syncthreads();
+  ptx::grid_launch_dependents();  // the next kernel of the stream may take SMs as this one's CTAs retire
 
   const long long units = static_cast<long long>(p.tiles) * p.chunks;
   const long long grid = gridDim.x;
@@ -159,9 +171,27 @@ __global__ void __launch_bounds__((NWARPS + 1) * 32, 1)
       ptx::prefetch_tensormap(&map_a);
       const uint64_t stream_policy = ptx::policy_evict_first();  // weights are read once
       const uint64_t keep_policy = ptx::policy_evict_last();     // every CTA re-reads A
-      long long it = 0;
+      // The weights do not depend on earlier kernels of the stream: start streaming them at once, one ring's worth.
+      // A (which an earlier kernel may have produced) is fetched only after the stream's earlier work has completed.
+      const long long mine = u1 - u0;
+      const long long ahead = mine < Cfg::kStages ? mine : Cfg::kStages;
+      for (long long j = 0; j < ahead; j++) {
+        const long long u = u0 + j;
+        const int tile = static_cast<int>(u / p.chunks), chunk = static_cast<int>(u % p.chunks);
+        const uint32_t dst = base + static_cast<int>(j) * Cfg::kStageBytes;
+        ptx::mbar_expect_tx(full0 + 8 * static_cast<int>(j), Cfg::kStageBytes);
+        ptx::tma_load_2d_hint(dst, &map_w, chunk * kChunkK, tile * Cfg::kRowsPerTile, full0 + 8 * static_cast<int>(j), stream_policy);
+      }
+      ptx::grid_dependency_wait();
+      for (long long j = 0; j < ahead; j++) {
+        const int chunk = static_cast<int>((u0 + j) % p.chunks);
+        const uint32_t dst = base + static_cast<int>(j) * Cfg::kStageBytes + Cfg::kWeightBytes;
+        ptx::tma_load_2d_hint(dst, &map_a, chunk * kChunkK, p.m0, full0 + 8 * static_cast<int>(j), keep_policy);
+        ptx::tma_load_2d_hint(dst + Cfg::kTokenBoxBytes, &map_a, chunk * kChunkK + 64, p.m0, full0 + 8 * static_cast<int>(j), keep_policy);
+      }
+      long long it = ahead;
       bool ok = true;
-      for (long long u = u0; u < u1 && ok; u++, it++) {
+      for (long long u = u0 + ahead; u < u1 && ok; u++, it++) {
         int tile = static_cast<int>(u / p.chunks), chunk = static_cast<int>(u % p.chunks);
         int s = static_cast<int>(it % Cfg::kStages);
         uint32_t ph = static_cast<uint32_t>((it / Cfg::kStages) & 1);
@@ -189,9 +219,13 @@ __global__ void __launch_bounds__((NWARPS + 1) * 32, 1)
 
   // ---------------- consumers
   const int g = lane >> 2, t = lane & 3;
+  // MMA row g of a 16-row block reads weight row rg (and rg + 8): a permutation chosen so that the two values of g in a
+  // quarter-warp differ in bit 2 of the row, which sends their 16-byte chunks to disjoint banks under the 128-byte swizzle.
+  const int rg = (g >> 1) | ((g & 1) << 2);
   float acc[RW][NT][4];
   long long it = 0;
   bool ok = true;
+  int segment = 0;
   long long u = u0;
   while (u < u1 && ok) {
     const int tile = static_cast<int>(u / p.chunks), c0 = static_cast<int>(u % p.chunks);
@@ -225,8 +259,8 @@ __global__ void __launch_bounds__((NWARPS + 1) * 32, 1)
         }
 #pragma unroll
         for (int rb = 0; rb < RW; rb++) {
-          // rows g and g+8 of this warp's 16-row block; both have (row & 7) == g
-          uint32_t r0 = wbase + ((warp * RW + rb) * 16 + g) * 128 + (((4 * h + t) ^ g) << 4);
+          // rows rg and rg+8 of this warp's 16-row block; both have (row & 7) == rg
+          uint32_t r0 = wbase + ((warp * RW + rb) * 16 + rg) * 128 + (((4 * h + t) ^ rg) << 4);
           uint4 w0 = ptx::lds128(r0);
           uint4 w1 = ptx::lds128(r0 + 8 * 128);
           const uint32_t w0v[4] = {w0.x, w0.y, w0.z, w0.w};
@@ -247,6 +281,7 @@ __global__ void __launch_bounds__((NWARPS + 1) * 32, 1)
     if (!ok) break;
 
     // ---- the segment's sums are complete: finish the tile, alone or with the other CTAs that share it
+    ptx::grid_dependency_wait();  // (scratch, counters and C may still be in use by the stream's previous kernel)
     bool finish = true;
     if (!(c0 == 0 && c1 == p.chunks)) {
       float4* mine = reinterpret_cast<float4*>(p.partials + (static_cast<size_t>(blockIdx.x) * 2 + (first_segment ? 0 : 1)) *
@@ -260,17 +295,20 @@ __global__ void __launch_bounds__((NWARPS + 1) * 32, 1)
       const long long tile_first_unit = static_cast<long long>(tile) * p.chunks;
       const int cta_first = range_owner(tile_first_unit, units, grid);
       const int cta_last = range_owner(tile_first_unit + p.chunks - 1, units, grid);
-      __threadfence();
+      // All consumer threads have stored their partial sums once they pass the barrier; one thread then publishes
+      // them: its gpu-scope fence is cumulative over what the barrier ordered before it.
       ptx::named_bar_sync(1, NWARPS * 32);
+      int* flag = last_flag + (segment & 1);  // (alternating slots: no barrier needed before the next segment rewrites it)
       if (threadIdx.x == 0) {
+        __threadfence();
         int arrived = atomicAdd(&p.counters[tile], 1);
         int last = arrived == cta_last - cta_first;
         if (last) atomicExch(&p.counters[tile], 0);  // zero again for the next launch
-        *last_flag = last;
+        *flag = last;
       }
       ptx::named_bar_sync(1, NWARPS * 32);
-      finish = *last_flag != 0;
-      ptx::named_bar_sync(1, NWARPS * 32);  // (everyone has read the flag before it is rewritten)
+      finish = *flag != 0;
+      segment++;
       if (finish) {
         __threadfence();
 #pragma unroll
@@ -296,7 +334,7 @@ __global__ void __launch_bounds__((NWARPS + 1) * 32, 1)
     if (finish) {
 #pragma unroll
       for (int rb = 0; rb < RW; rb++) {
-        const int row0 = tile * Cfg::kRowsPerTile + (warp * RW + rb) * 16 + g;
+        const int row0 = tile * Cfg::kRowsPerTile + (warp * RW + rb) * 16 + rg;
 #pragma unroll
         for (int half = 0; half < 2; half++) {
           const int col = row0 + 8 * half;  // weight row = output column
@@ -314,6 +352,11 @@ __global__ void __launch_bounds__((NWARPS + 1) * 32, 1)
     }
     u += c1 - c0;
   }
+  if (p.times != nullptr && threadIdx.x == 0) {
+    long long now;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
+    p.times[blockIdx.x * 3 + 2] = now;
+  }
 }
 
 // ------------------------------------------------------------------ host side
@@ -326,10 +369,11 @@ int launch_plain(cudaStream_t stream, const void* a, int64_t a_sm, const int8_t*
   return launched("qmm8_plain", grid, dim3(256), 0, stream);
 }
 
-template <int DT, int NT>
-int launch_skinny(int device, cudaStream_t stream, const void* a, int64_t a_sm, const int8_t* b, const void* scales, void* c,
-                  int m, int n, int k, int m0) {
-  constexpr int RW = 2, NWARPS = 8;
+long long* g_debug_times = nullptr;
+
+template <int DT, int NT, int RW, int NWARPS>
+int launch_skinny_cfg(int device, cudaStream_t stream, const void* a, int64_t a_sm, const int8_t* b, const void* scales, void* c,
+                      int m, int n, int k, int m0) {
   using Cfg = SkinnyCfg<NT, RW, NWARPS>;
   auto kernel = qmm8_skinny_kernel<DT, NT, RW, NWARPS>;
   static bool configured[64] = {};
@@ -362,8 +406,30 @@ int launch_skinny(int device, cudaStream_t stream, const void* a, int64_t a_sm, 
   p.n = n;
   p.k = k;
   p.m0 = m0;
-  kernel<<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(map_w, map_a, p);
+  p.times = g_debug_times;
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(Cfg::kThreads);
+  cfg.dynamicSmemBytes = Cfg::kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  TVB_CUDA(cudaLaunchKernelEx(&cfg, kernel, map_w, map_a, p));
   return launched("qmm8_skinny", dim3(grid), dim3(Cfg::kThreads), Cfg::kSmemBytes, stream);
+}
+
+template <int DT, int NT>
+int launch_skinny(int device, cudaStream_t stream, const void* a, int64_t a_sm, const int8_t* b, const void* scales, void* c,
+                  int m, int n, int k, int m0) {
+  static const int shape = [] {
+    const char* v = std::getenv("TVB200_QMM8_WARPS");
+    return v != nullptr ? std::atoi(v) : 8;
+  }();
+  if (shape == 16) return launch_skinny_cfg<DT, NT, 1, 16>(device, stream, a, a_sm, b, scales, c, m, n, k, m0);
+  return launch_skinny_cfg<DT, NT, 2, 8>(device, stream, a, a_sm, b, scales, c, m, n, k, m0);
 }
 
 bool skinny_ok(const void* a, int dtype, int64_t a_sm, const int8_t* b, int64_t m, int64_t n, int64_t k) {
@@ -376,6 +442,11 @@ bool skinny_ok(const void* a, int dtype, int64_t a_sm, const int8_t* b, int64_t 
 }  // namespace tvb
 
 using namespace tvb;
+
+// Diagnostics (not part of the public header): per-CTA SM id and start / end times of the next skinny launches.
+extern "C" __attribute__((visibility("default"))) void tvb_debug_qmm8_times(long long* device_buffer) {
+  g_debug_times = device_buffer;
+}
 
 extern "C" int tvb_qmm8(int device, const void* a, int dtype, int64_t a_sm, const int8_t* b, const void* scales, void* c,
                         int64_t m, int64_t n, int64_t k, int variant) {
