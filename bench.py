@@ -97,13 +97,11 @@ class ClockSampler:
     def __init__(self, device_index):
         self.proc, self.path = None, None
         try:
-            uuid = str(torch.cuda.get_device_properties(device_index).uuid)
-            if not uuid.startswith("GPU-"):
-                uuid = "GPU-" + uuid
             fd, self.path = tempfile.mkstemp(suffix=".csv")
             os.close(fd)
-            self.proc = subprocess.Popen(["nvidia-smi", "-i", uuid, f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                                          "-lms", "100"], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(device_index), f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "50"], stdout=open(self.path, "w"),
+                                         stderr=subprocess.DEVNULL)
         except Exception:
             self.proc = None
 
