@@ -117,6 +117,22 @@ TVB_API int tvb_fill_strided(int device, void* dst, int itemsize, uint64_t bits,
 TVB_API int tvb_qmm8(int device, const void* a, int dtype, int64_t a_sm, const int8_t* b, const void* scales, void* c,
              int64_t m, int64_t n, int64_t k, int variant);
 
+/* ---- tvb_qmm8's decode kernel for hosts that must not allocate (no counterpart in the reference) ----
+ * Some hosts cannot let a library call cudaMalloc on their behalf: a serving process that handed all of HBM to its own
+ * pool at start-up (so any later driver allocation fails), or one whose request path forbids calls that stall the
+ * whole device while the driver maps memory. tvb_qmm8 keeps the decode kernel's partial sums and tile counters in
+ * memory it allocates on first use; this entry point runs the same kernel with that scratch in an array built into the
+ * library (about 5.3 MB, resident on every GPU that loads the library until the process ends) and calls no cudaMalloc,
+ * cudaFree or other allocating routine. Same arguments as tvb_qmm8, with these limits, beyond which it returns -1 with
+ * a message: A float16 or bfloat16, m <= 64, k a multiple of 128, A's rows and B 16-byte aligned, n <= 1 048 576, a GPU of
+ * at most 160 SMs. `stream`: the cudaStream_t to queue on (NULL: the legacy default stream); the runtime's own stream is
+ * not used. The first call on a device looks the array's device address up (once, with that device current) and raises
+ * the kernel's shared-memory limit; make that first call before any stream capture begins. Every call uses the one
+ * array: it clears the counters it needs and then relies on stream order, so two calls that can overlap on the GPU
+ * (different streams, no dependency between them) race on it and must be ordered by the caller. */
+TVB_API int tvb_qmm8_static_scratch(int device, const void* a, int dtype, int64_t a_sm, const int8_t* b, const void* scales,
+                                    void* c, int64_t m, int64_t n, int64_t k, void* stream);
+
 /* ---- aten::_dyn_quant_pack_4bit_weight (replaces the cat of three casts,
  *      quant.cpp:139-143) ----
  * packed[0..nw) = float(weights bytes), then float(scales) [ns], then float(bias) [nbias]. */

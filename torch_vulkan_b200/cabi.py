@@ -48,6 +48,7 @@ SIGNATURES = {
     "tvb_copy_strided": (_i, [_i, _vp, _i, _c.POINTER(_i64), _vp, _i, _c.POINTER(_i64), _c.POINTER(_i64), _i]),
     "tvb_fill_strided": (_i, [_i, _vp, _i, _u64, _c.POINTER(_i64), _c.POINTER(_i64), _i]),
     "tvb_qmm8": (_i, [_i, _vp, _i, _i64, _vp, _vp, _vp, _i64, _i64, _i64, _i]),
+    "tvb_qmm8_static_scratch": (_i, [_i, _vp, _i, _i64, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
     "tvb_qmm4_pack": (_i, [_i, _vp, _i64, _vp, _i, _i64, _vp, _i, _i64, _vp]),
     "tvb_qmm4_quantize": (_i, [_i, _vp, _i, _i64, _i64, _i, _vp, _vp, _vp]),
     "tvb_qmm4_matmul": (_i, [_i, _vp, _vp, _vp, _vp, _i, _vp, _i, _i64, _i64, _i64, _i64, _vp]),

@@ -22,6 +22,7 @@
 #include <cuda.h>
 
 #include <cstdlib>
+#include <mutex>
 
 #include "../core/common.h"
 #include "../core/tensormap.h"
@@ -438,10 +439,119 @@ bool skinny_ok(const void* a, int dtype, int64_t a_sm, const int8_t* b, int64_t 
          n >= 1;
 }
 
+// ------------------------------------------------------------------ the same kernel without any allocation
+//
+// Scratch for tvb_qmm8_static_scratch: the tile counters, then the per-CTA partial sums, then a status word, in one
+// array that is part of the library's image (so every GPU that loads the library carries it until the process exits).
+constexpr int kStaticMaxCtas = 160;    // CTAs of one launch = SMs of the device
+constexpr int kStaticMaxTiles = 4096;  // 256-row tiles: n up to 1 048 576
+constexpr size_t kStaticCounterBytes = static_cast<size_t>(kStaticMaxTiles) * sizeof(int);
+constexpr size_t kStaticPartialBytes = static_cast<size_t>(kStaticMaxCtas) * 2 * SkinnyCfg<2, 2, 8>::kPartialFloats * sizeof(float);
+constexpr size_t kStaticScratchBytes = kStaticCounterBytes + kStaticPartialBytes + 256;
+
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+std::mutex g_static_mutex;
+void* g_static_scratch_ptr[64] = {};   // per device: the array's device address (the symbol itself is not one)
+bool g_static_configured[64][4] = {};
+
+// The device address of g_static_scratch on `device` (which must be current). Looked up once per device.
+int static_scratch_address(int device, unsigned char** out) {
+  std::lock_guard<std::mutex> lock(g_static_mutex);
+  if (g_static_scratch_ptr[device] == nullptr) {
+    void* ptr = nullptr;
+    cudaError_t err = cudaGetSymbolAddress(&ptr, g_static_scratch);
+    if (err != cudaSuccess) return fail_cuda("cudaGetSymbolAddress(g_static_scratch)", err);
+    g_static_scratch_ptr[device] = ptr;
+  }
+  *out = static_cast<unsigned char*>(g_static_scratch_ptr[device]);
+  return 0;
+}
+
+template <int DT, int NT>
+int launch_skinny_static(int device, int sms, cudaStream_t stream, unsigned char* scratch, const void* a, int64_t a_sm,
+                         const int8_t* b, const void* scales, void* c, int m, int n, int k, int m0) {
+  constexpr int RW = 2, NWARPS = 8;
+  using Cfg = SkinnyCfg<NT, RW, NWARPS>;
+  auto kernel = qmm8_skinny_kernel<DT, NT, RW, NWARPS>;
+  {
+    std::lock_guard<std::mutex> lock(g_static_mutex);
+    bool& done = g_static_configured[device][(DT == TVB_BF16 ? 0 : 2) + (NT - 1)];
+    if (!done) {
+      TVB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+      done = true;
+    }
+  }
+  CUtensorMap map_w, map_a;
+  if (make_tensor_map_2d(&map_w, b, CU_TENSOR_MAP_DATA_TYPE_UINT8, k, n, k, kChunkK, Cfg::kRowsPerTile,
+                         CU_TENSOR_MAP_SWIZZLE_128B) != 0)
+    return -1;
+  if (make_tensor_map_2d(&map_a, a, DT == TVB_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, k, m,
+                         a_sm * 2, 64, Cfg::kTokens, CU_TENSOR_MAP_SWIZZLE_128B) != 0)
+    return -1;
+  SkinnyParams p{};
+  p.tiles = static_cast<int>(ceil_div(n, Cfg::kRowsPerTile));
+  p.chunks = k / kChunkK;
+  const long long units = static_cast<long long>(p.tiles) * p.chunks;
+  const int grid = static_cast<int>(std::min<long long>(sms, units));
+  p.counters = reinterpret_cast<int*>(scratch);
+  p.partials = reinterpret_cast<float*>(scratch + kStaticCounterBytes);
+  p.status = reinterpret_cast<int*>(scratch + kStaticCounterBytes + kStaticPartialBytes);
+  p.times = nullptr;
+  p.scales = scales;
+  p.c = c;
+  p.m = m;
+  p.n = n;
+  p.k = k;
+  p.m0 = m0;
+  kernel<<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(map_w, map_a, p);
+  return launched("qmm8_skinny(static scratch)", dim3(grid), dim3(Cfg::kThreads), Cfg::kSmemBytes, stream);
+}
+
 }  // namespace
 }  // namespace tvb
 
 using namespace tvb;
+
+extern "C" int tvb_qmm8_static_scratch(int device, const void* a, int dtype, int64_t a_sm, const int8_t* b, const void* scales,
+                                       void* c, int64_t m, int64_t n, int64_t k, void* stream_handle) {
+  TVB_REQUIRE(device >= 0 && device < 64, "tvb_qmm8_static_scratch: device index out of range");
+  TVB_REQUIRE(dtype == TVB_F16 || dtype == TVB_BF16, "tvb_qmm8_static_scratch: A must be float16 or bfloat16");
+  TVB_REQUIRE(m >= 0 && n >= 0 && k >= 0, "tvb_qmm8_static_scratch: negative size");
+  if (m == 0 || n == 0) return 0;
+  TVB_REQUIRE(a != nullptr && b != nullptr && scales != nullptr && c != nullptr, "tvb_qmm8_static_scratch: NULL pointer");
+  TVB_REQUIRE(m <= 64, "tvb_qmm8_static_scratch: at most 64 rows of A (the decode kernel); use tvb_qmm8 beyond");
+  TVB_REQUIRE(skinny_ok(a, dtype, a_sm, b, m, n, k),
+              "tvb_qmm8_static_scratch: needs k a multiple of 128 and 16-byte aligned A rows and B; use tvb_qmm8 otherwise");
+  TVB_REQUIRE(n <= static_cast<int64_t>(kStaticMaxTiles) * 256 && k < (int64_t(1) << 31),
+              "tvb_qmm8_static_scratch: n exceeds the built-in scratch (1 048 576 output columns at most); use tvb_qmm8");
+  TVB_CUDA(cudaSetDevice(device));
+  int sms = 0;
+  TVB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
+  TVB_REQUIRE(sms >= 1 && sms <= kStaticMaxCtas,
+              "tvb_qmm8_static_scratch: this GPU has more SMs than the built-in scratch was sized for (160); use tvb_qmm8");
+  unsigned char* scratch = nullptr;
+  if (static_scratch_address(device, &scratch) != 0) return -1;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_handle);
+  // The array keeps whatever the previous call left: the counters and the status word must start at zero.
+  const int64_t tiles = ceil_div(n, 256);
+  TVB_CUDA(cudaMemsetAsync(scratch, 0, static_cast<size_t>(tiles) * sizeof(int), stream));
+  TVB_CUDA(cudaMemsetAsync(scratch + kStaticCounterBytes + kStaticPartialBytes, 0, sizeof(int), stream));
+  const int mi = static_cast<int>(m), ni = static_cast<int>(n), ki = static_cast<int>(k);
+  const int64_t stride = m == 1 ? k : a_sm;
+  for (int m0 = 0; m0 < mi; m0 += 16) {
+    const int rows = mi - m0;
+    int rc;
+    if (dtype == TVB_BF16)
+      rc = rows <= 8 ? launch_skinny_static<TVB_BF16, 1>(device, sms, stream, scratch, a, stride, b, scales, c, mi, ni, ki, m0)
+                     : launch_skinny_static<TVB_BF16, 2>(device, sms, stream, scratch, a, stride, b, scales, c, mi, ni, ki, m0);
+    else
+      rc = rows <= 8 ? launch_skinny_static<TVB_F16, 1>(device, sms, stream, scratch, a, stride, b, scales, c, mi, ni, ki, m0)
+                     : launch_skinny_static<TVB_F16, 2>(device, sms, stream, scratch, a, stride, b, scales, c, mi, ni, ki, m0);
+    if (rc != 0) return rc;
+  }
+  return 0;
+}
 
 // Diagnostics (not part of the public header): per-CTA SM id and start / end times of the next skinny launches.
 extern "C" __attribute__((visibility("default"))) void tvb_debug_qmm8_times(long long* device_buffer) {
