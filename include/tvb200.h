@@ -159,6 +159,17 @@ TVB_API uint64_t tvb_qmm4_workspace_bytes(int64_t m, int64_t k);
 TVB_API int tvb_qmm4(int device, const void* inp, int dtype, const float* packed, int has_bias, void* out, int64_t m,
              int64_t n, int64_t k, int64_t bs, void* workspace, uint64_t workspace_bytes);
 
+/* The same op on the tensor cores (tcgen05 kind::i8), still bit for bit: the fast route (quant.cpp:187-202 has no
+ * counterpart: the reference has one kernel). `prepared` is the packed vector's weights unpacked to int8, made once
+ * per packed tensor by tvb_qmm4_prepare (tvb_qmm4_prepared_bytes(n, k) bytes of device memory) and reusable for as long
+ * as the packed vector does not change. Needs k and bs multiples of 32. workspace: tvb_qmm4_tc_workspace_bytes(m, k). */
+TVB_API uint64_t tvb_qmm4_prepared_bytes(int64_t n, int64_t k);
+TVB_API int tvb_qmm4_prepare(int device, const float* packed, int64_t n, int64_t k, int64_t bs, void* prepared,
+                             uint64_t prepared_bytes);
+TVB_API uint64_t tvb_qmm4_tc_workspace_bytes(int64_t m, int64_t k);
+TVB_API int tvb_qmm4_tc(int device, const void* inp, int dtype, const float* packed, int has_bias, const void* prepared,
+                        void* out, int64_t m, int64_t n, int64_t k, int64_t bs, void* workspace, uint64_t workspace_bytes);
+
 /* ---- aten::_scaled_mm (replaces the chain of cast / mul / matmul / add / cast
  *      dispatches, quant.cpp:283-299) ----
  * out[m, n] = cast((a * scale_a) @ (b * scale_b) + bias) (float8 outputs: times

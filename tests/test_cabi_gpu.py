@@ -155,3 +155,49 @@ def test_scaled_mm_config4_sample(abi):
         ref64 = (a.double() * sa.double()) @ (b.double() * sb.double())
         ulp = torch.finfo(torch.bfloat16).eps * ref64.abs().clamp_min(2.0**-8 * ref64.abs().max())
         assert ((got.cpu().double() - ref64).abs() <= 2 * ulp).all()
+
+
+# ---------------------------------------------------------------- dyn-int4 on the tensor cores (bit-exact too)
+
+@pytest.mark.parametrize("m,k,n,bs,bias", [(1, 64, 4096, 32, False), (32, 128, 11008, 32, True), (5, 96, 70, 96, True),
+                                           (4, 256, 16, 64, True), (9, 64, 33, 64, False), (130, 512, 300, 32, True),
+                                           (257, 1024, 129, 128, False), (64, 4096, 256, 4096, True), (200, 2048, 520, 2048, False),
+                                           (128, 4096, 1024, 32, True)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_qmm4_tensor_core_path_bit_exact(abi, m, k, n, bs, bias, dtype):
+    if dtype == torch.bfloat16 and bs != k:
+        pytest.skip("bfloat16 inputs are channelwise only (the CPU's check)")
+    if m * n * k > 3e8:
+        # too slow for the scalar oracle: compare with the bit-exact CUDA-core kernel, itself checked against the oracle
+        x, w, sc, bvec = C.dyn4_case(m, k, n, bs, bias, dtype)
+        packed = abi.qmm4_pack(dev(w), dev(sc), dev(bvec))
+        want = abi.qmm4(dev(x), packed, bs, k, n)
+        abi.synchronize()
+        want = want.cpu()
+    else:
+        x, w, sc, bvec = C.dyn4_case(m, k, n, bs, bias, dtype)
+        packed_cpu = O.dyn_quant_pack_4bit_weight(w, sc, bvec, bs, k, n)
+        want = O.dyn_quant_matmul_4bit(x, packed_cpu, bs, k, n)
+        packed = dev(packed_cpu)
+    prepared = abi.qmm4_prepare(packed, n, k, bs)
+    got = abi.qmm4_tc(dev(x), packed, prepared, bs, k, n)
+    again = abi.qmm4_tc(dev(x), packed, prepared, bs, k, n)
+    abi.synchronize()
+    view = torch.int16 if dtype == torch.bfloat16 else torch.int32
+    assert torch.equal(got.cpu().view(view), want.view(view))
+    assert torch.equal(again.cpu().view(view), want.view(view))
+
+
+def test_qmm4_tensor_core_path_wide_scales(abi):
+    # float32 group scales with full mantissas: the drain must not use the 3*s shortcut
+    m, k, n, bs = 20, 256, 96, 64
+    x, w, _, bvec = C.dyn4_case(m, k, n, bs, True, torch.float32)
+    sc = torch.rand(n, k // bs, generator=C.gen(5)) / 10 + 1e-3
+    packed_cpu = O.dyn_quant_pack_4bit_weight(w, sc, bvec, bs, k, n)
+    want = O.dyn_quant_matmul_4bit(x, packed_cpu, bs, k, n)
+    packed = dev(packed_cpu)
+    prepared = abi.qmm4_prepare(packed, n, k, bs)
+    got = abi.qmm4_tc(dev(x), packed, prepared, bs, k, n)
+    abi.synchronize()
+    assert prepared[:4].cpu().view(torch.int32).item() == 1
+    assert torch.equal(got.cpu(), want)

@@ -14,6 +14,8 @@
 #include <ATen/native/Resize.h>
 #include <torch/library.h>
 
+#include <list>
+#include <mutex>
 #include <sstream>
 
 #include "backend.h"
@@ -86,6 +88,47 @@ at::Tensor dyn_quant_pack_4bit_weight(const at::Tensor& weights, const at::Tenso
   return packed;
 }
 
+// The tensor-core kernel reads the weights as int8 [n, k]; unpacking the packed vector's float-encoded bytes costs
+// about as much as a small product, so the result is kept per packed tensor: keyed by its storage, offset and size,
+// and dropped when the tensor's version counter moves (an in-place write) or its storage dies.
+struct PreparedWeights {
+  c10::weak_intrusive_ptr<c10::StorageImpl> storage;
+  const void* data;
+  int64_t numel, n, k, bs;
+  uint32_t version;
+  at::Tensor prepared;
+};
+
+std::mutex g_prepared_mutex;
+std::list<PreparedWeights> g_prepared;  // most recently used first
+constexpr size_t kMaxPrepared = 16;
+
+uint32_t version_of(const at::Tensor& t) { return t.is_inference() ? 0u : t._version(); }
+
+at::Tensor prepared_weights(const at::Tensor& packed, int dev, int64_t n, int64_t k, int64_t bs) {
+  std::lock_guard<std::mutex> lock(g_prepared_mutex);
+  c10::StorageImpl* impl = packed.storage().unsafeGetStorageImpl();
+  for (auto it = g_prepared.begin(); it != g_prepared.end();) {
+    if (it->storage.expired()) {
+      it = g_prepared.erase(it);
+      continue;
+    }
+    if (it->storage._unsafe_get_target() == impl && it->data == packed.const_data_ptr() && it->numel == packed.numel() &&
+        it->n == n && it->k == k && it->bs == bs && it->version == version_of(packed)) {
+      g_prepared.splice(g_prepared.begin(), g_prepared, it);
+      return g_prepared.front().prepared;
+    }
+    ++it;
+  }
+  const uint64_t bytes = tvb_qmm4_prepared_bytes(n, k);
+  at::Tensor prepared = at::empty({static_cast<int64_t>(bytes)}, packed.options().dtype(at::kByte));
+  check(tvb_qmm4_prepare(dev, static_cast<const float*>(gpu_address(packed)), n, k, bs, gpu_address_out(prepared), bytes));
+  g_prepared.push_front(PreparedWeights{c10::weak_intrusive_ptr<c10::StorageImpl>(packed.storage().getWeakStorageImpl()),
+                                        packed.const_data_ptr(), packed.numel(), n, k, bs, version_of(packed), prepared});
+  while (g_prepared.size() > kMaxPrepared) g_prepared.pop_back();
+  return prepared;
+}
+
 at::Tensor dyn_quant_matmul_4bit(const at::Tensor& inp, const at::Tensor& packed_weights, int64_t block_size,
                                  int64_t in_features, int64_t out_features) {
   constexpr const char* fn = "_dyn_quant_matmul_4bit_cpu";
@@ -106,9 +149,32 @@ at::Tensor dyn_quant_matmul_4bit(const at::Tensor& inp, const at::Tensor& packed
   if (out.numel() == 0) return out;
   at::Tensor x = inp.contiguous();
   at::Tensor packed = packed_weights.to(at::kFloat).contiguous();
+  const int dev = enter_device(inp);
+  // Both kernels are bit for bit the CPU's arithmetic; the tensor-core one takes every shape it can (k and the
+  // block size multiples of 32), the CUDA-core one the rest. TORCH_VK_QMM4=plain forces the latter (as the
+  // reference's TORCH_VK_GEMM switches kernels for its tests).
+  static const bool force_plain = [] {
+    const char* v = std::getenv("TORCH_VK_QMM4");
+    return v != nullptr && std::string(v) == "plain";
+  }();
+  if (!force_plain && K % 32 == 0 && block_size % 32 == 0) {
+    // the cache keys on the caller's tensor when it is already the float32 vector (the usual case)
+    const bool own = packed.is_same(packed_weights);
+    at::Tensor prepared = own ? prepared_weights(packed_weights, dev, N, K, block_size) : at::Tensor();
+    if (!own) {
+      const uint64_t bytes = tvb_qmm4_prepared_bytes(N, K);
+      prepared = at::empty({static_cast<int64_t>(bytes)}, inp.options().dtype(at::kByte));
+      check(tvb_qmm4_prepare(dev, static_cast<const float*>(gpu_address(packed)), N, K, block_size, gpu_address_out(prepared), bytes));
+    }
+    const uint64_t tc_bytes = tvb_qmm4_tc_workspace_bytes(M, K);
+    at::Tensor tc_ws = at::empty({static_cast<int64_t>(tc_bytes)}, inp.options().dtype(at::kByte));
+    check(tvb_qmm4_tc(dev, gpu_address(x), dtype_code(x.scalar_type()), static_cast<const float*>(gpu_address(packed)),
+                      bias_elements != 0 ? 1 : 0, gpu_address(prepared), gpu_address_out(out), M, N, K, block_size,
+                      gpu_address_out(tc_ws), tc_bytes));
+    return out;
+  }
   const uint64_t ws_bytes = tvb_qmm4_workspace_bytes(M, K);
   at::Tensor ws = at::empty({static_cast<int64_t>(ws_bytes)}, inp.options().dtype(at::kByte));
-  const int dev = enter_device(inp);
   check(tvb_qmm4(dev, gpu_address(x), dtype_code(x.scalar_type()), static_cast<const float*>(gpu_address(packed)),
                  bias_elements != 0 ? 1 : 0, gpu_address_out(out), M, N, K, block_size, gpu_address_out(ws), ws_bytes));
   return out;

@@ -1,0 +1,476 @@
+// aten::_dyn_quant_matmul_4bit for large m on the fifth-generation tensor cores, still bit for bit.
+//
+// The reference's PHASE 1 (crates/vkcore/shaders/qmm4.slang:183-247) scales every block of bs values of k by
+// its own float32 scale and adds the blocks up in order, so the int32 block sums cannot be merged: each one has
+// to leave the tensor core, be converted, multiplied and added with the reference's roundings. This kernel lets
+// tcgen05.mma kind::i8 produce the block sums and makes that drain as cheap as it can be:
+//
+//   * Operands: the int4 weights unpacked once to int8 [n, k] (tvb_qmm4_prepare; the ATen layer caches it per
+//     packed tensor), the activations quantised to int8 [m, k] by PHASE 0 with 64 extra columns per row holding
+//     two halves o1 + o2 = -zero_point. (q - zp) does not fit int8, but q, o1 and o2 do, so a block sum is three
+//     MMAs into the same accumulator: W.q + W.o1 + W.o2 (exact integers, same value as the shader's loop).
+//   * Orientation: weight rows ride the MMA's 128 rows (TMEM lanes), tokens its 128 columns, so each draining
+//     thread owns one output column n and keeps that column's block scale in a register.
+//   * Drain: tcgen05.ld brings 64 int32 sums per thread; float(iacc) * scale costs one integer add and one FMA:
+//     bits(0x4B400000 + iacc) is the float 12582912 + iacc exactly, and fma(that, s, -12582912 s) rounds the exact
+//     product iacc * s once, which is fl(float(iacc) * s). (Needs 3 s exact in float32, true for scales that came
+//     from bfloat16; otherwise, or for blocks over 1024 values, a convert and a multiply are used.) One more add
+//     accumulates, as the reference does; the first block assigns.
+//   * Four TMEM accumulator buffers (4 x 128 columns) let the MMAs of the next blocks run under the drain.
+//
+// Warp roles: 0-7 drain and epilogue (two warps per TMEM lane quarter, one per half of the tokens), 8 TMA
+// producer, 9 MMA issuer and TMEM owner. Every wait is bounded.
+#include <cuda.h>
+
+#include <cstdlib>
+
+#include "../core/common.h"
+#include "../core/tensormap.h"
+#include "numerics.cuh"
+#include "ptx.cuh"
+
+namespace tvb {
+namespace {
+
+constexpr int kTileN = 128;   // weight rows (output columns) per tile = MMA rows
+constexpr int kTileM = 128;   // tokens per tile = MMA columns
+constexpr int kStageK = 128;  // bytes of k per shared-memory stage (four 32-k MMA steps)
+constexpr int kStages = 6;
+constexpr int kStageBytes = (kTileN + kTileM) * kStageK;  // 32 KB
+constexpr int kOTileBytes = kTileM * kStageK;             // 16 KB: the tokens' o1 / o2 columns
+constexpr int kAccBuffers = 4;
+constexpr int kThreads = 320;
+constexpr int kSmemBytes = kStages * kStageBytes + 2 * kOTileBytes + 1024 + 256;
+constexpr int kExtraCols = 64;  // per activation row: 32 x o1, 32 x o2
+
+struct TcParams {
+  const float* scales;   // [n, ndrains] (inside the packed vector)
+  const float* bias;     // [n] or NULL
+  const float* recip;    // [m]
+  const int* wide_scales;  // device flag: some scale has more than 22 significant bits
+  void* out;             // [m, n] float32 or bfloat16
+  int* status;
+  int m, n, k;
+  int steps_per_drain;   // bs / 32
+  int ndrains;           // k / bs
+  int tiles_m, tiles_n;
+  int out_bf16;
+  int debug;  // diagnostics: 1 skips the TMEM loads and the folding, 2 the folding only (results are then wrong)
+};
+
+// PHASE 0 with the tensor-core layout: q rows of k + 64 bytes, the tail holding o1 (32 bytes) and o2 (32 bytes).
+template <int DT>
+__global__ void __launch_bounds__(256) qmm4_quantize_tc_kernel(const void* __restrict__ inp, int k, int groupwise,
+                                                               int8_t* __restrict__ q, float* __restrict__ recip_out,
+                                                               int32_t* __restrict__ neg_zp_out) {
+  __shared__ float red_min[8], red_max[8];
+  __shared__ float row_scale;
+  __shared__ int row_zp;
+  const int64_t base = static_cast<int64_t>(blockIdx.x) * k;
+  const int64_t qbase = static_cast<int64_t>(blockIdx.x) * (k + kExtraCols);
+  const int t = threadIdx.x;
+  float mn = 3.40282347e38f, mx = -3.40282347e38f;
+  for (int kk = t; kk < k; kk += 256) {
+    float v = load_float<DT>(inp, base + kk);
+    mn = fminf(mn, v);
+    mx = fmaxf(mx, v);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  }
+  if ((t & 31) == 0) {
+    red_min[t >> 5] = mn;
+    red_max[t >> 5] = mx;
+  }
+  __syncthreads();
+  if (t == 0) {
+    for (int i = 1; i < 8; i++) {
+      mn = fminf(mn, red_min[i]);
+      mx = fmaxf(mx, red_max[i]);
+    }
+    const float qmin = -128.0f, qmax = 127.0f;
+    float rmin = fminf(0.0f, mn), rmax = fmaxf(0.0f, mx);
+    float scale = rmin == rmax ? 1.0f : __fdiv_rn(qmax - qmin, __fsub_rn(rmax, rmin));
+    float recip = scale != 0.0f ? __fdiv_rn(1.0f, scale) : 0.0f;
+    float dmin = __fmul_rn(rmin, scale), dmax = __fmul_rn(rmax, scale);
+    float err = groupwise ? __fadd_rn(__fadd_rn(__fadd_rn(qmin, dmin), qmax), dmax)
+                          : __fadd_rn(__fadd_rn(qmin, dmin), __fadd_rn(qmax, dmax));
+    float zp = err > 0.0f ? __fsub_rn(qmin, dmin) : __fsub_rn(qmax, dmax);
+    zp = fminf(fmaxf(zp, qmin), qmax);
+    int izp = __float2int_rn(zp);
+    row_scale = scale;
+    row_zp = izp;
+    recip_out[blockIdx.x] = recip;
+    neg_zp_out[blockIdx.x] = -izp;
+  }
+  __syncthreads();
+  const float scale = row_scale;
+  const int zp = row_zp;
+  for (int kk = t; kk < k; kk += 256) {
+    float scaled = __fmul_rn(load_float<DT>(inp, base + kk), scale);
+    int v = static_cast<int>(roundf(scaled)) + zp;
+    q[qbase + kk] = static_cast<int8_t>(max(-128, min(127, v)));
+  }
+  if (t < kExtraCols) {
+    const int off = -zp;          // in [-127, 128]
+    const int o1 = off >> 1;      // both halves fit int8
+    q[qbase + k + t] = static_cast<int8_t>(t < 32 ? o1 : off - o1);
+  }
+}
+
+// The packed vector's float-encoded weight bytes -> int8 weights [n, k] (low nibble first, value nibble - 8).
+__global__ void qmm4_unpack_kernel(const float* __restrict__ packed, int64_t nbytes, int8_t* __restrict__ w) {
+  int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < nbytes; i += stride) {
+    uint32_t byte = static_cast<uint32_t>(packed[i]);
+    uint32_t lo = ((byte & 15u) - 8u) & 0xffu, hi = ((byte >> 4) - 8u) & 0xffu;
+    reinterpret_cast<uint16_t*>(w)[i] = static_cast<uint16_t>(lo | (hi << 8));
+  }
+}
+
+// Sets *flag when a scale's low two mantissa bits are not zero (3 * s would then not be exact in float32).
+__global__ void qmm4_scan_scales_kernel(const float* __restrict__ scales, int64_t count, int* __restrict__ flag) {
+  int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  int wide = 0;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < count; i += stride) {
+    uint32_t bits = __float_as_uint(scales[i]);
+    uint32_t exp = (bits >> 23) & 0xffu;
+    if ((bits & 3u) != 0u || (exp == 0u && (bits & 0x7fffffu) != 0u) || exp >= 0xf0u) wide = 1;
+  }
+  if (__any_sync(0xffffffffu, wide) && (threadIdx.x & 31) == 0) atomicOr(flag, 1);
+}
+
+// One block's 32 integer sums folded into 32 running outputs: x = fl(float(iacc) * s); acc = FIRST ? x : fl(acc + x).
+// Not WIDE: bits(iacc + 0x4B400000) is the float 12582912 + iacc exactly, and fma(that, s, -12582912 s) rounds the
+// exact product iacc * s once. WIDE: convert and multiply.
+template <bool WIDE, bool FIRST>
+__device__ __forceinline__ void fold_block(float (&acc)[32], const uint32_t (&r)[32], const float s, const float t) {
+#pragma unroll
+  for (int i = 0; i < 32; i++) {
+    const float x = WIDE ? __fmul_rn(static_cast<float>(static_cast<int>(r[i])), s)
+                         : __fmaf_rn(__uint_as_float(r[i] + 0x4B400000u), s, t);
+    acc[i] = FIRST ? x : __fadd_rn(acc[i], x);  // (the first block assigns: keeps -0)
+  }
+}
+
+// The drain and epilogue of warps 0-7. WIDE: scales with full mantissas or blocks over 1024 values.
+template <bool WIDE>
+__device__ __forceinline__ void drain_tiles(const TcParams& p, const uint32_t tmem_base, const uint32_t tfull0,
+                                            const uint32_t tempty0, volatile int* abort_flag, const int warp, const int lane) {
+  const int tiles = p.tiles_m * p.tiles_n;
+  const int quarter = warp & 3, half = warp >> 2;
+  const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(half * 64);
+  uint32_t buf = 0, buf_phase = 0;
+  bool ok = true;
+  for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
+    const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
+    const int col = tn * kTileN + quarter * 32 + lane;   // output column = weight row
+    const int col_ld = min(col, p.n - 1);
+    const int tok0 = tm * kTileM + half * 64;
+    const float* srow = p.scales + static_cast<int64_t>(col_ld) * p.ndrains;
+    float acc0[32], acc1[32];   // tokens tok0 .. tok0+31 and tok0+32 .. tok0+63
+    float s_next = __ldg(srow);
+    for (int d = 0; d < p.ndrains && ok; d++) {
+      const float s = s_next;
+      if (d + 1 < p.ndrains) s_next = __ldg(srow + d + 1);
+      const float t = __fmul_rn(-12582912.0f, s);  // exact when s has at most 22 significant bits
+      ok = ptx::mbar_wait(tfull0 + 8 * buf, buf_phase, abort_flag);
+      if (!ok) break;
+      ptx::tc_fence_after();
+      uint32_t r0[32], r1[32];
+      if (p.debug != 1) {
+        ptx::tmem_ld_32x32(lane_base + buf * kTileM, r0);
+        ptx::tmem_ld_32x32(lane_base + buf * kTileM + 32, r1);
+        ptx::tmem_ld_wait();
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; i++) r0[i] = r1[i] = 0;
+      }
+      ptx::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(tempty0 + 8 * buf);  // the sums are in registers: the buffer is free again
+      if (++buf == kAccBuffers) {
+        buf = 0;
+        buf_phase ^= 1u;
+      }
+      if (p.debug == 0) {
+        if (d == 0) {
+          fold_block<WIDE, true>(acc0, r0, s, t);
+          fold_block<WIDE, true>(acc1, r1, s, t);
+        } else {
+          fold_block<WIDE, false>(acc0, r0, s, t);
+          fold_block<WIDE, false>(acc1, r1, s, t);
+        }
+      } else if (d == 0) {
+#pragma unroll
+        for (int i = 0; i < 32; i++) {
+          acc0[i] = __uint_as_float(r0[i]);
+          acc1[i] = __uint_as_float(r1[i]);
+        }
+      }
+    }
+    if (!ok) break;
+    if (col < p.n) {
+      const float bias = p.bias != nullptr ? __ldg(p.bias + col) : 0.0f;
+      const float hi = p.out_bf16 ? 3.38953139e38f : 3.40282347e38f;
+#pragma unroll
+      for (int i = 0; i < 64; i++) {
+        const int tok = tok0 + i;
+        if (tok < p.m) {
+          float v = __fmul_rn(i < 32 ? acc0[i & 31] : acc1[i & 31], __ldg(p.recip + tok));
+          if (p.bias != nullptr) v = __fadd_rn(v, bias);
+          v = v < -hi ? -hi : v;  // (std::max / std::min: NaN passes)
+          v = hi < v ? hi : v;
+          const int64_t o = static_cast<int64_t>(tok) * p.n + col;
+          if (p.out_bf16) static_cast<uint16_t*>(p.out)[o] = static_cast<uint16_t>(__float_as_uint(v) >> 16);
+          else static_cast<float*>(p.out)[o] = v;
+        }
+      }
+    }
+  }
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+    qmm4_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_q, const TcParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* base_ptr = smem_raw + (base - ptx::smem_u32(smem_raw));
+  const uint32_t otile0 = base + kStages * kStageBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(base_ptr + kStages * kStageBytes + 2 * kOTileBytes);
+  const uint32_t full0 = ptx::smem_u32(bars), empty0 = full0 + 8 * kStages;
+  const uint32_t ofull0 = empty0 + 8 * kStages, oempty0 = ofull0 + 16;
+  const uint32_t tfull0 = oempty0 + 16, tempty0 = tfull0 + 8 * kAccBuffers;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 4 + 2 * kAccBuffers);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  static_assert((2 * kStages + 4 + 2 * kAccBuffers) * 8 + 8 <= 256, "barrier area too small");
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; s++) {
+      ptx::mbar_init(full0 + 8 * s, 1);
+      ptx::mbar_init(empty0 + 8 * s, 1);
+    }
+    for (int i = 0; i < 2; i++) {
+      ptx::mbar_init(ofull0 + 8 * i, 1);
+      ptx::mbar_init(oempty0 + 8 * i, 1);
+    }
+    for (int b = 0; b < kAccBuffers; b++) {
+      ptx::mbar_init(tfull0 + 8 * b, 1);
+      ptx::mbar_init(tempty0 + 8 * b, 8);
+    }
+    *abort_flag = 0;
+    ptx::fence_mbar_init();
+  }
+  if (warp == 9) ptx::tmem_alloc(ptx::smem_u32(tmem_slot), 512);
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const int tiles = p.tiles_m * p.tiles_n;
+  const int nstages = (p.k + kStageK - 1) / kStageK;
+  const int nsteps = p.k / 32;
+
+  if (warp == 8) {
+    if (lane == 0) {
+      ptx::prefetch_tensormap(&map_w);
+      ptx::prefetch_tensormap(&map_q);
+      long long it = 0;
+      int ti = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ti++) {
+        const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
+        const int slot = ti & 1;
+        ok = ptx::mbar_wait(oempty0 + 8 * slot, static_cast<uint32_t>(((ti >> 1) & 1) ^ 1), abort_flag);
+        if (!ok) break;
+        ptx::mbar_expect_tx(ofull0 + 8 * slot, kOTileBytes);
+        ptx::tma_load_2d(otile0 + slot * kOTileBytes, &map_q, p.k, tm * kTileM, ofull0 + 8 * slot);
+        for (int kb = 0; kb < nstages; kb++, it++) {
+          const int s = static_cast<int>(it % kStages);
+          ok = ptx::mbar_wait(empty0 + 8 * s, static_cast<uint32_t>(((it / kStages) & 1) ^ 1), abort_flag);
+          if (!ok) break;
+          const uint32_t dst = base + s * kStageBytes;
+          ptx::mbar_expect_tx(full0 + 8 * s, kStageBytes);
+          ptx::tma_load_2d(dst, &map_w, kb * kStageK, tn * kTileN, full0 + 8 * s);
+          ptx::tma_load_2d(dst + kTileN * kStageK, &map_q, kb * kStageK, tm * kTileM, full0 + 8 * s);
+        }
+      }
+      const long long first = it > kStages ? it - kStages : 0;
+      for (long long j = first; j < it; j++) {
+        volatile int never = 0;
+        ptx::mbar_wait(full0 + 8 * static_cast<int>(j % kStages), static_cast<uint32_t>((j / kStages) & 1), &never);
+      }
+      if (ti > 0) {
+        volatile int never = 0;
+        ptx::mbar_wait(ofull0 + 8 * ((ti - 1) & 1), static_cast<uint32_t>(((ti - 1) >> 1) & 1), &never);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 9) {
+    if (lane == 0) {
+      // int32 accumulators, signed 8-bit operands, both K-major, 128 x 128
+      const uint32_t idesc = ptx::tc_instr_desc(2, 1, 1, kTileN, kTileM);
+      // This one thread's instruction stream paces the tensor core (an MMA of this size lasts ~64 clocks), so the
+      // bookkeeping is kept to counters that are bumped, never divided.
+      uint32_t stage = 0, stage_phase = 0;      // shared-memory ring position
+      uint32_t buf = 0, buf_phase = 0;          // TMEM accumulator ring position
+      int in_drain = 0;
+      const int spd = p.steps_per_drain;
+      int ti = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ti++) {
+        const int slot = ti & 1;
+        ok = ptx::mbar_wait(ofull0 + 8 * slot, static_cast<uint32_t>((ti >> 1) & 1), abort_flag);
+        if (!ok) break;
+        const uint64_t o_desc = ptx::tc_smem_desc_sw128(otile0 + slot * kOTileBytes);
+        int steps_left = nsteps;
+        for (int kb = 0; kb < nstages && ok; kb++) {
+          ok = ptx::mbar_wait(full0 + 8 * stage, stage_phase, abort_flag);
+          if (!ok) break;
+          ptx::tc_fence_after();
+          uint64_t w_desc = ptx::tc_smem_desc_sw128(base + stage * kStageBytes);
+          uint64_t q_desc = ptx::tc_smem_desc_sw128(base + stage * kStageBytes + kTileN * kStageK);
+#pragma unroll
+          for (int j = 0; j < 4; j++) {
+            if (steps_left <= 0) break;
+            steps_left--;
+            if (in_drain == 0) {
+              ok = ptx::mbar_wait(tempty0 + 8 * buf, buf_phase ^ 1u, abort_flag);  // the drain warps have read it
+              if (!ok) break;
+              ptx::tc_fence_after();
+            }
+            const uint32_t d_tmem = tmem_base + buf * kTileM;
+            ptx::tc_mma<1>(d_tmem, w_desc, q_desc, idesc, in_drain != 0 ? 1u : 0u);
+            ptx::tc_mma<1>(d_tmem, w_desc, o_desc, idesc, 1u);      // + W . o1
+            ptx::tc_mma<1>(d_tmem, w_desc, o_desc + 2, idesc, 1u);  // + W . o2
+            w_desc += 2;  // the next 32 bytes of k, in the descriptor's 16-byte units
+            q_desc += 2;
+            if (++in_drain == spd) {
+              ptx::tc_commit(tfull0 + 8 * buf);
+              in_drain = 0;
+              if (++buf == kAccBuffers) {
+                buf = 0;
+                buf_phase ^= 1u;
+              }
+            }
+          }
+          ptx::tc_commit(empty0 + 8 * stage);
+          if (++stage == kStages) {
+            stage = 0;
+            stage_phase ^= 1u;
+          }
+        }
+        if (ok) ptx::tc_commit(oempty0 + 8 * slot);
+      }
+    }
+    __syncwarp();
+  } else {
+    // ---------------- drain: thread = one weight row (output column), 64 tokens
+    if (*p.wide_scales != 0 || p.steps_per_drain > 32) drain_tiles<true>(p, tmem_base, tfull0, tempty0, abort_flag, warp, lane);
+    else drain_tiles<false>(p, tmem_base, tfull0, tempty0, abort_flag, warp, lane);
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (threadIdx.x == 0 && *abort_flag != 0) atomicExch(p.status, 3);
+  if (warp == 9) {
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc(tmem_base, 512);
+  }
+}
+
+uint64_t align256(uint64_t x) { return (x + 255) & ~uint64_t(255); }
+
+}  // namespace
+}  // namespace tvb
+
+using namespace tvb;
+
+extern "C" uint64_t tvb_qmm4_prepared_bytes(int64_t n, int64_t k) {
+  return 256 + align256(static_cast<uint64_t>(n) * static_cast<uint64_t>(k));
+}
+
+extern "C" int tvb_qmm4_prepare(int device, const float* packed, int64_t n, int64_t k, int64_t bs, void* prepared,
+                                uint64_t prepared_bytes) {
+  TVB_REQUIRE(n > 0 && k > 0 && bs > 0 && k % 2 == 0 && k % bs == 0, "tvb_qmm4_prepare: bad shape");
+  TVB_REQUIRE(packed != nullptr && prepared != nullptr && prepared_bytes >= tvb_qmm4_prepared_bytes(n, k),
+              "tvb_qmm4_prepare: prepared buffer too small");
+  cudaStream_t stream;
+  if (enter(device, &stream) != 0) return -1;
+  int* flag = static_cast<int*>(prepared);
+  int8_t* w = static_cast<int8_t*>(prepared) + 256;
+  TVB_CUDA(cudaMemsetAsync(flag, 0, 256, stream));
+  const int64_t nbytes = n * k / 2, nscales = n * (k / bs);
+  const int cap = sm_count(device) * 16;
+  int grid = static_cast<int>(std::min<int64_t>(ceil_div(nbytes, 256), cap));
+  qmm4_unpack_kernel<<<grid, 256, 0, stream>>>(packed, nbytes, w);
+  if (launched("qmm4_unpack", dim3(grid), dim3(256), 0, stream) != 0) return -1;
+  grid = static_cast<int>(std::min<int64_t>(ceil_div(nscales, 256), cap));
+  qmm4_scan_scales_kernel<<<grid, 256, 0, stream>>>(packed + nbytes, nscales, flag);
+  return launched("qmm4_scan_scales", dim3(grid), dim3(256), 0, stream);
+}
+
+extern "C" uint64_t tvb_qmm4_tc_workspace_bytes(int64_t m, int64_t k) {
+  return align256(static_cast<uint64_t>(m) * static_cast<uint64_t>(k + kExtraCols)) + 2 * align256(static_cast<uint64_t>(m) * 4);
+}
+
+extern "C" int tvb_qmm4_tc(int device, const void* inp, int dtype, const float* packed, int has_bias, const void* prepared,
+                           void* out, int64_t m, int64_t n, int64_t k, int64_t bs, void* workspace, uint64_t workspace_bytes) {
+  TVB_REQUIRE(dtype == TVB_F32 || dtype == TVB_BF16, "tvb_qmm4_tc: input must be float32 or bfloat16");
+  TVB_REQUIRE(m >= 0 && n >= 0 && k > 0 && bs > 0, "tvb_qmm4_tc: bad size");
+  TVB_REQUIRE(k % 32 == 0 && bs % 32 == 0 && k % bs == 0, "tvb_qmm4_tc: k and the block size must be multiples of 32");
+  TVB_REQUIRE(m * (k + kExtraCols) < (int64_t(1) << 31) && n * k < (int64_t(1) << 32) && m * n < (int64_t(1) << 40),
+              "tvb_qmm4_tc: sizes beyond 32 bits");
+  if (m == 0 || n == 0) return 0;
+  TVB_REQUIRE(inp != nullptr && packed != nullptr && prepared != nullptr && out != nullptr, "tvb_qmm4_tc: NULL pointer");
+  TVB_REQUIRE(workspace != nullptr && workspace_bytes >= tvb_qmm4_tc_workspace_bytes(m, k), "tvb_qmm4_tc: workspace too small");
+  cudaStream_t stream;
+  if (enter(device, &stream) != 0) return -1;
+  const uint64_t qbytes = align256(static_cast<uint64_t>(m) * static_cast<uint64_t>(k + kExtraCols));
+  const uint64_t rbytes = align256(static_cast<uint64_t>(m) * 4);
+  int8_t* q = static_cast<int8_t*>(workspace);
+  float* recip = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + qbytes);
+  int32_t* neg_zp = reinterpret_cast<int32_t*>(static_cast<uint8_t*>(workspace) + qbytes + rbytes);
+  const int groupwise = bs != k ? 1 : 0;
+  dim3 qgrid(static_cast<unsigned>(m));
+  if (dtype == TVB_F32)
+    qmm4_quantize_tc_kernel<TVB_F32><<<qgrid, 256, 0, stream>>>(inp, static_cast<int>(k), groupwise, q, recip, neg_zp);
+  else
+    qmm4_quantize_tc_kernel<TVB_BF16><<<qgrid, 256, 0, stream>>>(inp, static_cast<int>(k), groupwise, q, recip, neg_zp);
+  if (launched("qmm4_quantize_tc", qgrid, dim3(256), 0, stream) != 0) return -1;
+
+  static bool configured[64] = {};
+  if (!configured[device & 63]) {
+    TVB_CUDA(cudaFuncSetAttribute(qmm4_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+    configured[device & 63] = true;
+  }
+  const int8_t* w = static_cast<const int8_t*>(prepared) + 256;
+  CUtensorMap map_w, map_q;
+  if (make_tensor_map_2d(&map_w, w, CU_TENSOR_MAP_DATA_TYPE_UINT8, k, n, k, kStageK, kTileN, CU_TENSOR_MAP_SWIZZLE_128B) != 0) return -1;
+  if (make_tensor_map_2d(&map_q, q, CU_TENSOR_MAP_DATA_TYPE_UINT8, k + kExtraCols, m, k + kExtraCols, kStageK, kTileM,
+                         CU_TENSOR_MAP_SWIZZLE_128B) != 0)
+    return -1;
+  TcParams p{};
+  const int64_t wcount = n * k / 2;
+  p.ndrains = static_cast<int>(k / bs);
+  p.steps_per_drain = static_cast<int>(bs / 32);
+  p.scales = packed + wcount;
+  p.bias = has_bias ? packed + wcount + n * p.ndrains : nullptr;
+  p.recip = recip;
+  p.wide_scales = static_cast<const int*>(prepared);
+  p.out = out;
+  if (status_word(device, &p.status) != 0) return -1;
+  p.m = static_cast<int>(m);
+  p.n = static_cast<int>(n);
+  p.k = static_cast<int>(k);
+  p.tiles_m = static_cast<int>(ceil_div(m, kTileM));
+  p.tiles_n = static_cast<int>(ceil_div(n, kTileN));
+  p.out_bf16 = dtype == TVB_BF16;
+  {
+    const char* v = std::getenv("TVB200_QMM4_DEBUG");
+    p.debug = v != nullptr ? std::atoi(v) : 0;
+  }
+  const int grid = static_cast<int>(std::min<int64_t>(sm_count(device), static_cast<int64_t>(p.tiles_m) * p.tiles_n));
+  qmm4_tc_kernel<<<grid, kThreads, kSmemBytes, stream>>>(map_w, map_q, p);
+  return launched("qmm4_tc", dim3(grid), dim3(kThreads), kSmemBytes, stream);
+}
