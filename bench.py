@@ -256,7 +256,7 @@ def main():
         import torch.distributed as dist
 
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        dist.init_process_group("nccl")  # (no device_id: with "vk" registered, torch takes that for the accelerator)
     peaks = measured_peaks()
 
     # ---- inputs: this rank's slice of the weight rows (output columns); A replicated
@@ -266,18 +266,11 @@ def main():
     s = s_full[rank * rows:(rank + 1) * rows].contiguous().to(dev)
     a_dev = {m: a_host[m].to(dev) for m in MS}
     a_pinned = {m: a_host[m].pin_memory() for m in MS}
-    gathered = {m: torch.empty(world, m, rows, dtype=torch.bfloat16, device=dev) for m in MS} if world > 1 else None
+    from torch_vulkan_b200 import shard
 
     def product(m, a):
-        c = torch._weight_int8pack_mm(a, w, s)
-        if world > 1:
-            # all ranks' column slices, [world, m, rows]; queued on the backend's stream after the product
-            import torch.distributed as dist
-
-            with torch.cuda.stream(stream):
-                dist.all_gather_into_tensor(tv.as_cuda(gathered[m]), tv.as_cuda(c))
-            return gathered[m]
-        return c
+        # every rank's column slice, then the NCCL all-gather into [m, N] (queued on the backend's stream)
+        return shard.weight_int8pack_mm(a, w, s) if world > 1 else torch._weight_int8pack_mm(a, w, s)
 
     def step_plain(i):
         for m in MS:
@@ -289,8 +282,7 @@ def main():
         if world > 1:
             import torch.distributed as dist
 
-            dist.barrier()
-            torch.cuda.synchronize()
+            shard.barrier()
 
     # ---- device-resident timing
     sampler = ClockSampler(local_rank) if rank == 0 else None
@@ -394,7 +386,7 @@ def main():
     if world > 1:
         import torch.distributed as dist
 
-        dist.barrier()
+        shard.barrier()
         dist.destroy_process_group()
 
 
