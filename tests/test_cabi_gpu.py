@@ -54,6 +54,21 @@ def test_qmm8_kernel_variants(abi, variant, dtype, m, k, n):
     assert (err <= tol).all(), f"max excess {(err - tol).max()}"
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("m,k,n", [(17, 64, 8), (128, 128, 256), (130, 144, 264), (64, 4096, 1000), (300, 1024, 515), (1, 256, 300),
+                                   (512, 2048 + 16, 768)])
+def test_qmm8_tcgen05(abi, dtype, m, k, n):
+    a, b, s = C.config_int8(m, k, n, dtype, seed=m + n)
+    want, tol = C.int8_want(a, b, s)
+    got = abi.qmm8(dev(a), dev(b), dev(s), variant=3)
+    sliced = abi.qmm8(dev(a)[::2], dev(b), dev(s), variant=3) if (k % 8 == 0 and m > 1) else None
+    abi.synchronize()
+    err = (got.cpu().float() - want.float()).abs()
+    assert (err <= tol).all(), f"max excess {(err - tol).max()}"
+    if sliced is not None:
+        assert ((sliced.cpu().float() - want[::2].float()).abs() <= tol[::2]).all()
+
+
 def test_qmm8_skinny_is_deterministic_and_repeatable(abi):
     a, b, s = C.config_int8(16, 1024, 3000, torch.bfloat16)
     da, db, ds = dev(a), dev(b), dev(s)

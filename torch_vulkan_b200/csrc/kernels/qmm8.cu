@@ -30,6 +30,12 @@
 #include "ptx.cuh"
 
 namespace tvb {
+
+// The tcgen05 kernel for m > 16 (qmm8_tc.cu).
+bool qmm8_tc_usable(const void* a, int dtype, int64_t a_sm, const int8_t* b, int64_t m, int64_t n, int64_t k);
+int qmm8_tc(int device, cudaStream_t stream, const void* a, int dtype, int64_t a_sm, const int8_t* b, const void* scales, void* c,
+            int64_t m, int64_t n, int64_t k);
+
 namespace {
 
 // ------------------------------------------------------------------ plain kernel
@@ -572,7 +578,11 @@ extern "C" int tvb_qmm8(int device, const void* a, int dtype, int64_t a_sm, cons
   bool can_skinny = skinny_ok(a, dtype, a_sm, b, m, n, k);
   TVB_REQUIRE(variant != 2 || can_skinny,
               "tvb_qmm8: the skinny kernel needs 16-bit A, m <= 64, k a multiple of 128, 16-byte aligned rows");
-  TVB_REQUIRE(variant >= 0 && variant <= 2, "tvb_qmm8: unknown kernel variant");
+  TVB_REQUIRE(variant >= 0 && variant <= 3, "tvb_qmm8: unknown kernel variant");
+  const bool can_tc = qmm8_tc_usable(a, dtype, a_sm, b, m, n, k);
+  TVB_REQUIRE(variant != 3 || can_tc, "tvb_qmm8: the tcgen05 kernel needs 16-bit A, k a multiple of 16, 16-byte aligned rows");
+  if (variant == 3 || (variant == 0 && can_tc && m > 16))
+    return qmm8_tc(device, stream, a, dtype, m == 1 ? k : a_sm, b, scales, c, m, n, k);
   if (variant == 2 || (variant == 0 && can_skinny)) {
     int64_t stride = m == 1 ? k : a_sm;  // (one row: any stride will do for the map)
     for (int m0 = 0; m0 < mi; m0 += 16) {
