@@ -226,6 +226,40 @@ def extra_configs(tv, stream, peaks, quick):
     return out
 
 
+def run_only(tv, stream, which, iters):
+    """One large-m configuration, `iters` launches after one warm-up (small enough to sit under a profiler)."""
+    if which == "fp8":
+        m = n = k = 4096
+        a, b, sa, sb = config_fp8(m, k, n, True)
+        av, bv, sav, sbv = a.to("vk"), b.t().to("vk").t(), sa.to("vk"), sb.to("vk")
+        fn = lambda: torch._scaled_mm(av, bv, sav, sbv, out_dtype=torch.bfloat16)  # noqa: E731
+        flops = 2.0 * m * n * k
+    elif which == "dyn4":
+        mm = 512
+        w, sc, bias = config_dyn4_weights()
+        packed = torch._dyn_quant_pack_4bit_weight(w.to("vk"), sc.to("vk"), bias.to("vk"), 32, 4096, 14336)
+        xv = torch.randn(mm, 4096, generator=gen(11)).to("vk")
+        fn = lambda: torch._dyn_quant_matmul_4bit(xv, packed, 32, 4096, 14336)  # noqa: E731
+        flops = 2.0 * mm * 14336 * 4096
+    else:
+        m, n, k = 2048, 14336, 4096
+        a = torch.randn(m, k, generator=gen(1)).to(torch.bfloat16).to("vk")
+        w = torch.randint(-127, 128, (n, k), dtype=torch.int8, generator=gen(2)).to("vk")
+        s = (torch.rand(n, generator=gen(3)) * (2e-2 - 1e-3) + 1e-3).to(torch.bfloat16).to("vk")
+        fn = lambda: torch._weight_int8pack_mm(a, w, s)  # noqa: E731
+        flops = 2.0 * m * n * k
+    fn()
+    tv.synchronize()
+    s0, e0 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s0.record(stream)
+    for _ in range(iters):
+        fn()
+    e0.record(stream)
+    tv.synchronize()
+    ms = s0.elapsed_time(e0) / iters
+    return {"only": which, "ms": ms, "tflops": flops / ms / 1e9, "iters": iters}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -234,6 +268,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extra", action="store_true", help="skip the large-m configurations")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline")
+    ap.add_argument("--only", default=None, choices=["fp8", "dyn4", "int8_large_m"],
+                    help="run one large-m configuration a few times and exit (for profilers); prints its own JSON line")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     rank = int(os.environ.get("RANK", "0"))
@@ -252,6 +288,9 @@ def main():
     tv.set_device(local_rank)
     dev = f"vk:{local_rank}"
     stream = tv.cuda_stream(local_rank)
+    if args.only is not None:
+        print(json.dumps(run_only(tv, stream, args.only, max(args.steps, 1) if args.steps != 200 else 3)), flush=True)
+        return
     if world > 1:
         import torch.distributed as dist
 

@@ -214,6 +214,16 @@ __device__ __forceinline__ uint64_t tc_smem_desc_sw128(uint32_t smem_addr) {
   return d;
 }
 
+// The same for tiles whose rows are 64 bytes of k (64-byte swizzle): groups of 8 rows 512 bytes apart.
+__device__ __forceinline__ uint64_t tc_smem_desc_sw64(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3ffffu) >> 4);
+  d |= static_cast<uint64_t>(512u >> 4) << 32;
+  d |= static_cast<uint64_t>(1) << 46;
+  d |= static_cast<uint64_t>(4) << 61;  // 64-byte swizzle
+  return d;
+}
+
 // Instruction descriptor: D format (1 float32, 2 int32), A / B formats (kind-specific codes),
 // both operands K-major, tile n x m.
 __host__ __device__ constexpr uint32_t tc_instr_desc(uint32_t d_fmt, uint32_t a_fmt, uint32_t b_fmt, uint32_t m, uint32_t n) {

@@ -112,16 +112,17 @@ int scaled_mm_tc(int device, cudaStream_t stream, const ScaledMmParams& p) {
     configured[device & 63] = true;
   }
   CUtensorMap map_a, map_b;
-  if (make_tensor_map_2d(&map_a, p.a, CU_TENSOR_MAP_DATA_TYPE_UINT8, p.k, p.m, p.a_s0, 128, Cfg::kBM,
-                         CU_TENSOR_MAP_SWIZZLE_128B) != 0)
+  if (make_tensor_map_2d(&map_a, p.a, CU_TENSOR_MAP_DATA_TYPE_UINT8, p.k, p.m, p.a_s0, kGemmStageK, Cfg::kBM,
+                         kGemmStageK == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B) != 0)
     return -1;
-  if (make_tensor_map_2d(&map_b, p.b, CU_TENSOR_MAP_DATA_TYPE_UINT8, p.k, p.n, p.b_s1, 128, kBN, CU_TENSOR_MAP_SWIZZLE_128B) != 0)
+  if (make_tensor_map_2d(&map_b, p.b, CU_TENSOR_MAP_DATA_TYPE_UINT8, p.k, p.n, p.b_s1, kGemmStageK, kBN,
+                         kGemmStageK == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B) != 0)
     return -1;
   GemmTcShape sh{};
   sh.m = static_cast<int>(p.m);
   sh.n = static_cast<int>(p.n);
-  sh.kblocks = static_cast<int>(ceil_div(p.k, 128));
-  sh.k_elems_per_block = 128;
+  sh.kblocks = static_cast<int>(ceil_div(p.k, kGemmStageK));
+  sh.k_elems_per_block = kGemmStageK;
   sh.tiles_m = static_cast<int>(ceil_div(p.m, Cfg::kBM));
   sh.tiles_n = static_cast<int>(ceil_div(p.n, kBN));
   ScaledEpilogue::Params ep{};
