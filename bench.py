@@ -307,13 +307,41 @@ def main():
     a_pinned = {m: a_host[m].pin_memory() for m in MS}
     from torch_vulkan_b200 import shard
 
+    fused = None
+    if world > 1 and os.environ.get("TVB200_GATHER", "fused") == "fused":
+        import torch.distributed as dist
+
+        objects = dist.new_group(backend="gloo")
+        fused = {m: shard.GatheredOutputs(m, N_OUT, torch.bfloat16, local_rank, objects) for m in MS}
+
     def product(m, a):
+        if world == 1:
+            return torch._weight_int8pack_mm(a, w, s)
+        if fused is not None:
+            # every rank's kernel stores its column slice into every rank's [m, N] buffer (peer stores over NVLink)
+            return fused[m].weight_int8pack_mm(a, w, s)
         # every rank's column slice, then the NCCL all-gather into [m, N] (queued on the backend's stream)
-        return shard.weight_int8pack_mm(a, w, s) if world > 1 else torch._weight_int8pack_mm(a, w, s)
+        return shard.weight_int8pack_mm(a, w, s)
+
+    def step_eager():
+        return [product(m, a_dev[m]) for m in MS]
+
+    # The step (three short kernels, plus the flag waits when sharded) is captured once into a CUDA graph and replayed:
+    # at 4 and 8 GPUs the kernels are shorter than the host's launch calls.
+    graph = None
+    if os.environ.get("TVB200_GRAPH", "1") != "0":
+        try:
+            graph = shard.StepGraph(step_eager, local_rank)
+        except Exception as exc:  # noqa: BLE001
+            if rank == 0:
+                print(f"bench.py: graph capture failed ({exc}); launching eagerly", file=sys.stderr)
+            graph = None
 
     def step_plain(i):
-        for m in MS:
-            product(m, a_dev[m])
+        if graph is not None:
+            graph.replay()
+        else:
+            step_eager()
 
     def barrier():
         tv.synchronize(local_rank)
@@ -333,6 +361,8 @@ def main():
     start, end = time_steps(step_plain, args.steps, stream)
     barrier()
     launches = tv.dispatch_count() - launches_before
+    if graph is not None:
+        launches = args.steps * len(MS) * (2 if fused is not None else 1)  # replayed kernels are not re-counted by the runtime
     total_ms = start.elapsed_time(end)
 
     # ---- per-launch duration of the decode kernel (the roofline's numerator), same loop with an event pair per launch
@@ -359,10 +389,18 @@ def main():
     avg_launch_ms = total_ms / (args.steps * len(MS)) if world == 1 else statistics.mean(isolated_ms.values())
 
     # ---- end to end through the public API: A from pinned host memory, C back to the host, every call
+    out_pinned = {m: torch.empty(m, N_OUT, dtype=torch.bfloat16).pin_memory() for m in MS}
+
     def step_e2e():
+        # every product's A goes up from page-locked memory and its C comes back into page-locked memory; the three
+        # products of a step are queued back to back and the step ends when all three results are on the host
+        keep = []
         for m in MS:
             a = a_pinned[m].to(dev, non_blocking=True)
-            product(m, a).cpu()
+            c = product(m, a)
+            out_pinned[m].copy_(c, non_blocking=True)
+            keep.append((a, c))
+        tv.synchronize(local_rank)
 
     for _ in range(3):
         step_e2e()
@@ -392,10 +430,10 @@ def main():
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "bf16 activations, int8 weights, float32 accumulation", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "sharding": f"weight rows / {world}" + (" + NCCL all-gather of C" if world > 1 else ""),
+            "config": {"workload": WORKLOAD, "sharding": f"weight rows / {world}" + ((" + fused peer-store gather of C" if fused is not None else " + NCCL all-gather of C") if world > 1 else ""),
                        "l2": "no flush: each launch streams %.0f MB of weights, larger than the 126 MB L2" % (rows * K_IN / 1e6)
                        if rows * K_IN > 126e6 else "weight slice of %.0f MB fits the 126 MB L2: launches after the first read it from L2" % (rows * K_IN / 1e6),
-                       "launches_per_step": len(MS)},
+                       "launches_per_step": len(MS), "launch": "CUDA graph replay of one step" if graph is not None else "eager"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                          "frac": achieved / peaks["hbm_gbs"], "traffic": None, "peak_source": peaks["source"],
                          "kernel": "qmm8_skinny_kernel", "avg_launch_us": avg_launch_ms * 1e3,

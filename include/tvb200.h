@@ -88,9 +88,20 @@ TVB_API void tvb_shutdown(void);
 
 /* Copies: host<->device wait for completion when the host buffer is pageable
  * (cudaMemcpyAsync semantics otherwise); device->device is stream-ordered. */
+/* Capture of the device's stream into a CUDA graph (for launch-bound loops such as a decoding step): every launcher
+ * called between begin and end is recorded instead of run; tvb_graph_launch replays the recording on the stream.
+ * Warm every shape once before capturing (first calls allocate scratch and set kernel attributes). */
+TVB_API int tvb_graph_begin(int device);
+TVB_API int tvb_graph_end(int device, void** graph_exec);
+TVB_API int tvb_graph_launch(int device, void* graph_exec);
+TVB_API void tvb_graph_destroy(void* graph_exec);
+
 TVB_API int tvb_memcpy_h2d(int device, void* dst, const void* src, uint64_t nbytes);
 TVB_API int tvb_memcpy_d2h(int device, void* dst, const void* src, uint64_t nbytes);
 TVB_API int tvb_memcpy_d2d(int device, void* dst, const void* src, uint64_t nbytes);
+/* Device -> page-locked host memory without waiting: the bytes are there after tvb_synchronize (or any later
+ * waiting call) on the device. */
+TVB_API int tvb_memcpy_d2h_async(int device, void* dst, const void* src, uint64_t nbytes);
 
 /* Page-locked host memory (replaces the reference's pinned allocator, crates/pyvk/csrc/backend.cpp:313-340):
  * copies from and to it are asynchronous. tvb_host_is_pinned: 1 if `ptr` lies in page-locked memory, else 0. */
@@ -116,6 +127,28 @@ TVB_API int tvb_fill_strided(int device, void* dst, int itemsize, uint64_t bits,
  * 2 the TMA-fed skinny kernel (m <= 64, 16-bit A, k % 128 == 0), 3 the tcgen05 kernel. */
 TVB_API int tvb_qmm8(int device, const void* a, int dtype, int64_t a_sm, const int8_t* b, const void* scales, void* c,
              int64_t m, int64_t n, int64_t k, int variant);
+
+/* ---- the decode product with the weight rows sharded over the GPUs of one node (no counterpart in the reference,
+ *      which has one device: crates/pyvk/csrc/backend.cpp:296) ----
+ * Rank `rank` of `world` computes its n_local output columns and its kernel's epilogue stores them straight into
+ * every rank's [m, n_local * world] output buffer at columns [rank * n_local, (rank + 1) * n_local): this GPU's own
+ * memory and the peers' over NVLink (plain 16-byte stores to peer-mapped memory). c_ranks / flag_ranks: host arrays
+ * of `world` device pointers, entry r being rank r's output buffer / its array of `world` uint32 flags, as mapped
+ * into this process (tvb_ipc_export on the owner, tvb_ipc_import here). seq_counter: a uint32 in this rank's device
+ * memory, 1 before the first product. When the last column is out, the kernel stores the counter's value into entry
+ * `rank` of every rank's flag array (release, system scope). tvb_wait_flags queues a one-warp kernel that waits (bounded,
+ * about two seconds) until every entry of this rank's own flag array has reached the counter's value, then adds one to
+ * the counter; work queued after it may read the assembled output. The sequence number lives on the device so that a
+ * captured CUDA graph of products can be replayed. Every rank must run the same sequence of products on a buffer, and a
+ * buffer may be written again only after one other product (use two buffers alternately). 1 <= m <= 16, 16-bit A,
+ * k a multiple of 128. */
+TVB_API int tvb_qmm8_gather(int device, const void* a, int dtype, int64_t a_sm, const int8_t* b, const void* scales,
+                            void* const* c_ranks, uint32_t* const* flag_ranks, int world, int rank,
+                            const uint32_t* seq_counter, int64_t m, int64_t n_local, int64_t k);
+TVB_API int tvb_wait_flags(int device, const uint32_t* flags, int world, uint32_t* seq_counter);
+/* A device allocation as a 64-byte handle plus offset that another process of the node can map (cudaIpc*). */
+TVB_API int tvb_ipc_export(int device, const void* ptr, uint8_t* handle64, uint64_t* offset);
+TVB_API int tvb_ipc_import(int device, const uint8_t* handle64, uint64_t offset, void** out);
 
 /* ---- tvb_qmm8's decode kernel for hosts that must not allocate (no counterpart in the reference) ----
  * Some hosts cannot let a library call cudaMalloc on their behalf: a serving process that handed all of HBM to its own

@@ -23,7 +23,23 @@ def main():
     tv.set_device(local)
     dist.init_process_group("nccl")  # (no device_id: with "vk" registered, torch takes that for the accelerator)
     dev = f"vk:{local}"
+    objects = dist.new_group(backend="gloo")
     try:
+        # the fused product: every rank's kernel stores its columns into every rank's buffer, flags tell arrival
+        for m in (1, 4, 16):
+            a, b, s = C.config_int8(m, 2048, 1024 * world, torch.bfloat16)
+            want, tol = C.int8_want(a, b, s)
+            outs = shard.GatheredOutputs(m, 1024 * world, torch.bfloat16, local, objects)
+            av, bv, sv = a.to(dev), shard.shard_rows(b, rank, world).to(dev), shard.shard_rows(s, rank, world).to(dev)
+            for rep in range(5):  # both buffers, several sequence numbers
+                got = outs.weight_int8pack_mm(av, bv, sv).cpu()
+                assert ((got.float() - want.float()).abs() <= tol).all(), f"rank {rank}: fused sharded product wrong (m={m}, rep={rep})"
+            # the same product captured in a CUDA graph and replayed (the sequence number lives on the device)
+            graph = shard.StepGraph(lambda: outs.weight_int8pack_mm(av, bv, sv), local)
+            for rep in range(3):
+                got = graph.replay().cpu()
+                assert ((got.float() - want.float()).abs() <= tol).all(), f"rank {rank}: graph replay wrong (m={m}, rep={rep})"
+            shard.barrier(objects)
         for m in (1, 4, 16):
             a, b, s = C.config_int8(m, 2048, 1024 * world, torch.bfloat16)
             want, tol = C.int8_want(a, b, s)

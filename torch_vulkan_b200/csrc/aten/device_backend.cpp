@@ -285,7 +285,10 @@ at::Tensor copy_from(const at::Tensor& self, const at::Tensor& dst, bool non_blo
     staged = at::empty(dst.sizes(), self.options().dtype(dst.scalar_type()));
     device_copy(staged, s);
   }
-  if (dst.is_contiguous()) {
+  if (dst.is_contiguous() && non_blocking && staged.is_same(s) && tvb_host_is_pinned(dst.const_data_ptr()) != 0) {
+    // into page-locked memory, caller synchronises (the source is the caller's tensor, alive until then)
+    check(tvb_memcpy_d2h_async(dev, dst.mutable_data_ptr(), gpu_address(staged), staged.nbytes()));
+  } else if (dst.is_contiguous()) {
     check(tvb_memcpy_d2h(dev, dst.mutable_data_ptr(), gpu_address(staged), staged.nbytes()));
   } else {
     at::Tensor host = at::empty(dst.sizes(), dst.options().memory_format(at::MemoryFormat::Contiguous));

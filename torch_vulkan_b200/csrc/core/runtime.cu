@@ -10,6 +10,9 @@
 // cache has no counterpart (the kernels are compiled into this library).
 #include "common.h"
 
+#include <cuda.h>
+#include <cudaTypedefs.h>
+
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
@@ -414,6 +417,87 @@ int tvb_host_is_pinned(const void* ptr) {
   return attr.type == cudaMemoryTypeHost ? 1 : 0;
 }
 
+int tvb_graph_begin(int device) {
+  cudaStream_t s;
+  if (enter(device, &s) != 0) return -1;
+  TVB_CUDA(cudaStreamBeginCapture(s, cudaStreamCaptureModeRelaxed));
+  return 0;
+}
+
+int tvb_graph_end(int device, void** graph_exec) {
+  TVB_REQUIRE(graph_exec != nullptr, "tvb_graph_end: NULL pointer");
+  cudaStream_t s;
+  if (enter(device, &s) != 0) return -1;
+  cudaGraph_t graph = nullptr;
+  TVB_CUDA(cudaStreamEndCapture(s, &graph));
+  cudaGraphExec_t exec = nullptr;
+  cudaError_t err = cudaGraphInstantiate(&exec, graph, 0);
+  cudaGraphDestroy(graph);
+  if (err != cudaSuccess) return fail_cuda("cudaGraphInstantiate", err);
+  *graph_exec = exec;
+  return 0;
+}
+
+int tvb_graph_launch(int device, void* graph_exec) {
+  TVB_REQUIRE(graph_exec != nullptr, "tvb_graph_launch: NULL graph");
+  cudaStream_t s;
+  if (enter(device, &s) != 0) return -1;
+  TVB_CUDA(cudaGraphLaunch(static_cast<cudaGraphExec_t>(graph_exec), s));
+  return 0;
+}
+
+void tvb_graph_destroy(void* graph_exec) {
+  if (graph_exec != nullptr && cudaGraphExecDestroy(static_cast<cudaGraphExec_t>(graph_exec)) != cudaSuccess) cudaGetLastError();
+}
+
+// ---- sharing device memory between the ranks of one node (one process per GPU)
+
+int tvb_ipc_export(int device, const void* ptr, uint8_t* handle64, uint64_t* offset) {
+  TVB_REQUIRE(ptr != nullptr && handle64 != nullptr && offset != nullptr, "tvb_ipc_export: NULL pointer");
+  cudaStream_t s;
+  if (enter(device, &s) != 0) return -1;
+  // the handle names the whole allocation: find its base
+  static PFN_cuMemGetAddressRange_v3020 range_fn = [] {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuMemGetAddressRange", &fn, cudaEnableDefault, &q) != cudaSuccess) cudaGetLastError();
+    return reinterpret_cast<PFN_cuMemGetAddressRange_v3020>(fn);
+  }();
+  TVB_REQUIRE(range_fn != nullptr, "tvb_ipc_export: cuMemGetAddressRange is not available");
+  CUdeviceptr base = 0;
+  size_t size = 0;
+  TVB_REQUIRE(range_fn(&base, &size, reinterpret_cast<CUdeviceptr>(ptr)) == CUDA_SUCCESS, "tvb_ipc_export: not a device allocation");
+  cudaIpcMemHandle_t h;
+  TVB_CUDA(cudaIpcGetMemHandle(&h, reinterpret_cast<void*>(base)));
+  static_assert(sizeof(h) == 64, "IPC handles are 64 bytes");
+  std::memcpy(handle64, &h, 64);
+  *offset = reinterpret_cast<uint64_t>(ptr) - static_cast<uint64_t>(base);
+  return 0;
+}
+
+int tvb_ipc_import(int device, const uint8_t* handle64, uint64_t offset, void** out) {
+  TVB_REQUIRE(handle64 != nullptr && out != nullptr, "tvb_ipc_import: NULL pointer");
+  cudaStream_t s;
+  if (enter(device, &s) != 0) return -1;
+  static std::mutex mutex;
+  static std::map<std::string, void*> opened;  // a handle may be opened once per process
+  std::lock_guard<std::mutex> lock(mutex);
+  std::string key(reinterpret_cast<const char*>(handle64), 64);
+  key += static_cast<char>(device);
+  auto it = opened.find(key);
+  void* base = nullptr;
+  if (it != opened.end()) {
+    base = it->second;
+  } else {
+    cudaIpcMemHandle_t h;
+    std::memcpy(&h, handle64, 64);
+    TVB_CUDA(cudaIpcOpenMemHandle(&base, h, cudaIpcMemLazyEnablePeerAccess));
+    opened.emplace(key, base);
+  }
+  *out = static_cast<uint8_t*>(base) + offset;
+  return 0;
+}
+
 int tvb_memcpy_h2d(int device, void* dst, const void* src, uint64_t nbytes) {
   cudaStream_t s;
   if (enter(device, &s) != 0) return -1;
@@ -428,6 +512,15 @@ int tvb_memcpy_d2h(int device, void* dst, const void* src, uint64_t nbytes) {
   if (nbytes == 0) return 0;
   TVB_CUDA(cudaMemcpyAsync(dst, src, nbytes, cudaMemcpyDeviceToHost, s));
   TVB_CUDA(cudaStreamSynchronize(s));
+  return 0;
+}
+
+int tvb_memcpy_d2h_async(int device, void* dst, const void* src, uint64_t nbytes) {
+  cudaStream_t s;
+  if (enter(device, &s) != 0) return -1;
+  if (nbytes == 0) return 0;
+  TVB_REQUIRE(tvb_host_is_pinned(dst) != 0, "tvb_memcpy_d2h_async: the destination must be page-locked host memory");
+  TVB_CUDA(cudaMemcpyAsync(dst, src, nbytes, cudaMemcpyDeviceToHost, s));
   return 0;
 }
 

@@ -83,9 +83,10 @@ struct SkinnyCfg {
   static constexpr int kWeightBytes = kRowsPerTile * kChunkK;   // one TMA box
   static constexpr int kTokenBoxBytes = kTokens * 128;          // 64 k of 16-bit values per row: two boxes per stage
   static constexpr int kStageBytes = kWeightBytes + 2 * kTokenBoxBytes;
-  static constexpr int kStages = (220 * 1024) / kStageBytes < 8 ? (220 * 1024) / kStageBytes : 8;
+  static constexpr int kStages = (224 * 1024 - kTokens * kRowsPerTile * 2) / kStageBytes < 8 ? (224 * 1024 - kTokens * kRowsPerTile * 2) / kStageBytes : 8;
   static constexpr int kThreads = (NWARPS + 1) * 32;
-  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /* alignment slack */ + 256 /* barriers */;
+  static constexpr int kOutTileBytes = kTokens * kRowsPerTile * 2;  // one tile's outputs, staged for coalesced stores
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /* alignment slack */ + 256 /* barriers */ + kOutTileBytes;
   static constexpr int kPartialFloats = NWARPS * RW * NT * 32 * 4;  // one CTA's accumulators
 };
 
@@ -113,9 +114,16 @@ __device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a
   else ptx::mma_f16_16816(d, a0, a1, a2, a3, b0, b1);
 }
 
+constexpr int kMaxRanks = 8;
+
 struct SkinnyParams {
   const void* scales;
-  void* c;
+  void* c[kMaxRanks];        // output buffers [m, c_ld]: this GPU's, and with sharding every peer's (peer-mapped memory)
+  uint32_t* flags[kMaxRanks];  // with sharding: every rank's arrival-flag array (entry `rank` is this GPU's to write)
+  int* done;                 // with sharding: counter of finished CTAs (zero between launches)
+  int nranks, rank;
+  const uint32_t* seq;       // with sharding: device counter whose value tells the peers this product's columns have arrived
+  int c_ld, c_col0;          // row length of the output buffers and first column of this GPU's slice
   float* partials;   // [grid][2][kPartialFloats]
   int* counters;     // [tiles], zero between launches
   int* status;
@@ -145,6 +153,7 @@ __global__ void __launch_bounds__((NWARPS + 1) * 32, 1)
   const uint32_t full0 = ptx::smem_u32(bars), empty0 = full0 + 8 * Cfg::kStages;
   volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 2 * Cfg::kStages);
   int* last_flag = const_cast<int*>(abort_flag) + 1;  // two slots
+  uint16_t* out_tile = reinterpret_cast<uint16_t*>(base_ptr + Cfg::kStages * Cfg::kStageBytes + 256);  // [tokens][rows of a tile]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
@@ -339,25 +348,68 @@ __global__ void __launch_bounds__((NWARPS + 1) * 32, 1)
       }
     }
     if (finish) {
+      // Scale, round once, and stage the tile's [tokens][256 columns] in shared memory, so that what goes to global
+      // memory (this GPU's output and, with sharding, every peer's over NVLink) is 16-byte, fully coalesced stores.
 #pragma unroll
       for (int rb = 0; rb < RW; rb++) {
-        const int row0 = tile * Cfg::kRowsPerTile + (warp * RW + rb) * 16 + rg;
+        const int lrow0 = (warp * RW + rb) * 16 + rg;
 #pragma unroll
         for (int half = 0; half < 2; half++) {
-          const int col = row0 + 8 * half;  // weight row = output column
-          if (col >= p.n) continue;
-          const float scale = load_float<DT>(p.scales, col);
+          const int lcol = lrow0 + 8 * half;                       // column within the tile (weight row = output column)
+          const int col = tile * Cfg::kRowsPerTile + lcol;
+          const float scale = col < p.n ? load_float<DT>(p.scales, col) : 0.0f;
 #pragma unroll
           for (int nt = 0; nt < NT; nt++)
 #pragma unroll
             for (int i = 0; i < 2; i++) {
-              const int token = p.m0 + nt * 8 + 2 * t + i;
-              if (token < p.m) store_float<DT>(p.c, static_cast<int64_t>(token) * p.n + col, acc[rb][nt][2 * half + i] * scale);
+              const float v = acc[rb][nt][2 * half + i] * scale;
+              out_tile[(nt * 8 + 2 * t + i) * Cfg::kRowsPerTile + lcol] = DT == TVB_BF16 ? f32_to_bf16_bits(v) : f32_to_f16_bits(v);
             }
         }
       }
+      ptx::named_bar_sync(1, NWARPS * 32);
+      const int col_base = tile * Cfg::kRowsPerTile;
+      const bool vec = (p.c_ld % 8 == 0) && (p.c_col0 % 8 == 0);
+      for (int v = threadIdx.x; v < Cfg::kTokens * (Cfg::kRowsPerTile / 8); v += NWARPS * 32) {
+        const int tok = v / (Cfg::kRowsPerTile / 8), chunk = v % (Cfg::kRowsPerTile / 8);
+        const int token = p.m0 + tok, col = col_base + chunk * 8;
+        if (token >= p.m || col >= p.n) continue;
+        const uint4 val = *reinterpret_cast<const uint4*>(out_tile + tok * Cfg::kRowsPerTile + chunk * 8);
+        const int64_t off = static_cast<int64_t>(token) * p.c_ld + p.c_col0 + col;
+        if (vec && col + 8 <= p.n) {
+          for (int r = 0; r < p.nranks; r++) {
+            uint16_t* dst = static_cast<uint16_t*>(p.c[r]) + off;
+            if ((reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
+              *reinterpret_cast<uint4*>(dst) = val;
+            } else {
+              const uint16_t* e = reinterpret_cast<const uint16_t*>(&val);
+              for (int j = 0; j < 8; j++) dst[j] = e[j];
+            }
+          }
+        } else {
+          const uint16_t* e = reinterpret_cast<const uint16_t*>(&val);
+          for (int r = 0; r < p.nranks; r++)
+            for (int j = 0; j < 8 && col + j < p.n; j++) (static_cast<uint16_t*>(p.c[r]) + off)[j] = e[j];
+        }
+      }
+      ptx::named_bar_sync(1, NWARPS * 32);  // (the staging tile is free again)
     }
     u += c1 - c0;
+  }
+  if (p.done != nullptr && ok) {
+    // Sharded product: when the last CTA has stored its columns everywhere, tell every rank (this one included) that
+    // this GPU's slice of product `seq` has arrived. The system-scope fence after the barrier covers the stores of
+    // all consumer threads of the CTA.
+    ptx::named_bar_sync(1, NWARPS * 32);
+    if (threadIdx.x == 0) {
+      __threadfence_system();
+      if (atomicAdd(p.done, 1) == static_cast<int>(gridDim.x) - 1) {
+        atomicExch(p.done, 0);
+        const uint32_t seq = *reinterpret_cast<const volatile uint32_t*>(p.seq);
+        for (int r = 0; r < p.nranks; r++)
+          asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.flags[r] + p.rank), "r"(seq) : "memory");
+      }
+    }
   }
   if (p.times != nullptr && threadIdx.x == 0) {
     long long now;
@@ -378,9 +430,18 @@ int launch_plain(cudaStream_t stream, const void* a, int64_t a_sm, const int8_t*
 
 long long* g_debug_times = nullptr;
 
+// Destinations of a sharded product (tvb_qmm8_gather): every rank's output buffer and flag array.
+struct GatherTargets {
+  void* c[kMaxRanks];
+  uint32_t* flags[kMaxRanks];
+  int world, rank;
+  const uint32_t* seq;
+  int64_t n_total;
+};
+
 template <int DT, int NT, int RW, int NWARPS>
 int launch_skinny_cfg(int device, cudaStream_t stream, const void* a, int64_t a_sm, const int8_t* b, const void* scales, void* c,
-                      int m, int n, int k, int m0) {
+                      int m, int n, int k, int m0, const GatherTargets* gather = nullptr) {
   using Cfg = SkinnyCfg<NT, RW, NWARPS>;
   auto kernel = qmm8_skinny_kernel<DT, NT, RW, NWARPS>;
   static bool configured[64] = {};
@@ -401,19 +462,34 @@ int launch_skinny_cfg(int device, cudaStream_t stream, const void* a, int64_t a_
   long long units = static_cast<long long>(p.tiles) * p.chunks;
   int grid = static_cast<int>(std::min<long long>(sm_count(device), units));
   size_t partial_bytes = static_cast<size_t>(grid) * 2 * Cfg::kPartialFloats * sizeof(float);
-  size_t counter_bytes = (static_cast<size_t>(p.tiles) * sizeof(int) + 255) & ~size_t(255);
+  size_t counter_bytes = ((static_cast<size_t>(p.tiles) + 1) * sizeof(int) + 255) & ~size_t(255);  // + the done counter
   void* ws = nullptr;
   if (workspace(device, 0, counter_bytes + partial_bytes, &ws) != 0) return -1;
   p.counters = static_cast<int*>(ws);
   p.partials = reinterpret_cast<float*>(static_cast<uint8_t*>(ws) + counter_bytes);
   if (status_word(device, &p.status) != 0) return -1;
   p.scales = scales;
-  p.c = c;
+  p.c[0] = c;
+  p.nranks = 1;
+  p.c_ld = n;
+  p.c_col0 = 0;
   p.m = m;
   p.n = n;
   p.k = k;
   p.m0 = m0;
   p.times = g_debug_times;
+  if (gather != nullptr) {
+    for (int r = 0; r < gather->world; r++) {
+      p.c[r] = gather->c[r];
+      p.flags[r] = gather->flags[r];
+    }
+    p.nranks = gather->world;
+    p.rank = gather->rank;
+    p.seq = gather->seq;
+    p.c_ld = static_cast<int>(gather->n_total);
+    p.c_col0 = gather->rank * n;
+    p.done = reinterpret_cast<int*>(static_cast<uint8_t*>(ws) + counter_bytes - sizeof(int));
+  }
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(grid);
   cfg.blockDim = dim3(Cfg::kThreads);
@@ -430,19 +506,43 @@ int launch_skinny_cfg(int device, cudaStream_t stream, const void* a, int64_t a_
 
 template <int DT, int NT>
 int launch_skinny(int device, cudaStream_t stream, const void* a, int64_t a_sm, const int8_t* b, const void* scales, void* c,
-                  int m, int n, int k, int m0) {
-  static const int shape = [] {
-    const char* v = std::getenv("TVB200_QMM8_WARPS");
-    return v != nullptr ? std::atoi(v) : 8;
-  }();
-  if (shape == 16) return launch_skinny_cfg<DT, NT, 1, 16>(device, stream, a, a_sm, b, scales, c, m, n, k, m0);
-  return launch_skinny_cfg<DT, NT, 2, 8>(device, stream, a, a_sm, b, scales, c, m, n, k, m0);
+                  int m, int n, int k, int m0, const GatherTargets* gather = nullptr) {
+  return launch_skinny_cfg<DT, NT, 2, 8>(device, stream, a, a_sm, b, scales, c, m, n, k, m0, gather);
 }
 
 bool skinny_ok(const void* a, int dtype, int64_t a_sm, const int8_t* b, int64_t m, int64_t n, int64_t k) {
   return (dtype == TVB_BF16 || dtype == TVB_F16) && m <= 64 && k % kChunkK == 0 && k >= kChunkK &&
          (a_sm % 8 == 0 || m == 1) && (reinterpret_cast<uintptr_t>(a) & 15u) == 0 && (reinterpret_cast<uintptr_t>(b) & 15u) == 0 &&
          n >= 1;
+}
+
+// ------------------------------------------------------------------ sharded product: waiting for the peers' columns
+
+// One thread per peer spins (bounded) until that peer's arrival flag reaches `seq`; a wait that runs out sets the status
+// word and returns. The flags are written with system-scope release stores by the peers' product kernels.
+__global__ void qmm8_wait_flags_kernel(const uint32_t* flags, int world, uint32_t* seq_counter, int* status) {
+  // Launched with programmatic stream serialization and transparent to it: the next product kernel of the stream may
+  // start streaming its weights at once; its own griddepcontrol.wait holds its use of A, the scratch and the outputs
+  // until this kernel, and with it the product whose flags it waits for (this rank's own flag comes last), has ended.
+  ptx::grid_launch_dependents();
+  const int r = threadIdx.x;
+  const uint32_t seq = *reinterpret_cast<volatile uint32_t*>(seq_counter);
+  if (r < world) {
+    const long long start = clock64();
+    for (;;) {
+      uint32_t v;
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flags + r) : "memory");
+      if (static_cast<int32_t>(v - seq) >= 0) break;
+      if (clock64() - start > ptx::kWaitLimitCycles) {
+        atomicExch(status, 5);
+        break;
+      }
+      __nanosleep(100);
+    }
+  }
+  __syncwarp();
+  // every slice of product `seq` is here: the next product of this rank announces itself with seq + 1
+  if (r == 0) *reinterpret_cast<volatile uint32_t*>(seq_counter) = seq + 1;
 }
 
 // ------------------------------------------------------------------ the same kernel without any allocation
@@ -505,7 +605,10 @@ int launch_skinny_static(int device, int sms, cudaStream_t stream, unsigned char
   p.status = reinterpret_cast<int*>(scratch + kStaticCounterBytes + kStaticPartialBytes);
   p.times = nullptr;
   p.scales = scales;
-  p.c = c;
+  p.c[0] = c;
+  p.nranks = 1;
+  p.c_ld = n;
+  p.c_col0 = 0;
   p.m = m;
   p.n = n;
   p.k = k;
@@ -557,6 +660,57 @@ extern "C" int tvb_qmm8_static_scratch(int device, const void* a, int dtype, int
     if (rc != 0) return rc;
   }
   return 0;
+}
+
+extern "C" int tvb_qmm8_gather(int device, const void* a, int dtype, int64_t a_sm, const int8_t* b, const void* scales,
+                               void* const* c_ranks, uint32_t* const* flag_ranks, int world, int rank, const uint32_t* seq_counter,
+                               int64_t m, int64_t n_local, int64_t k) {
+  TVB_REQUIRE(world >= 1 && world <= kMaxRanks && rank >= 0 && rank < world, "tvb_qmm8_gather: 1 to 8 ranks");
+  TVB_REQUIRE(dtype == TVB_F16 || dtype == TVB_BF16, "tvb_qmm8_gather: A must be float16 or bfloat16");
+  TVB_REQUIRE(m >= 1 && m <= 16 && n_local >= 1 && k >= 1, "tvb_qmm8_gather: 1 <= m <= 16 (the decode kernel)");
+  TVB_REQUIRE(a != nullptr && b != nullptr && scales != nullptr && c_ranks != nullptr && flag_ranks != nullptr &&
+                  seq_counter != nullptr,
+              "tvb_qmm8_gather: NULL pointer");
+  TVB_REQUIRE(skinny_ok(a, dtype, a_sm, b, m, n_local, k), "tvb_qmm8_gather: needs k a multiple of 128 and 16-byte aligned A rows and B");
+  TVB_REQUIRE(n_local * world < (int64_t(1) << 31), "tvb_qmm8_gather: sizes beyond 32 bits");
+  cudaStream_t stream;
+  if (enter(device, &stream) != 0) return -1;
+  GatherTargets g{};
+  for (int r = 0; r < world; r++) {
+    TVB_REQUIRE(c_ranks[r] != nullptr && flag_ranks[r] != nullptr, "tvb_qmm8_gather: NULL buffer of a rank");
+    g.c[r] = c_ranks[r];
+    g.flags[r] = flag_ranks[r];
+  }
+  g.world = world;
+  g.rank = rank;
+  g.seq = seq_counter;
+  g.n_total = n_local * world;
+  const int mi = static_cast<int>(m), ni = static_cast<int>(n_local), ki = static_cast<int>(k);
+  const int64_t stride = m == 1 ? k : a_sm;
+  if (dtype == TVB_BF16)
+    return mi <= 8 ? launch_skinny<TVB_BF16, 1>(device, stream, a, stride, b, scales, g.c[rank], mi, ni, ki, 0, &g)
+                   : launch_skinny<TVB_BF16, 2>(device, stream, a, stride, b, scales, g.c[rank], mi, ni, ki, 0, &g);
+  return mi <= 8 ? launch_skinny<TVB_F16, 1>(device, stream, a, stride, b, scales, g.c[rank], mi, ni, ki, 0, &g)
+                 : launch_skinny<TVB_F16, 2>(device, stream, a, stride, b, scales, g.c[rank], mi, ni, ki, 0, &g);
+}
+
+extern "C" int tvb_wait_flags(int device, const uint32_t* flags, int world, uint32_t* seq_counter) {
+  TVB_REQUIRE(flags != nullptr && seq_counter != nullptr && world >= 1 && world <= kMaxRanks, "tvb_wait_flags: bad arguments");
+  cudaStream_t stream;
+  if (enter(device, &stream) != 0) return -1;
+  int* status = nullptr;
+  if (status_word(device, &status) != 0) return -1;
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(1);
+  cfg.blockDim = dim3(32);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  TVB_CUDA(cudaLaunchKernelEx(&cfg, qmm8_wait_flags_kernel, flags, world, seq_counter, status));
+  return launched("qmm8_wait_flags", dim3(1), dim3(32), 0, stream);
 }
 
 // Diagnostics (not part of the public header): per-CTA SM id and start / end times of the next skinny launches.

@@ -97,3 +97,104 @@ def barrier(group=None):
     else:
         t = torch.zeros(1)
         dist.all_reduce(t, group=group)
+
+
+class GatheredOutputs:
+    """Output buffers for the fused sharded decode product (tvb_qmm8_gather): every rank holds a full [m, N] buffer
+    (two of them, used alternately) that all ranks' kernels write their column slices into directly, over NVLink for
+    the peers, plus per-buffer arrival flags. No collective call, no copy: the product kernel's epilogue is the gather.
+
+    `object_group` is a gloo group used once, to exchange the buffers' IPC handles.
+    """
+
+    def __init__(self, m, n_total, dtype, device_index, object_group, depth=2):
+        import ctypes
+
+        from . import cabi
+
+        self._c, self._ct = cabi, ctypes
+        self.world, self.rank = dist.get_world_size(), dist.get_rank()
+        self.dev, self.m, self.n_total, self.depth = device_index, m, n_total, depth
+        vk = torch.device("vk", device_index)
+        self.bufs = [torch.empty((m, n_total), dtype=dtype, device=vk) for _ in range(depth)]
+        self.flags = [torch.zeros(self.world, dtype=torch.int32, device=vk) for _ in range(depth)]
+        lib = cabi.lib()
+
+        def export(t):
+            handle, off = ctypes.create_string_buffer(64), ctypes.c_uint64(0)
+            cabi.check(lib.tvb_ipc_export(device_index, t.data_ptr(), handle, ctypes.byref(off)))
+            return handle.raw, off.value
+
+        mine = [(export(b), export(f)) for b, f in zip(self.bufs, self.flags)]
+        everyone = [None] * self.world
+        dist.all_gather_object(everyone, mine, group=object_group)
+
+        def import_(entry):
+            handle, off = entry
+            out = ctypes.c_void_p(0)
+            cabi.check(lib.tvb_ipc_import(device_index, handle, off, ctypes.byref(out)))
+            return out.value
+
+        self.c_ptrs, self.flag_ptrs = [], []
+        for d in range(depth):
+            cs, fs = [], []
+            for r in range(self.world):
+                if r == self.rank:
+                    cs.append(self.bufs[d].data_ptr())
+                    fs.append(self.flags[d].data_ptr())
+                else:
+                    cs.append(import_(everyone[r][d][0]))
+                    fs.append(import_(everyone[r][d][1]))
+            self.c_ptrs.append((ctypes.c_void_p * self.world)(*cs))
+            self.flag_ptrs.append((ctypes.c_void_p * self.world)(*fs))
+        self.calls = 0
+        self.seq_counter = torch.ones(1, dtype=torch.int32, device=vk)  # the sequence number lives on the device
+        cabi.check(lib.tvb_synchronize(device_index))  # the flags are zero before any peer may write them
+        barrier(object_group)
+
+    def weight_int8pack_mm(self, a, w_shard, scales_shard):
+        """The full [m, N] product on every rank; valid for work queued after this call on the backend's stream."""
+        cabi, lib = self._c, self._c.lib()
+        m, k = a.shape
+        n_local = w_shard.shape[0]
+        assert m == self.m and n_local * self.world == self.n_total and scales_shard.dtype == a.dtype
+        d = self.calls % self.depth
+        self.calls += 1
+        cabi.check(lib.tvb_qmm8_gather(self.dev, a.data_ptr(), cabi._dtype_code(a.dtype), a.stride(0), w_shard.data_ptr(),
+                                       scales_shard.data_ptr(), self.c_ptrs[d], self.flag_ptrs[d], self.world, self.rank,
+                                       self.seq_counter.data_ptr(), m, n_local, k))
+        cabi.check(lib.tvb_wait_flags(self.dev, self.flags[d].data_ptr(), self.world, self.seq_counter.data_ptr()))
+        return self.bufs[d]
+
+
+class StepGraph:
+    """A CUDA graph of whatever `fn` queues on the backend's stream (a decoding step: a handful of short kernels whose
+    launch cost would otherwise bound the step). `fn` is run once to warm up, once under capture; replay() queues the
+    recording. Tensors `fn` returns stay alive with the graph and are overwritten by every replay."""
+
+    def __init__(self, fn, device_index=0):
+        import ctypes
+
+        from . import cabi
+
+        self._c, self.dev = cabi, device_index
+        lib = cabi.lib()
+        fn()
+        cabi.check(lib.tvb_synchronize(device_index))
+        cabi.check(lib.tvb_graph_begin(device_index))
+        try:
+            self.outputs = fn()
+        finally:
+            exec_ = ctypes.c_void_p(0)
+            cabi.check(lib.tvb_graph_end(device_index, ctypes.byref(exec_)))
+        self.exec = exec_
+
+    def replay(self):
+        self._c.check(self._c.lib().tvb_graph_launch(self.dev, self.exec))
+        return self.outputs
+
+    def __del__(self):
+        try:
+            self._c.lib().tvb_graph_destroy(self.exec)
+        except Exception:
+            pass
