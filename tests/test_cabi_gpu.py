@@ -79,6 +79,17 @@ def test_qmm8_skinny_is_deterministic_and_repeatable(abi):
         assert torch.equal(first, again)
 
 
+def test_qmm8_skinny_scratch_layout_across_shapes(abi):
+    # a narrow product (whose partial sums land in scratch) followed by a wide one (more than 64 tiles of 256 columns,
+    # whose tile counters must not alias what the narrow one left behind)
+    for m, k, n in ((4, 1024, 300), (4, 256, 20000), (16, 512, 40000), (1, 1024, 700), (8, 256, 33000)):
+        a, b, s = C.config_int8(m, k, n, torch.bfloat16, seed=n)
+        want, tol = C.int8_want(a, b, s)
+        got = abi.qmm8(dev(a), dev(b), dev(s), variant=2)
+        abi.synchronize()
+        assert ((got.cpu().float() - want.float()).abs() <= tol).all(), (m, k, n)
+
+
 def test_qmm8_decode_shape_sample(abi):
     # the decode benchmark's k with a slice of its n: every SM's unit range crosses tiles
     a, b, s = C.config_int8(4, 8192, 3584, torch.bfloat16)

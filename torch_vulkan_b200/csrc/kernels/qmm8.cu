@@ -75,6 +75,8 @@ __global__ void __launch_bounds__(256) qmm8_plain_kernel(const void* __restrict_
 // ------------------------------------------------------------------ skinny kernel
 
 constexpr int kChunkK = 128;  // k values (= bytes of a weight row) per pipeline stage
+constexpr size_t kCounterBytes = 65536;                                   // scratch: tile counters first
+constexpr int kMaxTiles = static_cast<int>(kCounterBytes / sizeof(int)) - 1;  // (the last int counts finished CTAs)
 
 template <int NT, int RW, int NWARPS>
 struct SkinnyCfg {
@@ -462,7 +464,10 @@ int launch_skinny_cfg(int device, cudaStream_t stream, const void* a, int64_t a_
   long long units = static_cast<long long>(p.tiles) * p.chunks;
   int grid = static_cast<int>(std::min<long long>(sm_count(device), units));
   size_t partial_bytes = static_cast<size_t>(grid) * 2 * Cfg::kPartialFloats * sizeof(float);
-  size_t counter_bytes = ((static_cast<size_t>(p.tiles) + 1) * sizeof(int) + 255) & ~size_t(255);  // + the done counter
+  // Fixed layout, whatever the shape: 64 KB of tile counters (and, last, the finished-CTA counter), then the partial
+  // sums. The counters must stay zero between launches, so no launch may ever use their bytes for anything else.
+  constexpr size_t counter_bytes = kCounterBytes;
+  if (p.tiles > kMaxTiles) return fail("tvb_qmm8: more than 4 million output columns for the decode kernel");
   void* ws = nullptr;
   if (workspace(device, 0, counter_bytes + partial_bytes, &ws) != 0) return -1;
   p.counters = static_cast<int*>(ws);
