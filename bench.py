@@ -219,9 +219,13 @@ def extra_configs(tv, stream, peaks, quick):
     packed = torch._dyn_quant_pack_4bit_weight(w.to("vk"), sc.to("vk"), bias.to("vk"), 32, 4096, 14336)
     for mm in ((128,) if quick else (128, 512, 2048)):
         xv = torch.randn(mm, 4096, generator=gen(11)).to("vk")
-        ms = timed(lambda: torch._dyn_quant_matmul_4bit(xv, packed, 32, 4096, 14336), 3)
-        tops = 2.0 * mm * 14336 * 4096 / ms / 1e9
-        out[f"dyn_int4_m{mm}"] = {"tops": tops, "ms": ms, "frac_of_2x_measured_bf16": tops / (2 * peaks["bf16_tflops"])}
+        for mode in ("exact", "fast"):  # exact: bit for bit (the default); fast: TORCH_VK_QMM4=fast, rtol 1e-5
+            if mode == "fast":
+                os.environ["TORCH_VK_QMM4"] = "fast"
+            ms = timed(lambda: torch._dyn_quant_matmul_4bit(xv, packed, 32, 4096, 14336), 3)
+            os.environ.pop("TORCH_VK_QMM4", None)
+            tops = 2.0 * mm * 14336 * 4096 / ms / 1e9
+            out[f"dyn_int4_m{mm}_{mode}"] = {"tops": tops, "ms": ms, "frac_of_2x_measured_bf16": tops / (2 * peaks["bf16_tflops"])}
     tv.empty_cache()
     return out
 

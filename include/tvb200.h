@@ -203,6 +203,18 @@ TVB_API uint64_t tvb_qmm4_tc_workspace_bytes(int64_t m, int64_t k);
 TVB_API int tvb_qmm4_tc(int device, const void* inp, int dtype, const float* packed, int has_bias, const void* prepared,
                         void* out, int64_t m, int64_t n, int64_t k, int64_t bs, void* workspace, uint64_t workspace_bytes);
 
+/* The opt-in fast route of the same op (no counterpart in the reference): one float16 GEMM on tcgen05 over exact
+ * operands, (q - zero_point) and weight * block scale, accumulated over the whole of k in float32. Outputs differ from the
+ * exact routes by float32 accumulation order only (not bit for bit). tvb_qmm4_fast_prepare writes the float16 weights
+ * (tvb_qmm4_fast_prepared_bytes(n, k) bytes) and, if inexact_host is not NULL, waits and stores there whether some
+ * weight * scale product was not exact in float16 (then this route must not be used). k a multiple of 8. */
+TVB_API uint64_t tvb_qmm4_fast_prepared_bytes(int64_t n, int64_t k);
+TVB_API int tvb_qmm4_fast_prepare(int device, const float* packed, int64_t n, int64_t k, int64_t bs, void* prepared,
+                                  uint64_t prepared_bytes, int* inexact_host);
+TVB_API uint64_t tvb_qmm4_fast_workspace_bytes(int64_t m, int64_t k);
+TVB_API int tvb_qmm4_fast(int device, const void* inp, int dtype, const float* packed, int has_bias, const void* prepared,
+                          void* out, int64_t m, int64_t n, int64_t k, int64_t bs, void* workspace, uint64_t workspace_bytes);
+
 /* ---- aten::_scaled_mm (replaces the chain of cast / mul / matmul / add / cast
  *      dispatches, quant.cpp:283-299) ----
  * out[m, n] = cast((a * scale_a) @ (b * scale_b) + bias) (float8 outputs: times

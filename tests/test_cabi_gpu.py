@@ -227,3 +227,30 @@ def test_qmm4_tensor_core_path_wide_scales(abi):
     abi.synchronize()
     assert prepared[:4].cpu().view(torch.int32).item() == 1
     assert torch.equal(got.cpu(), want)
+
+
+# ---------------------------------------------------------------- dyn-int4, the opt-in fast route (not bit-exact)
+
+@pytest.mark.parametrize("m,k,n,bs,bias", [(32, 128, 11008, 32, True), (130, 512, 300, 32, True), (257, 1024, 129, 128, False),
+                                           (64, 4096, 256, 64, True), (5, 96, 70, 96, True)])
+def test_qmm4_fast_route_within_float32_accumulation(abi, m, k, n, bs, bias):
+    x, w, sc, bvec = C.dyn4_case(m, k, n, bs, bias, torch.float32)
+    sc = sc.to(torch.bfloat16)  # (block scales as the groupwise op takes them; channelwise float32 ones are not exact in float16)
+    packed_cpu = O.dyn_quant_pack_4bit_weight(w, sc, bvec, bs, k, n)
+    want = O.dyn_quant_matmul_4bit(x, packed_cpu, bs, k, n)
+    packed = dev(packed_cpu)
+    prepared, inexact = abi.qmm4_fast_prepare(packed, n, k, bs)
+    assert inexact == 0
+    got = abi.qmm4_fast(dev(x), packed, prepared, bs, k, n)
+    abi.synchronize()
+    # the benchmark's bound: rtol 1e-5, with a magnitude floor for outputs that cancel to near zero
+    assert torch.allclose(got.cpu(), want, rtol=1e-5, atol=1e-5 * float(want.abs().max()))
+
+
+def test_qmm4_fast_route_flags_inexact_scales(abi):
+    m, k, n, bs = 4, 256, 64, 64
+    x, w, _, bvec = C.dyn4_case(m, k, n, bs, True, torch.float32)
+    sc = torch.rand(n, k // bs, generator=C.gen(5)) / 10 + 1e-3  # full float32 mantissas
+    packed = dev(O.dyn_quant_pack_4bit_weight(w, sc, bvec, bs, k, n))
+    _, inexact = abi.qmm4_fast_prepare(packed, n, k, bs)
+    assert inexact == 1

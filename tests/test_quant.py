@@ -86,6 +86,22 @@ def test_dyn_quant_matmul_4bit_exact(m, k, n, bs, bias, dtype):
     assert torch.equal(got_cpu_packed.cpu(), want)
 
 
+def test_dyn_quant_matmul_4bit_fast_route_opt_in(monkeypatch):
+    # TORCH_VK_QMM4=fast: one float16 GEMM, float32 accumulation over all of k: within rtol 1e-5 (magnitude floor)
+    m, k, n, bs = 64, 512, 384, 32
+    x, w, sc, bvec = C.dyn4_case(m, k, n, bs, True, torch.float32)
+    packed = torch._dyn_quant_pack_4bit_weight(w, sc, bvec, bs, k, n)
+    want = torch._dyn_quant_matmul_4bit(x, packed, bs, k, n)
+    packed_vk, xv = packed.to("vk"), x.to("vk")
+    exact = torch._dyn_quant_matmul_4bit(xv, packed_vk, bs, k, n).cpu()
+    assert torch.equal(exact, want)
+    monkeypatch.setenv("TORCH_VK_QMM4", "fast")
+    fast = torch._dyn_quant_matmul_4bit(xv, packed_vk, bs, k, n).cpu()
+    monkeypatch.delenv("TORCH_VK_QMM4")
+    assert torch.allclose(fast, want, rtol=1e-5, atol=1e-5 * float(want.abs().max()))
+    assert torch.equal(torch._dyn_quant_matmul_4bit(xv, packed_vk, bs, k, n).cpu(), want)  # and exact again by default
+
+
 def test_dyn_quant_errors():
     x = torch.randn(2, 64).to("vk")
     w, sc, _ = C.pack_case(8, 64, 32, 3, False)

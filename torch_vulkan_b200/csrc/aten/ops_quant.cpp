@@ -96,6 +96,8 @@ struct PreparedWeights {
   const void* data;
   int64_t numel, n, k, bs;
   uint32_t version;
+  int kind;       // 0: int8 weights for the exact tensor-core kernel; 1: float16 weight * scale for the fast route
+  int inexact;    // kind 1: some weight * scale product is not exact in float16 (the fast route must not be used)
   at::Tensor prepared;
 };
 
@@ -105,7 +107,7 @@ constexpr size_t kMaxPrepared = 16;
 
 uint32_t version_of(const at::Tensor& t) { return t.is_inference() ? 0u : t._version(); }
 
-at::Tensor prepared_weights(const at::Tensor& packed, int dev, int64_t n, int64_t k, int64_t bs) {
+at::Tensor prepared_weights(const at::Tensor& packed, int dev, int64_t n, int64_t k, int64_t bs, int kind, int* inexact) {
   std::lock_guard<std::mutex> lock(g_prepared_mutex);
   c10::StorageImpl* impl = packed.storage().unsafeGetStorageImpl();
   for (auto it = g_prepared.begin(); it != g_prepared.end();) {
@@ -114,17 +116,23 @@ at::Tensor prepared_weights(const at::Tensor& packed, int dev, int64_t n, int64_
       continue;
     }
     if (it->storage._unsafe_get_target() == impl && it->data == packed.const_data_ptr() && it->numel == packed.numel() &&
-        it->n == n && it->k == k && it->bs == bs && it->version == version_of(packed)) {
+        it->n == n && it->k == k && it->bs == bs && it->kind == kind && it->version == version_of(packed)) {
       g_prepared.splice(g_prepared.begin(), g_prepared, it);
+      if (inexact != nullptr) *inexact = g_prepared.front().inexact;
       return g_prepared.front().prepared;
     }
     ++it;
   }
-  const uint64_t bytes = tvb_qmm4_prepared_bytes(n, k);
+  const uint64_t bytes = kind == 0 ? tvb_qmm4_prepared_bytes(n, k) : tvb_qmm4_fast_prepared_bytes(n, k);
   at::Tensor prepared = at::empty({static_cast<int64_t>(bytes)}, packed.options().dtype(at::kByte));
-  check(tvb_qmm4_prepare(dev, static_cast<const float*>(gpu_address(packed)), n, k, bs, gpu_address_out(prepared), bytes));
+  int flag = 0;
+  if (kind == 0)
+    check(tvb_qmm4_prepare(dev, static_cast<const float*>(gpu_address(packed)), n, k, bs, gpu_address_out(prepared), bytes));
+  else
+    check(tvb_qmm4_fast_prepare(dev, static_cast<const float*>(gpu_address(packed)), n, k, bs, gpu_address_out(prepared), bytes, &flag));
+  if (inexact != nullptr) *inexact = flag;
   g_prepared.push_front(PreparedWeights{c10::weak_intrusive_ptr<c10::StorageImpl>(packed.storage().getWeakStorageImpl()),
-                                        packed.const_data_ptr(), packed.numel(), n, k, bs, version_of(packed), prepared});
+                                        packed.const_data_ptr(), packed.numel(), n, k, bs, version_of(packed), kind, flag, prepared});
   while (g_prepared.size() > kMaxPrepared) g_prepared.pop_back();
   return prepared;
 }
@@ -153,14 +161,28 @@ at::Tensor dyn_quant_matmul_4bit(const at::Tensor& inp, const at::Tensor& packed
   // Both kernels are bit for bit the CPU's arithmetic; the tensor-core one takes every shape it can (k and the
   // block size multiples of 32), the CUDA-core one the rest. TORCH_VK_QMM4=plain forces the latter (as the
   // reference's TORCH_VK_GEMM switches kernels for its tests).
-  static const bool force_plain = [] {
-    const char* v = std::getenv("TORCH_VK_QMM4");
-    return v != nullptr && std::string(v) == "plain";
-  }();
+  // TORCH_VK_QMM4=fast opts into the float16 GEMM route: not bit for bit (float32 accumulation over the whole of k
+  // instead of per block), within rtol 1e-5 of the exact routes. It applies when every weight * scale is exact in
+  // float16 (block scales that came from bfloat16) and the packed vector is the caller's own float32 tensor.
+  const char* mode_env = std::getenv("TORCH_VK_QMM4");
+  const std::string mode = mode_env != nullptr ? mode_env : "";
+  const bool force_plain = mode == "plain";
+  if (mode == "fast" && K % 8 == 0 && packed.is_same(packed_weights)) {
+    int inexact = 0;
+    at::Tensor prepared = prepared_weights(packed_weights, dev, N, K, block_size, 1, &inexact);
+    if (inexact == 0) {
+      const uint64_t fbytes = tvb_qmm4_fast_workspace_bytes(M, K);
+      at::Tensor fws = at::empty({static_cast<int64_t>(fbytes)}, inp.options().dtype(at::kByte));
+      check(tvb_qmm4_fast(dev, gpu_address(x), dtype_code(x.scalar_type()), static_cast<const float*>(gpu_address(packed)),
+                          bias_elements != 0 ? 1 : 0, gpu_address(prepared), gpu_address_out(out), M, N, K, block_size,
+                          gpu_address_out(fws), fbytes));
+      return out;
+    }
+  }
   if (!force_plain && K % 32 == 0 && block_size % 32 == 0) {
     // the cache keys on the caller's tensor when it is already the float32 vector (the usual case)
     const bool own = packed.is_same(packed_weights);
-    at::Tensor prepared = own ? prepared_weights(packed_weights, dev, N, K, block_size) : at::Tensor();
+    at::Tensor prepared = own ? prepared_weights(packed_weights, dev, N, K, block_size, 0, nullptr) : at::Tensor();
     if (!own) {
       const uint64_t bytes = tvb_qmm4_prepared_bytes(N, K);
       prepared = at::empty({static_cast<int64_t>(bytes)}, inp.options().dtype(at::kByte));
