@@ -4,7 +4,7 @@
 // One persistent CTA per SM walks 128 x BN output tiles. Warp roles:
 //   warp 4, one lane: TMA producer. Fills a ring of shared-memory stages, each holding a
 //            128-row slice of A and a BN-row slice of B, 128 bytes of k wide, written by
-//            cp.async.bulk.tensor with the 128-byte swizzle (no cluster multicast).
+//            cp.async.bulk.tensor with the 128-byte swizzle (each CTA loads for itself only).
 //   warp 5, one lane: issues tcgen05.mma (four per stage, 32 bytes of k each) into one of two
 //            TMEM accumulator buffers (2 x BN columns of float32 / int32), and
 //            tcgen05.commit's each stage back to the producer and each finished tile to the

@@ -1,5 +1,5 @@
 // Thin wrappers over the sm_100a PTX this library uses directly: mbarriers,
-// TMA (cp.async.bulk.tensor, never with cluster multicast), tcgen05 (TMEM
+// TMA (cp.async.bulk.tensor, each CTA loading for itself only), tcgen05 (TMEM
 // allocation, MMA, commit, loads) and mma.sync. Every wait is bounded: a wait
 // that runs out raises the CTA's abort flag, which the kernels turn into a
 // status word for the host instead of hanging or trapping.

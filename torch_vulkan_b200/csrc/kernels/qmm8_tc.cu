@@ -7,7 +7,7 @@
 //
 // Persistent CTAs over 128 x 256 output tiles; per 64 values of k:
 //   warp 12 (two lanes) TMA: a 256-row x 64-byte box of int8 weights into a raw ring (no swizzle) and a 128-row x
-//                      128-byte box of A into the operand ring (128-byte swizzle); no multicast
+//                      128-byte box of A into the operand ring (128-byte swizzle); every CTA fetches its own copy
 //   warps 4-11         widen the raw weights to 16-bit floats in registers (byte permutes and one packed subtract per
 //                      pair, exact) and store them into the operand ring in the 128-byte-swizzled K-major layout
 //                      that the MMA's shared-memory descriptor expects
