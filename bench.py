@@ -227,6 +227,56 @@ def extra_configs(tv, stream, peaks, quick):
             tops = 2.0 * mm * 14336 * 4096 / ms / 1e9
             out[f"dyn_int4_m{mm}_{mode}"] = {"tops": tops, "ms": ms, "frac_of_2x_measured_bf16": tops / (2 * peaks["bf16_tflops"])}
     tv.empty_cache()
+    if not quick:
+        out.update(int8_stack(tv, stream))
+    return out
+
+
+def int8_stack(tv, stream, layers=32):
+    """The int8 weight-only Linears of a 32-layer decoder (hidden 4096: qkv 6144, o 4096, gate_up 28672, down from 14336;
+    7 GB of weights, every layer its own buffers), decoded as one replayed graph of 128 products per step. Between the
+    products stands the stack's glue only (the first 4096 columns of qkv feed o, the first 14336 of gate_up feed down)."""
+    from torch_vulkan_b200 import shard
+
+    shapes = [(6144, 4096), (4096, 4096), (28672, 4096), (4096, 14336)]
+    host = []
+    for i, (n, k) in enumerate(shapes):
+        w = torch.randint(-127, 128, (n, k), dtype=torch.int8, generator=gen(40 + i))
+        sc = (torch.rand(n, generator=gen(50 + i)) * 2e-3 + 1e-4).to(torch.bfloat16)
+        host.append((w, sc))
+    weights = [[(w.to("vk"), sc.to("vk")) for w, sc in host] for _ in range(layers)]
+    wbytes = layers * sum(n * k for n, k in shapes)
+    out = {}
+    for m in (1, 16):
+        x = torch.randn(m, 4096, generator=gen(60)).to(torch.bfloat16).to("vk")
+
+        def step():
+            keep, h = [], x
+            for (wq, sq), (wo, so), (wg, sg), (wd, sd) in weights:
+                qkv = torch._weight_int8pack_mm(h, wq, sq)
+                o = torch._weight_int8pack_mm(qkv[:, :4096], wo, so)
+                gu = torch._weight_int8pack_mm(o, wg, sg)
+                h = torch._weight_int8pack_mm(gu[:, :14336], wd, sd)
+                keep += [qkv, o, gu, h]
+            return keep
+
+        graph = shard.StepGraph(step)
+        for _ in range(3):
+            graph.replay()
+        tv.synchronize()
+        iters = 20
+        s0, e0 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s0.record(stream)
+        for _ in range(iters):
+            graph.replay()
+        e0.record(stream)
+        tv.synchronize()
+        ms = s0.elapsed_time(e0) / iters
+        out[f"int8_stack_32layers_m{m}"] = {"ms_per_token_step": ms, "weight_gbs": wbytes / ms / 1e6, "products": 4 * layers,
+                                             "weight_bytes": wbytes}
+        del graph
+    del weights
+    tv.empty_cache()
     return out
 
 
@@ -272,7 +322,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extra", action="store_true", help="skip the large-m configurations")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline")
-    ap.add_argument("--only", default=None, choices=["fp8", "dyn4", "int8_large_m"],
+    ap.add_argument("--only", default=None, choices=["fp8", "dyn4", "int8_large_m", "int8_stack"],
                     help="run one large-m configuration a few times and exit (for profilers); prints its own JSON line")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
@@ -292,6 +342,9 @@ def main():
     tv.set_device(local_rank)
     dev = f"vk:{local_rank}"
     stream = tv.cuda_stream(local_rank)
+    if args.only == "int8_stack":
+        print(json.dumps({"only": "int8_stack", **int8_stack(tv, stream)}), flush=True)
+        return
     if args.only is not None:
         print(json.dumps(run_only(tv, stream, args.only, max(args.steps, 1) if args.steps != 200 else 3)), flush=True)
         return

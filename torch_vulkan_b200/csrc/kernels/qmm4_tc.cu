@@ -55,7 +55,6 @@ struct TcParams {
   int ndrains;           // k / bs
   int tiles_m, tiles_n;
   int out_bf16;
-  int debug;  // diagnostics: 1 skips the TMEM loads and the folding, 2 the folding only (results are then wrong)
 };
 
 // PHASE 0 with the tensor-core layout: q rows of k + 64 bytes, the tail holding o1 (32 bytes) and o2 (32 bytes).
@@ -180,14 +179,9 @@ __device__ __forceinline__ void drain_tiles(const TcParams& p, const uint32_t tm
       if (!ok) break;
       ptx::tc_fence_after();
       uint32_t r0[32], r1[32];
-      if (p.debug != 1) {
-        ptx::tmem_ld_32x32(lane_base + buf * kTileM, r0);
-        ptx::tmem_ld_32x32(lane_base + buf * kTileM + 32, r1);
-        ptx::tmem_ld_wait();
-      } else {
-#pragma unroll
-        for (int i = 0; i < 32; i++) r0[i] = r1[i] = 0;
-      }
+      ptx::tmem_ld_32x32(lane_base + buf * kTileM, r0);
+      ptx::tmem_ld_32x32(lane_base + buf * kTileM + 32, r1);
+      ptx::tmem_ld_wait();
       ptx::tc_fence_before();
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(tempty0 + 8 * buf);  // the sums are in registers: the buffer is free again
@@ -195,20 +189,12 @@ __device__ __forceinline__ void drain_tiles(const TcParams& p, const uint32_t tm
         buf = 0;
         buf_phase ^= 1u;
       }
-      if (p.debug == 0) {
-        if (d == 0) {
-          fold_block<WIDE, true>(acc0, r0, s, t);
-          fold_block<WIDE, true>(acc1, r1, s, t);
-        } else {
-          fold_block<WIDE, false>(acc0, r0, s, t);
-          fold_block<WIDE, false>(acc1, r1, s, t);
-        }
-      } else if (d == 0) {
-#pragma unroll
-        for (int i = 0; i < 32; i++) {
-          acc0[i] = __uint_as_float(r0[i]);
-          acc1[i] = __uint_as_float(r1[i]);
-        }
+      if (d == 0) {
+        fold_block<WIDE, true>(acc0, r0, s, t);
+        fold_block<WIDE, true>(acc1, r1, s, t);
+      } else {
+        fold_block<WIDE, false>(acc0, r0, s, t);
+        fold_block<WIDE, false>(acc1, r1, s, t);
       }
     }
     if (!ok) break;
@@ -466,10 +452,6 @@ extern "C" int tvb_qmm4_tc(int device, const void* inp, int dtype, const float* 
   p.tiles_m = static_cast<int>(ceil_div(m, kTileM));
   p.tiles_n = static_cast<int>(ceil_div(n, kTileN));
   p.out_bf16 = dtype == TVB_BF16;
-  {
-    const char* v = std::getenv("TVB200_QMM4_DEBUG");
-    p.debug = v != nullptr ? std::atoi(v) : 0;
-  }
   const int grid = static_cast<int>(std::min<int64_t>(sm_count(device), static_cast<int64_t>(p.tiles_m) * p.tiles_n));
   qmm4_tc_kernel<<<grid, kThreads, kSmemBytes, stream>>>(map_w, map_q, p);
   return launched("qmm4_tc", dim3(grid), dim3(kThreads), kSmemBytes, stream);

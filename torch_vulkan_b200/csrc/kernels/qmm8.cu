@@ -129,7 +129,6 @@ struct SkinnyParams {
   float* partials;   // [grid][2][kPartialFloats]
   int* counters;     // [tiles], zero between launches
   int* status;
-  long long* times;  // optional [grid][3]: SM id, first and last globaltimer ns of each CTA (diagnostics), or NULL
   int m, n, k;
   int m0;            // first token row of this pass
   int tiles, chunks; // tiles = ceil(n / rows per tile), chunks = k / 128
@@ -159,14 +158,6 @@ __global__ void __launch_bounds__((NWARPS + 1) * 32, 1)
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
-    if (p.times != nullptr) {
-      unsigned smid;
-      long long now;
-      asm volatile("mov.u32 %0, %smid;" : "=r"(smid));
-      asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
-      p.times[blockIdx.x * 3] = smid;
-      p.times[blockIdx.x * 3 + 1] = now;
-    }
     for (int s = 0; s < Cfg::kStages; s++) {
       ptx::mbar_init(full0 + 8 * s, 1);
       ptx::mbar_init(empty0 + 8 * s, NWARPS);
@@ -413,11 +404,6 @@ __global__ void __launch_bounds__((NWARPS + 1) * 32, 1)
       }
     }
   }
-  if (p.times != nullptr && threadIdx.x == 0) {
-    long long now;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
-    p.times[blockIdx.x * 3 + 2] = now;
-  }
 }
 
 // ------------------------------------------------------------------ host side
@@ -429,8 +415,6 @@ int launch_plain(cudaStream_t stream, const void* a, int64_t a_sm, const int8_t*
   qmm8_plain_kernel<DT><<<grid, 256, 0, stream>>>(a, a_sm, b, scales, c, m, n, k);
   return launched("qmm8_plain", grid, dim3(256), 0, stream);
 }
-
-long long* g_debug_times = nullptr;
 
 // Destinations of a sharded product (tvb_qmm8_gather): every rank's output buffer and flag array.
 struct GatherTargets {
@@ -482,7 +466,6 @@ int launch_skinny_cfg(int device, cudaStream_t stream, const void* a, int64_t a_
   p.n = n;
   p.k = k;
   p.m0 = m0;
-  p.times = g_debug_times;
   if (gather != nullptr) {
     for (int r = 0; r < gather->world; r++) {
       p.c[r] = gather->c[r];
@@ -608,7 +591,6 @@ int launch_skinny_static(int device, int sms, cudaStream_t stream, unsigned char
   p.counters = reinterpret_cast<int*>(scratch);
   p.partials = reinterpret_cast<float*>(scratch + kStaticCounterBytes);
   p.status = reinterpret_cast<int*>(scratch + kStaticCounterBytes + kStaticPartialBytes);
-  p.times = nullptr;
   p.scales = scales;
   p.c[0] = c;
   p.nranks = 1;
@@ -716,11 +698,6 @@ extern "C" int tvb_wait_flags(int device, const uint32_t* flags, int world, uint
   cfg.numAttrs = 1;
   TVB_CUDA(cudaLaunchKernelEx(&cfg, qmm8_wait_flags_kernel, flags, world, seq_counter, status));
   return launched("qmm8_wait_flags", dim3(1), dim3(32), 0, stream);
-}
-
-// Diagnostics (not part of the public header): per-CTA SM id and start / end times of the next skinny launches.
-extern "C" __attribute__((visibility("default"))) void tvb_debug_qmm8_times(long long* device_buffer) {
-  g_debug_times = device_buffer;
 }
 
 extern "C" int tvb_qmm8(int device, const void* a, int dtype, int64_t a_sm, const int8_t* b, const void* scales, void* c,
