@@ -448,34 +448,53 @@ def main():
     # ---- end to end through the public API: A from pinned host memory, C back to the host, every call
     out_pinned = {m: torch.empty(m, N_OUT, dtype=torch.bfloat16).pin_memory() for m in MS}
 
-    def step_e2e():
+    def e2e_body():
         # every product's A goes up from page-locked memory and its C comes back into page-locked memory; the three
-        # products of a step are queued back to back and the step ends when all three results are on the host
-        keep = []
-        for m in MS:
-            a = a_pinned[m].to(dev, non_blocking=True)
-            c = product(m, a)
+        # products of a step are queued back to back
+        ups = [a_pinned[m].to(dev, non_blocking=True) for m in MS]
+        outs = [product(m, a) for m, a in zip(MS, ups)]
+        for m, c in zip(MS, outs):
             out_pinned[m].copy_(c, non_blocking=True)
-            keep.append((a, c))
-        tv.synchronize(local_rank)
+        return ups, outs
 
-    for _ in range(3):
-        step_e2e()
-    barrier()
+    def time_e2e(step):
+        for _ in range(3):
+            step()
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            step()
+        barrier()
+        return (time.perf_counter() - t0) / e2e_steps
+
+    def step_e2e_eager():
+        e2e_body()
+        tv.synchronize(local_rank)  # the step ends when all three results are on the host
+
     e2e_steps = max(5, min(args.steps, 30))
-    t0 = time.perf_counter()
-    for _ in range(e2e_steps):
-        step_e2e()
-    barrier()
-    e2e_s = (time.perf_counter() - t0) / e2e_steps
+    e2e_eager_s = time_e2e(step_e2e_eager)
+    e2e_s, e2e_how = e2e_eager_s, "eager: every copy and product queued by its own call"
+    if graph is not None:
+        # the same copies and products recorded once (the host buffers are fixed; a caller rewrites A in place) and replayed
+        e2e_graph = shard.StepGraph(e2e_body, local_rank)
+
+        def step_e2e_graph():
+            e2e_graph.replay()
+            tv.synchronize(local_rank)
+
+        e2e_s, e2e_how = time_e2e(step_e2e_graph), "CUDA graph replay of the step's copies and products, then a stream synchronize"
+        for m in MS:  # what came back through the replayed copies is what the eager calls deliver
+            want = product(m, a_dev[m]).cpu() if world == 1 else None
+            if want is not None and not torch.equal(want.view(torch.int16), out_pinned[m].view(torch.int16)):
+                raise SystemExit("bench.py: the replayed end-to-end step returned different results")
 
     # ---- max over ranks
     if world > 1:
         import torch.distributed as dist
 
-        t = torch.tensor([total_ms, e2e_s, avg_launch_ms], dtype=torch.float64, device=torch.device("cuda", local_rank))
+        t = torch.tensor([total_ms, e2e_s, avg_launch_ms, e2e_eager_s], dtype=torch.float64, device=torch.device("cuda", local_rank))
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        total_ms, e2e_s, avg_launch_ms = t.tolist()
+        total_ms, e2e_s, avg_launch_ms, e2e_eager_s = t.tolist()
 
     if rank == 0:
         step_bytes = sum(algorithmic_bytes(m, N_OUT, K_IN) for m in MS)  # whole job, all ranks
@@ -498,7 +517,7 @@ def main():
                          "isolated_launch_us_by_m": {str(m): isolated_ms[m] * 1e3 for m in MS}},
             "e2e": {"value": step_bytes / e2e_s / 1e9, "unit": UNIT,
                     "h2d_bytes_per_step": sum(2 * m * K_IN for m in MS), "d2h_bytes_per_step": sum(2 * m * N_OUT for m in MS),
-                    "ms_per_step": e2e_s * 1e3},
+                    "ms_per_step": e2e_s * 1e3, "how": e2e_how, "eager_value": step_bytes / e2e_eager_s / 1e9},
             "gpu_launches": int(launches),
             "clocks": clocks,
         }

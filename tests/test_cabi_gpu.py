@@ -90,6 +90,23 @@ def test_qmm8_skinny_scratch_layout_across_shapes(abi):
         assert ((got.cpu().float() - want.float()).abs() <= tol).all(), (m, k, n)
 
 
+@pytest.mark.parametrize("m", [1, 16])
+def test_qmm8_decode_is_deterministic(abi, m):
+    # Tiles are shared between CTAs; whichever of them finishes a tile, by whichever route (a CTA that finds the
+    # others' sums waiting takes a shortcut), the additions happen in one fixed order: every run gives the same bits.
+    a, b, s = C.config_int8(m, 8192, 7168, torch.bfloat16, seed=5)
+    ad, bd, sd = dev(a), dev(b), dev(s)
+    first = abi.qmm8(ad, bd, sd, variant=2)
+    abi.synchronize()
+    first = first.cpu()
+    want, tol = C.int8_want(a, b, s)
+    assert ((first.float() - want.float()).abs() <= tol).all()
+    for _ in range(25):
+        again = abi.qmm8(ad, bd, sd, variant=2)
+        abi.synchronize()
+        assert torch.equal(first.view(torch.int16), again.cpu().view(torch.int16))
+
+
 def test_qmm8_decode_shape_sample(abi):
     # the decode benchmark's k with a slice of its n: every SM's unit range crosses tiles
     a, b, s = C.config_int8(4, 8192, 3584, torch.bfloat16)

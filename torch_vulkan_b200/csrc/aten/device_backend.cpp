@@ -263,7 +263,7 @@ at::Tensor copy_from(const at::Tensor& self, const at::Tensor& dst, bool non_blo
   if (dst_vk) {
     TORCH_CHECK(self.device().is_cpu(), "device \"vk\": copies come from the CPU or from \"vk\", not from ", self.device());
     // host -> device: the bytes go up as they are; any conversion or striding happens on the device
-    at::Tensor host = self.expand(dst.sizes()).contiguous();
+    at::Tensor host = self.sizes() == dst.sizes() && self.is_contiguous() ? self : self.expand(dst.sizes()).contiguous();
     int dev = dst.device().index();
     if (host.scalar_type() == dst.scalar_type() && dst.is_contiguous()) {
       check(tvb_memcpy_h2d(dev, gpu_address_out(dst), host.const_data_ptr(), host.nbytes()));
@@ -273,6 +273,7 @@ at::Tensor copy_from(const at::Tensor& self, const at::Tensor& dst, bool non_blo
       device_copy(dst, staged);
     }
     // the host buffer may be pinned (the copy is then asynchronous) and must outlive it
+    // (a temporary made above is released on return: wait for the copy then too)
     if (!non_blocking || !host.is_same(self)) check(tvb_synchronize(dev));
     return dst;
   }

@@ -154,6 +154,7 @@ __global__ void __launch_bounds__((NWARPS + 1) * 32, 1)
   const uint32_t full0 = ptx::smem_u32(bars), empty0 = full0 + 8 * Cfg::kStages;
   volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 2 * Cfg::kStages);
   int* last_flag = const_cast<int*>(abort_flag) + 1;  // two slots
+  int* early_flag = last_flag + 2;  // set when every other contributor of the segment's tile was seen to have arrived
   uint16_t* out_tile = reinterpret_cast<uint16_t*>(base_ptr + Cfg::kStages * Cfg::kStageBytes + 256);  // [tokens][rows of a tile]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -164,6 +165,7 @@ __global__ void __launch_bounds__((NWARPS + 1) * 32, 1)
     }
     *abort_flag = 0;
     last_flag[0] = last_flag[1] = 0;
+    *early_flag = 0;
     ptx::fence_mbar_init();
   }
   __syncthreads();
@@ -240,18 +242,54 @@ __global__ void __launch_bounds__((NWARPS + 1) * 32, 1)
     const int tile = static_cast<int>(u / p.chunks), c0 = static_cast<int>(u % p.chunks);
     const int c1 = static_cast<int>(min(static_cast<long long>(p.chunks), c0 + (u1 - u)));
     const bool first_segment = (u == u0);
+    const bool whole_tile = c0 == 0 && c1 == p.chunks;
+    // The ranges that share this tile (consecutive CTAs). Their partial sums are always added in descending CTA order.
+    const long long tile_first_unit = static_cast<long long>(tile) * p.chunks;
+    const int cta_first = whole_tile ? static_cast<int>(blockIdx.x) : range_owner(tile_first_unit, units, grid);
+    const int cta_last = whole_tile ? static_cast<int>(blockIdx.x) : range_owner(tile_first_unit + p.chunks - 1, units, grid);
+    // A CTA that holds the tile's first k (the usual case for the last tile of its range) is added last. If, shortly
+    // before its segment ends, it sees that all the others have already arrived, it is certain to finish the tile: it
+    // then fetches their sums while its last chunks are in flight and skips the exchange through scratch altogether.
+    const bool may_be_early = !whole_tile && cta_first == static_cast<int>(blockIdx.x) && c1 - c0 >= 3;
+    bool early = false;
+    int peeked = 0;
+    float pre[RW][NT][4];
 #pragma unroll
     for (int rb = 0; rb < RW; rb++)
 #pragma unroll
       for (int nt = 0; nt < NT; nt++)
 #pragma unroll
-        for (int i = 0; i < 4; i++) acc[rb][nt][i] = 0.0f;
+        for (int i = 0; i < 4; i++) acc[rb][nt][i] = pre[rb][nt][i] = 0.0f;
 
     for (int chunk = c0; chunk < c1; chunk++, it++) {
       const int s = static_cast<int>(it % Cfg::kStages);
       const uint32_t ph = static_cast<uint32_t>((it / Cfg::kStages) & 1);
       ok = ptx::mbar_wait(full0 + 8 * s, ph, abort_flag);
       if (!ok) break;
+      // (past the first stage's barrier the stream's earlier kernels have completed: the producer waited for them)
+      if (may_be_early) {
+        if (chunk == c1 - 3) {
+          if (threadIdx.x == 0) asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(peeked) : "l"(p.counters + tile) : "memory");
+        } else if (chunk == c1 - 2) {
+          if (threadIdx.x == 0) *early_flag = peeked == cta_last - cta_first;
+        } else if (chunk == c1 - 1) {
+          ptx::named_bar_sync(1, NWARPS * 32);
+          early = *early_flag != 0;
+          if (early) {
+            // the highest contributor's sums: requested now, first needed after this segment's last chunk
+            const bool cta_first_segment = range_start(cta_last, units, grid) / p.chunks == tile;
+            const float4* theirs = reinterpret_cast<const float4*>(
+                p.partials + (static_cast<size_t>(cta_last) * 2 + (cta_first_segment ? 0 : 1)) * Cfg::kPartialFloats);
+#pragma unroll
+            for (int rb = 0; rb < RW; rb++)
+#pragma unroll
+              for (int nt = 0; nt < NT; nt++) {
+                float4 v = __ldcg(&theirs[((warp * RW + rb) * NT + nt) * 32 + lane]);
+                pre[rb][nt][0] = v.x; pre[rb][nt][1] = v.y; pre[rb][nt][2] = v.z; pre[rb][nt][3] = v.w;
+              }
+          }
+        }
+      }
       const uint32_t wbase = base + s * Cfg::kStageBytes;
       const uint32_t tbase = wbase + Cfg::kWeightBytes;
 #pragma unroll
@@ -292,7 +330,35 @@ __global__ void __launch_bounds__((NWARPS + 1) * 32, 1)
     // ---- the segment's sums are complete: finish the tile, alone or with the other CTAs that share it
     ptx::grid_dependency_wait();  // (scratch, counters and C may still be in use by the stream's previous kernel)
     bool finish = true;
-    if (!(c0 == 0 && c1 == p.chunks)) {
+    if (early) {
+      // every other contributor was counted before this CTA looked: nobody else will touch the counter again
+      if (threadIdx.x == 0) atomicExch(&p.counters[tile], 0);
+      // the same additions in the same order as the general path below: from zero, descending, this CTA's sums last
+#pragma unroll
+      for (int rb = 0; rb < RW; rb++)
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+          for (int i = 0; i < 4; i++) pre[rb][nt][i] = 0.0f + pre[rb][nt][i];
+      for (int cta = cta_last - 1; cta > cta_first; cta--) {
+        const bool cta_first_segment = range_start(cta, units, grid) / p.chunks == tile;
+        const float4* theirs = reinterpret_cast<const float4*>(
+            p.partials + (static_cast<size_t>(cta) * 2 + (cta_first_segment ? 0 : 1)) * Cfg::kPartialFloats);
+#pragma unroll
+        for (int rb = 0; rb < RW; rb++)
+#pragma unroll
+          for (int nt = 0; nt < NT; nt++) {
+            float4 v = __ldcg(&theirs[((warp * RW + rb) * NT + nt) * 32 + lane]);
+            pre[rb][nt][0] += v.x; pre[rb][nt][1] += v.y; pre[rb][nt][2] += v.z; pre[rb][nt][3] += v.w;
+          }
+      }
+#pragma unroll
+      for (int rb = 0; rb < RW; rb++)
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+          for (int i = 0; i < 4; i++) acc[rb][nt][i] = pre[rb][nt][i] + acc[rb][nt][i];
+    } else if (!whole_tile) {
       float4* mine = reinterpret_cast<float4*>(p.partials + (static_cast<size_t>(blockIdx.x) * 2 + (first_segment ? 0 : 1)) *
                                                                 Cfg::kPartialFloats);
 #pragma unroll
@@ -301,9 +367,6 @@ __global__ void __launch_bounds__((NWARPS + 1) * 32, 1)
         for (int nt = 0; nt < NT; nt++)
           __stcg(&mine[((warp * RW + rb) * NT + nt) * 32 + lane],
                  make_float4(acc[rb][nt][0], acc[rb][nt][1], acc[rb][nt][2], acc[rb][nt][3]));
-      const long long tile_first_unit = static_cast<long long>(tile) * p.chunks;
-      const int cta_first = range_owner(tile_first_unit, units, grid);
-      const int cta_last = range_owner(tile_first_unit + p.chunks - 1, units, grid);
       // All consumer threads have stored their partial sums once they pass the barrier; one thread then publishes
       // them: its gpu-scope fence is cumulative over what the barrier ordered before it.
       ptx::named_bar_sync(1, NWARPS * 32);
@@ -326,7 +389,7 @@ __global__ void __launch_bounds__((NWARPS + 1) * 32, 1)
           for (int nt = 0; nt < NT; nt++)
 #pragma unroll
             for (int i = 0; i < 4; i++) acc[rb][nt][i] = 0.0f;
-        for (int cta = cta_first; cta <= cta_last; cta++) {  // fixed order: the sum does not depend on who came last
+        for (int cta = cta_last; cta >= cta_first; cta--) {  // fixed order: the sum does not depend on who came last
           const bool cta_first_segment = range_start(cta, units, grid) / p.chunks == tile;
           const float4* theirs = reinterpret_cast<const float4*>(
               p.partials + (static_cast<size_t>(cta) * 2 + (cta_first_segment ? 0 : 1)) * Cfg::kPartialFloats);
