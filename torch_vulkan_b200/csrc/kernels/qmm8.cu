@@ -14,7 +14,11 @@
 //    Work is the list of (256-row tile, 128-k chunk) units cut into equal contiguous
 //    ranges, one per CTA, so every SM streams the same number of bytes whatever n is;
 //    a tile shared by several CTAs is finished by the last of them to arrive, which adds
-//    the partial sums in CTA order (deterministic), from scratch memory. The scale
+//    the partial sums in descending CTA order (deterministic), from scratch memory. Nobody
+//    ever waits for another CTA. Two shortcuts keep the consumers streaming: a range that
+//    leaves a shared tile behind hands the arrival to an otherwise idle agent warp and goes
+//    on at once; a CTA whose last tile has already been reached by all its other
+//    contributors fetches their sums under its last chunks and finishes from registers. The scale
 //    multiplies the finished sum: (sum a*b) * s instead of sum a*(b*s); both are within
 //    the float32 rounding the reference's tests allow (tests/python/test_quant.py:36-40).
 //  * qmm8_plain_kernel: any shape, stride and dtype (float32 A included), one warp per
@@ -86,7 +90,7 @@ struct SkinnyCfg {
   static constexpr int kTokenBoxBytes = kTokens * 128;          // 64 k of 16-bit values per row: two boxes per stage
   static constexpr int kStageBytes = kWeightBytes + 2 * kTokenBoxBytes;
   static constexpr int kStages = (224 * 1024 - kTokens * kRowsPerTile * 2) / kStageBytes < 8 ? (224 * 1024 - kTokens * kRowsPerTile * 2) / kStageBytes : 8;
-  static constexpr int kThreads = (NWARPS + 1) * 32;
+  static constexpr int kThreads = (NWARPS + 2) * 32;  // consumers, the producer warp, the agent warp
   static constexpr int kOutTileBytes = kTokens * kRowsPerTile * 2;  // one tile's outputs, staged for coalesced stores
   static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /* alignment slack */ + 256 /* barriers */ + kOutTileBytes;
   static constexpr int kPartialFloats = NWARPS * RW * NT * 32 * 4;  // one CTA's accumulators
@@ -134,15 +138,27 @@ struct SkinnyParams {
   int tiles, chunks; // tiles = ceil(n / rows per tile), chunks = k / 128
 };
 
-// First unit of CTA c when `units` units are cut into `grid` contiguous ranges.
-__device__ __forceinline__ long long range_start(long long c, long long units, long long grid) { return c * units / grid; }
+// First unit of CTA c when `units` units are cut into `grid` contiguous ranges. (32-bit arithmetic whenever the products
+// fit, which the kernel checks once: 64-bit division is a long instruction sequence, and these run between segments.)
+__device__ __forceinline__ long long range_start(long long c, long long units, long long grid, bool small) {
+  if (small) return static_cast<unsigned>(c) * static_cast<unsigned>(units) / static_cast<unsigned>(grid);
+  return c * units / grid;
+}
 // The CTA whose range holds unit x.
-__device__ __forceinline__ int range_owner(long long x, long long units, long long grid) {
+__device__ __forceinline__ int range_owner(long long x, long long units, long long grid, bool small) {
+  if (small)
+    return static_cast<int>((static_cast<unsigned>(x + 1) * static_cast<unsigned>(grid) + static_cast<unsigned>(units) - 1u) /
+                            static_cast<unsigned>(units)) - 1;
   return static_cast<int>(((x + 1) * grid + units - 1) / units - 1);
 }
 
+// The tile that holds unit u.
+__device__ __forceinline__ int unit_tile(long long u, int chunks, bool small) {
+  return small ? static_cast<int>(static_cast<unsigned>(u) / static_cast<unsigned>(chunks)) : static_cast<int>(u / chunks);
+}
+
 template <int DT, int NT, int RW, int NWARPS>
-__global__ void __launch_bounds__((NWARPS + 1) * 32, 1)
+__global__ void __launch_bounds__((NWARPS + 2) * 32, 1)
     qmm8_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
                        const SkinnyParams p) {
   using Cfg = SkinnyCfg<NT, RW, NWARPS>;
@@ -152,7 +168,8 @@ __global__ void __launch_bounds__((NWARPS + 1) * 32, 1)
   uint8_t* base_ptr = smem_raw + (base - ptx::smem_u32(smem_raw));
   uint64_t* bars = reinterpret_cast<uint64_t*>(base_ptr + Cfg::kStages * Cfg::kStageBytes);
   const uint32_t full0 = ptx::smem_u32(bars), empty0 = full0 + 8 * Cfg::kStages;
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 2 * Cfg::kStages);
+  const uint32_t agent_bar = empty0 + 8 * Cfg::kStages;  // the consumers have stored the partial sums of a segment they leave behind
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 2 * Cfg::kStages + 1);
   int* last_flag = const_cast<int*>(abort_flag) + 1;  // two slots
   int* early_flag = last_flag + 2;  // set when every other contributor of the segment's tile was seen to have arrived
   uint16_t* out_tile = reinterpret_cast<uint16_t*>(base_ptr + Cfg::kStages * Cfg::kStageBytes + 256);  // [tokens][rows of a tile]
@@ -163,6 +180,7 @@ __global__ void __launch_bounds__((NWARPS + 1) * 32, 1)
       ptx::mbar_init(full0 + 8 * s, 1);
       ptx::mbar_init(empty0 + 8 * s, NWARPS);
     }
+    ptx::mbar_init(agent_bar, NWARPS);
     *abort_flag = 0;
     last_flag[0] = last_flag[1] = 0;
     *early_flag = 0;
@@ -173,7 +191,8 @@ __global__ void __launch_bounds__((NWARPS + 1) * 32, 1)
 
   const long long units = static_cast<long long>(p.tiles) * p.chunks;
   const long long grid = gridDim.x;
-  const long long u0 = range_start(blockIdx.x, units, grid), u1 = range_start(blockIdx.x + 1, units, grid);
+  const bool small = (units + 1) * (grid + 1) < (1ll << 31);
+  const long long u0 = range_start(blockIdx.x, units, grid, small), u1 = range_start(blockIdx.x + 1, units, grid, small);
 
   if (warp == NWARPS) {
     // ---------------- producer: one lane issues every TMA copy
@@ -188,22 +207,27 @@ __global__ void __launch_bounds__((NWARPS + 1) * 32, 1)
       const long long ahead = mine < Cfg::kStages ? mine : Cfg::kStages;
       for (long long j = 0; j < ahead; j++) {
         const long long u = u0 + j;
-        const int tile = static_cast<int>(u / p.chunks), chunk = static_cast<int>(u % p.chunks);
+        const int tile = unit_tile(u, p.chunks, small), chunk = static_cast<int>(u - static_cast<long long>(tile) * p.chunks);
         const uint32_t dst = base + static_cast<int>(j) * Cfg::kStageBytes;
         ptx::mbar_expect_tx(full0 + 8 * static_cast<int>(j), Cfg::kStageBytes);
         ptx::tma_load_2d_hint(dst, &map_w, chunk * kChunkK, tile * Cfg::kRowsPerTile, full0 + 8 * static_cast<int>(j), stream_policy);
       }
       ptx::grid_dependency_wait();
       for (long long j = 0; j < ahead; j++) {
-        const int chunk = static_cast<int>((u0 + j) % p.chunks);
+        const int chunk = static_cast<int>(u0 + j - static_cast<long long>(unit_tile(u0 + j, p.chunks, small)) * p.chunks);
         const uint32_t dst = base + static_cast<int>(j) * Cfg::kStageBytes + Cfg::kWeightBytes;
         ptx::tma_load_2d_hint(dst, &map_a, chunk * kChunkK, p.m0, full0 + 8 * static_cast<int>(j), keep_policy);
         ptx::tma_load_2d_hint(dst + Cfg::kTokenBoxBytes, &map_a, chunk * kChunkK + 64, p.m0, full0 + 8 * static_cast<int>(j), keep_policy);
       }
       long long it = ahead;
       bool ok = true;
-      for (long long u = u0 + ahead; u < u1 && ok; u++, it++) {
-        int tile = static_cast<int>(u / p.chunks), chunk = static_cast<int>(u % p.chunks);
+      int tile = unit_tile(u0 + ahead, p.chunks, small);
+      int chunk = static_cast<int>(u0 + ahead - static_cast<long long>(tile) * p.chunks);
+      for (long long u = u0 + ahead; u < u1 && ok; u++, it++, chunk++) {
+        if (chunk == p.chunks) {
+          chunk = 0;
+          tile++;
+        }
         int s = static_cast<int>(it % Cfg::kStages);
         uint32_t ph = static_cast<uint32_t>((it / Cfg::kStages) & 1);
         ok = ptx::mbar_wait(empty0 + 8 * s, ph ^ 1u, abort_flag);
@@ -228,6 +252,68 @@ __global__ void __launch_bounds__((NWARPS + 1) * 32, 1)
     return;
   }
 
+  if (warp == NWARPS + 1) {
+    // ---------------- agent: arrival (and, rarely, completion) of the tile that this CTA's first segment shares
+    // A range that starts inside a tile and goes on beyond it leaves that tile's partial sums in scratch and moves on
+    // at once; this warp counts the arrival in the consumers' stead. Should it turn out to be the tile's last arrival
+    // (the other contributors normally come much later), this warp alone completes the tile.
+    const int tile = unit_tile(u0, p.chunks, small), c0 = static_cast<int>(u0 - static_cast<long long>(tile) * p.chunks);
+    const int c1 = static_cast<int>(min(static_cast<long long>(p.chunks), c0 + (u1 - u0)));
+    const bool left_behind = !(c0 == 0 && c1 == p.chunks) && u0 + (c1 - c0) < u1;
+    if (left_behind && ptx::mbar_wait(agent_bar, 0, abort_flag)) {
+      ptx::grid_dependency_wait();
+      const long long tile_first_unit = static_cast<long long>(tile) * p.chunks;
+      const int cta_first = range_owner(tile_first_unit, units, grid, small);
+      const int cta_last = range_owner(tile_first_unit + p.chunks - 1, units, grid, small);
+      int last = 0;
+      if (lane == 0) {
+        __threadfence();  // (cumulative over the consumers' stores, which the barrier ordered before this)
+        last = atomicAdd(&p.counters[tile], 1) == cta_last - cta_first;
+        if (last) atomicExch(&p.counters[tile], 0);
+      }
+      last = __shfl_sync(0xffffffffu, last, 0);
+      if (last) {
+        __threadfence();
+        const int g = lane >> 2, t = lane & 3, rg = (g >> 1) | ((g & 1) << 2);
+        for (int w = 0; w < NWARPS; w++)  // this warp plays every consumer warp's part in turn
+#pragma unroll
+          for (int rb = 0; rb < RW; rb++)
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++) {
+              float4 sum = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+              for (int cta = cta_last; cta >= cta_first; cta--) {  // the one fixed order of additions
+                const bool cta_first_segment = unit_tile(range_start(cta, units, grid, small), p.chunks, small) == tile;
+                const float4* theirs = reinterpret_cast<const float4*>(
+                    p.partials + (static_cast<size_t>(cta) * 2 + (cta_first_segment ? 0 : 1)) * Cfg::kPartialFloats);
+                const float4 v = __ldcg(&theirs[((w * RW + rb) * NT + nt) * 32 + lane]);
+                sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
+              }
+              const float vals[4] = {sum.x, sum.y, sum.z, sum.w};
+#pragma unroll
+              for (int half = 0; half < 2; half++) {
+                const int col = tile * Cfg::kRowsPerTile + (w * RW + rb) * 16 + rg + 8 * half;
+                if (col >= p.n) continue;
+                const float scale = load_float<DT>(p.scales, col);
+#pragma unroll
+                for (int i = 0; i < 2; i++) {
+                  const int token = p.m0 + nt * 8 + 2 * t + i;
+                  if (token >= p.m) continue;
+                  const float v = vals[2 * half + i] * scale;
+                  const uint16_t bits = DT == TVB_BF16 ? f32_to_bf16_bits(v) : f32_to_f16_bits(v);
+                  const int64_t off = static_cast<int64_t>(token) * p.c_ld + p.c_col0 + col;
+                  for (int r = 0; r < p.nranks; r++) static_cast<uint16_t*>(p.c[r])[off] = bits;
+                }
+              }
+            }
+      }
+    }
+    if (p.done != nullptr) {
+      __syncwarp();
+      ptx::named_bar_arrive(2, (NWARPS + 1) * 32);  // (its stores come before the CTA reports its columns as delivered)
+    }
+    return;
+  }
+
   // ---------------- consumers
   const int g = lane >> 2, t = lane & 3;
   // MMA row g of a 16-row block reads weight row rg (and rg + 8): a permutation chosen so that the two values of g in a
@@ -239,14 +325,14 @@ __global__ void __launch_bounds__((NWARPS + 1) * 32, 1)
   int segment = 0;
   long long u = u0;
   while (u < u1 && ok) {
-    const int tile = static_cast<int>(u / p.chunks), c0 = static_cast<int>(u % p.chunks);
+    const int tile = unit_tile(u, p.chunks, small), c0 = static_cast<int>(u - static_cast<long long>(tile) * p.chunks);
     const int c1 = static_cast<int>(min(static_cast<long long>(p.chunks), c0 + (u1 - u)));
     const bool first_segment = (u == u0);
     const bool whole_tile = c0 == 0 && c1 == p.chunks;
     // The ranges that share this tile (consecutive CTAs). Their partial sums are always added in descending CTA order.
     const long long tile_first_unit = static_cast<long long>(tile) * p.chunks;
-    const int cta_first = whole_tile ? static_cast<int>(blockIdx.x) : range_owner(tile_first_unit, units, grid);
-    const int cta_last = whole_tile ? static_cast<int>(blockIdx.x) : range_owner(tile_first_unit + p.chunks - 1, units, grid);
+    const int cta_first = whole_tile ? static_cast<int>(blockIdx.x) : range_owner(tile_first_unit, units, grid, small);
+    const int cta_last = whole_tile ? static_cast<int>(blockIdx.x) : range_owner(tile_first_unit + p.chunks - 1, units, grid, small);
     // A CTA that holds the tile's first k (the usual case for the last tile of its range) is added last. If, shortly
     // before its segment ends, it sees that all the others have already arrived, it is certain to finish the tile: it
     // then fetches their sums while its last chunks are in flight and skips the exchange through scratch altogether.
@@ -277,7 +363,7 @@ __global__ void __launch_bounds__((NWARPS + 1) * 32, 1)
           early = *early_flag != 0;
           if (early) {
             // the highest contributor's sums: requested now, first needed after this segment's last chunk
-            const bool cta_first_segment = range_start(cta_last, units, grid) / p.chunks == tile;
+            const bool cta_first_segment = unit_tile(range_start(cta_last, units, grid, small), p.chunks, small) == tile;
             const float4* theirs = reinterpret_cast<const float4*>(
                 p.partials + (static_cast<size_t>(cta_last) * 2 + (cta_first_segment ? 0 : 1)) * Cfg::kPartialFloats);
 #pragma unroll
@@ -341,7 +427,7 @@ __global__ void __launch_bounds__((NWARPS + 1) * 32, 1)
 #pragma unroll
           for (int i = 0; i < 4; i++) pre[rb][nt][i] = 0.0f + pre[rb][nt][i];
       for (int cta = cta_last - 1; cta > cta_first; cta--) {
-        const bool cta_first_segment = range_start(cta, units, grid) / p.chunks == tile;
+        const bool cta_first_segment = unit_tile(range_start(cta, units, grid, small), p.chunks, small) == tile;
         const float4* theirs = reinterpret_cast<const float4*>(
             p.partials + (static_cast<size_t>(cta) * 2 + (cta_first_segment ? 0 : 1)) * Cfg::kPartialFloats);
 #pragma unroll
@@ -367,39 +453,46 @@ __global__ void __launch_bounds__((NWARPS + 1) * 32, 1)
         for (int nt = 0; nt < NT; nt++)
           __stcg(&mine[((warp * RW + rb) * NT + nt) * 32 + lane],
                  make_float4(acc[rb][nt][0], acc[rb][nt][1], acc[rb][nt][2], acc[rb][nt][3]));
-      // All consumer threads have stored their partial sums once they pass the barrier; one thread then publishes
-      // them: its gpu-scope fence is cumulative over what the barrier ordered before it.
-      ptx::named_bar_sync(1, NWARPS * 32);
-      int* flag = last_flag + (segment & 1);  // (alternating slots: no barrier needed before the next segment rewrites it)
-      if (threadIdx.x == 0) {
-        __threadfence();
-        int arrived = atomicAdd(&p.counters[tile], 1);
-        int last = arrived == cta_last - cta_first;
-        if (last) atomicExch(&p.counters[tile], 0);  // zero again for the next launch
-        *flag = last;
-      }
-      ptx::named_bar_sync(1, NWARPS * 32);
-      finish = *flag != 0;
-      segment++;
-      if (finish) {
-        __threadfence();
-#pragma unroll
-        for (int rb = 0; rb < RW; rb++)
-#pragma unroll
-          for (int nt = 0; nt < NT; nt++)
-#pragma unroll
-            for (int i = 0; i < 4; i++) acc[rb][nt][i] = 0.0f;
-        for (int cta = cta_last; cta >= cta_first; cta--) {  // fixed order: the sum does not depend on who came last
-          const bool cta_first_segment = range_start(cta, units, grid) / p.chunks == tile;
-          const float4* theirs = reinterpret_cast<const float4*>(
-              p.partials + (static_cast<size_t>(cta) * 2 + (cta_first_segment ? 0 : 1)) * Cfg::kPartialFloats);
+      if (u + (c1 - c0) < u1) {
+        // More of the range follows: leave the tile to the agent warp (which counts this arrival) and go on at once.
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(agent_bar);
+        finish = false;
+      } else {
+        // All consumer threads have stored their partial sums once they pass the barrier; one thread then publishes
+        // them: its gpu-scope fence is cumulative over what the barrier ordered before it.
+        ptx::named_bar_sync(1, NWARPS * 32);
+        int* flag = last_flag + (segment & 1);  // (alternating slots: no barrier needed before the next segment rewrites it)
+        if (threadIdx.x == 0) {
+          __threadfence();
+          int arrived = atomicAdd(&p.counters[tile], 1);
+          int last = arrived == cta_last - cta_first;
+          if (last) atomicExch(&p.counters[tile], 0);  // zero again for the next launch
+          *flag = last;
+        }
+        ptx::named_bar_sync(1, NWARPS * 32);
+        finish = *flag != 0;
+        segment++;
+        if (finish) {
+          __threadfence();
 #pragma unroll
           for (int rb = 0; rb < RW; rb++)
 #pragma unroll
-            for (int nt = 0; nt < NT; nt++) {
-              float4 v = __ldcg(&theirs[((warp * RW + rb) * NT + nt) * 32 + lane]);
-              acc[rb][nt][0] += v.x; acc[rb][nt][1] += v.y; acc[rb][nt][2] += v.z; acc[rb][nt][3] += v.w;
-            }
+            for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+              for (int i = 0; i < 4; i++) acc[rb][nt][i] = 0.0f;
+          for (int cta = cta_last; cta >= cta_first; cta--) {  // fixed order: the sum does not depend on who came last
+            const bool cta_first_segment = unit_tile(range_start(cta, units, grid, small), p.chunks, small) == tile;
+            const float4* theirs = reinterpret_cast<const float4*>(
+                p.partials + (static_cast<size_t>(cta) * 2 + (cta_first_segment ? 0 : 1)) * Cfg::kPartialFloats);
+#pragma unroll
+            for (int rb = 0; rb < RW; rb++)
+#pragma unroll
+              for (int nt = 0; nt < NT; nt++) {
+                float4 v = __ldcg(&theirs[((warp * RW + rb) * NT + nt) * 32 + lane]);
+                acc[rb][nt][0] += v.x; acc[rb][nt][1] += v.y; acc[rb][nt][2] += v.z; acc[rb][nt][3] += v.w;
+              }
+          }
         }
       }
     }
@@ -456,7 +549,7 @@ __global__ void __launch_bounds__((NWARPS + 1) * 32, 1)
     // Sharded product: when the last CTA has stored its columns everywhere, tell every rank (this one included) that
     // this GPU's slice of product `seq` has arrived. The system-scope fence after the barrier covers the stores of
     // all consumer threads of the CTA.
-    ptx::named_bar_sync(1, NWARPS * 32);
+    ptx::named_bar_sync(2, (NWARPS + 1) * 32);  // (the agent warp arrives here too, after whatever it had to store)
     if (threadIdx.x == 0) {
       __threadfence_system();
       if (atomicAdd(p.done, 1) == static_cast<int>(gridDim.x) - 1) {
