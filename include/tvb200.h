@@ -119,6 +119,11 @@ TVB_API int tvb_copy_strided(int device, void* dst, int dst_dtype, const int64_t
 TVB_API int tvb_fill_strided(int device, void* dst, int itemsize, uint64_t bits, const int64_t* strides, const int64_t* sizes,
                      int ndim);
 
+/* c[i, j] += v[j] for a [m, n] matrix with row stride c_sm (elements): float32 addition, one rounding to c's dtype.
+ * The bias of a Linear whose product has no bias operand (the reference adds it with its generic add kernel,
+ * crates/pyvk/csrc/quant.cpp:296-297 does so inside _scaled_mm). float32, float16 and bfloat16, in any pairing. */
+TVB_API int tvb_add_rowvec(int device, void* c, int c_dtype, int64_t c_sm, const void* v, int v_dtype, int64_t m, int64_t n);
+
 /* ---- aten::_weight_int8pack_mm (replaces vkt_dispatch("qmm8_<f32|f16|bf16>", ...),
  *      crates/pyvk/csrc/quant.cpp:86-117; parameters as Q8Params, quant.cpp:31-37) ----
  * C[m, n] = A[m, k] @ (int8 B[n, k] * scales[n]).T, float32 accumulation, rounded once

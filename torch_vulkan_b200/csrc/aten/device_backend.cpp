@@ -336,6 +336,40 @@ at::Tensor& fill_tensor(at::Tensor& self, const at::Tensor& value) {
 
 at::Tensor& zero_(at::Tensor& self) { return fill_scalar(self, 0); }
 
+// ---------------------------------------------------------------- bias
+
+// self += other for the one shape a quantised Linear needs: `other` a vector over self's last dimension (its bias),
+// alpha 1, floating dtypes. Anything else is not implemented on this device (and is never run on the CPU instead).
+at::Tensor& add_rowvec_(at::Tensor& self, const at::Tensor& other, const at::Scalar& alpha) {
+  TORCH_CHECK_NOT_IMPLEMENTED(is_vk(self) && is_vk(other) && self.device() == other.device(),
+                              "add_ on device \"vk\": both tensors must be on the same \"vk\" device");
+  TORCH_CHECK_NOT_IMPLEMENTED(alpha.to<double>() == 1.0, "add_ on device \"vk\": only alpha = 1 is implemented");
+  TORCH_CHECK_NOT_IMPLEMENTED(self.dim() >= 1 && other.dim() == 1 && other.size(0) == self.size(-1) && other.is_contiguous(),
+                              "add_ on device \"vk\": only a contiguous vector over the last dimension (a bias) can be added, got ",
+                              self.sizes(), " += ", other.sizes());
+  const int cd = dtype_code(self.scalar_type()), vd = dtype_code(other.scalar_type());
+  TORCH_CHECK_NOT_IMPLEMENTED(at::isFloatingType(self.scalar_type()) && at::isFloatingType(other.scalar_type()) && cd >= 0 && vd >= 0,
+                              "add_ on device \"vk\": floating dtypes only");
+  if (self.numel() == 0) return self;
+  const int64_t n = self.size(-1);
+  TORCH_CHECK_NOT_IMPLEMENTED(self.stride(-1) == 1, "add_ on device \"vk\": the last dimension must be dense");
+  if (self.dim() <= 2) {
+    const int64_t m = self.dim() == 2 ? self.size(0) : 1;
+    const int64_t sm = self.dim() == 2 && m > 1 ? self.stride(0) : n;
+    check(tvb_add_rowvec(self.device().index(), gpu_address_out(self), cd, sm, gpu_address(other), vd, m, n));
+  } else {
+    TORCH_CHECK_NOT_IMPLEMENTED(self.is_contiguous(), "add_ on device \"vk\": more than two dimensions need a contiguous tensor");
+    check(tvb_add_rowvec(self.device().index(), gpu_address_out(self), cd, n, gpu_address(other), vd, self.numel() / n, n));
+  }
+  return self;
+}
+
+at::Tensor add_rowvec(const at::Tensor& self, const at::Tensor& other, const at::Scalar& alpha) {
+  at::Tensor out = at::empty_like(self, at::MemoryFormat::Contiguous);
+  out.copy_(self);
+  return add_rowvec_(out, other, alpha);
+}
+
 // ---------------------------------------------------------------- everything else
 
 void strict_fallback(const c10::OperatorHandle& op, torch::jit::Stack*) {
@@ -381,6 +415,8 @@ TORCH_LIBRARY_IMPL(aten, PrivateUse1, m) {
   m.impl("fill_.Scalar", &fill_scalar);
   m.impl("fill_.Tensor", &fill_tensor);
   m.impl("zero_", &zero_);
+  m.impl("add_.Tensor", &add_rowvec_);
+  m.impl("add.Tensor", &add_rowvec);
 }
 
 TORCH_LIBRARY_IMPL(_, PrivateUse1, m) {

@@ -116,6 +116,17 @@ __global__ void fill_strided_kernel(void* dst, FillParams p) {
   }
 }
 
+// c[i, j] = float32(c[i, j]) + float32(v[j]), rounded once to c's dtype: a Linear's bias (or any row vector) added in place.
+__global__ void add_rowvec_kernel(void* c, int c_dtype, int64_t c_sm, const void* v, int v_dtype, int64_t m, int64_t n) {
+  const int64_t total = m * n;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t e = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; e < total; e += stride) {
+    const int64_t i = e / n, j = e - i * n;
+    const int64_t o = i * c_sm + j;
+    store_float_rt(c, o, c_dtype, load_float_rt(c, o, c_dtype) + load_float_rt(v, j, v_dtype));
+  }
+}
+
 int grid_for(int device, int64_t numel, int block) {
   int64_t want = ceil_div(numel, block);
   int64_t cap = static_cast<int64_t>(sm_count(device)) * 16;
@@ -188,4 +199,17 @@ extern "C" int tvb_fill_strided(int device, void* dst, int itemsize, uint64_t bi
   int grid = grid_for(device, p.numel, 256);
   fill_strided_kernel<<<grid, 256, 0, stream>>>(dst, p);
   return launched("fill_strided", dim3(grid), dim3(256), 0, stream);
+}
+
+extern "C" int tvb_add_rowvec(int device, void* c, int c_dtype, int64_t c_sm, const void* v, int v_dtype, int64_t m, int64_t n) {
+  auto is_float = [](int dt) { return dt == TVB_F32 || dt == TVB_F16 || dt == TVB_BF16; };
+  TVB_REQUIRE(is_float(c_dtype) && is_float(v_dtype), "tvb_add_rowvec: float32, float16 or bfloat16 only");
+  TVB_REQUIRE(m >= 0 && n >= 0 && c_sm >= n, "tvb_add_rowvec: bad shape");
+  cudaStream_t stream;
+  if (enter(device, &stream) != 0) return -1;
+  if (m == 0 || n == 0) return 0;
+  TVB_REQUIRE(c != nullptr && v != nullptr, "tvb_add_rowvec: NULL pointer");
+  int grid = grid_for(device, m * n, 256);
+  add_rowvec_kernel<<<grid, 256, 0, stream>>>(c, c_dtype, c_sm, v, v_dtype, m, n);
+  return launched("add_rowvec", dim3(grid), dim3(256), 0, stream);
 }
