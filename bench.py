@@ -218,6 +218,13 @@ def extra_configs(tv, stream, peaks, quick):
         out["fp8_scaled_mm_8192_" + ("rowwise" if rowwise else "tensorwise")] = {
             "tflops": tf, "ms": ms, "frac_of_2x_measured_bf16": tf / (2 * peaks["bf16_tflops"]), "frac_of_nominal_fp8": tf / 4500.0}
         del av, bv
+    # the unquantised product on the same main loop (aten::mm, bfloat16), against the library GEMM the peak was measured with
+    a16 = torch.randn(m, k, generator=gen(21)).to(torch.bfloat16).to("vk")
+    w16 = torch.randn(n, k, generator=gen(22)).to(torch.bfloat16).to("vk")
+    ms = timed(lambda: torch.mm(a16, w16.t()), 5 if quick else 10)
+    tf = 2.0 * m * n * k / ms / 1e9
+    out["bf16_mm_8192"] = {"tflops": tf, "ms": ms, "frac_of_measured_bf16": tf / peaks["bf16_tflops"]}
+    del a16, w16
     w, sc, bias = config_dyn4_weights()
     packed = torch._dyn_quant_pack_4bit_weight(w.to("vk"), sc.to("vk"), bias.to("vk"), 32, 4096, 14336)
     for mm in ((128,) if quick else (128, 512, 2048)):
@@ -291,6 +298,12 @@ def run_only(tv, stream, which, iters):
         av, bv, sav, sbv = a.to("vk"), b.t().to("vk").t(), sa.to("vk"), sb.to("vk")
         fn = lambda: torch._scaled_mm(av, bv, sav, sbv, out_dtype=torch.bfloat16)  # noqa: E731
         flops = 2.0 * m * n * k
+    elif which == "bf16_mm":
+        m = n = k = 4096
+        a16 = torch.randn(m, k, generator=gen(21)).to(torch.bfloat16).to("vk")
+        w16 = torch.randn(n, k, generator=gen(22)).to(torch.bfloat16).to("vk")
+        fn = lambda: torch.mm(a16, w16.t())  # noqa: E731
+        flops = 2.0 * m * n * k
     elif which == "dyn4":
         mm = 512
         w, sc, bias = config_dyn4_weights()
@@ -325,7 +338,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extra", action="store_true", help="skip the large-m configurations")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline")
-    ap.add_argument("--only", default=None, choices=["fp8", "dyn4", "int8_large_m", "int8_stack"],
+    ap.add_argument("--only", default=None, choices=["fp8", "dyn4", "int8_large_m", "int8_stack", "bf16_mm"],
                     help="run one large-m configuration a few times and exit (for profilers); prints its own JSON line")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
@@ -444,7 +457,7 @@ def main():
     clocks = sampler.stop() if sampler is not None else None
     if clocks is not None:
         clocks["window"] = "warm-up, timed region and per-launch pass, plus identical untimed steps up to 1.5 s"
-    isolated_ms = {m: statistics.mean(s0.elapsed_time(e0) for mm, s0, e0 in pairs if mm == m) for m in MS}
+    isolated_ms = {m: statistics.median(s0.elapsed_time(e0) for mm, s0, e0 in pairs if mm == m) for m in MS}
     # average launch duration over the timed region: the region holds nothing but these launches, queued back to back
     avg_launch_ms = total_ms / (args.steps * len(MS)) if world == 1 else statistics.mean(isolated_ms.values())
 

@@ -234,6 +234,15 @@ TVB_API int tvb_scaled_mm(int device, const void* a, int a_dtype, int64_t a_s0, 
                   const void* bias, int bias_dtype, const float* scale_result, void* out, int out_dtype, int64_t m,
                   int64_t n, int64_t k, int variant);
 
+/* ---- aten::mm / aten::addmm for float32, float16 and bfloat16 (replaces the reference's gemm dispatches,
+ *      crates/pyvk/csrc/linalg.cpp:227-321, for the matrices either side of the quantised products) ----
+ * out[m, n] = A[m, k] @ B[k, n] (+ bias[n]), float32 accumulation, one rounding to out_dtype. A and B have one dtype;
+ * element (i, kk) of A at a[i * a_s0 + kk * a_s1], element (kk, j) of B at b[kk * b_s0 + j * b_s1]; out contiguous.
+ * variant: 0 automatic, 1 the plain CUDA-core kernel (any strides, float32 included), 2 the tcgen05 kernel (16-bit
+ * operands, both K-major: a_s1 == 1 and b_s0 == 1, rows 16-byte aligned). */
+TVB_API int tvb_mm(int device, const void* a, int dtype, int64_t a_s0, int64_t a_s1, const void* b, int64_t b_s0, int64_t b_s1,
+           const void* bias, int bias_dtype, void* out, int out_dtype, int64_t m, int64_t n, int64_t k, int variant);
+
 #ifdef __cplusplus
 }
 #endif

@@ -406,6 +406,7 @@ TORCH_LIBRARY_IMPL(aten, PrivateUse1, m) {
   m.impl("empty_strided", &empty_strided);
   m.impl("as_strided", &as_strided);
   m.impl("view", &view);
+  m.impl("_unsafe_view", &view);
   m.impl("_reshape_alias", &reshape_alias);
   m.impl("resize_", &resize_);
   m.impl("set_.source_Storage_storage_offset", &set_storage);

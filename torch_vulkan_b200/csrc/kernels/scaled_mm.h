@@ -1,4 +1,5 @@
-// Parameters shared by the two aten::_scaled_mm kernels (plain and tcgen05).
+// Parameters shared by the two aten::_scaled_mm kernels (plain and tcgen05), which also serve aten::mm / addmm
+// (operands of one 16- or 32-bit float type, no scales).
 #pragma once
 
 #include <cuda_runtime.h>
@@ -8,9 +9,9 @@
 namespace tvb {
 
 struct ScaledMmParams {
-  const void* a;         // float8 [m, k]: element (i, kk) at a[i * a_s0 + kk * a_s1]
-  const void* b;         // float8 [k, n]: element (kk, j) at b[kk * b_s0 + j * b_s1]
-  const float* scale_a;  // 1 or m values
+  const void* a;         // [m, k]: element (i, kk) at a[i * a_s0 + kk * a_s1]
+  const void* b;         // [k, n]: element (kk, j) at b[kk * b_s0 + j * b_s1]
+  const float* scale_a;  // 1 or m values; NULL (with scale_b): no scaling
   const float* scale_b;  // 1 or n values
   const void* bias;      // n values of bias_dtype, or NULL
   const float* scale_result;  // 1 value or NULL (float8 outputs only)
@@ -24,6 +25,6 @@ int scaled_mm_plain(cudaStream_t stream, const ScaledMmParams& p);
 // The tcgen05 kernel; `usable` tells whether the layout qualifies (K-major operands,
 // 16-byte aligned rows).
 bool scaled_mm_tc_usable(const ScaledMmParams& p);
-int scaled_mm_tc(int device, cudaStream_t stream, const ScaledMmParams& p);
+int scaled_mm_tc(int device, cudaStream_t stream, const ScaledMmParams& p);  // float8 (kind::f8f6f4) or float16 / bfloat16 (kind::f16)
 
 }  // namespace tvb

@@ -1,4 +1,5 @@
-// aten::_scaled_mm, the plain kernel: any strides, any float8 pair, any size.
+// aten::_scaled_mm, the plain kernel: any strides, any float8 pair, any size (and, without scales, aten::mm / addmm
+// of float32, float16 or bfloat16 matrices that the tcgen05 kernel does not take).
 //
 // Follows the reference's emulated product step by step (crates/pyvk/csrc/quant.cpp:283-299):
 // each operand upcast exactly to float32 and multiplied by its scale (a 0-dim scale or a
@@ -22,9 +23,7 @@ __global__ void __launch_bounds__(256) scaled_mm_plain_kernel(const ScaledMmPara
   __shared__ float bs[kTK][kBN + 1];
   const int t = threadIdx.x, tx = t & 15, ty = t >> 4;
   const int64_t row0 = static_cast<int64_t>(blockIdx.y) * kBM, col0 = static_cast<int64_t>(blockIdx.x) * kBN;
-  const uint8_t* a = static_cast<const uint8_t*>(p.a);
-  const uint8_t* b = static_cast<const uint8_t*>(p.b);
-  const int a_kind = p.a_dtype == TVB_E4M3 ? 0 : 1, b_kind = p.b_dtype == TVB_E4M3 ? 0 : 1;
+  const bool scaled = p.scale_a != nullptr;  // (aten::mm / addmm come through here without scales)
   float acc[4][4];
 #pragma unroll
   for (int i = 0; i < 4; i++)
@@ -38,14 +37,20 @@ __global__ void __launch_bounds__(256) scaled_mm_plain_kernel(const ScaledMmPara
       int r = p.a_s1 == 1 ? e / kTK : e % kBM, kk = p.a_s1 == 1 ? e % kTK : e / kBM;
       int64_t gm = row0 + r, gk = k0 + kk;
       float v = 0.0f;
-      if (gm < p.m && gk < p.k) v = f8_bits_to_f32(a[gm * p.a_s0 + gk * p.a_s1], a_kind) * p.scale_a[p.rowwise ? gm : 0];
+      if (gm < p.m && gk < p.k) {
+        v = load_float_rt(p.a, gm * p.a_s0 + gk * p.a_s1, p.a_dtype);
+        if (scaled) v *= p.scale_a[p.rowwise ? gm : 0];
+      }
       as[kk][r] = v;
     }
     for (int e = t; e < kBN * kTK; e += 256) {
       int c = p.b_s0 == 1 ? e / kTK : e % kBN, kk = p.b_s0 == 1 ? e % kTK : e / kBN;
       int64_t gn = col0 + c, gk = k0 + kk;
       float v = 0.0f;
-      if (gn < p.n && gk < p.k) v = f8_bits_to_f32(b[gk * p.b_s0 + gn * p.b_s1], b_kind) * p.scale_b[p.rowwise ? gn : 0];
+      if (gn < p.n && gk < p.k) {
+        v = load_float_rt(p.b, gk * p.b_s0 + gn * p.b_s1, p.b_dtype);
+        if (scaled) v *= p.scale_b[p.rowwise ? gn : 0];
+      }
       bs[kk][c] = v;
     }
     __syncthreads();

@@ -1,4 +1,5 @@
-// aten::_scaled_mm on the fifth-generation tensor cores: float8 operands straight into
+// aten::_scaled_mm (and, without scales, aten::mm / addmm of 16-bit floats: tvb_mm at the end of this file, kind::f16
+// on the same main loop) on the fifth-generation tensor cores: float8 operands straight into
 // tcgen05.mma kind::f8f6f4, float32 accumulation in tensor memory, and the scales, bias,
 // 1 / scale_result and the cast to the output type applied as the accumulators are read back.
 //
@@ -41,7 +42,7 @@ struct ScaledEpilogue {
       const int col = col0 + i;
       float s = 1.0f, b = 0.0f;
       if (col < n) {
-        s = p.rowwise ? p.scale_b[col] : p.scale_b[0];
+        if (p.scale_b != nullptr) s = p.rowwise ? p.scale_b[col] : p.scale_b[0];
         if (p.bias != nullptr) b = load_float_rt(p.bias, col, p.bias_dtype);
       }
       cs[i] = s;
@@ -56,7 +57,7 @@ struct ScaledEpilogue {
     const int warp = (threadIdx.x >> 5) & 3;
     const float* cs = reinterpret_cast<const float*>(smem) + warp * 2 * kBN + col_off;
     const float* cb = cs + kBN;
-    const float sa = p.rowwise ? p.scale_a[row] : p.scale_a[0];
+    const float sa = p.scale_a == nullptr ? 1.0f : (p.rowwise ? p.scale_a[row] : p.scale_a[0]);
     const bool f8_out = p.out_dtype == TVB_E4M3 || p.out_dtype == TVB_E5M2;
     const float inv = f8_out && p.scale_result != nullptr ? 1.0f / p.scale_result[0] : 1.0f;
     float v[32];
@@ -98,31 +99,35 @@ struct ScaledEpilogue {
 
 bool scaled_mm_tc_usable(const ScaledMmParams& p) {
   auto aligned = [](const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15u) == 0; };
-  return p.m >= 1 && p.n >= 1 && p.k >= 16 && p.a_s1 == 1 && p.b_s0 == 1 && p.a_s0 % 16 == 0 && p.b_s1 % 16 == 0 &&
+  const int64_t es = dtype_size(p.a_dtype);  // 1 (float8) or 2 (float16 / bfloat16): rows must be 16-byte multiples
+  if (es != 1 && es != 2) return false;
+  return p.m >= 1 && p.n >= 1 && p.k * es >= 16 && p.a_s1 == 1 && p.b_s0 == 1 && (p.a_s0 * es) % 16 == 0 && (p.b_s1 * es) % 16 == 0 &&
          p.a_s0 >= p.k && p.b_s1 >= p.k && aligned(p.a) && aligned(p.b) && p.m < (int64_t(1) << 31) && p.n < (int64_t(1) << 31) &&
-         p.k < (int64_t(1) << 31);
+         p.k < (int64_t(1) << 30);
 }
 
-int scaled_mm_tc(int device, cudaStream_t stream, const ScaledMmParams& p) {
+template <int KIND>
+int scaled_mm_tc_kind(int device, cudaStream_t stream, const ScaledMmParams& p) {
   using Cfg = GemmTcCfg<kBN, ScaledEpilogue::kSmemBytes>;
-  auto kernel = gemm_tc_kernel<0, kBN, ScaledEpilogue>;
+  auto kernel = gemm_tc_kernel<KIND, kBN, ScaledEpilogue>;
   static bool configured[64] = {};
   if (!configured[device & 63]) {
     TVB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
     configured[device & 63] = true;
   }
+  const int es = static_cast<int>(dtype_size(p.a_dtype));
+  const CUtensorMapDataType dt = es == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+                                         : (p.a_dtype == TVB_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16);
+  const int k_per_stage = kGemmStageK / es;
+  const CUtensorMapSwizzle swz = kGemmStageK == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B;
   CUtensorMap map_a, map_b;
-  if (make_tensor_map_2d(&map_a, p.a, CU_TENSOR_MAP_DATA_TYPE_UINT8, p.k, p.m, p.a_s0, kGemmStageK, Cfg::kBM,
-                         kGemmStageK == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B) != 0)
-    return -1;
-  if (make_tensor_map_2d(&map_b, p.b, CU_TENSOR_MAP_DATA_TYPE_UINT8, p.k, p.n, p.b_s1, kGemmStageK, kBN,
-                         kGemmStageK == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B) != 0)
-    return -1;
+  if (make_tensor_map_2d(&map_a, p.a, dt, p.k, p.m, p.a_s0 * es, k_per_stage, Cfg::kBM, swz) != 0) return -1;
+  if (make_tensor_map_2d(&map_b, p.b, dt, p.k, p.n, p.b_s1 * es, k_per_stage, kBN, swz) != 0) return -1;
   GemmTcShape sh{};
   sh.m = static_cast<int>(p.m);
   sh.n = static_cast<int>(p.n);
-  sh.kblocks = static_cast<int>(ceil_div(p.k, kGemmStageK));
-  sh.k_elems_per_block = kGemmStageK;
+  sh.kblocks = static_cast<int>(ceil_div(p.k, k_per_stage));
+  sh.k_elems_per_block = k_per_stage;
   sh.tiles_m = static_cast<int>(ceil_div(p.m, Cfg::kBM));
   sh.tiles_n = static_cast<int>(ceil_div(p.n, kBN));
   ScaledEpilogue::Params ep{};
@@ -135,13 +140,19 @@ int scaled_mm_tc(int device, cudaStream_t stream, const ScaledMmParams& p) {
   ep.out_dtype = p.out_dtype;
   ep.rowwise = p.rowwise;
   ep.vector_ok = (reinterpret_cast<uintptr_t>(p.out) & 15u) == 0 && (p.n * dtype_size(p.out_dtype)) % 16 == 0;
-  // float8 formats of kind::f8f6f4: 0 = e4m3, 1 = e5m2; float32 accumulators
-  const uint32_t idesc = ptx::tc_instr_desc(1, p.a_dtype == TVB_E4M3 ? 0 : 1, p.b_dtype == TVB_E4M3 ? 0 : 1, Cfg::kBM, kBN);
+  // operand formats: kind::f8f6f4 0 = e4m3, 1 = e5m2; kind::f16 0 = float16, 1 = bfloat16; float32 accumulators
+  const uint32_t fa = KIND == 0 ? (p.a_dtype == TVB_E4M3 ? 0 : 1) : (p.a_dtype == TVB_F16 ? 0 : 1);
+  const uint32_t fb = KIND == 0 ? (p.b_dtype == TVB_E4M3 ? 0 : 1) : (p.b_dtype == TVB_F16 ? 0 : 1);
+  const uint32_t idesc = ptx::tc_instr_desc(1, fa, fb, Cfg::kBM, kBN);
   int* status = nullptr;
   if (status_word(device, &status) != 0) return -1;
   const int grid = static_cast<int>(std::min<int64_t>(sm_count(device), static_cast<int64_t>(sh.tiles_m) * sh.tiles_n));
   kernel<<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(map_a, map_b, sh, idesc, ep, status);
-  return launched("scaled_mm_tc", dim3(grid), dim3(Cfg::kThreads), Cfg::kSmemBytes, stream);
+  return launched(KIND == 0 ? "scaled_mm_tc" : "mm_tc", dim3(grid), dim3(Cfg::kThreads), Cfg::kSmemBytes, stream);
+}
+
+int scaled_mm_tc(int device, cudaStream_t stream, const ScaledMmParams& p) {
+  return dtype_size(p.a_dtype) == 1 ? scaled_mm_tc_kind<0>(device, stream, p) : scaled_mm_tc_kind<2>(device, stream, p);
 }
 
 }  // namespace tvb
@@ -173,6 +184,29 @@ extern "C" int tvb_scaled_mm(int device, const void* a, int a_dtype, int64_t a_s
   TVB_REQUIRE(variant != 2 || usable, "tvb_scaled_mm: the tcgen05 kernel needs K-major operands with 16-byte aligned rows");
   // small problems do not fill one wave of 128 x 256 tiles: the plain kernel's 64 x 64 tiles spread them wider
   const bool big = m * n >= int64_t(128) * 256 * 8 && k >= 128;
+  if (variant == 2 || (variant == 0 && usable && big)) return scaled_mm_tc(device, stream, p);
+  return scaled_mm_plain(stream, p);
+}
+
+extern "C" int tvb_mm(int device, const void* a, int dtype, int64_t a_s0, int64_t a_s1, const void* b, int64_t b_s0, int64_t b_s1,
+                      const void* bias, int bias_dtype, void* out, int out_dtype, int64_t m, int64_t n, int64_t k, int variant) {
+  auto is_float = [](int dt) { return dt == TVB_F32 || dt == TVB_F16 || dt == TVB_BF16; };
+  TVB_REQUIRE(is_float(dtype) && is_float(out_dtype), "tvb_mm: float32, float16 or bfloat16 only");
+  TVB_REQUIRE(bias == nullptr || is_float(bias_dtype), "tvb_mm: the bias must be float32, float16 or bfloat16");
+  TVB_REQUIRE(m >= 0 && n >= 0 && k >= 0, "tvb_mm: negative size");
+  TVB_REQUIRE(variant >= 0 && variant <= 2, "tvb_mm: unknown kernel variant");
+  if (m == 0 || n == 0) return 0;
+  TVB_REQUIRE(out != nullptr && (k == 0 || (a != nullptr && b != nullptr)), "tvb_mm: NULL pointer");
+  cudaStream_t stream;
+  if (enter(device, &stream) != 0) return -1;
+  ScaledMmParams p{};
+  p.a = a; p.b = b; p.bias = bias; p.out = out;
+  p.m = m; p.n = n; p.k = k;
+  p.a_s0 = a_s0; p.a_s1 = a_s1; p.b_s0 = b_s0; p.b_s1 = b_s1;
+  p.a_dtype = dtype; p.b_dtype = dtype; p.bias_dtype = bias_dtype; p.out_dtype = out_dtype;
+  const bool usable = dtype != TVB_F32 && scaled_mm_tc_usable(p);
+  TVB_REQUIRE(variant != 2 || usable, "tvb_mm: the tcgen05 kernel needs 16-bit K-major operands with 16-byte aligned rows");
+  const bool big = m * n >= int64_t(128) * 256 * 8 && k >= 64;
   if (variant == 2 || (variant == 0 && usable && big)) return scaled_mm_tc(device, stream, p);
   return scaled_mm_plain(stream, p);
 }
