@@ -225,6 +225,15 @@ def extra_configs(tv, stream, peaks, quick):
     tf = 2.0 * m * n * k / ms / 1e9
     out["bf16_mm_8192"] = {"tflops": tf, "ms": ms, "frac_of_measured_bf16": tf / peaks["bf16_tflops"]}
     del a16, w16
+    # int8 weight-only at prefill sizes (weights widened once per call into scratch, then the same 16-bit main loop)
+    for mm, nn_, kk in ((2048, 14336, 4096),) if quick else ((2048, 14336, 4096), (8192, 8192, 8192)):
+        a8 = torch.randn(mm, kk, generator=gen(31)).to(torch.bfloat16).to("vk")
+        w8 = torch.randint(-127, 128, (nn_, kk), dtype=torch.int8, generator=gen(32)).to("vk")
+        s8 = (torch.rand(nn_, generator=gen(33)) * (2e-2 - 1e-3) + 1e-3).to(torch.bfloat16).to("vk")
+        ms = timed(lambda: torch._weight_int8pack_mm(a8, w8, s8), 5)
+        tf = 2.0 * mm * nn_ * kk / ms / 1e9
+        out[f"int8_weight_only_m{mm}_n{nn_}_k{kk}"] = {"tflops": tf, "ms": ms, "frac_of_measured_bf16": tf / peaks["bf16_tflops"]}
+        del a8, w8, s8
     w, sc, bias = config_dyn4_weights()
     packed = torch._dyn_quant_pack_4bit_weight(w.to("vk"), sc.to("vk"), bias.to("vk"), 32, 4096, 14336)
     for mm in ((128,) if quick else (128, 512, 2048)):

@@ -129,7 +129,9 @@ TVB_API int tvb_add_rowvec(int device, void* c, int c_dtype, int64_t c_sm, const
  * C[m, n] = A[m, k] @ (int8 B[n, k] * scales[n]).T, float32 accumulation, rounded once
  * to `dtype`. a_sm: A's row stride in elements (column stride 1). scales and C have A's
  * dtype; B and C are contiguous. variant: 0 automatic, 1 the plain CUDA-core kernel,
- * 2 the TMA-fed skinny kernel (m <= 64, 16-bit A, k % 128 == 0), 3 the tcgen05 kernel. */
+ * 2 the TMA-fed skinny kernel (m <= 64, 16-bit A, k % 128 == 0), 3 the tcgen05 kernel that widens the weights in
+ * its main loop, 4 the weights widened once into runtime-owned scratch (2 bytes per weight) and the 16-bit tcgen05
+ * GEMM over them (chosen from m = 1024 on). */
 TVB_API int tvb_qmm8(int device, const void* a, int dtype, int64_t a_sm, const int8_t* b, const void* scales, void* c,
              int64_t m, int64_t n, int64_t k, int variant);
 

@@ -69,6 +69,24 @@ def test_qmm8_tcgen05(abi, dtype, m, k, n):
         assert ((sliced.cpu().float() - want[::2].float()).abs() <= tol[::2]).all()
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("m,k,n", [(1024, 512, 768), (1500, 1040, 520), (17, 64, 8), (2048, 4096, 1000)])
+def test_qmm8_widened_gemm(abi, dtype, m, k, n):
+    # variant 4: the weights widened once into scratch, then the 16-bit tcgen05 GEMM with the scales in its epilogue;
+    # a second product with other weights must not see the first one's scratch
+    for seed in (m + n, m + n + 1):
+        a, b, s = C.config_int8(m, k, n, dtype, seed=seed)
+        want, tol = C.int8_want(a, b, s)
+        got = abi.qmm8(dev(a), dev(b), dev(s), variant=4)
+        abi.synchronize()
+        err = (got.cpu().float() - want.float()).abs()
+        assert (err <= tol).all(), f"max excess {(err - tol).max()}"
+    if m >= 1024:  # the automatic choice from 1024 rows on
+        auto = abi.qmm8(dev(a), dev(b), dev(s))
+        abi.synchronize()
+        assert torch.equal(auto.cpu(), got.cpu())
+
+
 def test_qmm8_skinny_is_deterministic_and_repeatable(abi):
     a, b, s = C.config_int8(16, 1024, 3000, torch.bfloat16)
     da, db, ds = dev(a), dev(b), dev(s)

@@ -39,6 +39,10 @@ namespace tvb {
 bool qmm8_tc_usable(const void* a, int dtype, int64_t a_sm, const int8_t* b, int64_t m, int64_t n, int64_t k);
 int qmm8_tc(int device, cudaStream_t stream, const void* a, int dtype, int64_t a_sm, const int8_t* b, const void* scales, void* c,
             int64_t m, int64_t n, int64_t k);
+// Very large m: the weights widened once into scratch, then the 16-bit tcgen05 GEMM (qmm8_tc.cu).
+bool qmm8_widen_gemm_usable(const void* a, int dtype, int64_t a_sm, const int8_t* b, int64_t m, int64_t n, int64_t k);
+int qmm8_widen_gemm(int device, cudaStream_t stream, const void* a, int dtype, int64_t a_sm, const int8_t* b, const void* scales,
+                    void* c, int64_t m, int64_t n, int64_t k);
 
 namespace {
 
@@ -870,9 +874,14 @@ extern "C" int tvb_qmm8(int device, const void* a, int dtype, int64_t a_sm, cons
   bool can_skinny = skinny_ok(a, dtype, a_sm, b, m, n, k);
   TVB_REQUIRE(variant != 2 || can_skinny,
               "tvb_qmm8: the skinny kernel needs 16-bit A, m <= 64, k a multiple of 128, 16-byte aligned rows");
-  TVB_REQUIRE(variant >= 0 && variant <= 3, "tvb_qmm8: unknown kernel variant");
+  TVB_REQUIRE(variant >= 0 && variant <= 4, "tvb_qmm8: unknown kernel variant");
   const bool can_tc = qmm8_tc_usable(a, dtype, a_sm, b, m, n, k);
   TVB_REQUIRE(variant != 3 || can_tc, "tvb_qmm8: the tcgen05 kernel needs 16-bit A, k a multiple of 16, 16-byte aligned rows");
+  const bool can_widen = qmm8_widen_gemm_usable(a, dtype, a_sm, b, m, n, k);
+  TVB_REQUIRE(variant != 4 || can_widen, "tvb_qmm8: the widened GEMM needs 16-bit A, k a multiple of 16, 16-byte aligned rows");
+  // the extra pass over the weights pays for itself from about 730 rows on (874 against 1237 TFLOP/s, 3 bytes per weight)
+  if (variant == 4 || (variant == 0 && can_widen && m >= 1024))
+    return qmm8_widen_gemm(device, stream, a, dtype, a_sm, b, scales, c, m, n, k);
   if (variant == 3 || (variant == 0 && can_tc && m > 16))
     return qmm8_tc(device, stream, a, dtype, m == 1 ? k : a_sm, b, scales, c, m, n, k);
   if (variant == 2 || (variant == 0 && can_skinny)) {

@@ -24,6 +24,7 @@
 #include "../core/tensormap.h"
 #include "numerics.cuh"
 #include "ptx.cuh"
+#include "scaled_mm.h"
 
 namespace tvb {
 namespace {
@@ -325,6 +326,76 @@ int qmm8_tc(int device, cudaStream_t stream, const void* a, int dtype, int64_t a
             int64_t m, int64_t n, int64_t k) {
   if (dtype == TVB_BF16) return launch_qmm8_tc<TVB_BF16>(device, stream, a, a_sm, b, scales, c, m, n, k);
   return launch_qmm8_tc<TVB_F16>(device, stream, a, a_sm, b, scales, c, m, n, k);
+}
+
+// ------------------------------------------------------------------ very large m: widen once, then the 16-bit GEMM
+//
+// From about a thousand rows of A on, widening the weights once into a scratch copy in A's dtype (n * k 16-bit values, a
+// pass over 3 bytes per weight) and running the plain 16-bit tcgen05 GEMM over it, with the scales in its epilogue, is
+// faster than widening inside the main loop (which the converter warps' ALU work bounds). The arithmetic is the same:
+// exact 16-bit weights, float32 accumulation, the finished sum times scales[n], one rounding.
+
+namespace {
+
+template <int DT>
+__global__ void qmm8_widen_kernel(const int8_t* __restrict__ b, uint16_t* __restrict__ wide, int64_t count16,
+                                  const void* __restrict__ scales, float* __restrict__ scales32, int n) {
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  const int64_t first = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  for (int64_t i = first; i < n; i += stride) scales32[i] = load_float<DT>(scales, i);
+  const uint4* src = reinterpret_cast<const uint4*>(b);
+  uint4* dst = reinterpret_cast<uint4*>(wide);
+  for (int64_t i = first; i < count16; i += stride) {  // 16 weights per step
+    const uint4 v = __ldcs(src + i);
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+    uint32_t o[8];
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+#pragma unroll
+      for (int h = 0; h < 2; h++) {
+        const float lo = static_cast<float>(static_cast<int8_t>(w[j] >> (16 * h)));
+        const float hi = static_cast<float>(static_cast<int8_t>(w[j] >> (16 * h + 8)));
+        o[2 * j + h] = DT == TVB_BF16 ? (static_cast<uint32_t>(f32_to_bf16_bits(lo)) | (static_cast<uint32_t>(f32_to_bf16_bits(hi)) << 16))
+                                      : (static_cast<uint32_t>(f32_to_f16_bits(lo)) | (static_cast<uint32_t>(f32_to_f16_bits(hi)) << 16));
+      }
+    }
+    dst[2 * i] = make_uint4(o[0], o[1], o[2], o[3]);
+    dst[2 * i + 1] = make_uint4(o[4], o[5], o[6], o[7]);
+  }
+}
+
+}  // namespace
+
+bool qmm8_widen_gemm_usable(const void* a, int dtype, int64_t a_sm, const int8_t* b, int64_t m, int64_t n, int64_t k) {
+  return qmm8_tc_usable(a, dtype, a_sm, b, m, n, k) && (n * k) % 16 == 0 && k % 8 == 0;
+}
+
+int qmm8_widen_gemm(int device, cudaStream_t stream, const void* a, int dtype, int64_t a_sm, const int8_t* b, const void* scales,
+                    void* c, int64_t m, int64_t n, int64_t k) {
+  const uint64_t wide_bytes = static_cast<uint64_t>(n) * k * 2;
+  const uint64_t scale_off = (wide_bytes + 255) & ~uint64_t(255);
+  void* ws = nullptr;
+  if (workspace(device, 1, scale_off + static_cast<uint64_t>(n) * 4, &ws) != 0) return -1;
+  uint16_t* wide = static_cast<uint16_t*>(ws);
+  float* scales32 = reinterpret_cast<float*>(static_cast<uint8_t*>(ws) + scale_off);
+  const int64_t count16 = n * k / 16;
+  const int grid = static_cast<int>(std::min<int64_t>(static_cast<int64_t>(sm_count(device)) * 16, ceil_div(count16, 256)));
+  if (dtype == TVB_BF16) qmm8_widen_kernel<TVB_BF16><<<grid, 256, 0, stream>>>(b, wide, count16, scales, scales32, static_cast<int>(n));
+  else qmm8_widen_kernel<TVB_F16><<<grid, 256, 0, stream>>>(b, wide, count16, scales, scales32, static_cast<int>(n));
+  if (launched("qmm8_widen", dim3(grid), dim3(256), 0, stream) != 0) return -1;
+  ScaledMmParams p{};
+  p.a = a;
+  p.b = wide;
+  p.scale_a = nullptr;      // (the epilogue multiplies by 1 for A ...)
+  p.scale_b = scales32;     // (... and by scales[n] for the columns)
+  p.rowwise = 1;
+  p.out = c;
+  p.m = m; p.n = n; p.k = k;
+  p.a_s0 = a_sm; p.a_s1 = 1;
+  p.b_s0 = 1; p.b_s1 = k;   // B[kk, j] = wide[j * k + kk]
+  p.a_dtype = dtype; p.b_dtype = dtype; p.out_dtype = dtype; p.bias_dtype = TVB_F32;
+  if (!scaled_mm_tc_usable(p)) return fail("tvb_qmm8: the widened GEMM needs 16-byte aligned rows");
+  return scaled_mm_tc(device, stream, p);
 }
 
 }  // namespace tvb
