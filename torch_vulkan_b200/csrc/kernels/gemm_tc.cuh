@@ -1,17 +1,20 @@
 // The tcgen05 GEMM main loop shared by the large-m kernels of this library:
 // D[m, n] = A[m, k] . B[n, k]^T with both operands K-major in global memory.
 //
-// One persistent CTA per SM walks 128 x BN output tiles. Warp roles:
-//   warp 4, one lane: TMA producer. Fills a ring of shared-memory stages, each holding a
-//            128-row slice of A and a BN-row slice of B, 128 bytes of k wide, written by
+// One persistent CTA per SM walks BM x BN output tiles, BM = 128 or 256. Warp roles (E = BM / 32 epilogue warps):
+//   warp E, one lane: TMA producer. Fills a ring of shared-memory stages, each holding a
+//            BM-row slice of A and a BN-row slice of B, 128 bytes of k wide, written by
 //            cp.async.bulk.tensor with the 128-byte swizzle (each CTA loads for itself only).
-//   warp 5, one lane: issues tcgen05.mma (four per stage, 32 bytes of k each) into one of two
-//            TMEM accumulator buffers (2 x BN columns of float32 / int32), and
+//   warp E+1, one lane: issues tcgen05.mma (per stage four steps of 32 bytes of k, each step one MMA per 128 rows
+//            of the tile) into TMEM accumulators (BN columns of float32 / int32 per 128 rows), and
 //            tcgen05.commit's each stage back to the producer and each finished tile to the
 //            epilogue. The warp also owns the TMEM allocation.
-//   warps 0-3: epilogue. Each warp reads its 32 TMEM lanes (one output row per thread)
-//            32 columns at a time with tcgen05.ld and hands them to the Epilogue policy,
-//            while the MMA warp already works on the next tile in the other buffer.
+//   warps 0..E-1: epilogue. Each warp reads its 32 TMEM lanes (one output row per thread)
+//            32 columns at a time with tcgen05.ld and hands them to the Epilogue policy.
+// BM = 128: two accumulator buffers, so the MMA warp already works on the next tile while a tile is read back.
+// BM = 256: both 128-row halves share every B stage, which cuts the operand bytes per MMA by a third: the ring then
+//            covers the latency of the copies (with 128 rows it does not, and the tensor pipe idles ~40 % of the time);
+//            the accumulators fill the whole tensor memory, so a tile's read-back is not overlapped.
 // All mbarrier waits are bounded (ptx::mbar_wait); a wait that runs out makes every role
 // leave its loop, the TMEM allocation is released, and the status word tells the host.
 #pragma once
@@ -33,13 +36,21 @@ struct GemmTcShape {
 // stages in the same shared memory) is supported by the code below and was measured 15 % slower on 8192^3 float8.
 constexpr int kGemmStageK = 128;
 
-template <int BN, int EPI_SMEM>
+template <int BN, int EPI_SMEM, int BM = 128>
 struct GemmTcCfg {
-  static constexpr int kBM = 128;
+  static_assert(BM == 128 || BM == 256, "tiles are 128 or 256 rows");
+  static constexpr int kBM = BM;
+  static constexpr int kHalves = BM / 128;        // MMAs per k step (one per 128 rows)
+  static constexpr int kEpiWarps = BM / 32;
   static constexpr int kStageA = kBM * kGemmStageK, kStageB = BN * kGemmStageK, kStage = kStageA + kStageB;
-  static constexpr int kStages = (200 * 1024 - EPI_SMEM) / kStage < 8 ? (200 * 1024 - EPI_SMEM) / kStage : 8;
-  static constexpr int kThreads = 192;
-  static constexpr int kTmemCols = 2 * BN <= 32 ? 32 : (2 * BN <= 64 ? 64 : (2 * BN <= 128 ? 128 : (2 * BN <= 256 ? 256 : 512)));
+  static constexpr int kBudget = (BM == 128 ? 200 : 224) * 1024 - EPI_SMEM;
+  static constexpr int kStages = kBudget / kStage < 8 ? kBudget / kStage : 8;
+  static constexpr int kThreads = (kEpiWarps + 2) * 32;
+  static constexpr int kAccCols = kHalves * BN;   // TMEM columns of one tile's accumulators
+  static constexpr int kAccBufs = 2 * kAccCols <= 512 ? 2 : 1;
+  static constexpr int kWant = kAccBufs * kAccCols;
+  static constexpr int kTmemCols = kWant <= 32 ? 32 : (kWant <= 64 ? 64 : (kWant <= 128 ? 128 : (kWant <= 256 ? 256 : 512)));
+  static_assert(kWant <= 512, "the accumulators do not fit the tensor memory");
   static constexpr int kBarBytes = 256;
   static constexpr int kSmemBytes = kStages * kStage + 1024 + kBarBytes + EPI_SMEM;
 };
@@ -52,11 +63,12 @@ struct GemmTcCfg {
 //   __device__ static void store(const Params&, const uint8_t* smem, int row, int col_tile0, int col_off,
 //                                const uint32_t (&acc)[32], int m, int n);
 //       thread `row`'s 32 accumulators for columns col_tile0 + col_off ... + 31
-template <int KIND, int BN, class Epi>
-__global__ void __launch_bounds__(192, 1)
+template <int KIND, int BN, class Epi, int BM = 128>
+__global__ void __launch_bounds__((BM / 32 + 2) * 32, 1)
     gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmTcShape sh,
                    const uint32_t idesc, const typename Epi::Params ep, int* status) {
-  using Cfg = GemmTcCfg<BN, Epi::kSmemBytes>;
+  using Cfg = GemmTcCfg<BN, Epi::kSmemBytes, BM>;
+  constexpr int kProducerWarp = Cfg::kEpiWarps, kMmaWarp = Cfg::kEpiWarps + 1;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* base_ptr = smem_raw + (base - ptx::smem_u32(smem_raw));
@@ -77,19 +89,19 @@ __global__ void __launch_bounds__(192, 1)
     }
     for (int a = 0; a < 2; a++) {
       ptx::mbar_init(tfull0 + 8 * a, 1);
-      ptx::mbar_init(tempty0 + 8 * a, 128);
+      ptx::mbar_init(tempty0 + 8 * a, Cfg::kEpiWarps * 32);
     }
     *abort_flag = 0;
     ptx::fence_mbar_init();
   }
-  if (warp == 5) ptx::tmem_alloc(ptx::smem_u32(tmem_slot), Cfg::kTmemCols);
+  if (warp == kMmaWarp) ptx::tmem_alloc(ptx::smem_u32(tmem_slot), Cfg::kTmemCols);
   ptx::tc_fence_before();
   __syncthreads();
   ptx::tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   const int tiles = sh.tiles_m * sh.tiles_n;
 
-  if (warp == 4) {
+  if (warp == kProducerWarp) {
     if (lane == 0) {
       ptx::prefetch_tensormap(&map_a);
       ptx::prefetch_tensormap(&map_b);
@@ -116,18 +128,18 @@ __global__ void __launch_bounds__(192, 1)
       }
     }
     __syncwarp();
-  } else if (warp == 5) {
+  } else if (warp == kMmaWarp) {
     if (lane == 0) {
       long long it = 0;
       int titer = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, titer++) {
-        const int acc = titer & 1;
-        const uint32_t aph = static_cast<uint32_t>((titer >> 1) & 1);
+        const int acc = titer % Cfg::kAccBufs;
+        const uint32_t aph = static_cast<uint32_t>((titer / Cfg::kAccBufs) & 1);
         ok = ptx::mbar_wait(tempty0 + 8 * acc, aph ^ 1u, abort_flag);  // the epilogue has drained this buffer
         if (!ok) break;
         ptx::tc_fence_after();
-        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * Cfg::kAccCols);
         for (int kb = 0; kb < sh.kblocks; kb++, it++) {
           const int s = static_cast<int>(it % Cfg::kStages);
           const uint32_t ph = static_cast<uint32_t>((it / Cfg::kStages) & 1);
@@ -139,7 +151,10 @@ __global__ void __launch_bounds__(192, 1)
                                                     : ptx::tc_smem_desc_sw128(base + s * Cfg::kStage + Cfg::kStageA);
 #pragma unroll
           for (int j = 0; j < kGemmStageK / 32; j++)  // 32 bytes of k per instruction: +2 in the descriptor's 16-byte units
-            ptx::tc_mma<KIND>(d_tmem, a_desc + 2 * j, b_desc + 2 * j, idesc, (kb | j) != 0 ? 1u : 0u);
+#pragma unroll
+            for (int h = 0; h < Cfg::kHalves; h++)  // rows 128 h ... of the tile: 128 * 128 bytes further into the A stage
+              ptx::tc_mma<KIND>(d_tmem + h * BN, a_desc + (h * 128 * kGemmStageK >> 4) + 2 * j, b_desc + 2 * j, idesc,
+                                (kb | j) != 0 ? 1u : 0u);
           ptx::tc_commit(empty0 + 8 * s);
         }
         if (ok) ptx::tc_commit(tfull0 + 8 * acc);
@@ -151,14 +166,17 @@ __global__ void __launch_bounds__(192, 1)
     bool ok = true;
     for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, titer++) {
       const int tm = tile % sh.tiles_m, tn = tile / sh.tiles_m;
-      const int acc = titer & 1;
-      const uint32_t aph = static_cast<uint32_t>((titer >> 1) & 1);
+      const int acc = titer % Cfg::kAccBufs;
+      const uint32_t aph = static_cast<uint32_t>((titer / Cfg::kAccBufs) & 1);
       Epi::begin_tile(ep, epi_smem, tm * Cfg::kBM, tn * BN, sh.m, sh.n, threadIdx.x);
       ok = ptx::mbar_wait(tfull0 + 8 * acc, aph, abort_flag);
       if (!ok) break;
       ptx::tc_fence_after();
+      // warp w reads TMEM lanes 32 (w % 4) ...; warps 4-7 (256-row tiles) the second half's accumulators, BN columns on
+      const int half = warp >> 2;
       const int row = tm * Cfg::kBM + warp * 32 + lane;
-      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + static_cast<uint32_t>(acc * BN);
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16) +
+                             static_cast<uint32_t>(acc * Cfg::kAccCols + half * BN);
 #pragma unroll 1
       for (int c = 0; c < BN / 32; c++) {
         uint32_t r[32];
@@ -173,7 +191,7 @@ __global__ void __launch_bounds__(192, 1)
   ptx::tc_fence_before();
   __syncthreads();
   if (threadIdx.x == 0 && *abort_flag != 0) atomicExch(status, 2);
-  if (warp == 5) {
+  if (warp == kMmaWarp) {
     ptx::tc_fence_after();
     ptx::tmem_dealloc(tmem_base, Cfg::kTmemCols);
   }

@@ -8,6 +8,8 @@
 // a cast, seven dispatches in all. Float8 products are exact in float32, so
 // (sum a*b) * scale_a[i] * scale_b[j] differs from sum (a*scale_a)(b*scale_b) only by
 // float32 roundings, inside the bound the reference's test uses (tests/python/test_quant.py:124-128).
+#include <cstdlib>
+
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
@@ -22,7 +24,8 @@ namespace {
 
 constexpr int kBN = 256;
 
-struct ScaledEpilogue {
+template <int WARPS>
+struct ScaledEpilogueT {
   struct Params {
     const float* scale_a;
     const float* scale_b;
@@ -31,7 +34,7 @@ struct ScaledEpilogue {
     void* out;
     int bias_dtype, out_dtype, rowwise, vector_ok;
   };
-  static constexpr int kSmemBytes = 4 * kBN * 2 * 4;  // per epilogue warp: column scales and biases of the tile
+  static constexpr int kSmemBytes = WARPS * kBN * 2 * 4;  // per epilogue warp: column scales and biases of the tile
 
   __device__ static void begin_tile(const Params& p, uint8_t* smem, int row0, int col0, int m, int n, int tid) {
     const int warp = tid >> 5, lane = tid & 31;
@@ -54,7 +57,7 @@ struct ScaledEpilogue {
   __device__ static void store(const Params& p, const uint8_t* smem, int row, int col_tile0, int col_off,
                                const uint32_t (&acc)[32], int m, int n) {
     if (row >= m) return;
-    const int warp = (threadIdx.x >> 5) & 3;
+    const int warp = (threadIdx.x >> 5) % WARPS;
     const float* cs = reinterpret_cast<const float*>(smem) + warp * 2 * kBN + col_off;
     const float* cb = cs + kBN;
     const float sa = p.scale_a == nullptr ? 1.0f : (p.rowwise ? p.scale_a[row] : p.scale_a[0]);
@@ -106,10 +109,11 @@ bool scaled_mm_tc_usable(const ScaledMmParams& p) {
          p.k < (int64_t(1) << 30);
 }
 
-template <int KIND>
-int scaled_mm_tc_kind(int device, cudaStream_t stream, const ScaledMmParams& p) {
-  using Cfg = GemmTcCfg<kBN, ScaledEpilogue::kSmemBytes>;
-  auto kernel = gemm_tc_kernel<KIND, kBN, ScaledEpilogue>;
+template <int KIND, int BM>
+int scaled_mm_tc_tile(int device, cudaStream_t stream, const ScaledMmParams& p) {
+  using ScaledEpilogue = ScaledEpilogueT<BM / 32>;
+  using Cfg = GemmTcCfg<kBN, ScaledEpilogue::kSmemBytes, BM>;
+  auto kernel = gemm_tc_kernel<KIND, kBN, ScaledEpilogue, BM>;
   static bool configured[64] = {};
   if (!configured[device & 63]) {
     TVB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
@@ -130,7 +134,7 @@ int scaled_mm_tc_kind(int device, cudaStream_t stream, const ScaledMmParams& p) 
   sh.k_elems_per_block = k_per_stage;
   sh.tiles_m = static_cast<int>(ceil_div(p.m, Cfg::kBM));
   sh.tiles_n = static_cast<int>(ceil_div(p.n, kBN));
-  ScaledEpilogue::Params ep{};
+  typename ScaledEpilogue::Params ep{};
   ep.scale_a = p.scale_a;
   ep.scale_b = p.scale_b;
   ep.bias = p.bias;
@@ -143,12 +147,31 @@ int scaled_mm_tc_kind(int device, cudaStream_t stream, const ScaledMmParams& p) 
   // operand formats: kind::f8f6f4 0 = e4m3, 1 = e5m2; kind::f16 0 = float16, 1 = bfloat16; float32 accumulators
   const uint32_t fa = KIND == 0 ? (p.a_dtype == TVB_E4M3 ? 0 : 1) : (p.a_dtype == TVB_F16 ? 0 : 1);
   const uint32_t fb = KIND == 0 ? (p.b_dtype == TVB_E4M3 ? 0 : 1) : (p.b_dtype == TVB_F16 ? 0 : 1);
-  const uint32_t idesc = ptx::tc_instr_desc(1, fa, fb, Cfg::kBM, kBN);
+  const uint32_t idesc = ptx::tc_instr_desc(1, fa, fb, 128, kBN);  // (every MMA covers 128 rows of the tile)
   int* status = nullptr;
   if (status_word(device, &status) != 0) return -1;
   const int grid = static_cast<int>(std::min<int64_t>(sm_count(device), static_cast<int64_t>(sh.tiles_m) * sh.tiles_n));
   kernel<<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(map_a, map_b, sh, idesc, ep, status);
   return launched(KIND == 0 ? "scaled_mm_tc" : "mm_tc", dim3(grid), dim3(Cfg::kThreads), Cfg::kSmemBytes, stream);
+}
+
+// 256-row tiles keep the tensor pipe fed, but their read-back is not overlapped and there are half as many of them.
+// Measured against 128-row tiles (8192 x 8192 outputs): +14 % from 16 KB of k per row on, +6 % at 8 KB, -8 % at 2 KB. They
+// are taken when k is long enough and the tiles still fill the SMs as evenly.
+template <int KIND>
+int scaled_mm_tc_kind(int device, cudaStream_t stream, const ScaledMmParams& p) {
+  static const int forced = [] { const char* v = std::getenv("TVB200_GEMM_BM"); return v != nullptr ? std::atoi(v) : 0; }();
+  const int64_t sms = sm_count(device);
+  const int64_t k_bytes = p.k * static_cast<int64_t>(dtype_size(p.a_dtype));
+  const double gain = k_bytes >= 16384 ? 1.14 : (k_bytes >= 8192 ? 1.05 : 0.9);
+  auto waves_cost = [&](int64_t bm) {  // time in units of one wave of 128-row tiles
+    const int64_t tiles = ceil_div(p.m, bm) * ceil_div(p.n, kBN);
+    return static_cast<double>(ceil_div(tiles, sms)) * (bm == 256 ? 2.0 / gain : 1.0);
+  };
+  bool big = p.m > 128 && waves_cost(256) < waves_cost(128);
+  if (forced == 128) big = false;
+  if (forced == 256) big = true;
+  return big ? scaled_mm_tc_tile<KIND, 256>(device, stream, p) : scaled_mm_tc_tile<KIND, 128>(device, stream, p);
 }
 
 int scaled_mm_tc(int device, cudaStream_t stream, const ScaledMmParams& p) {
