@@ -301,8 +301,8 @@ def int8_stack(tv, stream, layers=32):
 
 def run_only(tv, stream, which, iters):
     """One large-m configuration, `iters` launches after one warm-up (small enough to sit under a profiler)."""
-    if which == "fp8":
-        m = n = k = 4096
+    if which in ("fp8", "fp8_big"):
+        m = n = k = 4096 if which == "fp8" else 8192
         a, b, sa, sb = config_fp8(m, k, n, True)
         av, bv, sav, sbv = a.to("vk"), b.t().to("vk").t(), sa.to("vk"), sb.to("vk")
         fn = lambda: torch._scaled_mm(av, bv, sav, sbv, out_dtype=torch.bfloat16)  # noqa: E731
@@ -347,7 +347,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extra", action="store_true", help="skip the large-m configurations")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline")
-    ap.add_argument("--only", default=None, choices=["fp8", "dyn4", "int8_large_m", "int8_stack", "bf16_mm"],
+    ap.add_argument("--only", default=None, choices=["fp8", "fp8_big", "dyn4", "int8_large_m", "int8_stack", "bf16_mm"],
                     help="run one large-m configuration a few times and exit (for profilers); prints its own JSON line")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)

@@ -55,6 +55,19 @@ struct GemmTcCfg {
   static constexpr int kSmemBytes = kStages * kStage + 1024 + kBarBytes + EPI_SMEM;
 };
 
+// Tile order: bands of `band` tile rows, walked column by column, so that the ~148 tiles in flight at any time cover a
+// near-square patch of the output and share operand panels in L2 (band * BM rows of A against 148 / band * BN rows of B;
+// the two are about equal for band = 16 with 128 x 256 tiles and 12 with 256 x 256 tiles).
+__device__ __forceinline__ void gemm_tile_coords(int tile, int tiles_m, int tiles_n, int band, int& tm, int& tn) {
+  const int per_band = band * tiles_n;
+  const int b = tile / per_band;
+  const int first = b * band;
+  const int rows = tiles_m - first < band ? tiles_m - first : band;
+  const int r = tile - b * per_band;
+  tm = first + r % rows;
+  tn = r / rows;
+}
+
 // Epilogue policy interface:
 //   struct Params;                       kernel parameters of the epilogue
 //   static constexpr int kSmemBytes;     per-CTA shared memory of the epilogue
@@ -108,7 +121,8 @@ __global__ void __launch_bounds__((BM / 32 + 2) * 32, 1)
       long long it = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
-        const int tm = tile % sh.tiles_m, tn = tile / sh.tiles_m;
+        int tm, tn;
+        gemm_tile_coords(tile, sh.tiles_m, sh.tiles_n, BM == 128 ? 16 : 12, tm, tn);
         for (int kb = 0; kb < sh.kblocks; kb++, it++) {
           const int s = static_cast<int>(it % Cfg::kStages);
           const uint32_t ph = static_cast<uint32_t>((it / Cfg::kStages) & 1);
@@ -165,7 +179,8 @@ __global__ void __launch_bounds__((BM / 32 + 2) * 32, 1)
     int titer = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, titer++) {
-      const int tm = tile % sh.tiles_m, tn = tile / sh.tiles_m;
+      int tm, tn;
+      gemm_tile_coords(tile, sh.tiles_m, sh.tiles_n, BM == 128 ? 16 : 12, tm, tn);
       const int acc = titer % Cfg::kAccBufs;
       const uint32_t aph = static_cast<uint32_t>((titer / Cfg::kAccBufs) & 1);
       Epi::begin_tile(ep, epi_smem, tm * Cfg::kBM, tn * BN, sh.m, sh.n, threadIdx.x);
