@@ -245,6 +245,20 @@ def extra_configs(tv, stream, peaks, quick):
             os.environ.pop("TORCH_VK_QMM4", None)
             tops = 2.0 * mm * 14336 * 4096 / ms / 1e9
             out[f"dyn_int4_m{mm}_{mode}"] = {"tops": tops, "ms": ms, "frac_of_2x_measured_bf16": tops / (2 * peaks["bf16_tflops"])}
+    # dyn-int4 decoding (at most 16 rows): twelve products replayed as one graph, against the bytes of the real int4 data
+    # (29.36 MB of nibbles + 3.67 MB of block scales + bias, activations and outputs)
+    from torch_vulkan_b200 import shard
+
+    packs = [packed] + [torch._dyn_quant_pack_4bit_weight(torch.roll(w, i, 0).to("vk"), sc.to("vk"), bias.to("vk"), 32, 4096, 14336)
+                        for i in (1, 2, 3)]  # four weight sets in turn: 147 MB in their decode form, more than the L2 holds
+    for mm in (1, 16):
+        xv = torch.randn(mm, 4096, generator=gen(12)).to("vk")
+        graph = shard.StepGraph(lambda: [torch._dyn_quant_matmul_4bit(xv, packs[i % 4], 32, 4096, 14336) for i in range(12)])
+        ms = timed(graph.replay, 5) / 12
+        nbytes = 14336 * 4096 // 2 + 14336 * 128 * 2 + 14336 * 4 + mm * 4096 * 4 + mm * 14336 * 4
+        out[f"dyn_int4_decode_m{mm}"] = {"us": ms * 1e3, "weight_gbs": nbytes / ms / 1e6, "frac_of_measured_hbm": nbytes / ms / 1e6 / peaks["hbm_gbs"]}
+        del graph
+    del packs
     tv.empty_cache()
     if not quick:
         out.update(int8_stack(tv, stream))
@@ -313,6 +327,22 @@ def run_only(tv, stream, which, iters):
         w16 = torch.randn(n, k, generator=gen(22)).to(torch.bfloat16).to("vk")
         fn = lambda: torch.mm(a16, w16.t())  # noqa: E731
         flops = 2.0 * m * n * k
+    elif which == "dyn4_decode":
+        # four weight sets in turn (147 MB of int4 data and scales in their decode form, more than the L2 holds)
+        mm = 16
+        w, sc, bias = config_dyn4_weights()
+        packs = [torch._dyn_quant_pack_4bit_weight(torch.roll(w, i, 0).to("vk"), sc.to("vk"), bias.to("vk"), 32, 4096, 14336)
+                 for i in range(4)]
+        xv = torch.randn(mm, 4096, generator=gen(11)).to("vk")
+        state = {"i": 0}
+
+        def fn():
+            state["i"] += 1
+            return torch._dyn_quant_matmul_4bit(xv, packs[state["i"] % 4], 32, 4096, 14336)
+
+        for _ in range(4):
+            fn()
+        flops = 2.0 * mm * 14336 * 4096
     elif which == "dyn4":
         mm = 512
         w, sc, bias = config_dyn4_weights()
@@ -347,7 +377,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extra", action="store_true", help="skip the large-m configurations")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline")
-    ap.add_argument("--only", default=None, choices=["fp8", "fp8_big", "dyn4", "int8_large_m", "int8_stack", "bf16_mm"],
+    ap.add_argument("--only", default=None, choices=["fp8", "fp8_big", "dyn4", "dyn4_decode", "int8_large_m", "int8_stack", "bf16_mm"],
                     help="run one large-m configuration a few times and exit (for profilers); prints its own JSON line")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)

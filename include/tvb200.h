@@ -222,6 +222,19 @@ TVB_API uint64_t tvb_qmm4_fast_workspace_bytes(int64_t m, int64_t k);
 TVB_API int tvb_qmm4_fast(int device, const void* inp, int dtype, const float* packed, int has_bias, const void* prepared,
                           void* out, int64_t m, int64_t n, int64_t k, int64_t bs, void* workspace, uint64_t workspace_bytes);
 
+/* ---- aten::_dyn_quant_matmul_4bit for at most 16 rows (decoding): the int4 weights streamed from HBM once, bit for bit
+ *      the same results as tvb_qmm4 (replaces the two dispatches of crates/pyvk/csrc/quant.cpp:187-202 for small m) ----
+ * tvb_qmm4_decode_usable: 1 when the kernel takes the shape (m <= 16, n % 8 == 0, k % 256 == 0, k <= 4096, bs % 32 == 0,
+ * (k / 8) % bs == 0). tvb_qmm4_decode_prepare re-tiles the packed vector's weights and scales once per packed tensor
+ * (0.5 byte per weight + 4 bytes per block scale; 16-byte aligned buffer of tvb_qmm4_decode_prepared_bytes). */
+TVB_API int tvb_qmm4_decode_usable(int64_t m, int64_t n, int64_t k, int64_t bs);
+TVB_API uint64_t tvb_qmm4_decode_prepared_bytes(int64_t n, int64_t k, int64_t bs);
+TVB_API int tvb_qmm4_decode_prepare(int device, const float* packed, int64_t n, int64_t k, int64_t bs, void* prepared,
+                            uint64_t prepared_bytes);
+TVB_API uint64_t tvb_qmm4_decode_workspace_bytes(int64_t m, int64_t k);
+TVB_API int tvb_qmm4_decode(int device, const void* inp, int dtype, const float* packed, int has_bias, const void* prepared,
+                    void* out, int64_t m, int64_t n, int64_t k, int64_t bs, void* workspace, uint64_t workspace_bytes);
+
 /* ---- aten::_scaled_mm (replaces the chain of cast / mul / matmul / add / cast
  *      dispatches, quant.cpp:283-299) ----
  * out[m, n] = cast((a * scale_a) @ (b * scale_b) + bias) (float8 outputs: times

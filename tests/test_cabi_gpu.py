@@ -264,6 +264,40 @@ def test_qmm4_tensor_core_path_wide_scales(abi):
     assert torch.equal(got.cpu(), want)
 
 
+# ---------------------------------------------------------------- dyn-int4, the decode kernel (at most 16 rows, bit-exact)
+
+@pytest.mark.parametrize("m", [1, 3, 8, 9, 16])
+@pytest.mark.parametrize("k,n,bs,bias", [(512, 8, 32, True), (512, 40, 32, False), (1024, 264, 128, True), (2048, 96, 64, False),
+                                          (4096, 1000, 32, True), (4096, 512, 512, True), (512, 2400, 64, True),
+                                          (8192, 48, 256, True), (1536, 20000, 32, False)])
+def test_qmm4_decode_bit_exact(abi, m, k, n, bs, bias):
+    assert abi.lib().tvb_qmm4_decode_usable(m, n, k, bs) == 1
+    x, w, sc, bvec = C.dyn4_case(m, k, n, bs, bias, torch.float32)
+    packed_cpu = O.dyn_quant_pack_4bit_weight(w, sc, bvec, bs, k, n)
+    want = O.dyn_quant_matmul_4bit(x, packed_cpu, bs, k, n)
+    packed = dev(packed_cpu)
+    prepared = abi.qmm4_decode_prepare(packed, n, k, bs)
+    got = abi.qmm4_decode(dev(x), packed, prepared, bs, k, n)
+    again = abi.qmm4_decode(dev(x), packed, prepared, bs, k, n)
+    abi.synchronize()
+    assert torch.equal(got.cpu().view(torch.int32), want.view(torch.int32))
+    assert torch.equal(again.cpu().view(torch.int32), want.view(torch.int32))
+
+
+def test_qmm4_decode_full_size_and_limits(abi):
+    # the benchmark's weights at m = 16 against the tensor-core kernel (itself checked against the oracle)
+    m, k, n, bs = 16, 4096, 14336, 32
+    x, w, sc, bvec = C.dyn4_case(m, k, n, bs, True, torch.float32)
+    packed = abi.qmm4_pack(dev(w), dev(sc), dev(bvec))
+    want = abi.qmm4_tc(dev(x), packed, abi.qmm4_prepare(packed, n, k, bs), bs, k, n)
+    got = abi.qmm4_decode(dev(x), packed, abi.qmm4_decode_prepare(packed, n, k, bs), bs, k, n)
+    abi.synchronize()
+    assert torch.equal(got.cpu(), want.cpu())
+    lib = abi.lib()
+    for shape in ((17, 64, 512, 32), (4, 60, 512, 32), (4, 64, 16384, 32), (4, 64, 4096, 4096), (4, 64, 768, 32), (4, 64, 1024, 96)):
+        assert lib.tvb_qmm4_decode_usable(*shape) == 0, shape  # m > 16, n % 8, k too long, one block per row, k % 512, 512 % bs
+
+
 # ---------------------------------------------------------------- dyn-int4, the opt-in fast route (not bit-exact)
 
 @pytest.mark.parametrize("m,k,n,bs,bias", [(32, 128, 11008, 32, True), (130, 512, 300, 32, True), (257, 1024, 129, 128, False),

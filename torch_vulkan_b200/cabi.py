@@ -68,6 +68,11 @@ SIGNATURES = {
     "tvb_qmm4_prepared_bytes": (_u64, [_i64, _i64]),
     "tvb_qmm4_prepare": (_i, [_i, _vp, _i64, _i64, _i64, _vp, _u64]),
     "tvb_qmm4_tc_workspace_bytes": (_u64, [_i64, _i64]),
+    "tvb_qmm4_decode_usable": (_i, [_i64, _i64, _i64, _i64]),
+    "tvb_qmm4_decode_prepared_bytes": (_u64, [_i64, _i64, _i64]),
+    "tvb_qmm4_decode_prepare": (_i, [_i, _vp, _i64, _i64, _i64, _vp, _u64]),
+    "tvb_qmm4_decode_workspace_bytes": (_u64, [_i64, _i64]),
+    "tvb_qmm4_decode": (_i, [_i, _vp, _i, _vp, _i, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _u64]),
     "tvb_qmm4_tc": (_i, [_i, _vp, _i, _vp, _i, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _u64]),
     "tvb_qmm4_fast_prepared_bytes": (_u64, [_i64, _i64]),
     "tvb_qmm4_fast_prepare": (_i, [_i, _vp, _i64, _i64, _i64, _vp, _u64, _c.POINTER(_i)]),
@@ -210,6 +215,28 @@ def qmm4_tc(x, packed, prepared, bs, k, n):
     ws = torch.empty(max(nbytes, 1), dtype=torch.uint8, device=x.device)
     check(lib().tvb_qmm4_tc(_dev(x), _ptr(x), _dtype_code(x.dtype), _ptr(packed), has_bias, _ptr(prepared), _ptr(out), m, n, k,
                             bs, _ptr(ws), nbytes))
+    return out
+
+
+def qmm4_decode_prepare(packed, n, k, bs):
+    import torch
+
+    nbytes = lib().tvb_qmm4_decode_prepared_bytes(n, k, bs)
+    prepared = torch.empty(nbytes, dtype=torch.uint8, device=packed.device)
+    check(lib().tvb_qmm4_decode_prepare(_dev(packed), _ptr(packed), n, k, bs, _ptr(prepared), nbytes))
+    return prepared
+
+
+def qmm4_decode(x, packed, prepared, bs, k, n):
+    import torch
+
+    m = x.shape[0]
+    has_bias = 1 if packed.numel() - (n * k // 2 + n * (k // bs)) else 0
+    out = torch.empty((m, n), dtype=x.dtype, device=x.device)
+    nbytes = lib().tvb_qmm4_decode_workspace_bytes(m, k)
+    ws = torch.empty(max(nbytes, 1), dtype=torch.uint8, device=x.device)
+    check(lib().tvb_qmm4_decode(_dev(x), _ptr(x), _dtype_code(x.dtype), _ptr(packed), has_bias, _ptr(prepared), _ptr(out), m, n,
+                                k, bs, _ptr(ws), nbytes))
     return out
 
 

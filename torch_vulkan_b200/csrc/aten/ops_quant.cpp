@@ -96,7 +96,8 @@ struct PreparedWeights {
   const void* data;
   int64_t numel, n, k, bs;
   uint32_t version;
-  int kind;       // 0: int8 weights for the exact tensor-core kernel; 1: float16 weight * scale for the fast route
+  int kind;       // 0: int8 weights for the exact tensor-core kernel; 1: float16 weight * scale for the fast route;
+                  // 2: nibbles and scales tiled for the decode kernel
   int inexact;    // kind 1: some weight * scale product is not exact in float16 (the fast route must not be used)
   at::Tensor prepared;
 };
@@ -123,11 +124,14 @@ at::Tensor prepared_weights(const at::Tensor& packed, int dev, int64_t n, int64_
     }
     ++it;
   }
-  const uint64_t bytes = kind == 0 ? tvb_qmm4_prepared_bytes(n, k) : tvb_qmm4_fast_prepared_bytes(n, k);
+  const uint64_t bytes = kind == 0 ? tvb_qmm4_prepared_bytes(n, k)
+                                   : (kind == 1 ? tvb_qmm4_fast_prepared_bytes(n, k) : tvb_qmm4_decode_prepared_bytes(n, k, bs));
   at::Tensor prepared = at::empty({static_cast<int64_t>(bytes)}, packed.options().dtype(at::kByte));
   int flag = 0;
   if (kind == 0)
     check(tvb_qmm4_prepare(dev, static_cast<const float*>(gpu_address(packed)), n, k, bs, gpu_address_out(prepared), bytes));
+  else if (kind == 2)
+    check(tvb_qmm4_decode_prepare(dev, static_cast<const float*>(gpu_address(packed)), n, k, bs, gpu_address_out(prepared), bytes));
   else
     check(tvb_qmm4_fast_prepare(dev, static_cast<const float*>(gpu_address(packed)), n, k, bs, gpu_address_out(prepared), bytes, &flag));
   if (inexact != nullptr) *inexact = flag;
@@ -159,7 +163,8 @@ at::Tensor dyn_quant_matmul_4bit(const at::Tensor& inp, const at::Tensor& packed
   at::Tensor packed = packed_weights.to(at::kFloat).contiguous();
   const int dev = enter_device(inp);
   // Both kernels are bit for bit the CPU's arithmetic; the tensor-core one takes every shape it can (k and the
-  // block size multiples of 32), the CUDA-core one the rest. TORCH_VK_QMM4=plain forces the latter (as the
+  // block size multiples of 32), the CUDA-core one the rest, and up to 16 rows go to the decode kernel where it takes
+  // the shape. TORCH_VK_QMM4=plain forces the CUDA-core kernel, =tc keeps small m on the tensor-core kernel (as the
   // reference's TORCH_VK_GEMM switches kernels for its tests).
   // TORCH_VK_QMM4=fast opts into the float16 GEMM route: not bit for bit (float32 accumulation over the whole of k
   // instead of per block), within rtol 1e-5 of the exact routes. It applies when every weight * scale is exact in
@@ -167,7 +172,8 @@ at::Tensor dyn_quant_matmul_4bit(const at::Tensor& inp, const at::Tensor& packed
   const char* mode_env = std::getenv("TORCH_VK_QMM4");
   const std::string mode = mode_env != nullptr ? mode_env : "";
   const bool force_plain = mode == "plain";
-  if (mode == "fast" && K % 8 == 0 && packed.is_same(packed_weights)) {
+  const bool decode = !force_plain && mode != "tc" && tvb_qmm4_decode_usable(M, N, K, block_size) != 0 && packed.is_same(packed_weights);
+  if (mode == "fast" && !decode && K % 8 == 0 && packed.is_same(packed_weights)) {
     int inexact = 0;
     at::Tensor prepared = prepared_weights(packed_weights, dev, N, K, block_size, 1, &inexact);
     if (inexact == 0) {
@@ -178,6 +184,16 @@ at::Tensor dyn_quant_matmul_4bit(const at::Tensor& inp, const at::Tensor& packed
                           gpu_address_out(fws), fbytes));
       return out;
     }
+  }
+  if (decode) {
+    // decoding (at most 16 rows): the int4 weights, re-tiled once per packed tensor, streamed from HBM once
+    at::Tensor prepared = prepared_weights(packed_weights, dev, N, K, block_size, 2, nullptr);
+    const uint64_t dbytes = tvb_qmm4_decode_workspace_bytes(M, K);
+    at::Tensor dws = at::empty({static_cast<int64_t>(dbytes)}, inp.options().dtype(at::kByte));
+    check(tvb_qmm4_decode(dev, gpu_address(x), dtype_code(x.scalar_type()), static_cast<const float*>(gpu_address(packed)),
+                          bias_elements != 0 ? 1 : 0, gpu_address(prepared), gpu_address_out(out), M, N, K, block_size,
+                          gpu_address_out(dws), dbytes));
+    return out;
   }
   if (!force_plain && K % 32 == 0 && block_size % 32 == 0) {
     // the cache keys on the caller's tensor when it is already the float32 vector (the usual case)

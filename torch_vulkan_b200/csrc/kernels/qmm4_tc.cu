@@ -65,6 +65,7 @@ __global__ void __launch_bounds__(256) qmm4_quantize_tc_kernel(const void* __res
   __shared__ float red_min[8], red_max[8];
   __shared__ float row_scale;
   __shared__ int row_zp;
+  ptx::grid_launch_dependents();  // (a kernel launched with programmatic serialization may start its own prologue now)
   const int64_t base = static_cast<int64_t>(blockIdx.x) * k;
   const int64_t qbase = static_cast<int64_t>(blockIdx.x) * (k + kExtraCols);
   const int t = threadIdx.x;
@@ -368,6 +369,21 @@ __global__ void __launch_bounds__(kThreads, 1)
 uint64_t align256(uint64_t x) { return (x + 255) & ~uint64_t(255); }
 
 }  // namespace
+}  // namespace tvb
+
+namespace tvb {
+
+// PHASE 0 in the tensor-core layout, for the other kernels that read it (qmm4_decode.cu).
+int qmm4_quantize_rows(cudaStream_t stream, const void* inp, int dtype, int64_t m, int64_t k, int groupwise, int8_t* q, float* recip,
+                       int32_t* neg_zp) {
+  dim3 qgrid(static_cast<unsigned>(m));
+  if (dtype == TVB_F32)
+    qmm4_quantize_tc_kernel<TVB_F32><<<qgrid, 256, 0, stream>>>(inp, static_cast<int>(k), groupwise, q, recip, neg_zp);
+  else
+    qmm4_quantize_tc_kernel<TVB_BF16><<<qgrid, 256, 0, stream>>>(inp, static_cast<int>(k), groupwise, q, recip, neg_zp);
+  return launched("qmm4_quantize_tc", qgrid, dim3(256), 0, stream);
+}
+
 }  // namespace tvb
 
 using namespace tvb;
