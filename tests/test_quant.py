@@ -147,6 +147,20 @@ def test_scaled_mm_errors():
         torch._scaled_mm(a, b, one, one, bias=torch.ones(5, device="vk"), out_dtype=torch.float32)
 
 
+@pytest.mark.parametrize("m", [1, 7, 16, 17, 32, 33])
+def test_dyn_quant_matmul_4bit_decode_sizes_match_cpu(m):
+    # up to 32 rows go through the decode kernel (one or two passes of 16 rows), more through the tensor-core kernel: all
+    # bit for bit the CPU's result
+    k, n, bs = 1024, 264, 64
+    x, w, sc, bvec = C.dyn4_case(m, k, n, bs, True, torch.float32)
+    packed_cpu = torch._dyn_quant_pack_4bit_weight(w, sc, bvec, bs, k, n)
+    want = torch._dyn_quant_matmul_4bit(x, packed_cpu, bs, k, n)
+    packed = torch._dyn_quant_pack_4bit_weight(w.to("vk"), sc.to("vk"), bvec.to("vk"), bs, k, n)
+    got = torch._dyn_quant_matmul_4bit(x.to("vk"), packed, bs, k, n)
+    again = torch._dyn_quant_matmul_4bit(x.to("vk"), packed, bs, k, n)  # (the prepared weights come from the cache now)
+    assert torch.equal(got.cpu(), want) and torch.equal(again.cpu(), want)
+
+
 def test_unimplemented_ops_raise_instead_of_falling_back():
     x = torch.ones(4, device="vk")
     with pytest.raises(NotImplementedError, match="no B200 kernel"):

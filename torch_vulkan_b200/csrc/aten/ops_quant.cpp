@@ -172,7 +172,9 @@ at::Tensor dyn_quant_matmul_4bit(const at::Tensor& inp, const at::Tensor& packed
   const char* mode_env = std::getenv("TORCH_VK_QMM4");
   const std::string mode = mode_env != nullptr ? mode_env : "";
   const bool force_plain = mode == "plain";
-  const bool decode = !force_plain && mode != "tc" && tvb_qmm4_decode_usable(M, N, K, block_size) != 0 && packed.is_same(packed_weights);
+  // (up to 32 rows as two passes of the 16-row decode kernel: still faster than one 128-row tensor-core tile)
+  const bool decode = !force_plain && mode != "tc" && M <= 32 && tvb_qmm4_decode_usable(std::min<int64_t>(M, 16), N, K, block_size) != 0 &&
+                      packed.is_same(packed_weights);
   if (mode == "fast" && !decode && K % 8 == 0 && packed.is_same(packed_weights)) {
     int inexact = 0;
     at::Tensor prepared = prepared_weights(packed_weights, dev, N, K, block_size, 1, &inexact);
@@ -188,11 +190,15 @@ at::Tensor dyn_quant_matmul_4bit(const at::Tensor& inp, const at::Tensor& packed
   if (decode) {
     // decoding (at most 16 rows): the int4 weights, re-tiled once per packed tensor, streamed from HBM once
     at::Tensor prepared = prepared_weights(packed_weights, dev, N, K, block_size, 2, nullptr);
-    const uint64_t dbytes = tvb_qmm4_decode_workspace_bytes(M, K);
-    at::Tensor dws = at::empty({static_cast<int64_t>(dbytes)}, inp.options().dtype(at::kByte));
-    check(tvb_qmm4_decode(dev, gpu_address(x), dtype_code(x.scalar_type()), static_cast<const float*>(gpu_address(packed)),
-                          bias_elements != 0 ? 1 : 0, gpu_address(prepared), gpu_address_out(out), M, N, K, block_size,
-                          gpu_address_out(dws), dbytes));
+    for (int64_t r0 = 0; r0 < M; r0 += 16) {
+      const int64_t rows = std::min<int64_t>(16, M - r0);
+      const uint64_t dbytes = tvb_qmm4_decode_workspace_bytes(rows, K);
+      at::Tensor dws = at::empty({static_cast<int64_t>(dbytes)}, inp.options().dtype(at::kByte));
+      at::Tensor xr = x.narrow(0, r0, rows), outr = out.narrow(0, r0, rows);  // (whole rows of contiguous matrices)
+      check(tvb_qmm4_decode(dev, gpu_address(xr), dtype_code(x.scalar_type()), static_cast<const float*>(gpu_address(packed)),
+                            bias_elements != 0 ? 1 : 0, gpu_address(prepared), gpu_address_out(outr), rows, N, K, block_size,
+                            gpu_address_out(dws), dbytes));
+    }
     return out;
   }
   if (!force_plain && K % 32 == 0 && block_size % 32 == 0) {
