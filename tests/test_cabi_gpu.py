@@ -125,6 +125,30 @@ def test_qmm8_decode_is_deterministic(abi, m):
         assert torch.equal(first.view(torch.int16), again.cpu().view(torch.int16))
 
 
+def test_qmm8_decode_back_to_back_launches_agree(abi):
+    # Launches queued without waiting overlap (programmatic dependent launch): CTAs start at different times, so which
+    # contributor of a shared tile arrives last, and through which of the kernel's routes the tile is finished, varies from
+    # launch to launch. The result must not: every repeat equals the first, unhurried one bit for bit.
+    shapes = [(16, 8192, 7168), (4, 4096, 4096), (1, 8192, 3584), (8, 2048, 12288), (16, 14336, 4096)]
+    cases = []
+    for i, (m, k, n) in enumerate(shapes):
+        a, b, s = C.config_int8(m, k, n, torch.bfloat16, seed=40 + i)
+        ad, bd, sd = dev(a), dev(b), dev(s)
+        first = abi.qmm8(ad, bd, sd)
+        abi.synchronize()
+        want, tol = C.int8_want(a, b, s)
+        assert ((first.cpu().float() - want.float()).abs() <= tol).all(), (m, k, n)
+        cases.append((ad, bd, sd, first.cpu().view(torch.int16)))
+    outs = []
+    for rep in range(40):
+        for ci in ((rep * 3) % 5, (rep * 3 + 1) % 5, (rep * 3 + 2) % 5):
+            ad, bd, sd, _ = cases[ci]
+            outs.append((ci, abi.qmm8(ad, bd, sd)))
+    abi.synchronize()
+    for ci, out in outs:
+        assert torch.equal(out.cpu().view(torch.int16), cases[ci][3]), shapes[ci]
+
+
 def test_qmm8_decode_shape_sample(abi):
     # the decode benchmark's k with a slice of its n: every SM's unit range crosses tiles
     a, b, s = C.config_int8(4, 8192, 3584, torch.bfloat16)
