@@ -80,6 +80,71 @@ __global__ void __launch_bounds__(256) qmm8_plain_kernel(const void* __restrict_
   }
 }
 
+// ------------------------------------------------------------------ float32 A, aligned rows
+//
+// float32 activations cannot ride the 16-bit tensor-core operands exactly, so this stays on the CUDA cores: a warp owns
+// four output columns and up to eight rows of A; its lanes walk k together (4 values per lane and step, so that a step's
+// loads are one contiguous 512 bytes of each A row and 128 bytes of each weight row), every A value is used for four
+// columns, float32 fmaf accumulation, a shuffle tree at the end, the scale applied to the finished sum.
+// Needs k % 4 == 0 and 16-byte aligned rows of A; 4-byte aligned rows of B follow from k % 4 == 0.
+constexpr int kF32Rows = 8, kF32Cols = 4;
+
+__global__ void __launch_bounds__(256) qmm8_f32_kernel(const float* __restrict__ a, int64_t a_sm, const int8_t* __restrict__ b,
+                                                       const float* __restrict__ scales, float* __restrict__ c, int m, int n,
+                                                       int k) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int col0 = (blockIdx.x * 8 + warp) * kF32Cols;
+  if (col0 >= n) return;
+  const uint32_t* brow[kF32Cols];
+#pragma unroll
+  for (int j = 0; j < kF32Cols; j++)  // (columns past n read the last row again; their sums are dropped)
+    brow[j] = reinterpret_cast<const uint32_t*>(b + static_cast<int64_t>(min(col0 + j, n - 1)) * k);
+  for (int r0 = blockIdx.y * kF32Rows; r0 < m; r0 += gridDim.y * kF32Rows) {
+    const int rows = min(kF32Rows, m - r0);
+    float acc[kF32Rows][kF32Cols];
+#pragma unroll
+    for (int r = 0; r < kF32Rows; r++)
+#pragma unroll
+      for (int j = 0; j < kF32Cols; j++) acc[r][j] = 0.0f;
+    // the weights of the step after this one are requested before this step's arithmetic (their latency is the loop's)
+    uint32_t ahead[kF32Cols];
+#pragma unroll
+    for (int j = 0; j < kF32Cols; j++) ahead[j] = lane * 4 < k ? __ldcs(brow[j] + lane) : 0u;
+    for (int kk = lane * 4; kk < k; kk += 128) {
+      float w[kF32Cols][4];
+#pragma unroll
+      for (int j = 0; j < kF32Cols; j++) {
+        const uint32_t word = ahead[j];
+        if (kk + 128 < k) ahead[j] = __ldcs(brow[j] + ((kk + 128) >> 2));
+#pragma unroll
+        for (int i = 0; i < 4; i++) w[j][i] = static_cast<float>(static_cast<int>(static_cast<int8_t>(word >> (8 * i))));
+      }
+#pragma unroll
+      for (int r = 0; r < kF32Rows; r++) {
+        if (r < rows) {
+          const float4 av = *reinterpret_cast<const float4*>(a + static_cast<int64_t>(r0 + r) * a_sm + kk);
+#pragma unroll
+          for (int j = 0; j < kF32Cols; j++) {
+            acc[r][j] = fmaf(av.x, w[j][0], acc[r][j]);
+            acc[r][j] = fmaf(av.y, w[j][1], acc[r][j]);
+            acc[r][j] = fmaf(av.z, w[j][2], acc[r][j]);
+            acc[r][j] = fmaf(av.w, w[j][3], acc[r][j]);
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < kF32Rows; r++)
+#pragma unroll
+      for (int j = 0; j < kF32Cols; j++) {
+        float v = acc[r][j];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+        if (lane == 0 && r < rows && col0 + j < n) c[static_cast<int64_t>(r0 + r) * n + col0 + j] = v * scales[col0 + j];
+      }
+  }
+}
+
 // ------------------------------------------------------------------ skinny kernel
 
 constexpr int kChunkK = 128;  // k values (= bytes of a weight row) per pipeline stage
@@ -903,6 +968,14 @@ extern "C" int tvb_qmm8(int device, const void* a, int dtype, int64_t a_sm, cons
       if (rc != 0) return rc;
     }
     return 0;
+  }
+  if (dtype == TVB_F32 && variant == 0 && k % 4 == 0 && (a_sm % 4 == 0 || m == 1) && (reinterpret_cast<uintptr_t>(a) & 15u) == 0 &&
+      (reinterpret_cast<uintptr_t>(b) & 3u) == 0) {
+    // float32 A with aligned rows; row passes side by side in the grid (the weights of a typical layer stay in L2 between them)
+    dim3 grid(static_cast<unsigned>(ceil_div(n, 8 * kF32Cols)), static_cast<unsigned>(std::min<int64_t>(ceil_div(m, kF32Rows), 64)));
+    qmm8_f32_kernel<<<grid, 256, 0, stream>>>(static_cast<const float*>(a), m == 1 ? k : a_sm, b, static_cast<const float*>(scales),
+                                              static_cast<float*>(c), mi, ni, ki);
+    return launched("qmm8_f32", grid, dim3(256), 0, stream);
   }
   switch (dtype) {
     case TVB_F32: return launch_plain<TVB_F32>(stream, a, a_sm, b, scales, c, mi, ni, ki);
