@@ -95,10 +95,10 @@ __global__ void __launch_bounds__(256) qmm8_f32_kernel(const float* __restrict__
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int col0 = (blockIdx.x * 8 + warp) * kF32Cols;
   if (col0 >= n) return;
-  const uint32_t* brow[kF32Cols];
+  const uint4* brow[kF32Cols];
 #pragma unroll
   for (int j = 0; j < kF32Cols; j++)  // (columns past n read the last row again; their sums are dropped)
-    brow[j] = reinterpret_cast<const uint32_t*>(b + static_cast<int64_t>(min(col0 + j, n - 1)) * k);
+    brow[j] = reinterpret_cast<const uint4*>(b + static_cast<int64_t>(min(col0 + j, n - 1)) * k);
   for (int r0 = blockIdx.y * kF32Rows; r0 < m; r0 += gridDim.y * kF32Rows) {
     const int rows = min(kF32Rows, m - r0);
     float acc[kF32Rows][kF32Cols];
@@ -106,29 +106,38 @@ __global__ void __launch_bounds__(256) qmm8_f32_kernel(const float* __restrict__
     for (int r = 0; r < kF32Rows; r++)
 #pragma unroll
       for (int j = 0; j < kF32Cols; j++) acc[r][j] = 0.0f;
-    // the weights of the step after this one are requested before this step's arithmetic (their latency is the loop's)
-    uint32_t ahead[kF32Cols];
+    // A lane takes 16 consecutive values of k per step (a warp: 512). The weights of the step after this one are
+    // requested before this step's arithmetic: their latency is the loop's.
+    uint4 ahead[kF32Cols];
 #pragma unroll
-    for (int j = 0; j < kF32Cols; j++) ahead[j] = lane * 4 < k ? __ldcs(brow[j] + lane) : 0u;
-    for (int kk = lane * 4; kk < k; kk += 128) {
-      float w[kF32Cols][4];
+    for (int j = 0; j < kF32Cols; j++) ahead[j] = lane * 16 < k ? __ldcs(brow[j] + lane) : make_uint4(0u, 0u, 0u, 0u);
+    for (int kk = lane * 16; kk < k; kk += 512) {
+      uint4 cur[kF32Cols];
 #pragma unroll
       for (int j = 0; j < kF32Cols; j++) {
-        const uint32_t word = ahead[j];
-        if (kk + 128 < k) ahead[j] = __ldcs(brow[j] + ((kk + 128) >> 2));
-#pragma unroll
-        for (int i = 0; i < 4; i++) w[j][i] = static_cast<float>(static_cast<int>(static_cast<int8_t>(word >> (8 * i))));
+        cur[j] = ahead[j];
+        if (kk + 512 < k) ahead[j] = __ldcs(brow[j] + ((kk + 512) >> 4));
       }
 #pragma unroll
-      for (int r = 0; r < kF32Rows; r++) {
-        if (r < rows) {
-          const float4 av = *reinterpret_cast<const float4*>(a + static_cast<int64_t>(r0 + r) * a_sm + kk);
+      for (int q = 0; q < 4; q++) {  // four values of k at a time
+        float w[kF32Cols][4];
 #pragma unroll
-          for (int j = 0; j < kF32Cols; j++) {
-            acc[r][j] = fmaf(av.x, w[j][0], acc[r][j]);
-            acc[r][j] = fmaf(av.y, w[j][1], acc[r][j]);
-            acc[r][j] = fmaf(av.z, w[j][2], acc[r][j]);
-            acc[r][j] = fmaf(av.w, w[j][3], acc[r][j]);
+        for (int j = 0; j < kF32Cols; j++) {
+          const uint32_t word = q == 0 ? cur[j].x : (q == 1 ? cur[j].y : (q == 2 ? cur[j].z : cur[j].w));
+#pragma unroll
+          for (int i = 0; i < 4; i++) w[j][i] = static_cast<float>(static_cast<int>(static_cast<int8_t>(word >> (8 * i))));
+        }
+#pragma unroll
+        for (int r = 0; r < kF32Rows; r++) {
+          if (r < rows) {
+            const float4 av = *reinterpret_cast<const float4*>(a + static_cast<int64_t>(r0 + r) * a_sm + kk + 4 * q);
+#pragma unroll
+            for (int j = 0; j < kF32Cols; j++) {
+              acc[r][j] = fmaf(av.x, w[j][0], acc[r][j]);
+              acc[r][j] = fmaf(av.y, w[j][1], acc[r][j]);
+              acc[r][j] = fmaf(av.z, w[j][2], acc[r][j]);
+              acc[r][j] = fmaf(av.w, w[j][3], acc[r][j]);
+            }
           }
         }
       }
@@ -969,8 +978,8 @@ extern "C" int tvb_qmm8(int device, const void* a, int dtype, int64_t a_sm, cons
     }
     return 0;
   }
-  if (dtype == TVB_F32 && variant == 0 && k % 4 == 0 && (a_sm % 4 == 0 || m == 1) && (reinterpret_cast<uintptr_t>(a) & 15u) == 0 &&
-      (reinterpret_cast<uintptr_t>(b) & 3u) == 0) {
+  if (dtype == TVB_F32 && variant == 0 && k % 16 == 0 && (a_sm % 4 == 0 || m == 1) && (reinterpret_cast<uintptr_t>(a) & 15u) == 0 &&
+      (reinterpret_cast<uintptr_t>(b) & 15u) == 0) {
     // float32 A with aligned rows; row passes side by side in the grid (the weights of a typical layer stay in L2 between them)
     dim3 grid(static_cast<unsigned>(ceil_div(n, 8 * kF32Cols)), static_cast<unsigned>(std::min<int64_t>(ceil_div(m, kF32Rows), 64)));
     qmm8_f32_kernel<<<grid, 256, 0, stream>>>(static_cast<const float*>(a), m == 1 ? k : a_sm, b, static_cast<const float*>(scales),
