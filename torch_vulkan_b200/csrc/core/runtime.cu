@@ -326,7 +326,16 @@ int tvb_empty_cache(int device) {
   cudaError_t err = cudaStreamSynchronize(s);
   {
     std::lock_guard<std::mutex> lock(g_mutex);
-    trim_locked(g_devices[device]);
+    DeviceState& d = g_devices[device];
+    trim_locked(d);
+    // the kernels' large scratch areas (slot 1: the widened weights of tvb_qmm8) go too; they come back on demand
+    for (int slot = 1; slot < 4; slot++) {
+      if (d.ws[slot] != nullptr) {
+        cudaFree(d.ws[slot]);
+        d.ws[slot] = nullptr;
+        d.ws_size[slot] = 0;
+      }
+    }
   }
   if (err != cudaSuccess) return fail_cuda("cudaStreamSynchronize", err);
   return 0;

@@ -142,16 +142,29 @@ __global__ void __launch_bounds__(kWarps * 32, 1) qmm4_decode_kernel(const Decod
   ptx::grid_dependency_wait();
   // Activation fragments, once per CTA. A lane's 8 values of k within a step are 8 t ... 8 t + 7; the weights' low nibbles
   // are the even ones, the high nibbles the odd ones, and the MMA's k slots pair them the same way on both operands.
-  for (int e = threadIdx.x; e < steps * 32; e += kWarps * 32) {
-    const int step = e >> 5, ln = e & 31, fg = ln >> 2, ft = ln & 3;
-    const int kk = step * 32 + 8 * ft;
-    uint2 lo = make_uint2(0u, 0u), hi = make_uint2(0u, 0u);
-    if (fg < p.m) lo = *reinterpret_cast<const uint2*>(p.q + fg * qstride + kk);
-    if (fg + 8 < p.m) hi = *reinterpret_cast<const uint2*>(p.q + (fg + 8) * qstride + kk);
-    frags[e] = make_uint4(ptx::prmt(lo.x, lo.y, 0x6420u),   // row g, even k
-                          ptx::prmt(hi.x, hi.y, 0x6420u),   // row g + 8, even k
-                          ptx::prmt(lo.x, lo.y, 0x7531u),   // row g, odd k
-                          ptx::prmt(hi.x, hi.y, 0x7531u));  // row g + 8, odd k
+  // (all of a thread's loads are issued before any is used: their latencies overlap instead of adding up)
+  constexpr int kBatch = 8;
+  for (int e0 = threadIdx.x; e0 < steps * 32; e0 += kBatch * kWarps * 32) {
+    uint2 lo[kBatch], hi[kBatch];
+#pragma unroll
+    for (int i = 0; i < kBatch; i++) {
+      const int e = e0 + i * kWarps * 32;
+      const int step = e >> 5, ln = e & 31, fg = ln >> 2, ft = ln & 3;
+      const int kk = step * 32 + 8 * ft;
+      lo[i] = make_uint2(0u, 0u);
+      hi[i] = make_uint2(0u, 0u);
+      if (e < steps * 32 && fg < p.m) lo[i] = *reinterpret_cast<const uint2*>(p.q + fg * qstride + kk);
+      if (e < steps * 32 && fg + 8 < p.m) hi[i] = *reinterpret_cast<const uint2*>(p.q + (fg + 8) * qstride + kk);
+    }
+#pragma unroll
+    for (int i = 0; i < kBatch; i++) {
+      const int e = e0 + i * kWarps * 32;
+      if (e < steps * 32)
+        frags[e] = make_uint4(ptx::prmt(lo[i].x, lo[i].y, 0x6420u),   // row g, even k
+                              ptx::prmt(hi[i].x, hi[i].y, 0x6420u),   // row g + 8, even k
+                              ptx::prmt(lo[i].x, lo[i].y, 0x7531u),   // row g, odd k
+                              ptx::prmt(hi[i].x, hi[i].y, 0x7531u));  // row g + 8, odd k
+    }
   }
   // -zero_point, the same for every k: in [-127, 128]. All but 128 fit one int8 operand; a row with 128 (zero point -128)
   // takes a second one holding the 1 that is left over.
@@ -175,34 +188,54 @@ __global__ void __launch_bounds__(kWarps * 32, 1) qmm4_decode_kernel(const Decod
     // (-0 is the neutral element of float addition for every addend, signed zeros included: adding the first block to
     // it is the reference's assignment)
     float sum[4] = {-0.0f, -0.0f, -0.0f, -0.0f};
-    int acc[4] = {0, 0, 0, 0};
+    int carry[4] = {0, 0, 0, 0};  // the integer sum of the block in progress
     for (int c = 0; c < p.chunks && ok; c++, use++) {
       const int slot = static_cast<int>(use % p.slots);
       ok = ptx::mbar_wait(bar0 + 8 * slot, static_cast<uint32_t>((use / p.slots) & 1), abort_flag);
       if (!ok) break;
       const uint32_t rec = ring + slot * p.record_bytes;
+      // Four steps at a time, stage by stage (loads, nibble conversion, MMAs into separate accumulators, then the blocks'
+      // float arithmetic in order): each stage's instructions are independent of one another, which is what keeps a warp
+      // issuing while loads and MMAs are in flight.
+      constexpr int kBatch = 4;
 #pragma unroll
-      for (int st = 0; st < kChunkSteps; st++) {
-        const int step = c * kChunkSteps + st;
-        const uint4 a = ptx::lds128(base + (step * 32 + lane) * 16);
-        // this lane's 8 weights of the step: column g, k = 8 t ... 8 t + 7, as 8 nibbles
-        const uint32_t w = lds32(rec + (st * kCols + g) * 16 + 4 * t);
-        const uint32_t b_even = nibbles_to_int8(w & 0x0f0f0f0fu);
-        const uint32_t b_odd = nibbles_to_int8((w >> 4) & 0x0f0f0f0fu);
-        mma_s8_16832(acc, a.x, a.y, a.z, a.w, b_even, b_odd);
-        mma_s8_16832(acc, o1_lo, o1_hi, o1_lo, o1_hi, b_even, b_odd);
-        if (second) mma_s8_16832(acc, o2_lo, o2_hi, o2_lo, o2_hi, b_even, b_odd);
-        if ((st + 1) % SPB == 0) {
-          // the block is complete: float(sum) * scale, added in block order
-          const int blk_in_chunk = st / SPB;
-          const float2 sc = lds64f(rec + kChunkWeightBytes + (blk_in_chunk * kCols + 2 * t) * 4);
-          sum[0] = __fadd_rn(sum[0], __fmul_rn(exact_float(acc[0]), sc.x));
-          sum[1] = __fadd_rn(sum[1], __fmul_rn(exact_float(acc[1]), sc.y));
-          if (HI) {
-            sum[2] = __fadd_rn(sum[2], __fmul_rn(exact_float(acc[2]), sc.x));
-            sum[3] = __fadd_rn(sum[3], __fmul_rn(exact_float(acc[3]), sc.y));
+      for (int st0 = 0; st0 < kChunkSteps; st0 += kBatch) {
+        uint4 a[kBatch];
+        uint32_t w[kBatch];
+#pragma unroll
+        for (int i = 0; i < kBatch; i++) {
+          a[i] = ptx::lds128(base + ((c * kChunkSteps + st0 + i) * 32 + lane) * 16);
+          // this lane's 8 weights of the step: column g, k = 8 t ... 8 t + 7, as 8 nibbles
+          w[i] = lds32(rec + ((st0 + i) * kCols + g) * 16 + 4 * t);
+        }
+        int acc[kBatch][4], acc_o[kBatch][4];
+#pragma unroll
+        for (int i = 0; i < kBatch; i++) {
+          const uint32_t b_even = nibbles_to_int8(w[i] & 0x0f0f0f0fu);
+          const uint32_t b_odd = nibbles_to_int8((w[i] >> 4) & 0x0f0f0f0fu);
+#pragma unroll
+          for (int j = 0; j < 4; j++) acc[i][j] = acc_o[i][j] = 0;
+          mma_s8_16832(acc[i], a[i].x, a[i].y, a[i].z, a[i].w, b_even, b_odd);
+          mma_s8_16832(acc_o[i], o1_lo, o1_hi, o1_lo, o1_hi, b_even, b_odd);
+          if (second) mma_s8_16832(acc_o[i], o2_lo, o2_hi, o2_lo, o2_hi, b_even, b_odd);
+        }
+#pragma unroll
+        for (int i = 0; i < kBatch; i++) {
+          const int st = st0 + i;
+#pragma unroll
+          for (int j = 0; j < 4; j++) carry[j] += acc[i][j] + acc_o[i][j];  // (integer sums: exact in any order)
+          if ((st + 1) % SPB == 0) {
+            // the block is complete: float(sum) * scale, added in block order
+            const int blk_in_chunk = st / SPB;
+            const float2 sc = lds64f(rec + kChunkWeightBytes + (blk_in_chunk * kCols + 2 * t) * 4);
+            sum[0] = __fadd_rn(sum[0], __fmul_rn(exact_float(carry[0]), sc.x));
+            sum[1] = __fadd_rn(sum[1], __fmul_rn(exact_float(carry[1]), sc.y));
+            if (HI) {
+              sum[2] = __fadd_rn(sum[2], __fmul_rn(exact_float(carry[2]), sc.x));
+              sum[3] = __fadd_rn(sum[3], __fmul_rn(exact_float(carry[3]), sc.y));
+            }
+            carry[0] = carry[1] = carry[2] = carry[3] = 0;
           }
-          acc[0] = acc[1] = acc[2] = acc[3] = 0;
         }
       }
       // the slot is free: bring in the record `slots` further on
