@@ -137,6 +137,7 @@ __global__ void __launch_bounds__(kWarps * 32, 1) qmm4_decode_kernel(const Decod
     }
   };
   __syncthreads();  // (the barriers are initialised)
+  ptx::grid_launch_dependents();  // (the next product's PHASE 0 may be launched; it waits for this kernel before it touches memory)
   // The weights do not depend on the kernel before this one (PHASE 0, which writes q): start their stream, then wait.
   if (lane == 0 && first_grp < p.groups) fill_ring(first_grp, 0);
   ptx::grid_dependency_wait();

@@ -66,6 +66,7 @@ __global__ void __launch_bounds__(256) qmm4_quantize_tc_kernel(const void* __res
   __shared__ float row_scale;
   __shared__ int row_zp;
   ptx::grid_launch_dependents();  // (a kernel launched with programmatic serialization may start its own prologue now)
+  ptx::grid_dependency_wait();    // (and this one, launched that way itself, touches memory only after its predecessors)
   const int64_t base = static_cast<int64_t>(blockIdx.x) * k;
   const int64_t qbase = static_cast<int64_t>(blockIdx.x) * (k + kExtraCols);
   const int t = threadIdx.x;
@@ -377,10 +378,23 @@ namespace tvb {
 int qmm4_quantize_rows(cudaStream_t stream, const void* inp, int dtype, int64_t m, int64_t k, int groupwise, int8_t* q, float* recip,
                        int32_t* neg_zp) {
   dim3 qgrid(static_cast<unsigned>(m));
-  if (dtype == TVB_F32)
-    qmm4_quantize_tc_kernel<TVB_F32><<<qgrid, 256, 0, stream>>>(inp, static_cast<int>(k), groupwise, q, recip, neg_zp);
-  else
-    qmm4_quantize_tc_kernel<TVB_BF16><<<qgrid, 256, 0, stream>>>(inp, static_cast<int>(k), groupwise, q, recip, neg_zp);
+  // Launched with programmatic stream serialization: in a stream of decoding products its launch latency hides behind the
+  // previous product (whose completion it still waits for before it reads or writes anything).
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = qgrid;
+  cfg.blockDim = dim3(256);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  const int ki = static_cast<int>(k);
+  if (dtype == TVB_F32) {
+    TVB_CUDA(cudaLaunchKernelEx(&cfg, qmm4_quantize_tc_kernel<TVB_F32>, inp, ki, groupwise, q, recip, neg_zp));
+  } else {
+    TVB_CUDA(cudaLaunchKernelEx(&cfg, qmm4_quantize_tc_kernel<TVB_BF16>, inp, ki, groupwise, q, recip, neg_zp));
+  }
   return launched("qmm4_quantize_tc", qgrid, dim3(256), 0, stream);
 }
 
