@@ -28,6 +28,7 @@
 #include "../core/tensormap.h"
 #include "numerics.cuh"
 #include "ptx.cuh"
+#include "qmm4_phase0.cuh"
 
 namespace tvb {
 namespace {
@@ -91,28 +92,17 @@ __global__ void __launch_bounds__(256) qmm4_quantize_tc_kernel(const void* __res
       mn = fminf(mn, red_min[i]);
       mx = fmaxf(mx, red_max[i]);
     }
-    const float qmin = -128.0f, qmax = 127.0f;
-    float rmin = fminf(0.0f, mn), rmax = fmaxf(0.0f, mx);
-    float scale = rmin == rmax ? 1.0f : __fdiv_rn(qmax - qmin, __fsub_rn(rmax, rmin));
-    float recip = scale != 0.0f ? __fdiv_rn(1.0f, scale) : 0.0f;
-    float dmin = __fmul_rn(rmin, scale), dmax = __fmul_rn(rmax, scale);
-    float err = groupwise ? __fadd_rn(__fadd_rn(__fadd_rn(qmin, dmin), qmax), dmax)
-                          : __fadd_rn(__fadd_rn(qmin, dmin), __fadd_rn(qmax, dmax));
-    float zp = err > 0.0f ? __fsub_rn(qmin, dmin) : __fsub_rn(qmax, dmax);
-    zp = fminf(fmaxf(zp, qmin), qmax);
-    int izp = __float2int_rn(zp);
-    row_scale = scale;
-    row_zp = izp;
-    recip_out[blockIdx.x] = recip;
-    neg_zp_out[blockIdx.x] = -izp;
+    const Phase0Row row = phase0_row(mn, mx, groupwise);
+    row_scale = row.scale;
+    row_zp = row.zero_point;
+    recip_out[blockIdx.x] = row.recip;
+    neg_zp_out[blockIdx.x] = -row.zero_point;
   }
   __syncthreads();
   const float scale = row_scale;
   const int zp = row_zp;
   for (int kk = t; kk < k; kk += 256) {
-    float scaled = __fmul_rn(load_float<DT>(inp, base + kk), scale);
-    int v = static_cast<int>(roundf(scaled)) + zp;
-    q[qbase + kk] = static_cast<int8_t>(max(-128, min(127, v)));
+    q[qbase + kk] = static_cast<int8_t>(phase0_code(load_float<DT>(inp, base + kk), scale, zp));
   }
   if (t < kExtraCols) {
     const int off = -zp;          // in [-127, 128]
