@@ -28,12 +28,18 @@ __version__ = "0.1.0"
 
 torch.utils.rename_privateuse1_backend("vk")
 
-try:
-    from . import _native  # registers the C++ backend
-except ImportError as exc:  # no silent fallback: without the extension nothing works
-    raise ImportError(
-        "torch_vulkan_b200._native is not built (or libtvb200.so is missing): run "
-        "`python -m torch_vulkan_b200._build`. There is no pure-Python or CPU path.") from exc
+# `python -m torch_vulkan_b200._build` has to get past this file on a tree where nothing is built yet: that one command
+# runs without the extension (and does nothing but build it).
+_building = any(arg == "torch_vulkan_b200._build" for arg in getattr(sys, "orig_argv", []))
+if _building:
+    _native = None
+else:
+    try:
+        from . import _native  # registers the C++ backend
+    except ImportError as exc:  # no silent fallback: without the extension nothing works
+        raise ImportError(
+            "torch_vulkan_b200._native is not built (or libtvb200.so is missing): run "
+            "`python -m torch_vulkan_b200._build`. There is no pure-Python or CPU path.") from exc
 
 torch.utils.generate_methods_for_privateuse1_backend()
 
@@ -161,4 +167,5 @@ sys.modules["torch.vk"] = torch.vk
 @atexit.register
 def _shutdown():
     # Finish queued work and release the pools before interpreter teardown.
-    _native.shutdown()
+    if _native is not None:
+        _native.shutdown()
