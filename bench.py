@@ -351,7 +351,8 @@ def run_only(tv, stream, which, iters):
         fn = lambda: torch._dyn_quant_matmul_4bit(xv, packed, 32, 4096, 14336)  # noqa: E731
         flops = 2.0 * mm * 14336 * 4096
     else:
-        m, n, k = 2048, 14336, 4096
+        # int8_large_m: weights widened once, then the 16-bit GEMM; int8_mid_m: the kernel that widens in its main loop
+        m, n, k = (2048 if which == "int8_large_m" else 512), 14336, 4096
         a = torch.randn(m, k, generator=gen(1)).to(torch.bfloat16).to("vk")
         w = torch.randint(-127, 128, (n, k), dtype=torch.int8, generator=gen(2)).to("vk")
         s = (torch.rand(n, generator=gen(3)) * (2e-2 - 1e-3) + 1e-3).to(torch.bfloat16).to("vk")
@@ -377,7 +378,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extra", action="store_true", help="skip the large-m configurations")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline")
-    ap.add_argument("--only", default=None, choices=["fp8", "fp8_big", "dyn4", "dyn4_decode", "int8_large_m", "int8_stack", "bf16_mm"],
+    ap.add_argument("--only", default=None, choices=["fp8", "fp8_big", "dyn4", "dyn4_decode", "int8_large_m", "int8_mid_m", "int8_stack", "bf16_mm"],
                     help="run one large-m configuration a few times and exit (for profilers); prints its own JSON line")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
