@@ -135,6 +135,17 @@ TVB_API int tvb_add_rowvec(int device, void* c, int c_dtype, int64_t c_sm, const
 TVB_API int tvb_qmm8(int device, const void* a, int dtype, int64_t a_sm, const int8_t* b, const void* scales, void* c,
              int64_t m, int64_t n, int64_t k, int variant);
 
+/* ---- the same product with weights widened ahead of time (prefill: many rows of A, the same weights call after call) ----
+ * tvb_qmm8_widen converts B and scales once into a caller-owned buffer of tvb_qmm8_widened_bytes(n, k) bytes (256-byte
+ * aligned; n * k weights in A's 16-bit dtype, then the scales in float32); tvb_qmm8_widened multiplies with them: the
+ * arithmetic of tvb_qmm8's variant 4 without its per-call pass over the weights. dtype: TVB_F16 or TVB_BF16; k % 16 == 0;
+ * rows of A 16-byte aligned. (The ATen layer keeps such buffers per weight tensor, within a byte budget.) */
+TVB_API uint64_t tvb_qmm8_widened_bytes(int64_t n, int64_t k);
+TVB_API int tvb_qmm8_widen(int device, const int8_t* b, const void* scales, int dtype, int64_t n, int64_t k, void* widened,
+                   uint64_t widened_bytes);
+TVB_API int tvb_qmm8_widened(int device, const void* a, int dtype, int64_t a_sm, const void* widened, void* c, int64_t m, int64_t n,
+                     int64_t k);
+
 /* ---- the decode product with the weight rows sharded over the GPUs of one node (no counterpart in the reference,
  *      which has one device: crates/pyvk/csrc/backend.cpp:296) ----
  * Rank `rank` of `world` computes its n_local output columns and its kernel's epilogue stores them straight into

@@ -161,6 +161,28 @@ def test_dyn_quant_matmul_4bit_decode_sizes_match_cpu(m):
     assert torch.equal(got.cpu(), want) and torch.equal(again.cpu(), want)
 
 
+def test_weight_int8pack_mm_prefill_reuses_widened_weights():
+    # 512 rows and more: a 16-bit GEMM over a widened copy of the weights that is kept between calls; writing into the
+    # weights or the scales must invalidate it
+    m, k, n = 640, 1024, 776
+    a, b, s = C.config_int8(m, k, n, torch.bfloat16, seed=3)
+    av, bv, sv = a.to("vk"), b.to("vk"), s.to("vk")
+    want, tol = C.int8_want(a, b, s)
+    first = torch._weight_int8pack_mm(av, bv, sv).cpu()
+    again = torch._weight_int8pack_mm(av, bv, sv).cpu()  # (from the cache)
+    assert ((first.float() - want.float()).abs() <= tol).all()
+    assert torch.equal(first.view(torch.int16), again.view(torch.int16))
+    b2 = torch.roll(b, 5, 0)
+    bv.copy_(b2.to("vk"))  # in place: the version counter moves
+    want2, tol2 = C.int8_want(a, b2, s)
+    got2 = torch._weight_int8pack_mm(av, bv, sv).cpu()
+    assert ((got2.float() - want2.float()).abs() <= tol2).all()
+    s2 = (s.float() * 2).to(torch.bfloat16)
+    sv.copy_(s2.to("vk"))
+    got3 = torch._weight_int8pack_mm(av, bv, sv).cpu()
+    assert torch.equal(got3.float(), got2.float() * 2)  # scales doubled exactly
+
+
 def test_unimplemented_ops_raise_instead_of_falling_back():
     x = torch.ones(4, device="vk")
     with pytest.raises(NotImplementedError, match="no B200 kernel"):

@@ -49,6 +49,9 @@ SIGNATURES = {
     "tvb_copy_strided": (_i, [_i, _vp, _i, _c.POINTER(_i64), _vp, _i, _c.POINTER(_i64), _c.POINTER(_i64), _i]),
     "tvb_fill_strided": (_i, [_i, _vp, _i, _u64, _c.POINTER(_i64), _c.POINTER(_i64), _i]),
     "tvb_add_rowvec": (_i, [_i, _vp, _i, _i64, _vp, _i, _i64, _i64]),
+    "tvb_qmm8_widened_bytes": (_u64, [_i64, _i64]),
+    "tvb_qmm8_widen": (_i, [_i, _vp, _vp, _i, _i64, _i64, _vp, _u64]),
+    "tvb_qmm8_widened": (_i, [_i, _vp, _i, _i64, _vp, _vp, _i64, _i64, _i64]),
     "tvb_mm": (_i, [_i, _vp, _i, _i64, _i64, _vp, _i64, _i64, _vp, _i, _vp, _i, _i64, _i64, _i64, _i]),
     "tvb_qmm8": (_i, [_i, _vp, _i, _i64, _vp, _vp, _vp, _i64, _i64, _i64, _i]),
     "tvb_qmm8_gather": (_i, [_i, _vp, _i, _i64, _vp, _vp, _c.POINTER(_vp), _c.POINTER(_vp), _i, _i, _vp, _i64, _i64, _i64]),

@@ -14,6 +14,8 @@
 #include <ATen/native/Resize.h>
 #include <torch/library.h>
 
+#include <algorithm>
+#include <cstdlib>
 #include <list>
 #include <mutex>
 #include <sstream>
@@ -35,6 +37,68 @@ void require_vk(const char* op, std::initializer_list<const at::Tensor*> tensors
 
 // ------------------------------------------------------------------ int8 weight-only
 
+uint32_t tensor_version(const at::Tensor& t) { return t.is_inference() ? 0u : t._version(); }
+
+// With many rows of A (prefill) the product is a 16-bit GEMM over the weights widened to A's dtype, and the widening pass
+// (3 bytes of traffic per weight) is worth keeping when the same weights come back call after call: widened copies are kept
+// per (weight tensor, scales tensor, dtype), least recently used first out, within TORCH_VK_QMM8_CACHE_MB megabytes (default
+// 16384: a 7-billion-parameter model's worth of bfloat16 copies on a 180 GB part; 0 turns the cache off). An entry is dropped
+// when either tensor's storage dies or its version counter moves.
+struct WidenedWeights {
+  c10::weak_intrusive_ptr<c10::StorageImpl> b_storage, s_storage;
+  const void *b_data, *s_data;
+  int64_t n, k;
+  uint32_t b_version, s_version;
+  int dtype;
+  at::Tensor widened;
+};
+
+std::mutex g_widened_mutex;
+std::list<WidenedWeights> g_widened;  // most recently used first
+uint64_t g_widened_bytes = 0;
+
+uint64_t widened_budget() {
+  static const uint64_t budget = [] {
+    const char* v = std::getenv("TORCH_VK_QMM8_CACHE_MB");
+    return static_cast<uint64_t>(v != nullptr ? std::max<long long>(0, std::atoll(v)) : 16384) << 20;
+  }();
+  return budget;
+}
+
+// The widened copy of (B, scales) in `dtype`, from the cache or made now; an undefined tensor when it does not fit the budget.
+at::Tensor widened_weights(const at::Tensor& B, const at::Tensor& s, int dev, int dtype, int64_t n, int64_t k) {
+  const uint64_t bytes = tvb_qmm8_widened_bytes(n, k);
+  if (bytes > widened_budget()) return at::Tensor();
+  std::lock_guard<std::mutex> lock(g_widened_mutex);
+  c10::StorageImpl* bi = B.storage().unsafeGetStorageImpl();
+  c10::StorageImpl* si = s.storage().unsafeGetStorageImpl();
+  for (auto it = g_widened.begin(); it != g_widened.end();) {
+    if (it->b_storage.expired() || it->s_storage.expired()) {
+      g_widened_bytes -= it->widened.numel();
+      it = g_widened.erase(it);
+      continue;
+    }
+    if (it->b_storage._unsafe_get_target() == bi && it->s_storage._unsafe_get_target() == si && it->b_data == B.const_data_ptr() &&
+        it->s_data == s.const_data_ptr() && it->n == n && it->k == k && it->dtype == dtype && it->b_version == tensor_version(B) &&
+        it->s_version == tensor_version(s)) {
+      g_widened.splice(g_widened.begin(), g_widened, it);
+      return g_widened.front().widened;
+    }
+    ++it;
+  }
+  at::Tensor widened = at::empty({static_cast<int64_t>(bytes)}, B.options().dtype(at::kByte));
+  check(tvb_qmm8_widen(dev, static_cast<const int8_t*>(gpu_address(B)), gpu_address(s), dtype, n, k, gpu_address_out(widened), bytes));
+  g_widened.push_front(WidenedWeights{c10::weak_intrusive_ptr<c10::StorageImpl>(B.storage().getWeakStorageImpl()),
+                                      c10::weak_intrusive_ptr<c10::StorageImpl>(s.storage().getWeakStorageImpl()), B.const_data_ptr(),
+                                      s.const_data_ptr(), n, k, tensor_version(B), tensor_version(s), dtype, widened});
+  g_widened_bytes += bytes;
+  while (g_widened_bytes > widened_budget() && g_widened.size() > 1) {
+    g_widened_bytes -= g_widened.back().widened.numel();
+    g_widened.pop_back();
+  }
+  return widened;
+}
+
 at::Tensor weight_int8pack_mm(const at::Tensor& A, const at::Tensor& B, const at::Tensor& scales) {
   constexpr const char* fn = "_weight_int8pack_mm_cpu";  // (the messages name the CPU kernel, as the reference's do)
   const int64_t M = A.size(0), N = B.size(0), K = A.size(1);
@@ -52,6 +116,18 @@ at::Tensor weight_int8pack_mm(const at::Tensor& A, const at::Tensor& B, const at
   if (C.numel() == 0) return C;
   at::Tensor s = scales.to(A.scalar_type()).contiguous();  // (the CPU reads the scales in A's dtype)
   const int dev = enter_device(A);
+  const int dt = dtype_code(A.scalar_type());
+  // From 512 rows on, 16-bit A, aligned rows: the GEMM over cached widened weights (keyed on the caller's own scales tensor,
+  // so only when no converted copy of it was needed).
+  if (M >= 512 && (dt == TVB_BF16 || dt == TVB_F16) && K % 16 == 0 && A.stride(0) % 8 == 0 && A.stride(0) >= K &&
+      (reinterpret_cast<uintptr_t>(gpu_address(A)) & 15u) == 0 && (reinterpret_cast<uintptr_t>(gpu_address(B)) & 15u) == 0 &&
+      s.is_same(scales)) {
+    at::Tensor widened = widened_weights(B, s, dev, dt, N, K);
+    if (widened.defined()) {
+      check(tvb_qmm8_widened(dev, gpu_address(A), dt, A.stride(0), gpu_address(widened), gpu_address_out(C), M, N, K));
+      return C;
+    }
+  }
   check(tvb_qmm8(dev, gpu_address(A), dtype_code(A.scalar_type()), A.stride(0), static_cast<const int8_t*>(gpu_address(B)),
                  gpu_address(s), gpu_address_out(C), M, N, K, 0));
   return C;

@@ -370,24 +370,26 @@ bool qmm8_widen_gemm_usable(const void* a, int dtype, int64_t a_sm, const int8_t
   return qmm8_tc_usable(a, dtype, a_sm, b, m, n, k) && (n * k) % 16 == 0 && k % 8 == 0;
 }
 
-int qmm8_widen_gemm(int device, cudaStream_t stream, const void* a, int dtype, int64_t a_sm, const int8_t* b, const void* scales,
-                    void* c, int64_t m, int64_t n, int64_t k) {
-  const uint64_t wide_bytes = static_cast<uint64_t>(n) * k * 2;
-  const uint64_t scale_off = (wide_bytes + 255) & ~uint64_t(255);
-  void* ws = nullptr;
-  if (workspace(device, 1, scale_off + static_cast<uint64_t>(n) * 4, &ws) != 0) return -1;
-  uint16_t* wide = static_cast<uint16_t*>(ws);
-  float* scales32 = reinterpret_cast<float*>(static_cast<uint8_t*>(ws) + scale_off);
+// [n * k 16-bit weights][256-byte aligned: n float32 scales]
+uint64_t widened_scale_offset(int64_t n, int64_t k) { return (static_cast<uint64_t>(n) * k * 2 + 255) & ~uint64_t(255); }
+
+int qmm8_widen_into(int device, cudaStream_t stream, const int8_t* b, const void* scales, int dtype, int64_t n, int64_t k, void* widened) {
+  uint16_t* wide = static_cast<uint16_t*>(widened);
+  float* scales32 = reinterpret_cast<float*>(static_cast<uint8_t*>(widened) + widened_scale_offset(n, k));
   const int64_t count16 = n * k / 16;
   const int grid = static_cast<int>(std::min<int64_t>(static_cast<int64_t>(sm_count(device)) * 16, ceil_div(count16, 256)));
   if (dtype == TVB_BF16) qmm8_widen_kernel<TVB_BF16><<<grid, 256, 0, stream>>>(b, wide, count16, scales, scales32, static_cast<int>(n));
   else qmm8_widen_kernel<TVB_F16><<<grid, 256, 0, stream>>>(b, wide, count16, scales, scales32, static_cast<int>(n));
-  if (launched("qmm8_widen", dim3(grid), dim3(256), 0, stream) != 0) return -1;
+  return launched("qmm8_widen", dim3(grid), dim3(256), 0, stream);
+}
+
+int qmm8_widened_gemm(int device, cudaStream_t stream, const void* a, int dtype, int64_t a_sm, const void* widened, void* c, int64_t m,
+                      int64_t n, int64_t k) {
   ScaledMmParams p{};
   p.a = a;
-  p.b = wide;
+  p.b = widened;
   p.scale_a = nullptr;      // (the epilogue multiplies by 1 for A ...)
-  p.scale_b = scales32;     // (... and by scales[n] for the columns)
+  p.scale_b = reinterpret_cast<const float*>(static_cast<const uint8_t*>(widened) + widened_scale_offset(n, k));  // (... by scales[n] for the columns)
   p.rowwise = 1;
   p.out = c;
   p.m = m; p.n = n; p.k = k;
@@ -398,4 +400,42 @@ int qmm8_widen_gemm(int device, cudaStream_t stream, const void* a, int dtype, i
   return scaled_mm_tc(device, stream, p);
 }
 
+int qmm8_widen_gemm(int device, cudaStream_t stream, const void* a, int dtype, int64_t a_sm, const int8_t* b, const void* scales,
+                    void* c, int64_t m, int64_t n, int64_t k) {
+  void* ws = nullptr;
+  if (workspace(device, 1, widened_scale_offset(n, k) + static_cast<uint64_t>(n) * 4, &ws) != 0) return -1;
+  if (qmm8_widen_into(device, stream, b, scales, dtype, n, k, ws) != 0) return -1;
+  return qmm8_widened_gemm(device, stream, a, dtype, a_sm, ws, c, m, n, k);
+}
+
 }  // namespace tvb
+
+using namespace tvb;
+
+extern "C" uint64_t tvb_qmm8_widened_bytes(int64_t n, int64_t k) {
+  return widened_scale_offset(n, k) + static_cast<uint64_t>(n) * 4;
+}
+
+extern "C" int tvb_qmm8_widen(int device, const int8_t* b, const void* scales, int dtype, int64_t n, int64_t k, void* widened,
+                              uint64_t widened_bytes) {
+  TVB_REQUIRE(dtype == TVB_F16 || dtype == TVB_BF16, "tvb_qmm8_widen: float16 or bfloat16 only");
+  TVB_REQUIRE(n >= 1 && k >= 16 && k % 16 == 0 && (n * k) % 16 == 0, "tvb_qmm8_widen: k must be a multiple of 16");
+  TVB_REQUIRE(b != nullptr && scales != nullptr && widened != nullptr && widened_bytes >= tvb_qmm8_widened_bytes(n, k),
+              "tvb_qmm8_widen: NULL pointer or buffer too small");
+  TVB_REQUIRE((reinterpret_cast<uintptr_t>(b) & 15u) == 0 && (reinterpret_cast<uintptr_t>(widened) & 255u) == 0,
+              "tvb_qmm8_widen: B must be 16-byte and the buffer 256-byte aligned");
+  cudaStream_t stream;
+  if (enter(device, &stream) != 0) return -1;
+  return qmm8_widen_into(device, stream, b, scales, dtype, n, k, widened);
+}
+
+extern "C" int tvb_qmm8_widened(int device, const void* a, int dtype, int64_t a_sm, const void* widened, void* c, int64_t m, int64_t n,
+                                int64_t k) {
+  TVB_REQUIRE(dtype == TVB_F16 || dtype == TVB_BF16, "tvb_qmm8_widened: float16 or bfloat16 only");
+  TVB_REQUIRE(m >= 0 && n >= 0 && k >= 16 && k % 16 == 0, "tvb_qmm8_widened: bad size");
+  if (m == 0 || n == 0) return 0;
+  TVB_REQUIRE(a != nullptr && widened != nullptr && c != nullptr, "tvb_qmm8_widened: NULL pointer");
+  cudaStream_t stream;
+  if (enter(device, &stream) != 0) return -1;
+  return qmm8_widened_gemm(device, stream, a, dtype, m == 1 ? k : a_sm, widened, c, m, n, k);
+}
