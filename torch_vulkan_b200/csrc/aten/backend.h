@@ -37,6 +37,10 @@ int enter_device(const at::Tensor& t);
 // raises instead of running on the CPU.
 [[noreturn]] void no_fallback(const char* op, const std::string& why);
 
+// Drops the forms of weights that the ops derive and keep per weight tensor (ops_quant.cpp): prepared int4 weights, widened
+// int8 weights.
+void clear_weight_caches();
+
 void register_backend();
 void shutdown_backend();
 

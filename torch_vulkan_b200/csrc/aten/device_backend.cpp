@@ -396,7 +396,10 @@ void register_backend() {
   at::RegisterPrivateUse1HooksInterface(new VkHooks());
 }
 
-void shutdown_backend() { tvb_shutdown(); }
+void shutdown_backend() {
+  clear_weight_caches();  // (their tensors go back to the pool before the pool goes)
+  tvb_shutdown();
+}
 
 }  // namespace vkb
 

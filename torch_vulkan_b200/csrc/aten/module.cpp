@@ -56,7 +56,13 @@ PYBIND11_MODULE(_native, m) {
   m.def("synchronize", [](int device) { vkb::check(tvb_synchronize(device)); }, py::arg("device") = 0);
   m.def("dispatch_count", [] { return tvb_dispatch_count(); });
   m.def("memory_stats", &memory_stats, py::arg("device") = 0);
-  m.def("empty_cache", [](int device) { vkb::check(tvb_empty_cache(device)); }, py::arg("device") = 0);
+  m.def(
+      "empty_cache",
+      [](int device) {
+        vkb::clear_weight_caches();  // (the derived forms of weights kept by the ops: they are rebuilt on demand)
+        vkb::check(tvb_empty_cache(device));
+      },
+      py::arg("device") = 0);
   m.def("stream", [](int device) { return reinterpret_cast<uintptr_t>(tvb_stream(device)); }, py::arg("device") = 0);
   m.def("set_stream", [](int device, uintptr_t s) { vkb::check(tvb_set_stream(device, reinterpret_cast<void*>(s))); });
   m.def("set_device", [](int device) { vkb::check(tvb_set_device(device)); });

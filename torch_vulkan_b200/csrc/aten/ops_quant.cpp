@@ -404,6 +404,17 @@ at::Tensor scaled_mm(const at::Tensor& mat_a, const at::Tensor& mat_b, const at:
 }
 
 }  // namespace
+
+void clear_weight_caches() {
+  {
+    std::lock_guard<std::mutex> lock(g_prepared_mutex);
+    g_prepared.clear();
+  }
+  std::lock_guard<std::mutex> lock(g_widened_mutex);
+  g_widened.clear();
+  g_widened_bytes = 0;
+}
+
 }  // namespace vkb
 
 TORCH_LIBRARY_IMPL(aten, PrivateUse1, m) {
