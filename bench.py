@@ -351,12 +351,20 @@ def run_only(tv, stream, which, iters):
         fn = lambda: torch._dyn_quant_matmul_4bit(xv, packed, 32, 4096, 14336)  # noqa: E731
         flops = 2.0 * mm * 14336 * 4096
     else:
-        # int8_large_m: the 16-bit GEMM over (cached) widened weights; int8_mid_m: the kernel that widens in its main loop
+        # int8_large_m: the 16-bit GEMM over (cached) widened weights; int8_mid_m: the kernel that widens in its main loop,
+        # which needs no copy of the weights
         m, n, k = (2048 if which == "int8_large_m" else 256), 14336, 4096
         a = torch.randn(m, k, generator=gen(1)).to(torch.bfloat16).to("vk")
         w = torch.randint(-127, 128, (n, k), dtype=torch.int8, generator=gen(2)).to("vk")
         s = (torch.rand(n, generator=gen(3)) * (2e-2 - 1e-3) + 1e-3).to(torch.bfloat16).to("vk")
-        fn = lambda: torch._weight_int8pack_mm(a, w, s)  # noqa: E731
+        if which == "int8_large_m":
+            fn = lambda: torch._weight_int8pack_mm(a, w, s)  # noqa: E731
+        else:
+            # straight through the C ABI, variant 3: the kernel the op falls back to when its budget for widened copies is spent
+            from torch_vulkan_b200 import cabi
+
+            ac, wc, sc_ = tv.as_cuda(a), tv.as_cuda(w), tv.as_cuda(s)
+            fn = lambda: cabi.qmm8(ac, wc, sc_, variant=3)  # noqa: E731
         flops = 2.0 * m * n * k
     fn()
     tv.synchronize()

@@ -961,7 +961,9 @@ extern "C" int tvb_qmm8(int device, const void* a, int dtype, int64_t a_sm, cons
   // the extra pass over the weights pays for itself from about 730 rows on (874 against 1237 TFLOP/s, 3 bytes per weight)
   if (variant == 4 || (variant == 0 && can_widen && m >= 1024))
     return qmm8_widen_gemm(device, stream, a, dtype, a_sm, b, scales, c, m, n, k);
-  if (variant == 3 || (variant == 0 && can_tc && m > 16))
+  // 17-32 rows: two passes of the decode kernel stream the weights twice and still beat one 128-row tensor-core tile
+  const bool two_passes = can_skinny && m <= 32;
+  if (variant == 3 || (variant == 0 && can_tc && m > 16 && !two_passes))
     return qmm8_tc(device, stream, a, dtype, m == 1 ? k : a_sm, b, scales, c, m, n, k);
   if (variant == 2 || (variant == 0 && can_skinny)) {
     int64_t stride = m == 1 ? k : a_sm;  // (one row: any stride will do for the map)
