@@ -155,6 +155,10 @@ def run_reference(args, rank):
     """The reference arm: the CPU kernel the reference falls back to (crates/pyvk/csrc/quant.cpp:77), all host threads."""
     if rank != 0:
         return
+    # torchrun gives every rank OMP_NUM_THREADS=1; this arm is rank 0 alone and takes the host's cores
+    host_threads = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    if torch.get_num_threads() < host_threads:
+        torch.set_num_threads(host_threads)
     a, w, s = make_inputs(N_OUT)
     step_bytes = sum(algorithmic_bytes(m, N_OUT, K_IN) for m in MS)
     for _ in range(max(args.warmup, 1)):
