@@ -269,6 +269,14 @@ TVB_API int tvb_scaled_mm(int device, const void* a, int a_dtype, int64_t a_s0, 
 TVB_API int tvb_mm(int device, const void* a, int dtype, int64_t a_s0, int64_t a_s1, const void* b, int64_t b_s0, int64_t b_s1,
            const void* bias, int bias_dtype, void* out, int out_dtype, int64_t m, int64_t n, int64_t k, int variant);
 
+/* The same product with a matrix added before the one rounding: out = A @ B (+ bias[n]) + residual[m, n], the form
+ * aten::addmm takes with a full `self` (a decoder block's residual stream added in the product's epilogue instead of by
+ * a kernel of its own). Row i of the residual starts residual_ld elements after row i - 1 (>= n); its dtype is one of
+ * the three floats and need not be the operands'. residual == NULL: tvb_mm. `out` may be the residual itself. */
+TVB_API int tvb_addmm(int device, const void* a, int dtype, int64_t a_s0, int64_t a_s1, const void* b, int64_t b_s0, int64_t b_s1,
+              const void* bias, int bias_dtype, const void* residual, int residual_dtype, int64_t residual_ld, void* out,
+              int out_dtype, int64_t m, int64_t n, int64_t k, int variant);
+
 #ifdef __cplusplus
 }
 #endif

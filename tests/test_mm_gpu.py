@@ -50,6 +50,61 @@ def test_tvb_mm_tensor_core_kernel(dtype, m, k, n):
     assert ((plain.double() - want).abs() <= tol).all()
 
 
+def raw_addmm(a, b, residual, variant, out=None):
+    m, k = a.shape
+    n = b.shape[1]
+    out = torch.empty(m, n, dtype=a.dtype, device="vk") if out is None else out
+    code = cabi._dtype_code(a.dtype)
+    cabi.check(cabi.lib().tvb_addmm(0, a.data_ptr(), code, a.stride(0), a.stride(1), b.data_ptr(), b.stride(0), b.stride(1),
+                                    None, code, residual.data_ptr(), cabi._dtype_code(residual.dtype), residual.stride(0),
+                                    out.data_ptr(), code, m, n, k, variant))
+    cabi.synchronize()
+    return out.cpu()
+
+
+@pytest.mark.parametrize("dtype,res_dtype", [(torch.bfloat16, torch.bfloat16), (torch.float16, torch.float16),
+                                             (torch.bfloat16, torch.float32)])
+@pytest.mark.parametrize("m,k,n", [(128, 64, 256), (300, 520, 1000), (129, 72, 264), (260, 128, 77)])
+def test_tvb_addmm_residual_in_the_epilogue(dtype, res_dtype, m, k, n):
+    a = torch.randn(m, k, generator=gen(11)).to(dtype)
+    w = torch.randn(n, k, generator=gen(12)).to(dtype)
+    res = (torch.randn(m, n, generator=gen(13)) * 4).to(res_dtype)
+    want, tol = bound(a, w.t(), dtype)
+    want = want + res.double()
+    tol = tol + EPS[dtype] * res.double().abs()
+    for variant in (2, 1):
+        got = raw_addmm(a.to("vk"), w.to("vk").t(), res.to("vk"), variant)
+        assert ((got.double() - want).abs() <= tol).all(), variant
+    # rows of the residual further apart than n (a slice of a wider matrix), and the output written over the residual
+    wide = torch.zeros(m, n + 24, dtype=res_dtype)
+    wide[:, 8:8 + n] = res
+    got = raw_addmm(a.to("vk"), w.to("vk").t(), wide.to("vk")[:, 8:8 + n], 2)
+    assert ((got.double() - want).abs() <= tol).all()
+    if res_dtype == dtype:
+        inplace = res.to("vk")
+        got = raw_addmm(a.to("vk"), w.to("vk").t(), inplace, 2, out=inplace)
+        assert ((got.double() - want).abs() <= tol).all()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_aten_addmm_with_a_matrix(dtype):
+    for m, k, n in ((5, 7, 3), (256, 512, 1024), (1, 64, 48)):
+        a = torch.randn(m, k, generator=gen(14)).to(dtype)
+        b = torch.randn(k, n, generator=gen(15)).to(dtype)
+        res = torch.randn(m, n, generator=gen(16)).to(dtype)
+        want, tol = bound(a, b, dtype)
+        want = want + res.double()
+        tol = tol + EPS[dtype] * res.double().abs()
+        got = torch.addmm(res.to("vk"), a.to("vk"), b.to("vk")).cpu()
+        assert got.shape == (m, n) and ((got.double() - want).abs() <= tol).all()
+        res_t = res.t().contiguous().to("vk").t()  # a column-major residual is copied to rows first
+        got = torch.addmm(res_t, a.to("vk"), b.to("vk")).cpu()
+        assert ((got.double() - want).abs() <= tol).all()
+        stream = res.to("vk")  # x = x + a @ b, written over x
+        torch.addmm(stream, a.to("vk"), b.to("vk"), out=stream)
+        assert ((stream.cpu().double() - want).abs() <= tol).all()
+
+
 def test_tvb_mm_rejects_what_it_cannot_take():
     a = torch.randn(16, 32).to("vk")
     b = torch.randn(32, 8).to("vk")
@@ -90,7 +145,7 @@ def test_aten_mm_errors():
     with pytest.raises(NotImplementedError):
         torch.mm(a.to(torch.int32), a.t().contiguous().to(torch.int32))
     with pytest.raises(NotImplementedError):
-        torch.addmm(torch.randn(4, 3).to("vk"), a, torch.randn(5, 3).to("vk"))  # a full matrix is not a bias
+        torch.addmm(torch.randn(4, 1).to("vk"), a, torch.randn(5, 3).to("vk"))  # neither a bias vector nor a full matrix
     with pytest.raises(NotImplementedError):
         torch.addmm(torch.randn(3).to("vk"), a, torch.randn(5, 3).to("vk"), beta=0.5)
 

@@ -53,6 +53,7 @@ SIGNATURES = {
     "tvb_qmm8_widen": (_i, [_i, _vp, _vp, _i, _i64, _i64, _vp, _u64]),
     "tvb_qmm8_widened": (_i, [_i, _vp, _i, _i64, _vp, _vp, _i64, _i64, _i64]),
     "tvb_mm": (_i, [_i, _vp, _i, _i64, _i64, _vp, _i64, _i64, _vp, _i, _vp, _i, _i64, _i64, _i64, _i]),
+    "tvb_addmm": (_i, [_i, _vp, _i, _i64, _i64, _vp, _i64, _i64, _vp, _i, _vp, _i, _i64, _vp, _i, _i64, _i64, _i64, _i]),
     "tvb_qmm8": (_i, [_i, _vp, _i, _i64, _vp, _vp, _vp, _i64, _i64, _i64, _i]),
     "tvb_qmm8_gather": (_i, [_i, _vp, _i, _i64, _vp, _vp, _c.POINTER(_vp), _c.POINTER(_vp), _i, _i, _vp, _i64, _i64, _i64]),
     "tvb_wait_flags": (_i, [_i, _vp, _i, _vp]),

@@ -24,8 +24,10 @@ void check_operands(const char* op, const at::Tensor& a, const at::Tensor& b) {
     no_fallback(op, std::string("no kernel multiplies ") + c10::toString(a.scalar_type()) + " matrices");
 }
 
-// out = a @ b (+ bias): `bias` is undefined or a vector of n values.
-void product(const at::Tensor& a_in, const at::Tensor& b_in, const at::Tensor& bias, at::Tensor& out) {
+// out = a @ b (+ bias) (+ residual): `bias` is undefined or a vector of n values, `residual` undefined or an [m, n] matrix
+// (which may be `out` itself: every element is read by the thread that then writes it).
+void product(const at::Tensor& a_in, const at::Tensor& b_in, const at::Tensor& bias, const at::Tensor& residual_in,
+             at::Tensor& out) {
   const int64_t M = a_in.size(0), K = a_in.size(1), N = b_in.size(1);
   at::native::resize_output(out, {M, N});
   if (out.numel() == 0) return;
@@ -39,6 +41,8 @@ void product(const at::Tensor& a_in, const at::Tensor& b_in, const at::Tensor& b
     if (a.stride(1) != 1 || a.stride(0) % 8 != 0 || a.stride(0) < K) a = a.contiguous();
     if (b.stride(0) != 1 || b.stride(1) % 8 != 0 || b.stride(1) < K) b = b.t().contiguous().t();
   }
+  at::Tensor residual = residual_in;
+  if (residual.defined() && M > 1 && (residual.stride(1) != 1 || residual.stride(0) < N)) residual = residual.contiguous();
   at::Tensor dst = out.is_contiguous() ? out : at::empty({M, N}, out.options());
   at::Tensor bv;
   int bias_dtype = TVB_F32;
@@ -47,9 +51,11 @@ void product(const at::Tensor& a_in, const at::Tensor& b_in, const at::Tensor& b
     bias_dtype = dtype_code(bv.scalar_type());
   }
   const int dev = enter_device(a);
-  check(tvb_mm(dev, gpu_address(a), d, a.stride(0), a.stride(1), gpu_address(b), b.stride(0), b.stride(1),
-               bias.defined() ? gpu_address(bv) : nullptr, bias_dtype, gpu_address_out(dst), dtype_code(out.scalar_type()), M, N, K,
-               0));
+  check(tvb_addmm(dev, gpu_address(a), d, a.stride(0), a.stride(1), gpu_address(b), b.stride(0), b.stride(1),
+                  bias.defined() ? gpu_address(bv) : nullptr, bias_dtype, residual.defined() ? gpu_address(residual) : nullptr,
+                  residual.defined() ? dtype_code(residual.scalar_type()) : TVB_F32,
+                  residual.defined() ? (M > 1 ? residual.stride(0) : N) : 0, gpu_address_out(dst), dtype_code(out.scalar_type()), M,
+                  N, K, 0));
   if (!dst.is_same(out)) out.copy_(dst);
 }
 
@@ -58,7 +64,7 @@ at::Tensor& mm_out(const at::Tensor& self, const at::Tensor& mat2, at::Tensor& o
   TORCH_CHECK(out.scalar_type() == self.scalar_type(), "Expected out tensor to have dtype ", self.scalar_type(), ", but got ",
               out.scalar_type(), " instead");
   if (!is_vk(out)) no_fallback("aten::mm", "out is not on \"vk\"");
-  product(self, mat2, at::Tensor(), out);
+  product(self, mat2, at::Tensor(), at::Tensor(), out);
   return out;
 }
 
@@ -74,13 +80,17 @@ at::Tensor& addmm_out(const at::Tensor& self, const at::Tensor& mat1, const at::
               " and ", mat1.scalar_type());
   if (!is_vk(self) || !is_vk(out)) no_fallback("aten::addmm", "an operand is not on \"vk\"");
   const int64_t N = mat2.size(1);
-  // what a Linear passes: its bias, one value per output column, beta = alpha = 1
+  const int64_t M = mat1.size(0);
+  // what a Linear passes: its bias, one value per output column; or a full matrix (the residual stream a block adds its
+  // projection to); beta = alpha = 1 either way
   const bool row_bias = (self.dim() == 1 && self.size(0) == N) || (self.dim() == 2 && self.size(0) == 1 && self.size(1) == N);
-  TORCH_CHECK_NOT_IMPLEMENTED(row_bias && beta.to<double>() == 1.0 && alpha.to<double>() == 1.0,
-                              "aten::addmm on device \"vk\": only a bias vector of ", N,
-                              " values with beta = alpha = 1 is implemented (got self of shape ", self.sizes(), ")");
+  const bool matrix = self.dim() == 2 && self.size(0) == M && self.size(1) == N;
+  TORCH_CHECK_NOT_IMPLEMENTED((row_bias || matrix) && beta.to<double>() == 1.0 && alpha.to<double>() == 1.0,
+                              "aten::addmm on device \"vk\": only a bias vector of ", N, " values or a matrix of ", M, " x ", N,
+                              " with beta = alpha = 1 is implemented (got self of shape ", self.sizes(), ")");
   TORCH_CHECK(out.scalar_type() == mat1.scalar_type(), "Expected out tensor to have dtype ", mat1.scalar_type());
-  product(mat1, mat2, self.reshape({N}), out);
+  if (row_bias) product(mat1, mat2, self.reshape({N}), at::Tensor(), out);
+  else product(mat1, mat2, at::Tensor(), self, out);
   return out;
 }
 

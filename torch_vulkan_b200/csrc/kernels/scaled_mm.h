@@ -15,10 +15,12 @@ struct ScaledMmParams {
   const float* scale_b;  // 1 or n values
   const void* bias;      // n values of bias_dtype, or NULL
   const float* scale_result;  // 1 value or NULL (float8 outputs only)
+  const void* residual;  // [m, n] of residual_dtype added to the product before the rounding (row i at residual + i * residual_ld), or NULL
   void* out;             // contiguous [m, n] of out_dtype
   int64_t m, n, k;
   int64_t a_s0, a_s1, b_s0, b_s1;
-  int a_dtype, b_dtype, bias_dtype, out_dtype, rowwise;
+  int64_t residual_ld;
+  int a_dtype, b_dtype, bias_dtype, out_dtype, rowwise, residual_dtype;
 };
 
 int scaled_mm_plain(cudaStream_t stream, const ScaledMmParams& p);

@@ -80,6 +80,7 @@ __global__ void __launch_bounds__(256) scaled_mm_plain_kernel(const ScaledMmPara
       if (gn >= p.n) continue;
       float v = acc[i][j];
       if (p.bias != nullptr) v += load_float_rt(p.bias, gn, p.bias_dtype);
+      if (p.residual != nullptr) v += load_float_rt(p.residual, gm * p.residual_ld + gn, p.residual_dtype);
       if (f8_out) v *= inv;
       store_float_rt(p.out, gm * p.n + gn, p.out_dtype, v);
     }

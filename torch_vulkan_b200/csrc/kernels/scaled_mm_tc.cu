@@ -24,15 +24,18 @@ namespace {
 
 constexpr int kBN = 256;
 
-template <int WARPS>
+// RES: the instantiation that also adds a residual matrix (aten::addmm with a full `self`); the others carry no code for it.
+template <int WARPS, bool RES>
 struct ScaledEpilogueT {
   struct Params {
     const float* scale_a;
     const float* scale_b;
     const void* bias;
     const float* scale_result;
+    const void* residual;
+    int64_t residual_ld;
     void* out;
-    int bias_dtype, out_dtype, rowwise, vector_ok;
+    int bias_dtype, out_dtype, rowwise, vector_ok, residual_dtype, residual_vector_ok;
   };
   static constexpr int kSmemBytes = WARPS * kBN * 2 * 4;  // per epilogue warp: column scales and biases of the tile
 
@@ -54,6 +57,42 @@ struct ScaledEpilogueT {
     __syncwarp();
   }
 
+  // v += the 32 values of the residual's row `row` from column `col` on (times `inv`, as the product was): 16-byte loads
+  // where the row segment is aligned and whole, one value at a time at the matrix's ragged edge.
+  __device__ static void add_residual(const Params& p, int row, int col, int n, float inv, float (&v)[32]) {
+    const int64_t r = static_cast<int64_t>(row) * p.residual_ld + col;
+    if (p.residual_vector_ok && col + 32 <= n) {
+      if (p.residual_dtype == TVB_F32) {
+        const float4* src = reinterpret_cast<const float4*>(static_cast<const float*>(p.residual) + r);
+#pragma unroll
+        for (int q = 0; q < 8; q++) {
+          const float4 x = src[q];
+          v[4 * q] += x.x * inv; v[4 * q + 1] += x.y * inv; v[4 * q + 2] += x.z * inv; v[4 * q + 3] += x.w * inv;
+        }
+        return;
+      }
+      if (p.residual_dtype == TVB_BF16 || p.residual_dtype == TVB_F16) {
+        const uint4* src = reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(p.residual) + r);
+#pragma unroll
+        for (int q = 0; q < 4; q++) {
+          const uint4 x = src[q];
+          const uint32_t w[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+          for (int j = 0; j < 4; j++) {
+            float2 f;
+            if (p.residual_dtype == TVB_BF16) f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[j]));
+            else f = __half22float2(*reinterpret_cast<const __half2*>(&w[j]));
+            v[q * 8 + 2 * j] += f.x * inv;
+            v[q * 8 + 2 * j + 1] += f.y * inv;
+          }
+        }
+        return;
+      }
+    }
+    for (int i = 0; i < 32; i++)
+      if (col + i < n) v[i] += load_float_rt(p.residual, r + i, p.residual_dtype) * inv;
+  }
+
   __device__ static void store(const Params& p, const uint8_t* smem, int row, int col_tile0, int col_off,
                                const uint32_t (&acc)[32], int m, int n) {
     if (row >= m) return;
@@ -71,6 +110,7 @@ struct ScaledEpilogueT {
     }
     const int col = col_tile0 + col_off;
     const int64_t o = static_cast<int64_t>(row) * n + col;
+    if constexpr (RES) add_residual(p, row, col, n, inv, v);
     if (p.vector_ok && col + 32 <= n) {
       if (p.out_dtype == TVB_BF16) {
         uint4* dst = reinterpret_cast<uint4*>(static_cast<uint16_t*>(p.out) + o);
@@ -109,9 +149,9 @@ bool scaled_mm_tc_usable(const ScaledMmParams& p) {
          p.k < (int64_t(1) << 30);
 }
 
-template <int KIND, int BM>
+template <int KIND, int BM, bool RES>
 int scaled_mm_tc_tile(int device, cudaStream_t stream, const ScaledMmParams& p) {
-  using ScaledEpilogue = ScaledEpilogueT<BM / 32>;
+  using ScaledEpilogue = ScaledEpilogueT<BM / 32, RES>;
   using Cfg = GemmTcCfg<kBN, ScaledEpilogue::kSmemBytes, BM>;
   auto kernel = gemm_tc_kernel<KIND, kBN, ScaledEpilogue, BM>;
   static bool configured[64] = {};
@@ -144,6 +184,11 @@ int scaled_mm_tc_tile(int device, cudaStream_t stream, const ScaledMmParams& p) 
   ep.out_dtype = p.out_dtype;
   ep.rowwise = p.rowwise;
   ep.vector_ok = (reinterpret_cast<uintptr_t>(p.out) & 15u) == 0 && (p.n * dtype_size(p.out_dtype)) % 16 == 0;
+  ep.residual = p.residual;
+  ep.residual_ld = p.residual_ld;
+  ep.residual_dtype = p.residual_dtype;
+  ep.residual_vector_ok = p.residual != nullptr && (reinterpret_cast<uintptr_t>(p.residual) & 15u) == 0 &&
+                          (p.residual_ld * dtype_size(p.residual_dtype)) % 16 == 0;
   // operand formats: kind::f8f6f4 0 = e4m3, 1 = e5m2; kind::f16 0 = float16, 1 = bfloat16; float32 accumulators
   const uint32_t fa = KIND == 0 ? (p.a_dtype == TVB_E4M3 ? 0 : 1) : (p.a_dtype == TVB_F16 ? 0 : 1);
   const uint32_t fb = KIND == 0 ? (p.b_dtype == TVB_E4M3 ? 0 : 1) : (p.b_dtype == TVB_F16 ? 0 : 1);
@@ -171,7 +216,12 @@ int scaled_mm_tc_kind(int device, cudaStream_t stream, const ScaledMmParams& p) 
   bool big = p.m > 128 && waves_cost(256) < waves_cost(128);
   if (forced == 128) big = false;
   if (forced == 256) big = true;
-  return big ? scaled_mm_tc_tile<KIND, 256>(device, stream, p) : scaled_mm_tc_tile<KIND, 128>(device, stream, p);
+  if constexpr (KIND == 2) {  // (only aten::addmm passes a residual, and only 16-bit operands come with one)
+    if (p.residual != nullptr)
+      return big ? scaled_mm_tc_tile<KIND, 256, true>(device, stream, p) : scaled_mm_tc_tile<KIND, 128, true>(device, stream, p);
+  }
+  if (p.residual != nullptr) return fail("scaled_mm_tc: a residual goes with 16-bit operands only");
+  return big ? scaled_mm_tc_tile<KIND, 256, false>(device, stream, p) : scaled_mm_tc_tile<KIND, 128, false>(device, stream, p);
 }
 
 int scaled_mm_tc(int device, cudaStream_t stream, const ScaledMmParams& p) {
@@ -211,11 +261,14 @@ extern "C" int tvb_scaled_mm(int device, const void* a, int a_dtype, int64_t a_s
   return scaled_mm_plain(stream, p);
 }
 
-extern "C" int tvb_mm(int device, const void* a, int dtype, int64_t a_s0, int64_t a_s1, const void* b, int64_t b_s0, int64_t b_s1,
-                      const void* bias, int bias_dtype, void* out, int out_dtype, int64_t m, int64_t n, int64_t k, int variant) {
+extern "C" int tvb_addmm(int device, const void* a, int dtype, int64_t a_s0, int64_t a_s1, const void* b, int64_t b_s0,
+                         int64_t b_s1, const void* bias, int bias_dtype, const void* residual, int residual_dtype,
+                         int64_t residual_ld, void* out, int out_dtype, int64_t m, int64_t n, int64_t k, int variant) {
   auto is_float = [](int dt) { return dt == TVB_F32 || dt == TVB_F16 || dt == TVB_BF16; };
   TVB_REQUIRE(is_float(dtype) && is_float(out_dtype), "tvb_mm: float32, float16 or bfloat16 only");
   TVB_REQUIRE(bias == nullptr || is_float(bias_dtype), "tvb_mm: the bias must be float32, float16 or bfloat16");
+  TVB_REQUIRE(residual == nullptr || (is_float(residual_dtype) && residual_ld >= n),
+              "tvb_addmm: the residual must be float32, float16 or bfloat16 with rows at least n apart");
   TVB_REQUIRE(m >= 0 && n >= 0 && k >= 0, "tvb_mm: negative size");
   TVB_REQUIRE(variant >= 0 && variant <= 2, "tvb_mm: unknown kernel variant");
   if (m == 0 || n == 0) return 0;
@@ -224,6 +277,7 @@ extern "C" int tvb_mm(int device, const void* a, int dtype, int64_t a_s0, int64_
   if (enter(device, &stream) != 0) return -1;
   ScaledMmParams p{};
   p.a = a; p.b = b; p.bias = bias; p.out = out;
+  p.residual = residual; p.residual_dtype = residual_dtype; p.residual_ld = residual_ld;
   p.m = m; p.n = n; p.k = k;
   p.a_s0 = a_s0; p.a_s1 = a_s1; p.b_s0 = b_s0; p.b_s1 = b_s1;
   p.a_dtype = dtype; p.b_dtype = dtype; p.bias_dtype = bias_dtype; p.out_dtype = out_dtype;
@@ -232,4 +286,10 @@ extern "C" int tvb_mm(int device, const void* a, int dtype, int64_t a_s0, int64_
   const bool big = m * n >= int64_t(128) * 256 * 8 && k >= 64;
   if (variant == 2 || (variant == 0 && usable && big)) return scaled_mm_tc(device, stream, p);
   return scaled_mm_plain(stream, p);
+}
+
+extern "C" int tvb_mm(int device, const void* a, int dtype, int64_t a_s0, int64_t a_s1, const void* b, int64_t b_s0, int64_t b_s1,
+                      const void* bias, int bias_dtype, void* out, int out_dtype, int64_t m, int64_t n, int64_t k, int variant) {
+  return tvb_addmm(device, a, dtype, a_s0, a_s1, b, b_s0, b_s1, bias, bias_dtype, nullptr, TVB_F32, 0, out, out_dtype, m, n, k,
+                   variant);
 }
