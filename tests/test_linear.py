@@ -58,6 +58,10 @@ def test_int8_linear_cpu_forward(dtype):
     want = x @ (q.float() * s.to(dtype).float()[:, None]).t() + lin.bias.to(dtype).float()
     tol = {torch.float32: 1e-4, torch.bfloat16: 2e-2, torch.float16: 4e-3}[dtype]
     assert ((y.float() - want).abs() <= tol * want.abs().max()).all()
+    res = torch.randn(2, 5, 96, generator=torch.Generator().manual_seed(5)).to(dtype)
+    assert torch.equal(mod(x.to(dtype), residual=res), y + res)
+    with pytest.raises(ValueError):
+        mod(x.to(dtype), residual=res[0])
     with pytest.raises(TypeError):
         mod(x.to(torch.float64))
 
@@ -160,10 +164,33 @@ def test_add_bias_on_vk_and_its_limits():
     v = y.to("vk")[:, :8]  # a strided view: rows are 12 apart
     v += b[:8].to("vk")
     assert torch.equal(v.cpu(), y[:, :8] + b[:8])
+    r = torch.randn(5, 12, generator=torch.Generator().manual_seed(10)).to(torch.bfloat16)
+    assert torch.equal((y.to("vk") + r.to("vk")).cpu(), y + r)  # a tensor of the same shape: the residual stream
+    y3 = torch.randn(2, 3, 8, generator=torch.Generator().manual_seed(11))
+    got3 = y3.to("vk")
+    got3 += (y3 * 2).to("vk")
+    assert torch.equal(got3.cpu(), y3 + y3 * 2)
     with pytest.raises(NotImplementedError):
-        y.to("vk") + y.to("vk")  # only a bias vector is implemented
+        y.to("vk") + y[:, :1].to("vk")  # no broadcasting other than a bias vector
+    with pytest.raises(NotImplementedError):
+        y.to("vk")[:, :8] + r.to("vk")[:, :8]  # same shape, but not contiguous
     with pytest.raises(NotImplementedError):
         torch.add(y.to("vk"), b.to("vk"), alpha=2)
+
+
+@pytest.mark.gpu
+def test_linears_add_the_residual_on_vk():
+    lin = make_linear(512, 384)
+    x = torch.randn(2, 5, 512, generator=torch.Generator().manual_seed(21))
+    res = torch.randn(2, 5, 384, generator=torch.Generator().manual_seed(22))
+    i8 = L.Int8Linear.from_float(lin, dtype=torch.bfloat16).to("vk")
+    xb, rb = x.to(torch.bfloat16).to("vk"), res.to(torch.bfloat16)
+    assert torch.equal(i8(xb, residual=rb.to("vk")).cpu(), i8(xb).cpu() + rb)  # the same two roundings as the two steps
+    i4 = L.DynInt4Linear.from_float(lin, block_size=32, device="vk")
+    i4_cpu = L.DynInt4Linear.from_float(lin, block_size=32)
+    assert torch.equal(i4(x.to("vk"), residual=res.to("vk")).cpu(), i4_cpu(x, residual=res.clone()))
+    with pytest.raises(ValueError):
+        i4(x.to("vk"), residual=res[:1].to("vk"))
 
 
 @pytest.mark.gpu

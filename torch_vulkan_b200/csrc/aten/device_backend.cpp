@@ -338,19 +338,25 @@ at::Tensor& zero_(at::Tensor& self) { return fill_scalar(self, 0); }
 
 // ---------------------------------------------------------------- bias
 
-// self += other for the one shape a quantised Linear needs: `other` a vector over self's last dimension (its bias),
-// alpha 1, floating dtypes. Anything else is not implemented on this device (and is never run on the CPU instead).
+// self += other for the two shapes a quantised Linear needs: `other` a vector over self's last dimension (its bias), or
+// a contiguous tensor of self's own shape (the residual stream its output joins); alpha 1, floating dtypes. Anything else
+// is not implemented on this device (and is never run on the CPU instead).
 at::Tensor& add_rowvec_(at::Tensor& self, const at::Tensor& other, const at::Scalar& alpha) {
   TORCH_CHECK_NOT_IMPLEMENTED(is_vk(self) && is_vk(other) && self.device() == other.device(),
                               "add_ on device \"vk\": both tensors must be on the same \"vk\" device");
   TORCH_CHECK_NOT_IMPLEMENTED(alpha.to<double>() == 1.0, "add_ on device \"vk\": only alpha = 1 is implemented");
-  TORCH_CHECK_NOT_IMPLEMENTED(self.dim() >= 1 && other.dim() == 1 && other.size(0) == self.size(-1) && other.is_contiguous(),
-                              "add_ on device \"vk\": only a contiguous vector over the last dimension (a bias) can be added, got ",
-                              self.sizes(), " += ", other.sizes());
+  const bool same_shape = self.dim() >= 2 && other.sizes() == self.sizes() && self.is_contiguous() && other.is_contiguous();
+  TORCH_CHECK_NOT_IMPLEMENTED(same_shape || (self.dim() >= 1 && other.dim() == 1 && other.size(0) == self.size(-1) && other.is_contiguous()),
+                              "add_ on device \"vk\": only a contiguous vector over the last dimension (a bias) or a contiguous "
+                              "tensor of the same shape can be added, got ", self.sizes(), " += ", other.sizes());
   const int cd = dtype_code(self.scalar_type()), vd = dtype_code(other.scalar_type());
   TORCH_CHECK_NOT_IMPLEMENTED(at::isFloatingType(self.scalar_type()) && at::isFloatingType(other.scalar_type()) && cd >= 0 && vd >= 0,
                               "add_ on device \"vk\": floating dtypes only");
   if (self.numel() == 0) return self;
+  if (same_shape) {  // one row of numel values
+    check(tvb_add_rowvec(self.device().index(), gpu_address_out(self), cd, self.numel(), gpu_address(other), vd, 1, self.numel()));
+    return self;
+  }
   const int64_t n = self.size(-1);
   TORCH_CHECK_NOT_IMPLEMENTED(self.stride(-1) == 1, "add_ on device \"vk\": the last dimension must be dense");
   if (self.dim() <= 2) {
@@ -365,6 +371,9 @@ at::Tensor& add_rowvec_(at::Tensor& self, const at::Tensor& other, const at::Sca
 }
 
 at::Tensor add_rowvec(const at::Tensor& self, const at::Tensor& other, const at::Scalar& alpha) {
+  // (the result of two dtypes would take the promoted one; only the in-place form, which keeps self's, mixes them)
+  TORCH_CHECK_NOT_IMPLEMENTED(self.scalar_type() == other.scalar_type(), "add on device \"vk\": both tensors must have one dtype, got ",
+                              self.scalar_type(), " and ", other.scalar_type());
   at::Tensor out = at::empty_like(self, at::MemoryFormat::Contiguous);
   out.copy_(self);
   return add_rowvec_(out, other, alpha);

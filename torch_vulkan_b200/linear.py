@@ -53,6 +53,15 @@ class _ShardedMixin:
             return y_local
         return _shard.all_gather_columns(y_local, self._group)
 
+    def _finish(self, y_local, lead, residual):
+        """The full output in the caller's shape, with the residual stream (a tensor of that shape) added in place."""
+        y = self._gather(y_local).reshape(*lead, self.full_out_features)
+        if residual is not None:
+            if residual.shape != y.shape:
+                raise ValueError(f"residual of shape {tuple(residual.shape)} for an output of shape {tuple(y.shape)}")
+            y += residual.contiguous()
+        return y
+
 
 class Int8Linear(nn.Module, _ShardedMixin):
     """y = x @ (weight_int8 * scales[:, None]).T + bias through aten::_weight_int8pack_mm.
@@ -83,7 +92,8 @@ class Int8Linear(nn.Module, _ShardedMixin):
         out.rank, out.world, out._group, out.full_out_features = rank, world, group, self.out_features
         return out
 
-    def forward(self, x):
+    def forward(self, x, residual=None):
+        """`residual`: a tensor of the output's shape added to it (x + proj(h) of a decoder block in one call)."""
         lead = x.shape[:-1]
         x2 = x.reshape(-1, self.in_features)
         if x2.dtype != self.scales.dtype:
@@ -91,7 +101,7 @@ class Int8Linear(nn.Module, _ShardedMixin):
         y = torch._weight_int8pack_mm(x2, self.weight, self.scales)
         if self.bias is not None:
             y += self.bias
-        return self._gather(y).reshape(*lead, self.full_out_features)
+        return self._finish(y, lead, residual)
 
     def extra_repr(self):
         return (f"in_features={self.in_features}, out_features={self.full_out_features}, bias={self.bias is not None}, "
@@ -136,11 +146,11 @@ class DynInt4Linear(nn.Module, _ShardedMixin):
         out.rank, out.world, out._group, out.full_out_features = rank, world, group, self.out_features
         return out
 
-    def forward(self, x):
+    def forward(self, x, residual=None):
         lead = x.shape[:-1]
         x2 = x.reshape(-1, self.in_features)
         y = torch._dyn_quant_matmul_4bit(x2, self.packed, self.block_size, self.in_features, self.out_features)
-        return self._gather(y).reshape(*lead, self.full_out_features)
+        return self._finish(y, lead, residual)
 
     def extra_repr(self):
         return (f"in_features={self.in_features}, out_features={self.full_out_features}, block_size={self.block_size}"
