@@ -312,6 +312,45 @@ def int8_stack(tv, stream, layers=32):
         out[f"int8_stack_32layers_m{m}"] = {"ms_per_token_step": ms, "weight_gbs": wbytes / ms / 1e6, "products": 4 * layers,
                                              "weight_bytes": wbytes}
         del graph
+
+        # The same stack with its two residual additions (after o and after down): in the decode kernel's epilogue
+        # (tvb_qmm8_linear, 128 launches per step) against a product and an add each (192 launches).
+        def step_residual(fused):
+            from torch_vulkan_b200 import _native
+
+            def run():
+                keep, h = [], x
+                for (wq, sq), (wo, so), (wg, sg), (wd, sd) in weights:
+                    qkv = torch._weight_int8pack_mm(h, wq, sq)
+                    if fused:
+                        o = _native.int8_linear(qkv[:, :4096], wo, so, None, h)
+                    else:
+                        o = torch._weight_int8pack_mm(qkv[:, :4096], wo, so)
+                        o += h
+                    gu = torch._weight_int8pack_mm(o, wg, sg)
+                    if fused:
+                        h = _native.int8_linear(gu[:, :14336], wd, sd, None, o)
+                    else:
+                        h = torch._weight_int8pack_mm(gu[:, :14336], wd, sd)
+                        h += o
+                    keep += [qkv, o, gu, h]
+                return keep
+
+            return run
+
+        for label, fused in (("residual_in_epilogue", True), ("residual_as_own_launch", False)):
+            graph = shard.StepGraph(step_residual(fused))
+            for _ in range(3):
+                graph.replay()
+            tv.synchronize()
+            s0, e0 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s0.record(stream)
+            for _ in range(iters):
+                graph.replay()
+            e0.record(stream)
+            tv.synchronize()
+            out[f"int8_stack_32layers_m{m}"][label + "_ms"] = s0.elapsed_time(e0) / iters
+            del graph
     del weights
     tv.empty_cache()
     return out

@@ -168,6 +168,16 @@ TVB_API int tvb_wait_flags(int device, const uint32_t* flags, int world, uint32_
 TVB_API int tvb_ipc_export(int device, const void* ptr, uint8_t* handle64, uint64_t* offset);
 TVB_API int tvb_ipc_import(int device, const uint8_t* handle64, uint64_t offset, void** out);
 
+/* A Linear over the same product: c = round(round(round(A @ (B * scales).T) + bias[n]) + residual[m, n]), every sum rounded
+ * to A's dtype as the separate steps (tvb_qmm8, tvb_add_rowvec twice) would round it, so the result is bit for bit theirs.
+ * bias and residual are of A's dtype, contiguous, and either may be NULL. With at most 32 rows in a shape the decode
+ * kernel takes (see tvb_qmm8) the adds happen in that kernel's epilogue, where a tile's finished sums are scaled: no
+ * further launch, and c may then be the residual itself (x += proj(h) in place). Any other shape runs the product and
+ * then one pass per operand. The reference has no such entry point (its op stops at the product,
+ * crates/pyvk/csrc/quant.cpp:59-119); this is the caller's next step folded in. */
+TVB_API int tvb_qmm8_linear(int device, const void* a, int dtype, int64_t a_sm, const int8_t* b, const void* scales, const void* bias,
+                    const void* residual, void* c, int64_t m, int64_t n, int64_t k);
+
 /* ---- tvb_qmm8's decode kernel for hosts that must not allocate (no counterpart in the reference) ----
  * Some hosts cannot let a library call cudaMalloc on their behalf: a serving process that handed all of HBM to its own
  * pool at start-up (so any later driver allocation fails), or one whose request path forbids calls that stall the

@@ -149,6 +149,37 @@ def test_qmm8_decode_back_to_back_launches_agree(abi):
         assert torch.equal(out.cpu().view(torch.int16), cases[ci][3]), shapes[ci]
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("m,k,n", [(1, 256, 257), (5, 1024, 300), (16, 2048, 4099), (16, 8192, 8192), (20, 512, 1000),
+                                   (32, 4096, 4096), (8, 14336, 4096), (40, 512, 300), (3, 200, 64)])
+def test_qmm8_linear_equals_product_then_adds(abi, dtype, m, k, n):
+    # bias and residual added where the decode kernel finishes a tile (m <= 32, k a multiple of 128), by further passes
+    # otherwise: either way bit for bit the product followed by the two adds, each rounded to the dtype
+    a, b, s = C.config_int8(m, k, n, dtype, seed=3 * m + n)
+    bias = torch.randn(n, generator=torch.Generator().manual_seed(n)).to(dtype)
+    res = (torch.randn(m, n, generator=torch.Generator().manual_seed(m)) * 4).to(dtype)
+    ad, bd, sd, biasd, resd = dev(a), dev(b), dev(s), dev(bias), dev(res)
+    prod = abi.qmm8(ad, bd, sd)
+    abi.synchronize()
+    prod = prod.cpu()
+    both = abi.qmm8_linear(ad, bd, sd, biasd, resd)
+    only_bias = abi.qmm8_linear(ad, bd, sd, biasd, None)
+    only_res = abi.qmm8_linear(ad, bd, sd, None, resd)
+    neither = abi.qmm8_linear(ad, bd, sd)
+    abi.synchronize()
+    bits = lambda t: t.cpu().view(torch.int16)  # noqa: E731
+    assert torch.equal(bits(neither), bits(prod))
+    assert torch.equal(bits(only_bias), bits(prod + bias))
+    assert torch.equal(bits(only_res), bits(prod + res))
+    assert torch.equal(bits(both), bits((prod + bias) + res))
+    assert torch.equal(resd.cpu(), res)  # (the operands are left alone)
+    if m <= 32 and k % 128 == 0:
+        stream = resd.clone()  # x += proj(h): the output over the residual
+        abi.qmm8_linear(ad, bd, sd, biasd, stream, out=stream)
+        abi.synchronize()
+        assert torch.equal(bits(stream), bits((prod + bias) + res))
+
+
 def test_qmm8_decode_shape_sample(abi):
     # the decode benchmark's k with a slice of its n: every SM's unit range crosses tiles
     a, b, s = C.config_int8(4, 8192, 3584, torch.bfloat16)

@@ -186,6 +186,11 @@ def test_linears_add_the_residual_on_vk():
     i8 = L.Int8Linear.from_float(lin, dtype=torch.bfloat16).to("vk")
     xb, rb = x.to(torch.bfloat16).to("vk"), res.to(torch.bfloat16)
     assert torch.equal(i8(xb, residual=rb.to("vk")).cpu(), i8(xb).cpu() + rb)  # the same two roundings as the two steps
+    many = torch.randn(3, 40, 512, generator=torch.Generator().manual_seed(23)).to(torch.bfloat16)  # more rows than are decoded
+    rmany = torch.randn(3, 40, 384, generator=torch.Generator().manual_seed(24)).to(torch.bfloat16)
+    assert torch.equal(i8(many.to("vk"), residual=rmany.to("vk")).cpu(), i8(many.to("vk")).cpu() + rmany)
+    with pytest.raises(ValueError):
+        i8(xb, residual=rb[:1].to("vk"))
     i4 = L.DynInt4Linear.from_float(lin, block_size=32, device="vk")
     i4_cpu = L.DynInt4Linear.from_float(lin, block_size=32)
     assert torch.equal(i4(x.to("vk"), residual=res.to("vk")).cpu(), i4_cpu(x, residual=res.clone()))

@@ -55,6 +55,7 @@ SIGNATURES = {
     "tvb_mm": (_i, [_i, _vp, _i, _i64, _i64, _vp, _i64, _i64, _vp, _i, _vp, _i, _i64, _i64, _i64, _i]),
     "tvb_addmm": (_i, [_i, _vp, _i, _i64, _i64, _vp, _i64, _i64, _vp, _i, _vp, _i, _i64, _vp, _i, _i64, _i64, _i64, _i]),
     "tvb_qmm8": (_i, [_i, _vp, _i, _i64, _vp, _vp, _vp, _i64, _i64, _i64, _i]),
+    "tvb_qmm8_linear": (_i, [_i, _vp, _i, _i64, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64]),
     "tvb_qmm8_gather": (_i, [_i, _vp, _i, _i64, _vp, _vp, _c.POINTER(_vp), _c.POINTER(_vp), _i, _i, _vp, _i64, _i64, _i64]),
     "tvb_wait_flags": (_i, [_i, _vp, _i, _vp]),
     "tvb_graph_begin": (_i, [_i]),
@@ -144,6 +145,22 @@ def qmm8(a, b, scales, variant=0):
     assert scales.dtype == a.dtype and b.dtype == torch.int8 and b.is_contiguous()
     c = torch.empty((m, n), dtype=a.dtype, device=a.device)
     check(lib().tvb_qmm8(_dev(a), _ptr(a), _dtype_code(a.dtype), a.stride(0), _ptr(b), _ptr(scales), _ptr(c), m, n, k, variant))
+    return c
+
+
+def qmm8_linear(a, b, scales, bias=None, residual=None, out=None):
+    """tvb_qmm8_linear on device tensors: the product of `qmm8`, + bias [n], + residual [m, n] (A's dtype; either may be None).
+    `out` may be the residual itself where the decode kernel runs (at most 32 rows)."""
+    import torch
+
+    m, k = a.shape
+    n = b.shape[0]
+    assert scales.dtype == a.dtype and b.dtype == torch.int8 and b.is_contiguous()
+    assert bias is None or (bias.dtype == a.dtype and bias.shape == (n,) and bias.is_contiguous())
+    assert residual is None or (residual.dtype == a.dtype and residual.shape == (m, n) and residual.is_contiguous())
+    c = torch.empty((m, n), dtype=a.dtype, device=a.device) if out is None else out
+    check(lib().tvb_qmm8_linear(_dev(a), _ptr(a), _dtype_code(a.dtype), a.stride(0), _ptr(b), _ptr(scales), _ptr(bias),
+                                _ptr(residual), _ptr(c), m, n, k))
     return c
 
 

@@ -41,6 +41,11 @@ int enter_device(const at::Tensor& t);
 // int8 weights.
 void clear_weight_caches();
 
+// aten::_weight_int8pack_mm followed by the two adds of a Linear (bias [n], residual [m, n]; either may be undefined), in one
+// launch where the decode kernel runs (ops_quant.cpp).
+at::Tensor int8_linear(const at::Tensor& A, const at::Tensor& B, const at::Tensor& scales, const at::Tensor& bias,
+                       const at::Tensor& residual);
+
 void register_backend();
 void shutdown_backend();
 

@@ -70,5 +70,12 @@ PYBIND11_MODULE(_native, m) {
   m.def("fallback_counts", [] { return std::vector<std::pair<std::string, uint64_t>>(); });
   m.def("as_cuda", [](const at::Tensor& t) { return alias_on(t, vkb::kDevice, c10::DeviceType::CUDA); });
   m.def("from_cuda", [](const at::Tensor& t) { return alias_on(t, c10::DeviceType::CUDA, vkb::kDevice); });
+  m.def(
+      "int8_linear",
+      [](const at::Tensor& a, const at::Tensor& b, const at::Tensor& scales, const std::optional<at::Tensor>& bias,
+         const std::optional<at::Tensor>& residual) {
+        return vkb::int8_linear(a, b, scales, bias.value_or(at::Tensor()), residual.value_or(at::Tensor()));
+      },
+      py::arg("a"), py::arg("b"), py::arg("scales"), py::arg("bias") = py::none(), py::arg("residual") = py::none());
   m.def("shutdown", &vkb::shutdown_backend);
 }

@@ -138,6 +138,44 @@ at::Tensor weight_int8pack_mm(const at::Tensor& A, const at::Tensor& B, const at
   return C;
 }
 
+}  // namespace
+
+// The int8 weight-only Linear in one call: the product, + bias, + residual (each defined or not), rounded step by step as
+// the three ops would. At most 32 rows of 16-bit A: one launch of the decode kernel does all three (tvb_qmm8_linear).
+// More rows: the op above (with its cached widened weights), then the adds.
+at::Tensor int8_linear(const at::Tensor& A, const at::Tensor& B, const at::Tensor& scales, const at::Tensor& bias,
+                       const at::Tensor& residual) {
+  if (!bias.defined() && !residual.defined()) return weight_int8pack_mm(A, B, scales);
+  TORCH_CHECK(A.dim() == 2 && B.dim() == 2 && A.size(1) == B.size(1), "int8_linear: A [m, k] and B [n, k] expected");
+  const int64_t M = A.size(0), N = B.size(0), K = A.size(1);
+  require_vk("int8_linear", {&A, &B, &scales, &bias, &residual});
+  TORCH_CHECK(!bias.defined() || (bias.dim() == 1 && bias.size(0) == N && bias.scalar_type() == A.scalar_type()),
+              "int8_linear: the bias must hold ", N, " values of A's dtype");
+  TORCH_CHECK(!residual.defined() || (residual.dim() == 2 && residual.size(0) == M && residual.size(1) == N &&
+                                      residual.scalar_type() == A.scalar_type()),
+              "int8_linear: the residual must be [", M, ", ", N, "] of A's dtype");
+  const int dt = dtype_code(A.scalar_type());
+  const bool decode = M >= 1 && M <= 32 && (dt == TVB_BF16 || dt == TVB_F16) && A.stride(1) == 1 && B.is_contiguous() &&
+                      B.scalar_type() == at::kChar && scales.dim() == 1 && scales.size(0) == N &&
+                      scales.scalar_type() == A.scalar_type() && scales.is_contiguous();
+  if (!decode) {
+    at::Tensor C = weight_int8pack_mm(A, B, scales);
+    if (bias.defined()) C.add_(bias.contiguous());
+    if (residual.defined()) C.add_(residual.contiguous());
+    return C;
+  }
+  at::Tensor C = at::empty({M, N}, A.options());
+  at::Tensor bv = bias.defined() ? bias.contiguous() : at::Tensor();
+  at::Tensor rv = residual.defined() ? residual.contiguous() : at::Tensor();
+  const int dev = enter_device(A);
+  check(tvb_qmm8_linear(dev, gpu_address(A), dt, A.stride(0), static_cast<const int8_t*>(gpu_address(B)), gpu_address(scales),
+                        bv.defined() ? gpu_address(bv) : nullptr, rv.defined() ? gpu_address(rv) : nullptr, gpu_address_out(C), M,
+                        N, K));
+  return C;
+}
+
+namespace {
+
 // ------------------------------------------------------------------ dynamic int8 x int4
 
 void check_group_size(const char* fn, int64_t block_size, int64_t in_features) {

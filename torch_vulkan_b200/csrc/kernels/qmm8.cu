@@ -214,7 +214,29 @@ struct SkinnyParams {
   int m, n, k;
   int m0;            // first token row of this pass
   int tiles, chunks; // tiles = ceil(n / rows per tile), chunks = k / 128
+  const void* bias;      // n values of A's dtype added to the rounded product (rounded again), or NULL
+  const void* residual;  // [m, c_ld] of A's dtype, laid out like the output, added after the bias (rounded again), or NULL
 };
+
+// What a Linear does after the product, in the thread that holds the finished value: + bias[col], then + residual[token,
+// col], each sum rounded to the output type as the separate kernels would round it (so the fused result is bit for bit
+// that of product, add, add).
+template <int DT>
+__device__ __forceinline__ float half_bits_to_float(uint16_t h) {
+  return DT == TVB_BF16 ? __uint_as_float(static_cast<uint32_t>(h) << 16) : __half2float(__ushort_as_half(h));
+}
+template <int DT>
+__device__ __forceinline__ uint16_t float_to_half_bits(float v) {
+  return DT == TVB_BF16 ? f32_to_bf16_bits(v) : f32_to_f16_bits(v);
+}
+template <int DT>
+__device__ __forceinline__ uint16_t skinny_epilogue(const SkinnyParams& p, uint16_t bits, int token, int col) {
+  if (p.bias != nullptr) bits = float_to_half_bits<DT>(half_bits_to_float<DT>(bits) + load_float<DT>(p.bias, col));
+  if (p.residual != nullptr)
+    bits = float_to_half_bits<DT>(half_bits_to_float<DT>(bits) +
+                                  load_float<DT>(p.residual, static_cast<int64_t>(token) * p.c_ld + p.c_col0 + col));
+  return bits;
+}
 
 // First unit of CTA c when `units` units are cut into `grid` contiguous ranges. (32-bit arithmetic whenever the products
 // fit, which the kernel checks once: 64-bit division is a long instruction sequence, and these run between segments.)
@@ -235,7 +257,9 @@ __device__ __forceinline__ int unit_tile(long long u, int chunks, bool small) {
   return small ? static_cast<int>(static_cast<unsigned>(u) / static_cast<unsigned>(chunks)) : static_cast<int>(u / chunks);
 }
 
-template <int DT, int NT, int RW, int NWARPS>
+// ADDS: the instantiation whose epilogue also adds a bias and a residual (tvb_qmm8_linear); the plain product carries no
+// code for them (with it in one kernel, behind a test of the two pointers, every launch was 0.65 us slower).
+template <int DT, int NT, int RW, int NWARPS, bool ADDS = false>
 __global__ void __launch_bounds__((NWARPS + 2) * 32, 1)
     qmm8_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
                        const SkinnyParams p) {
@@ -377,7 +401,8 @@ __global__ void __launch_bounds__((NWARPS + 2) * 32, 1)
                   const int token = p.m0 + nt * 8 + 2 * t + i;
                   if (token >= p.m) continue;
                   const float v = vals[2 * half + i] * scale;
-                  const uint16_t bits = DT == TVB_BF16 ? f32_to_bf16_bits(v) : f32_to_f16_bits(v);
+                  uint16_t bits = DT == TVB_BF16 ? f32_to_bf16_bits(v) : f32_to_f16_bits(v);
+                  if constexpr (ADDS) bits = skinny_epilogue<DT>(p, bits, token, col);
                   const int64_t off = static_cast<int64_t>(token) * p.c_ld + p.c_col0 + col;
                   for (int r = 0; r < p.nranks; r++) static_cast<uint16_t*>(p.c[r])[off] = bits;
                 }
@@ -425,12 +450,49 @@ __global__ void __launch_bounds__((NWARPS + 2) * 32, 1)
 #pragma unroll
         for (int i = 0; i < 4; i++) acc[rb][nt][i] = pre[rb][nt][i] = 0.0f;
 
+    // This thread's columns' scales, asked for now: each is read once per launch, so the load goes to DRAM, and at the
+    // end of the segment (where the finished sums need it) it would wait in line behind the other SMs' weight traffic.
+    float scale_pre[RW][2];
+#pragma unroll
+    for (int rb = 0; rb < RW; rb++)
+#pragma unroll
+      for (int half = 0; half < 2; half++) {
+        const int col = tile * Cfg::kRowsPerTile + (warp * RW + rb) * 16 + rg + 8 * half;
+        scale_pre[rb][half] = col < p.n ? load_float<DT>(p.scales, col) : 0.0f;
+      }
+    float bias_pre[ADDS ? RW : 1][2];
+    uint16_t residual_pre[ADDS ? RW : 1][NT][4];
+
     for (int chunk = c0; chunk < c1; chunk++, it++) {
       const int s = static_cast<int>(it % Cfg::kStages);
       const uint32_t ph = static_cast<uint32_t>((it / Cfg::kStages) & 1);
       ok = ptx::mbar_wait(full0 + 8 * s, ph, abort_flag);
       if (!ok) break;
       // (past the first stage's barrier the stream's earlier kernels have completed: the producer waited for them)
+      if constexpr (ADDS) {
+        if (chunk == c0) {
+          // the values this thread would add if it finishes the tile, for the same reason asked for early; the residual
+          // may be the previous kernel's output, hence not before that kernel has ended
+          ptx::grid_dependency_wait();
+#pragma unroll
+          for (int rb = 0; rb < RW; rb++)
+#pragma unroll
+            for (int half = 0; half < 2; half++) {
+              const int col = tile * Cfg::kRowsPerTile + (warp * RW + rb) * 16 + rg + 8 * half;
+              bias_pre[rb][half] = p.bias != nullptr && col < p.n ? load_float<DT>(p.bias, col) : 0.0f;
+#pragma unroll
+              for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+                for (int i = 0; i < 2; i++) {
+                  const int token = p.m0 + nt * 8 + 2 * t + i;
+                  residual_pre[rb][nt][2 * half + i] =
+                      p.residual != nullptr && col < p.n && token < p.m
+                          ? static_cast<const uint16_t*>(p.residual)[static_cast<int64_t>(token) * p.c_ld + p.c_col0 + col]
+                          : uint16_t(0);
+                }
+            }
+        }
+      }
       if (may_be_early) {
         if (chunk == c1 - 3) {
           if (threadIdx.x == 0) asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(peeked) : "l"(p.counters + tile) : "memory");
@@ -584,13 +646,19 @@ __global__ void __launch_bounds__((NWARPS + 2) * 32, 1)
         for (int half = 0; half < 2; half++) {
           const int lcol = lrow0 + 8 * half;                       // column within the tile (weight row = output column)
           const int col = tile * Cfg::kRowsPerTile + lcol;
-          const float scale = col < p.n ? load_float<DT>(p.scales, col) : 0.0f;
+          const float scale = scale_pre[rb][half];
 #pragma unroll
           for (int nt = 0; nt < NT; nt++)
 #pragma unroll
             for (int i = 0; i < 2; i++) {
               const float v = acc[rb][nt][2 * half + i] * scale;
-              out_tile[(nt * 8 + 2 * t + i) * Cfg::kRowsPerTile + lcol] = DT == TVB_BF16 ? f32_to_bf16_bits(v) : f32_to_f16_bits(v);
+              uint16_t bits = float_to_half_bits<DT>(v);
+              if constexpr (ADDS) {
+                if (p.bias != nullptr) bits = float_to_half_bits<DT>(half_bits_to_float<DT>(bits) + bias_pre[rb][half]);
+                if (p.residual != nullptr)
+                  bits = float_to_half_bits<DT>(half_bits_to_float<DT>(bits) + half_bits_to_float<DT>(residual_pre[rb][nt][2 * half + i]));
+              }
+              out_tile[(nt * 8 + 2 * t + i) * Cfg::kRowsPerTile + lcol] = bits;
             }
         }
       }
@@ -651,6 +719,12 @@ int launch_plain(cudaStream_t stream, const void* a, int64_t a_sm, const int8_t*
 }
 
 // Destinations of a sharded product (tvb_qmm8_gather): every rank's output buffer and flag array.
+// What tvb_qmm8_linear adds to the product in the decode kernel's epilogue (either may be NULL).
+struct SkinnyAdds {
+  const void* bias;
+  const void* residual;
+};
+
 struct GatherTargets {
   void* c[kMaxRanks];
   uint32_t* flags[kMaxRanks];
@@ -659,11 +733,11 @@ struct GatherTargets {
   int64_t n_total;
 };
 
-template <int DT, int NT, int RW, int NWARPS>
+template <int DT, int NT, int RW, int NWARPS, bool ADDS = false>
 int launch_skinny_cfg(int device, cudaStream_t stream, const void* a, int64_t a_sm, const int8_t* b, const void* scales, void* c,
-                      int m, int n, int k, int m0, const GatherTargets* gather = nullptr) {
+                      int m, int n, int k, int m0, const GatherTargets* gather = nullptr, const SkinnyAdds* adds = nullptr) {
   using Cfg = SkinnyCfg<NT, RW, NWARPS>;
-  auto kernel = qmm8_skinny_kernel<DT, NT, RW, NWARPS>;
+  auto kernel = qmm8_skinny_kernel<DT, NT, RW, NWARPS, ADDS>;
   static bool configured[64] = {};
   if (!configured[device & 63]) {
     TVB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
@@ -700,6 +774,10 @@ int launch_skinny_cfg(int device, cudaStream_t stream, const void* a, int64_t a_
   p.n = n;
   p.k = k;
   p.m0 = m0;
+  if (adds != nullptr) {
+    p.bias = adds->bias;
+    p.residual = adds->residual;
+  }
   if (gather != nullptr) {
     for (int r = 0; r < gather->world; r++) {
       p.c[r] = gather->c[r];
@@ -728,12 +806,15 @@ int launch_skinny_cfg(int device, cudaStream_t stream, const void* a, int64_t a_
 
 template <int DT, int NT>
 int launch_skinny(int device, cudaStream_t stream, const void* a, int64_t a_sm, const int8_t* b, const void* scales, void* c,
-                  int m, int n, int k, int m0, const GatherTargets* gather = nullptr) {
+                  int m, int n, int k, int m0, const GatherTargets* gather = nullptr, const SkinnyAdds* adds = nullptr) {
   // Small weight matrices (a decoder's qkv, o and down projections) are cut into 128-row tiles: twice as many tiles, so half
   // as many CTAs share each and the completion of shared tiles, which dominates such short launches, is shorter. Large ones
   // keep 256-row tiles (fewer token fragments read per weight). Measured on a 32-layer stack: 4-6 % per decoding step.
-  if (static_cast<int64_t>(n) * k < (int64_t(64) << 20))
-    return launch_skinny_cfg<DT, NT, 1, 8>(device, stream, a, a_sm, b, scales, c, m, n, k, m0, gather);
+  const bool small = static_cast<int64_t>(n) * k < (int64_t(64) << 20);
+  if (adds != nullptr && gather == nullptr)
+    return small ? launch_skinny_cfg<DT, NT, 1, 8, true>(device, stream, a, a_sm, b, scales, c, m, n, k, m0, nullptr, adds)
+                 : launch_skinny_cfg<DT, NT, 2, 8, true>(device, stream, a, a_sm, b, scales, c, m, n, k, m0, nullptr, adds);
+  if (small) return launch_skinny_cfg<DT, NT, 1, 8>(device, stream, a, a_sm, b, scales, c, m, n, k, m0, gather);
   return launch_skinny_cfg<DT, NT, 2, 8>(device, stream, a, a_sm, b, scales, c, m, n, k, m0, gather);
 }
 
@@ -939,6 +1020,24 @@ extern "C" int tvb_wait_flags(int device, const uint32_t* flags, int world, uint
   return launched("qmm8_wait_flags", dim3(1), dim3(32), 0, stream);
 }
 
+// The decode kernel over all rows of A, 16 per pass.
+static int skinny_passes(int device, cudaStream_t stream, const void* a, int dtype, int64_t a_sm, const int8_t* b, const void* scales,
+                         void* c, int mi, int ni, int ki, const SkinnyAdds* adds) {
+  const int64_t stride = mi == 1 ? ki : a_sm;  // (one row: any stride will do for the map)
+  for (int m0 = 0; m0 < mi; m0 += 16) {
+    const int rows = mi - m0;
+    int rc;
+    if (dtype == TVB_BF16)
+      rc = rows <= 8 ? launch_skinny<TVB_BF16, 1>(device, stream, a, stride, b, scales, c, mi, ni, ki, m0, nullptr, adds)
+                     : launch_skinny<TVB_BF16, 2>(device, stream, a, stride, b, scales, c, mi, ni, ki, m0, nullptr, adds);
+    else
+      rc = rows <= 8 ? launch_skinny<TVB_F16, 1>(device, stream, a, stride, b, scales, c, mi, ni, ki, m0, nullptr, adds)
+                     : launch_skinny<TVB_F16, 2>(device, stream, a, stride, b, scales, c, mi, ni, ki, m0, nullptr, adds);
+    if (rc != 0) return rc;
+  }
+  return 0;
+}
+
 extern "C" int tvb_qmm8(int device, const void* a, int dtype, int64_t a_sm, const int8_t* b, const void* scales, void* c,
                         int64_t m, int64_t n, int64_t k, int variant) {
   TVB_REQUIRE(dtype == TVB_F32 || dtype == TVB_F16 || dtype == TVB_BF16, "tvb_qmm8: A must be float32, float16 or bfloat16");
@@ -965,21 +1064,7 @@ extern "C" int tvb_qmm8(int device, const void* a, int dtype, int64_t a_sm, cons
   const bool two_passes = can_skinny && m <= 32;
   if (variant == 3 || (variant == 0 && can_tc && m > 16 && !two_passes))
     return qmm8_tc(device, stream, a, dtype, m == 1 ? k : a_sm, b, scales, c, m, n, k);
-  if (variant == 2 || (variant == 0 && can_skinny)) {
-    int64_t stride = m == 1 ? k : a_sm;  // (one row: any stride will do for the map)
-    for (int m0 = 0; m0 < mi; m0 += 16) {
-      int rows = mi - m0;
-      int rc;
-      if (dtype == TVB_BF16)
-        rc = rows <= 8 ? launch_skinny<TVB_BF16, 1>(device, stream, a, stride, b, scales, c, mi, ni, ki, m0)
-                       : launch_skinny<TVB_BF16, 2>(device, stream, a, stride, b, scales, c, mi, ni, ki, m0);
-      else
-        rc = rows <= 8 ? launch_skinny<TVB_F16, 1>(device, stream, a, stride, b, scales, c, mi, ni, ki, m0)
-                       : launch_skinny<TVB_F16, 2>(device, stream, a, stride, b, scales, c, mi, ni, ki, m0);
-      if (rc != 0) return rc;
-    }
-    return 0;
-  }
+  if (variant == 2 || (variant == 0 && can_skinny)) return skinny_passes(device, stream, a, dtype, a_sm, b, scales, c, mi, ni, ki, nullptr);
   if (dtype == TVB_F32 && variant == 0 && k % 16 == 0 && (a_sm % 4 == 0 || m == 1) && (reinterpret_cast<uintptr_t>(a) & 15u) == 0 &&
       (reinterpret_cast<uintptr_t>(b) & 15u) == 0) {
     // float32 A with aligned rows; row passes side by side in the grid (the weights of a typical layer stay in L2 between them)
@@ -993,4 +1078,28 @@ extern "C" int tvb_qmm8(int device, const void* a, int dtype, int64_t a_sm, cons
     case TVB_F16: return launch_plain<TVB_F16>(stream, a, a_sm, b, scales, c, mi, ni, ki);
     default: return launch_plain<TVB_BF16>(stream, a, a_sm, b, scales, c, mi, ni, ki);
   }
+}
+
+extern "C" int tvb_qmm8_linear(int device, const void* a, int dtype, int64_t a_sm, const int8_t* b, const void* scales,
+                               const void* bias, const void* residual, void* c, int64_t m, int64_t n, int64_t k) {
+  if (bias == nullptr && residual == nullptr) return tvb_qmm8(device, a, dtype, a_sm, b, scales, c, m, n, k, 0);
+  TVB_REQUIRE(dtype == TVB_F32 || dtype == TVB_F16 || dtype == TVB_BF16, "tvb_qmm8_linear: A must be float32, float16 or bfloat16");
+  TVB_REQUIRE(m >= 0 && n >= 0 && k >= 0 && m < (int64_t(1) << 31) && n < (int64_t(1) << 31) && k < (int64_t(1) << 31),
+              "tvb_qmm8_linear: bad size");
+  if (m == 0 || n == 0) return 0;
+  TVB_REQUIRE(c != nullptr && scales != nullptr && (k == 0 || (a != nullptr && b != nullptr)), "tvb_qmm8_linear: NULL pointer");
+  // at most 32 rows in a shape the decode kernel takes: the adds happen where the product is finished
+  if (skinny_ok(a, dtype, a_sm, b, m, n, k) && m <= 32) {
+    cudaStream_t stream;
+    if (enter(device, &stream) != 0) return -1;
+    const SkinnyAdds adds{bias, residual};
+    return skinny_passes(device, stream, a, dtype, a_sm, b, scales, c, static_cast<int>(m), static_cast<int>(n), static_cast<int>(k),
+                         &adds);
+  }
+  // any other shape: the product, then one pass per operand (the same roundings)
+  TVB_REQUIRE(residual != c, "tvb_qmm8_linear: the output may take the residual's place only where the decode kernel runs");
+  int rc = tvb_qmm8(device, a, dtype, a_sm, b, scales, c, m, n, k, 0);
+  if (rc == 0 && bias != nullptr) rc = tvb_add_rowvec(device, c, dtype, n, bias, dtype, m, n);
+  if (rc == 0 && residual != nullptr) rc = tvb_add_rowvec(device, c, dtype, m * n, residual, dtype, 1, m * n);
+  return rc;
 }

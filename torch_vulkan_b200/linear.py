@@ -98,6 +98,13 @@ class Int8Linear(nn.Module, _ShardedMixin):
         x2 = x.reshape(-1, self.in_features)
         if x2.dtype != self.scales.dtype:
             raise TypeError(f"Int8Linear holds {self.scales.dtype} scales; got {x2.dtype} activations")
+        if x2.device.type == "vk" and self.world == 1 and (self.bias is not None or residual is not None):
+            # one call for product, bias and residual (one launch when at most 32 rows are decoded); same roundings
+            if residual is not None and residual.shape != (*lead, self.out_features):
+                raise ValueError(f"residual of shape {tuple(residual.shape)} for an output of shape {(*lead, self.out_features)}")
+            from . import _native
+            r2 = None if residual is None else residual.reshape(-1, self.out_features)
+            return _native.int8_linear(x2, self.weight, self.scales, self.bias, r2).reshape(*lead, self.out_features)
         y = torch._weight_int8pack_mm(x2, self.weight, self.scales)
         if self.bias is not None:
             y += self.bias
