@@ -461,7 +461,7 @@ __global__ void __launch_bounds__((NWARPS + 2) * 32, 1)
         scale_pre[rb][half] = col < p.n ? load_float<DT>(p.scales, col) : 0.0f;
       }
     float bias_pre[ADDS ? RW : 1][2];
-    uint16_t residual_pre[ADDS ? RW : 1][NT][4];
+    uint32_t residual_pre[ADDS ? RW : 1][NT][2];  // [..][half]: the values of tokens 2t (low 16 bits) and 2t + 1
 
     for (int chunk = c0; chunk < c1; chunk++, it++) {
       const int s = static_cast<int>(it % Cfg::kStages);
@@ -481,15 +481,18 @@ __global__ void __launch_bounds__((NWARPS + 2) * 32, 1)
               const int col = tile * Cfg::kRowsPerTile + (warp * RW + rb) * 16 + rg + 8 * half;
               bias_pre[rb][half] = p.bias != nullptr && col < p.n ? load_float<DT>(p.bias, col) : 0.0f;
 #pragma unroll
-              for (int nt = 0; nt < NT; nt++)
+              for (int nt = 0; nt < NT; nt++) {
+                uint32_t pair = 0;
 #pragma unroll
                 for (int i = 0; i < 2; i++) {
                   const int token = p.m0 + nt * 8 + 2 * t + i;
-                  residual_pre[rb][nt][2 * half + i] =
-                      p.residual != nullptr && col < p.n && token < p.m
-                          ? static_cast<const uint16_t*>(p.residual)[static_cast<int64_t>(token) * p.c_ld + p.c_col0 + col]
-                          : uint16_t(0);
+                  if (p.residual != nullptr && col < p.n && token < p.m)
+                    pair |= static_cast<uint32_t>(
+                                static_cast<const uint16_t*>(p.residual)[static_cast<int64_t>(token) * p.c_ld + p.c_col0 + col])
+                            << (16 * i);
                 }
+                residual_pre[rb][nt][half] = pair;
+              }
             }
         }
       }
@@ -656,7 +659,7 @@ __global__ void __launch_bounds__((NWARPS + 2) * 32, 1)
               if constexpr (ADDS) {
                 if (p.bias != nullptr) bits = float_to_half_bits<DT>(half_bits_to_float<DT>(bits) + bias_pre[rb][half]);
                 if (p.residual != nullptr)
-                  bits = float_to_half_bits<DT>(half_bits_to_float<DT>(bits) + half_bits_to_float<DT>(residual_pre[rb][nt][2 * half + i]));
+                  bits = float_to_half_bits<DT>(half_bits_to_float<DT>(bits) + half_bits_to_float<DT>(static_cast<uint16_t>(residual_pre[rb][nt][half] >> (16 * i))));
               }
               out_tile[(nt * 8 + 2 * t + i) * Cfg::kRowsPerTile + lcol] = bits;
             }
