@@ -463,39 +463,46 @@ __global__ void __launch_bounds__((NWARPS + 2) * 32, 1)
     float bias_pre[ADDS ? RW : 1][2];
     uint32_t residual_pre[ADDS ? RW : 1][NT][2];  // [..][half]: the values of tokens 2t (low 16 bits) and 2t + 1
 
+    if constexpr (ADDS) {
+      // (the first stage of the segment has landed: the producer has waited for the stream's earlier kernels by then.
+      // Waiting here as well as in the loop below is harmless: only the consumers release a stage.)
+      const int s0 = static_cast<int>(it % Cfg::kStages);
+      const uint32_t ph0 = static_cast<uint32_t>((it / Cfg::kStages) & 1);
+      ok = ptx::mbar_wait(full0 + 8 * s0, ph0, abort_flag);
+      if (!ok) break;
+      {
+      // the values this thread would add if it finishes the tile, for the same reason asked for early; the residual
+      // may be the previous kernel's output, hence not before that kernel has ended
+      ptx::grid_dependency_wait();
+#pragma unroll
+      for (int rb = 0; rb < RW; rb++)
+#pragma unroll
+        for (int half = 0; half < 2; half++) {
+          const int col = tile * Cfg::kRowsPerTile + (warp * RW + rb) * 16 + rg + 8 * half;
+          bias_pre[rb][half] = p.bias != nullptr && col < p.n ? load_float<DT>(p.bias, col) : 0.0f;
+#pragma unroll
+          for (int nt = 0; nt < NT; nt++) {
+            uint32_t pair = 0;
+#pragma unroll
+            for (int i = 0; i < 2; i++) {
+              const int token = p.m0 + nt * 8 + 2 * t + i;
+              if (p.residual != nullptr && col < p.n && token < p.m)
+                pair |= static_cast<uint32_t>(
+                            static_cast<const uint16_t*>(p.residual)[static_cast<int64_t>(token) * p.c_ld + p.c_col0 + col])
+                        << (16 * i);
+            }
+            residual_pre[rb][nt][half] = pair;
+          }
+        }
+      }
+    }
+
     for (int chunk = c0; chunk < c1; chunk++, it++) {
       const int s = static_cast<int>(it % Cfg::kStages);
       const uint32_t ph = static_cast<uint32_t>((it / Cfg::kStages) & 1);
       ok = ptx::mbar_wait(full0 + 8 * s, ph, abort_flag);
       if (!ok) break;
       // (past the first stage's barrier the stream's earlier kernels have completed: the producer waited for them)
-      if constexpr (ADDS) {
-        if (chunk == c0) {
-          // the values this thread would add if it finishes the tile, for the same reason asked for early; the residual
-          // may be the previous kernel's output, hence not before that kernel has ended
-          ptx::grid_dependency_wait();
-#pragma unroll
-          for (int rb = 0; rb < RW; rb++)
-#pragma unroll
-            for (int half = 0; half < 2; half++) {
-              const int col = tile * Cfg::kRowsPerTile + (warp * RW + rb) * 16 + rg + 8 * half;
-              bias_pre[rb][half] = p.bias != nullptr && col < p.n ? load_float<DT>(p.bias, col) : 0.0f;
-#pragma unroll
-              for (int nt = 0; nt < NT; nt++) {
-                uint32_t pair = 0;
-#pragma unroll
-                for (int i = 0; i < 2; i++) {
-                  const int token = p.m0 + nt * 8 + 2 * t + i;
-                  if (p.residual != nullptr && col < p.n && token < p.m)
-                    pair |= static_cast<uint32_t>(
-                                static_cast<const uint16_t*>(p.residual)[static_cast<int64_t>(token) * p.c_ld + p.c_col0 + col])
-                            << (16 * i);
-                }
-                residual_pre[rb][nt][half] = pair;
-              }
-            }
-        }
-      }
       if (may_be_early) {
         if (chunk == c1 - 3) {
           if (threadIdx.x == 0) asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(peeked) : "l"(p.counters + tile) : "memory");
