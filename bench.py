@@ -7,23 +7,29 @@ weight-only product, `aten::_weight_int8pack_mm` with bf16 A[M, 8192] for M in
 {1, 4, 16} against int8 W[28672, 8192] and bf16 per-channel scales. One step is
 the three products (one per M). The metric is weight-streaming bandwidth: the
 algorithmic bytes of the three launches (weights + scales + A + C) per second.
-With N GPUs the weight rows (output columns) are sharded N ways, every rank runs
-its slice and the outputs are assembled with an NCCL all-gather (strong scaling).
+With N GPUs the weight rows (output columns) are sharded N ways; every rank's
+kernel stores its columns straight into every rank's output buffer (peer stores
+over NVLink) and counts their arrival, so the product is its own all-gather
+(strong scaling). Every rank then rotates through enough distinct copies of its
+weight slice that each launch streams from HBM, and the gathered outputs are
+checked against the CPU product before and after the timed loops.
 
 One JSON line is printed by rank 0. `value` is timed on the device with the
 inputs resident in HBM; `e2e` runs the same step through the public API from
 pinned host memory (copy of A up, copy of C down, every call); `roofline` is the
 decode kernel against the measured HBM copy bandwidth; `cpu_baseline` is
 PyTorch's CPU kernel for the same op (the kernel the reference falls back to and
-is validated against) timed on this host's cores; `extra` holds the large-m
-configurations (dyn-int4 and float8) in TFLOP/s.
+is validated against) timed on this host's cores; `extra` holds the other
+benchmark configurations, each with its own roofline and CPU baseline.
 
 `--impl reference` times that CPU kernel alone, on the same workload and metric.
 """
 
 import argparse
 import json
+import math
 import os
+import re
 import statistics
 import subprocess
 import sys
@@ -40,14 +46,13 @@ MS = (1, 4, 16)
 METRIC = "int8_weight_only_decode_weight_bandwidth"
 UNIT = "GB/s"
 WORKLOAD = "config2: _weight_int8pack_mm bf16 A[M,8192] M in {1,4,16} x int8 W[28672,8192] + bf16 scales[28672]"
+L2_BYTES = 126e6
+DTYPE_NOTE = "bf16 activations, int8 weights, float32 accumulation"
 
 
-NCU_DRAM_BYTES_PER_LAUNCH = 241.64e6  # one decode launch of this workload on one GPU, from the committed ncu capture
-
-
-def algorithmic_bytes(m, n, k):
-    """Weights + scales + A + C of one product (bf16 activations, int8 weights)."""
-    return n * k + 2 * n + 2 * m * k + 2 * m * n
+def algorithmic_bytes(m, n, k, act_bytes=2):
+    """Weights + scales + A + C of one int8 weight-only product."""
+    return n * k + act_bytes * n + act_bytes * m * k + act_bytes * m * n
 
 
 def gen(seed):
@@ -59,6 +64,20 @@ def make_inputs(n_rows, rank_seed=0):
     s = (torch.rand(n_rows, generator=gen(3 + rank_seed)) * (2e-2 - 1e-3) + 1e-3).to(torch.bfloat16)
     a = {m: torch.randn(m, K_IN, generator=gen(1 + m)).to(torch.bfloat16) for m in MS}
     return a, w, s
+
+
+def int8_expected(a, w, s, chunk=4096):
+    """The reference test's expected value and error bound for _weight_int8pack_mm (tests/python/test_quant.py:31-37):
+    the float32 product rounded to A's dtype, and eps * |want| + 2^-20 * (|A| @ |W * s|). Row chunks bound the memory."""
+    af = a.float()
+    wants, mags = [], []
+    for r0 in range(0, w.shape[0], chunk):
+        ws = w[r0:r0 + chunk].float() * s[r0:r0 + chunk].float()[:, None]
+        wants.append(af @ ws.t())
+        mags.append(af.abs() @ ws.abs().t())
+    want = torch.cat(wants, 1).to(a.dtype)
+    tol = torch.finfo(a.dtype).eps * want.float().abs() + 2.0 ** -20 * torch.cat(mags, 1)
+    return want, tol
 
 
 def config_fp8(m, k, n, rowwise):
@@ -88,6 +107,22 @@ def measured_peaks():
             p = json.load(f)
         return {"hbm_gbs": p["hbm_gbs"], "bf16_tflops": p["bf16_tflops"], "source": "measured"}
     return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+def profiled_traffic():
+    """DRAM bytes per decode launch from the committed ncu summary (its `roofline.traffic` line), or None."""
+    path = os.path.join(ROOT, "profiles", "qmm8_skinny_config2.md")
+    try:
+        with open(path) as f:
+            found = re.search(r"([0-9.]+) MB \(the figure `bench\.py` reports as `roofline\.traffic`\)", f.read())
+        return float(found.group(1)) * 1e6 if found else None
+    except OSError:
+        return None
+
+
+def roof(bound, achieved, peak, unit, kernel, peak_note):
+    return {"bound": bound, "achieved": achieved, "peak": peak, "unit": unit, "frac": achieved / peak, "kernel": kernel,
+            "peak_source": peak_note}
 
 
 class ClockSampler:
@@ -137,16 +172,18 @@ class ClockSampler:
         return out
 
 
-def cpu_reference_time(a, w, s, budget_s):
-    """Seconds per step of PyTorch's CPU _weight_int8pack_mm on the full workload (all host threads)."""
-    for m in MS:
-        torch._weight_int8pack_mm(a[m], w, s)  # warm call
+def host_threads():
+    return len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+
+
+def cpu_time(fn, budget_s, min_reps=3, max_reps=50):
+    """Median seconds of fn() on the host after one warm call, repeated within a time budget."""
+    fn()
     times = []
     t_end = time.perf_counter() + budget_s
-    while len(times) < 3 or (time.perf_counter() < t_end and len(times) < 50):
+    while len(times) < min_reps or (time.perf_counter() < t_end and len(times) < max_reps):
         t0 = time.perf_counter()
-        for m in MS:
-            torch._weight_int8pack_mm(a[m], w, s)
+        fn()
         times.append(time.perf_counter() - t0)
     return statistics.median(times), len(times)
 
@@ -156,9 +193,8 @@ def run_reference(args, rank):
     if rank != 0:
         return
     # torchrun gives every rank OMP_NUM_THREADS=1; this arm is rank 0 alone and takes the host's cores
-    host_threads = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
-    if torch.get_num_threads() < host_threads:
-        torch.set_num_threads(host_threads)
+    if torch.get_num_threads() < host_threads():
+        torch.set_num_threads(host_threads())
     a, w, s = make_inputs(N_OUT)
     step_bytes = sum(algorithmic_bytes(m, N_OUT, K_IN) for m in MS)
     for _ in range(max(args.warmup, 1)):
@@ -174,8 +210,8 @@ def run_reference(args, rank):
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-        "dtype": "bf16 activations, int8 weights, float32 accumulation", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "device": "host CPU", "torch": torch.__version__, "os_cpu_count": os.cpu_count()},
+        "dtype": DTYPE_NOTE, "data": "synthetic", "config": {"workload": WORKLOAD},
+        "details": {"device": "host CPU", "torch": torch.__version__, "os_cpu_count": os.cpu_count()},
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "reference",
                          "sample": "the full workload, every step: torch._weight_int8pack_mm on CPU tensors, the kernel the "
                                    "reference hands this op to without a GPU and checks its shader against"},
@@ -185,107 +221,208 @@ def run_reference(args, rank):
     print(json.dumps(line), flush=True)
 
 
-def time_steps(fn, steps, stream):
-    """Runs fn(step) `steps` times between two events on `stream`; returns the events."""
-    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    start.record(stream)
-    for i in range(steps):
-        fn(i)
-    end.record(stream)
-    return start, end
+class Timer:
+    """CUDA-event timing on the backend's stream."""
 
+    def __init__(self, tv, stream, device_index):
+        self.tv, self.stream, self.dev = tv, stream, device_index
 
-def extra_configs(tv, stream, peaks, quick):
-    """Large-m configurations, one GPU: float8 _scaled_mm 8192^3 and dyn-int4 [M,4096]x[14336,4096]."""
-    out = {}
+    def region(self, fn, iters):
+        """Milliseconds of `iters` calls of fn(i) queued back to back between two events."""
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record(self.stream)
+        for i in range(iters):
+            fn(i)
+        e.record(self.stream)
+        self.tv.synchronize(self.dev)
+        return s.elapsed_time(e)
 
-    def timed(fn, iters):
-        for _ in range(3):
+    def median(self, fn, iters, warm=3):
+        """Median milliseconds of one fn(), an event pair per call."""
+        for _ in range(warm):
             fn()
-        tv.synchronize()
+        self.tv.synchronize(self.dev)
         evs = []
         for _ in range(iters):
             s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            s.record(stream)
+            s.record(self.stream)
             fn()
-            e.record(stream)
+            e.record(self.stream)
             evs.append((s, e))
-        tv.synchronize()
+        self.tv.synchronize(self.dev)
         return statistics.median(s.elapsed_time(e) for s, e in evs)
 
+
+# ---------------------------------------------------------------------------------------------- extras, one GPU
+
+def extra_config1(tv, timer, peaks, cpu):
+    """Config 1: _weight_int8pack_mm, float32 A[32,4096] x int8 W[4096,4096] + float32 scales. The 17 MB of weights fit the
+    L2, so twelve distinct weight copies are used in turn for the HBM figure (201 MB, more than the L2 holds) and one copy for
+    the L2-resident figure; both replay a graph of twelve products."""
+    from torch_vulkan_b200 import shard
+
+    m, k, n = 32, 4096, 4096
+    a = torch.randn(m, k, generator=gen(1))
+    w = torch.randint(-127, 128, (n, k), dtype=torch.int8, generator=gen(2))
+    s = torch.rand(n, generator=gen(3)) * (2e-2 - 1e-3) + 1e-3
+    av, sv = a.to("vk"), s.to("vk")
+    copies = [torch.roll(w, 16 * i, 0).to("vk") for i in range(12)]
+    scales = [torch.roll(s, 16 * i, 0).to("vk") for i in range(12)]
+    got = torch._weight_int8pack_mm(av, copies[0], sv).cpu()
+    want, tol = int8_expected(a, w, s)
+    if not ((got - want).abs() <= tol).all():
+        raise SystemExit("bench.py: config 1 product outside the reference's bound")
+    nbytes = algorithmic_bytes(m, n, k, act_bytes=4)
+    out = {}
+    for label, pick in (("hbm_streaming", lambda i: i), ("l2_resident", lambda i: 0)):
+        graph = shard.StepGraph(lambda: [torch._weight_int8pack_mm(av, copies[pick(i)], scales[pick(i)]) for i in range(12)])
+        us = timer.median(graph.replay, 7) / 12 * 1e3
+        out[label] = {"us_per_product": us, "weight_gbs": nbytes / us / 1e3}
+        del graph
+    res = {"workload": "config1: _weight_int8pack_mm f32 A[32,4096] x int8 W[4096,4096] + f32 scales[4096]", **out,
+           "roofline": roof("hbm", out["hbm_streaming"]["weight_gbs"], peaks["hbm_gbs"], "GB/s", "qmm8_f32split_tc_kernel",
+                            peaks["source"] + " HBM copy bandwidth; 17.84 MB per product, twelve weight copies in turn")}
+    if cpu:
+        sec, reps = cpu_time(lambda: torch._weight_int8pack_mm(a, w, s), 2.0)
+        res["cpu_baseline"] = {"value": nbytes / sec / 1e9, "unit": "GB/s", "ms": sec * 1e3, "cores": torch.get_num_threads(),
+                               "kind": "reference", "sample": f"{reps} full products (median), torch._weight_int8pack_mm on CPU"}
+    del copies, scales
+    return {"config1_int8_f32": res}
+
+
+def extra_fp8(tv, timer, peaks, cpu, quick):
+    """Config 4: float8 _scaled_mm 8192^3, tensor-wise and row-wise scales, bf16 output."""
+    out = {}
     m = n = k = 8192
+    peak = 2 * peaks["bf16_tflops"]
     for rowwise in (False, True):
         a, b, sa, sb = config_fp8(m, k, n, rowwise)
         av, bv, sav, sbv = a.to("vk"), b.t().to("vk").t(), sa.to("vk"), sb.to("vk")
-        ms = timed(lambda: torch._scaled_mm(av, bv, sav, sbv, out_dtype=torch.bfloat16), 5 if quick else 10)
+        ms = timer.median(lambda: torch._scaled_mm(av, bv, sav, sbv, out_dtype=torch.bfloat16), 5 if quick else 10)
         tf = 2.0 * m * n * k / ms / 1e9
-        out["fp8_scaled_mm_8192_" + ("rowwise" if rowwise else "tensorwise")] = {
-            "tflops": tf, "ms": ms, "frac_of_2x_measured_bf16": tf / (2 * peaks["bf16_tflops"]), "frac_of_nominal_fp8": tf / 4500.0}
+        key = "fp8_scaled_mm_8192_" + ("rowwise" if rowwise else "tensorwise")
+        out[key] = {"tflops": tf, "ms": ms, "frac_of_2x_measured_bf16": tf / peak, "frac_of_nominal_fp8": tf / 4500.0,
+                    "roofline": roof("tensor", tf, peak, "TFLOP/s", "gemm_tc_kernel<kind::f8f6f4>",
+                                     "2 x the " + peaks["source"] + " bf16 GEMM figure (no float8 peak was measured)")}
+        if cpu:
+            # the reference's emulated formula (crates/pyvk/csrc/quant.cpp:283-299) with the host's sgemm, on a 2048^3 corner
+            c = 2048
+            ac, bc = a[:c, :c], b[:c, :c]
+            sac = sa[:c] if rowwise else sa
+            sbc = sb[:, :c] if rowwise else sb
+            sec, reps = cpu_time(lambda: ((ac.float() * sac) @ (bc.float() * sbc)).to(torch.bfloat16), 1.5)
+            out[key]["cpu_baseline"] = {"value": 2.0 * c ** 3 / sec / 1e12, "unit": "TFLOP/s", "cores": torch.get_num_threads(),
+                                        "kind": "reference", "ms_extrapolated_to_8192": sec * 64 * 1e3,
+                                        "sample": f"{reps} runs (median) of the emulated formula on a 2048^3 corner of the operands; "
+                                                  "the 8192^3 time is 64 times that, extrapolated"}
         del av, bv
-    # the unquantised product on the same main loop (aten::mm, bfloat16), against the library GEMM the peak was measured with
+    return out
+
+
+def extra_mm(tv, timer, peaks, quick):
+    """The unquantised products either side of the path: aten::mm bf16 8192^3 and int8 weight-only at prefill sizes."""
+    out = {}
+    m = n = k = 8192
     a16 = torch.randn(m, k, generator=gen(21)).to(torch.bfloat16).to("vk")
     w16 = torch.randn(n, k, generator=gen(22)).to(torch.bfloat16).to("vk")
-    ms = timed(lambda: torch.mm(a16, w16.t()), 5 if quick else 10)
+    ms = timer.median(lambda: torch.mm(a16, w16.t()), 5 if quick else 10)
     tf = 2.0 * m * n * k / ms / 1e9
     out["bf16_mm_8192"] = {"tflops": tf, "ms": ms, "frac_of_measured_bf16": tf / peaks["bf16_tflops"]}
     del a16, w16
-    # int8 weight-only at prefill sizes (weights widened once per call into scratch, then the same 16-bit main loop)
     for mm, nn_, kk in ((2048, 14336, 4096),) if quick else ((2048, 14336, 4096), (8192, 8192, 8192)):
         a8 = torch.randn(mm, kk, generator=gen(31)).to(torch.bfloat16).to("vk")
         w8 = torch.randint(-127, 128, (nn_, kk), dtype=torch.int8, generator=gen(32)).to("vk")
         s8 = (torch.rand(nn_, generator=gen(33)) * (2e-2 - 1e-3) + 1e-3).to(torch.bfloat16).to("vk")
-        ms = timed(lambda: torch._weight_int8pack_mm(a8, w8, s8), 5)
+        ms = timer.median(lambda: torch._weight_int8pack_mm(a8, w8, s8), 5)
         tf = 2.0 * mm * nn_ * kk / ms / 1e9
         out[f"int8_weight_only_m{mm}_n{nn_}_k{kk}"] = {"tflops": tf, "ms": ms, "frac_of_measured_bf16": tf / peaks["bf16_tflops"]}
         del a8, w8, s8
-    w, sc, bias = config_dyn4_weights()
-    packed = torch._dyn_quant_pack_4bit_weight(w.to("vk"), sc.to("vk"), bias.to("vk"), 32, 4096, 14336)
-    for mm in ((128,) if quick else (128, 512, 2048)):
-        xv = torch.randn(mm, 4096, generator=gen(11)).to("vk")
-        for mode in ("exact", "fast"):  # exact: bit for bit (the default); fast: TORCH_VK_QMM4=fast, rtol 1e-5
-            if mode == "fast":
-                os.environ["TORCH_VK_QMM4"] = "fast"
-            ms = timed(lambda: torch._dyn_quant_matmul_4bit(xv, packed, 32, 4096, 14336), 3)
-            os.environ.pop("TORCH_VK_QMM4", None)
-            tops = 2.0 * mm * 14336 * 4096 / ms / 1e9
-            out[f"dyn_int4_m{mm}_{mode}"] = {"tops": tops, "ms": ms, "frac_of_2x_measured_bf16": tops / (2 * peaks["bf16_tflops"])}
-    # dyn-int4 decoding (at most 16 rows): twelve products replayed as one graph, against the bytes of the real int4 data
-    # (29.36 MB of nibbles + 3.67 MB of block scales + bias, activations and outputs)
-    from torch_vulkan_b200 import shard
-
-    packs = [packed] + [torch._dyn_quant_pack_4bit_weight(torch.roll(w, i, 0).to("vk"), sc.to("vk"), bias.to("vk"), 32, 4096, 14336)
-                        for i in (1, 2, 3)]  # four weight sets in turn: 147 MB in their decode form, more than the L2 holds
-    for mm in (1, 16):
-        xv = torch.randn(mm, 4096, generator=gen(12)).to("vk")
-        graph = shard.StepGraph(lambda: [torch._dyn_quant_matmul_4bit(xv, packs[i % 4], 32, 4096, 14336) for i in range(12)])
-        ms = timed(graph.replay, 5) / 12
-        nbytes = 14336 * 4096 // 2 + 14336 * 128 * 2 + 14336 * 4 + mm * 4096 * 4 + mm * 14336 * 4
-        out[f"dyn_int4_decode_m{mm}"] = {"us": ms * 1e3, "weight_gbs": nbytes / ms / 1e6, "frac_of_measured_hbm": nbytes / ms / 1e6 / peaks["hbm_gbs"]}
-        del graph
-    del packs
-    tv.empty_cache()
-    if not quick:
-        out.update(int8_stack(tv, stream))
     return out
 
 
-def int8_stack(tv, stream, layers=32):
-    """The int8 weight-only Linears of a 32-layer decoder (hidden 4096: qkv 6144, o 4096, gate_up 28672, down from 14336;
-    7 GB of weights, every layer its own buffers), decoded as one replayed graph of 128 products per step. Between the
-    products stands the stack's glue only (the first 4096 columns of qkv feed o, the first 14336 of gate_up feed down)."""
+def extra_dyn4(tv, timer, peaks, cpu, quick):
+    """Config 3: _dyn_quant_matmul_4bit, float32 [M,4096] x int4 [14336,4096], block 32, bias; plus its decoding shapes."""
     from torch_vulkan_b200 import shard
 
-    shapes = [(6144, 4096), (4096, 4096), (28672, 4096), (4096, 14336)]
+    out = {}
+    n, k, bs = 14336, 4096, 32
+    w, sc, bias = config_dyn4_weights()
+    packed = torch._dyn_quant_pack_4bit_weight(w.to("vk"), sc.to("vk"), bias.to("vk"), bs, k, n)
+    peak = 2 * peaks["bf16_tflops"]
+    cpu_row_s = None
+    if cpu:
+        # PyTorch's CPU kernel runs at about 1 GOP/s: a 16-row slice is timed and scaled by rows (rows are independent,
+        # crates/vkcore/shaders/qmm4.slang:134)
+        packed_cpu = torch._dyn_quant_pack_4bit_weight(w, sc, bias, bs, k, n)
+        x16 = torch.randn(16, k, generator=gen(11))
+        sec, _ = cpu_time(lambda: torch._dyn_quant_matmul_4bit(x16, packed_cpu, bs, k, n), 3.0, min_reps=1, max_reps=3)
+        cpu_row_s = sec / 16
+        del packed_cpu
+    for mm in ((128,) if quick else (128, 512, 2048)):
+        xv = torch.randn(mm, k, generator=gen(11)).to("vk")
+        for mode in ("exact", "fast"):  # exact: bit for bit (the default); fast: TORCH_VK_QMM4=fast, rtol 1e-5
+            if mode == "fast":
+                os.environ["TORCH_VK_QMM4"] = "fast"
+            ms = timer.median(lambda: torch._dyn_quant_matmul_4bit(xv, packed, bs, k, n), 5)
+            os.environ.pop("TORCH_VK_QMM4", None)
+            tops = 2.0 * mm * n * k / ms / 1e9
+            entry = {"tops": tops, "ms": ms, "frac_of_2x_measured_bf16": tops / peak,
+                     "roofline": roof("tensor", tops, peak, "TOP/s",
+                                      "qmm4_tc_kernel<kind::i8>" if mode == "exact" else "gemm_tc_kernel<kind::f16> (fast route)",
+                                      "2 x the " + peaks["source"] + " bf16 GEMM figure (no int8 peak was measured)")}
+            if cpu_row_s is not None and mode == "exact":
+                entry["cpu_baseline"] = {"value": 2.0 * n * k / cpu_row_s / 1e12, "unit": "TOP/s", "cores": torch.get_num_threads(),
+                                         "kind": "reference", "ms_extrapolated": cpu_row_s * mm * 1e3,
+                                         "sample": "torch._dyn_quant_matmul_4bit on CPU, a 16-row slice timed and scaled by rows: extrapolated"}
+            out[f"dyn_int4_m{mm}_{mode}"] = entry
+    # decoding (at most 16 rows): twelve products replayed as one graph, against the bytes of the real int4 data
+    # (29.36 MB of nibbles + 3.67 MB of block scales + bias, activations and outputs)
+    packs = [packed] + [torch._dyn_quant_pack_4bit_weight(torch.roll(w, i, 0).to("vk"), sc.to("vk"), bias.to("vk"), bs, k, n)
+                        for i in (1, 2, 3)]  # four weight sets in turn: 147 MB in their decode form, more than the L2 holds
+    for mm in (1, 16):
+        xv = torch.randn(mm, k, generator=gen(12)).to("vk")
+        graph = shard.StepGraph(lambda: [torch._dyn_quant_matmul_4bit(xv, packs[i % 4], bs, k, n) for i in range(12)])
+        ms = timer.median(graph.replay, 5) / 12
+        nbytes = n * k // 2 + n * (k // bs) * 2 + n * 4 + mm * k * 4 + mm * n * 4
+        gbs = nbytes / ms / 1e6
+        entry = {"us": ms * 1e3, "weight_gbs": gbs, "frac_of_measured_hbm": gbs / peaks["hbm_gbs"],
+                 "roofline": roof("hbm", gbs, peaks["hbm_gbs"], "GB/s", "qmm4_decode_kernel", peaks["source"] + " HBM copy bandwidth")}
+        if cpu_row_s is not None:
+            entry["cpu_baseline"] = {"value": nbytes / (cpu_row_s * mm) / 1e9, "unit": "GB/s", "cores": torch.get_num_threads(),
+                                     "kind": "reference", "sample": "the 16-row CPU timing above scaled by rows: extrapolated"}
+        out[f"dyn_int4_decode_m{mm}"] = entry
+        del graph
+    del packs
+    tv.empty_cache()
+    return out
+
+
+STACK_SHAPES = [(6144, 4096), (4096, 4096), (28672, 4096), (4096, 14336)]  # qkv, o, gate_up, down: (n, k)
+
+
+def stack_host_weights():
     host = []
-    for i, (n, k) in enumerate(shapes):
+    for i, (n, k) in enumerate(STACK_SHAPES):
         w = torch.randint(-127, 128, (n, k), dtype=torch.int8, generator=gen(40 + i))
         sc = (torch.rand(n, generator=gen(50 + i)) * 2e-3 + 1e-4).to(torch.bfloat16)
         host.append((w, sc))
+    return host
+
+
+def int8_stack(tv, timer, peaks, cpu, ms_list=(1, 8, 64), layers=32):
+    """Config 5 on one GPU: the int8 weight-only Linears of a 32-layer decoder (hidden 4096: qkv 6144, o 4096, gate_up 28672,
+    down from 14336; 7 GB of weights, every layer its own buffers), decoded as one replayed graph of 128 products per step.
+    Between the products stands the stack's glue only (the first 4096 columns of qkv feed o, the first 14336 of gate_up feed
+    down)."""
+    from torch_vulkan_b200 import _native, shard
+
+    host = stack_host_weights()
     weights = [[(w.to("vk"), sc.to("vk")) for w, sc in host] for _ in range(layers)]
-    wbytes = layers * sum(n * k for n, k in shapes)
+    wbytes = layers * sum(n * k for n, k in STACK_SHAPES)
     out = {}
-    for m in (1, 16):
-        x = torch.randn(m, 4096, generator=gen(60)).to(torch.bfloat16).to("vk")
+    for m in ms_list:
+        x_host = torch.randn(m, 4096, generator=gen(60)).to(torch.bfloat16)
+        x = x_host.to("vk")
 
         def step():
             keep, h = [], x
@@ -300,64 +437,159 @@ def int8_stack(tv, stream, layers=32):
         graph = shard.StepGraph(step)
         for _ in range(3):
             graph.replay()
-        tv.synchronize()
-        iters = 20
-        s0, e0 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        s0.record(stream)
-        for _ in range(iters):
-            graph.replay()
-        e0.record(stream)
-        tv.synchronize()
-        ms = s0.elapsed_time(e0) / iters
-        out[f"int8_stack_32layers_m{m}"] = {"ms_per_token_step": ms, "weight_gbs": wbytes / ms / 1e6, "products": 4 * layers,
-                                             "weight_bytes": wbytes}
+        iters = 10
+        ms = timer.region(lambda i: graph.replay(), iters) / iters
+        gbs = wbytes / ms / 1e6
+        entry = {"ms_per_token_step": ms, "weight_gbs": gbs, "products": 4 * layers, "weight_bytes": wbytes,
+                 "roofline": roof("hbm", gbs, peaks["hbm_gbs"], "GB/s", "qmm8_skinny_kernel" if m <= 32 else "qmm8 tcgen05 kernels",
+                                  peaks["source"] + " HBM copy bandwidth, weight bytes only")}
         del graph
+        if m == 1 or m == 16:
+            # The same stack with its two residual additions (after o and after down): in the decode kernel's epilogue
+            # (tvb_qmm8_linear, 128 launches per step) against a product and an add each (192 launches).
+            def step_residual(fused):
+                def run():
+                    keep, h = [], x
+                    for (wq, sq), (wo, so), (wg, sg), (wd, sd) in weights:
+                        qkv = torch._weight_int8pack_mm(h, wq, sq)
+                        if fused:
+                            o = _native.int8_linear(qkv[:, :4096], wo, so, None, h)
+                        else:
+                            o = torch._weight_int8pack_mm(qkv[:, :4096], wo, so)
+                            o += h
+                        gu = torch._weight_int8pack_mm(o, wg, sg)
+                        if fused:
+                            h = _native.int8_linear(gu[:, :14336], wd, sd, None, o)
+                        else:
+                            h = torch._weight_int8pack_mm(gu[:, :14336], wd, sd)
+                            h += o
+                        keep += [qkv, o, gu, h]
+                    return keep
 
-        # The same stack with its two residual additions (after o and after down): in the decode kernel's epilogue
-        # (tvb_qmm8_linear, 128 launches per step) against a product and an add each (192 launches).
-        def step_residual(fused):
-            from torch_vulkan_b200 import _native
+                return run
 
-            def run():
-                keep, h = [], x
-                for (wq, sq), (wo, so), (wg, sg), (wd, sd) in weights:
-                    qkv = torch._weight_int8pack_mm(h, wq, sq)
-                    if fused:
-                        o = _native.int8_linear(qkv[:, :4096], wo, so, None, h)
-                    else:
-                        o = torch._weight_int8pack_mm(qkv[:, :4096], wo, so)
-                        o += h
-                    gu = torch._weight_int8pack_mm(o, wg, sg)
-                    if fused:
-                        h = _native.int8_linear(gu[:, :14336], wd, sd, None, o)
-                    else:
-                        h = torch._weight_int8pack_mm(gu[:, :14336], wd, sd)
-                        h += o
-                    keep += [qkv, o, gu, h]
-                return keep
+            for label, fused in (("residual_in_epilogue", True), ("residual_as_own_launch", False)):
+                graph = shard.StepGraph(step_residual(fused))
+                for _ in range(3):
+                    graph.replay()
+                entry[label + "_ms"] = timer.region(lambda i: graph.replay(), iters) / iters
+                del graph
+        if cpu:
+            def cpu_pass():
+                h = x_host
+                for _ in range(layers):
+                    qkv = torch._weight_int8pack_mm(h, *host[0])
+                    o = torch._weight_int8pack_mm(qkv[:, :4096].contiguous(), *host[1])
+                    gu = torch._weight_int8pack_mm(o, *host[2])
+                    h = torch._weight_int8pack_mm(gu[:, :14336].contiguous(), *host[3])
+                return h
 
-            return run
-
-        for label, fused in (("residual_in_epilogue", True), ("residual_as_own_launch", False)):
-            graph = shard.StepGraph(step_residual(fused))
-            for _ in range(3):
-                graph.replay()
-            tv.synchronize()
-            s0, e0 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            s0.record(stream)
-            for _ in range(iters):
-                graph.replay()
-            e0.record(stream)
-            tv.synchronize()
-            out[f"int8_stack_32layers_m{m}"][label + "_ms"] = s0.elapsed_time(e0) / iters
-            del graph
+            sec, reps = cpu_time(cpu_pass, 2.0, min_reps=1, max_reps=5)
+            entry["cpu_baseline"] = {"value": wbytes / sec / 1e9, "unit": "GB/s", "ms_per_token_step": sec * 1e3,
+                                     "cores": torch.get_num_threads(), "kind": "reference",
+                                     "sample": f"{reps} passes (median) of the 128 products with torch._weight_int8pack_mm on CPU "
+                                               "(one set of the four weight matrices reused by every layer)"}
+        out[f"int8_stack_32layers_m{m}"] = entry
     del weights
     tv.empty_cache()
     return out
 
 
-def run_only(tv, stream, which, iters):
-    """One large-m configuration, `iters` launches after one warm-up (small enough to sit under a profiler)."""
+# ---------------------------------------------------------------------------------------------- extras, N GPUs
+
+def int8_stack_sharded(tv, timer, peaks, channel, rank, world, dev, ms_list=(1, 8, 64), layers=32):
+    """Config 5 with every Linear's weight rows sharded `world` ways: 128 fused sharded products per step, each kernel
+    storing its columns into every rank's buffer and waiting by itself for the previous product's columns from all ranks (no
+    call between the products), one wait at the end of the step; the whole step is one replayed graph. The last layer's
+    products are checked on every rank against the CPU product of the gathered inputs."""
+    from torch_vulkan_b200 import shard
+
+    host = stack_host_weights()
+    weights = [[(shard.shard_rows(w, rank, world).to(dev), shard.shard_rows(sc, rank, world).to(dev)) for w, sc in host]
+               for _ in range(layers)]
+    wbytes = layers * sum(n * k for n, k in STACK_SHAPES)
+    out = {}
+    for m in ms_list:
+        x = torch.randn(m, 4096, generator=gen(60)).to(torch.bfloat16).to(dev)
+        outs = [shard.GatheredOutputs(m, n, torch.bfloat16, channel, depth=1) for n, _ in STACK_SHAPES]
+
+        def step():
+            h = x
+            for (wq, sq), (wo, so), (wg, sg), (wd, sd) in weights:
+                qkv = outs[0].weight_int8pack_mm(h, wq, sq)
+                o = outs[1].weight_int8pack_mm(qkv[:, :4096], wo, so)
+                gu = outs[2].weight_int8pack_mm(o, wg, sg)
+                h = outs[3].weight_int8pack_mm(gu[:, :14336], wd, sd)
+            channel.wait()
+            return qkv, o, gu, h
+
+        graph = shard.StepGraph(step, channel.dev)
+        for _ in range(3):
+            graph.replay()
+        tv.synchronize(channel.dev)
+        shard.barrier()
+        iters = 10
+        ms = timer.region(lambda i: graph.replay(), iters) / iters
+        qkv, o, gu, h = [t.cpu() for t in graph.outputs]
+        for got, a_in, (w, sc), name in ((o, qkv[:, :4096], host[1], "o"), (gu, o, host[2], "gate_up"), (h, gu[:, :14336], host[3], "down")):
+            want, tol = int8_expected(a_in.contiguous(), w, sc)
+            if not ((got.float() - want.float()).abs() <= tol).all():
+                raise SystemExit(f"bench.py: rank {rank}: sharded stack, last layer's {name} product outside the reference's bound (m={m})")
+        t = torch.tensor([ms], dtype=torch.float64, device=torch.device("cuda", channel.dev))
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+        ms = t.item()
+        gbs = wbytes / ms / 1e6
+        out[f"int8_stack_32layers_m{m}_sharded"] = {
+            "ms_per_token_step": ms, "weight_gbs": gbs, "products": 4 * layers, "weight_bytes": wbytes, "n_gpus": world,
+            "launches_per_step": 4 * layers * ((m + 15) // 16) + 1, "checked": "last layer's o, gate_up and down products on every rank",
+            "roofline": roof("hbm", gbs / world, peaks["hbm_gbs"], "GB/s", "qmm8_skinny_kernel (sharded, fused gather)",
+                             peaks["source"] + " HBM copy bandwidth per GPU, weight bytes only")}
+        del graph, outs
+    del weights
+    tv.empty_cache()
+    return out
+
+
+def fp8_sharded(tv, timer, peaks, rank, world, dev):
+    """Config 4 with B's columns sharded `world` ways: every rank multiplies A by its [8192, 8192 / world] slice and the
+    [8192, 8192] output is assembled on every rank. Each rank checks 64 rows of the assembled output against the
+    reference's formula."""
+    from torch_vulkan_b200 import shard
+
+    out = {}
+    m = n = k = 8192
+    for rowwise in (False, True):
+        a, b, sa, sb = config_fp8(m, k, n, rowwise)
+        b_sh, sb_sh = shard.shard_scaled_mm_b(b, sb, rank, world)
+        av, bv = a.to(dev), b_sh.t().contiguous().to(dev).t()
+        sav, sbv = sa.to(dev), sb_sh.to(dev)
+        fn = lambda: shard.scaled_mm(av, bv, sav, sbv, out_dtype=torch.bfloat16)  # noqa: E731
+        got = fn()
+        r0 = 64 * rank
+        af, bf = a[r0:r0 + 64].float() * (sa[r0:r0 + 64] if rowwise else sa), b.float() * sb
+        want = (af @ bf).to(torch.bfloat16)
+        tol = torch.finfo(torch.bfloat16).eps * want.float().abs() + 2.0 ** -20 * (af.abs() @ bf.abs())
+        if not ((got[r0:r0 + 64].cpu().float() - want.float()).abs() <= tol).all():
+            raise SystemExit(f"bench.py: rank {rank}: sharded float8 product outside the reference's bound")
+        shard.barrier()
+        ms = timer.median(fn, 5)
+        t = torch.tensor([ms], dtype=torch.float64, device=torch.device("cuda", torch.cuda.current_device()))
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+        ms = t.item()
+        tf = 2.0 * m * n * k / ms / 1e9
+        out["fp8_scaled_mm_8192_" + ("rowwise" if rowwise else "tensorwise") + "_sharded"] = {
+            "tflops": tf, "ms": ms, "n_gpus": world, "gather": "NCCL all-gather of the column slices",
+            "checked": "64 rows of the assembled output on every rank",
+            "roofline": roof("tensor", tf / world, 2 * peaks["bf16_tflops"], "TFLOP/s", "gemm_tc_kernel<kind::f8f6f4> + all-gather",
+                             "2 x the " + peaks["source"] + " bf16 GEMM figure per GPU")}
+        del av, bv
+    tv.empty_cache()
+    return out
+
+
+def run_only(tv, timer, which, iters, slice_world):
+    """One configuration, `iters` launches after one warm-up (small enough to sit under a profiler)."""
+    stream = timer.stream
     if which in ("fp8", "fp8_big"):
         m = n = k = 4096 if which == "fp8" else 8192
         a, b, sa, sb = config_fp8(m, k, n, True)
@@ -370,6 +602,36 @@ def run_only(tv, stream, which, iters):
         w16 = torch.randn(n, k, generator=gen(22)).to(torch.bfloat16).to("vk")
         fn = lambda: torch.mm(a16, w16.t())  # noqa: E731
         flops = 2.0 * m * n * k
+    elif which == "config1":
+        m, k, n = 32, 4096, 4096
+        av = torch.randn(m, k, generator=gen(1)).to("vk")
+        w = torch.randint(-127, 128, (n, k), dtype=torch.int8, generator=gen(2))
+        sv = (torch.rand(n, generator=gen(3)) * (2e-2 - 1e-3) + 1e-3).to("vk")
+        copies = [torch.roll(w, 16 * i, 0).to("vk") for i in range(12)]
+        state = {"i": 0}
+
+        def fn():
+            state["i"] += 1
+            return torch._weight_int8pack_mm(av, copies[state["i"] % 12], sv)
+
+        flops = 2.0 * m * n * k
+    elif which == "int8_slice":
+        # the weight slice one rank of `slice_world` owns in config 2, on one GPU: enough copies in turn to stream from HBM
+        rows = N_OUT // slice_world
+        nsets = weight_sets(rows * K_IN, slice_world)
+        w = torch.randint(-127, 128, (rows, K_IN), dtype=torch.int8, generator=gen(2))
+        sv = (torch.rand(rows, generator=gen(3)) * (2e-2 - 1e-3) + 1e-3).to(torch.bfloat16).to("vk")
+        copies = [torch.roll(w, 16 * i, 0).to("vk") for i in range(nsets)]
+        a = {m: torch.randn(m, K_IN, generator=gen(1 + m)).to(torch.bfloat16).to("vk") for m in MS}
+        from torch_vulkan_b200 import shard
+
+        res = {"only": which, "rows": rows, "weight_sets": nsets, "us_per_launch_by_m": {}}
+        for m in MS:
+            graph = shard.StepGraph(lambda: [torch._weight_int8pack_mm(a[m], copies[i % nsets], sv) for i in range(4 * nsets)])
+            res["us_per_launch_by_m"][str(m)] = timer.median(graph.replay, max(iters, 3)) / (4 * nsets) * 1e3
+            del graph
+        res["hbm_floor_us"] = rows * K_IN / 6543.1e3
+        return res
     elif which == "dyn4_decode":
         # four weight sets in turn (147 MB of int4 data and scales in their decode form, more than the L2 holds)
         mm = 16
@@ -411,14 +673,17 @@ def run_only(tv, stream, which, iters):
         flops = 2.0 * m * n * k
     fn()
     tv.synchronize()
-    s0, e0 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    s0.record(stream)
-    for _ in range(iters):
-        fn()
-    e0.record(stream)
-    tv.synchronize()
-    ms = s0.elapsed_time(e0) / iters
+    ms = timer.region(lambda i: fn(), iters) / iters
     return {"only": which, "ms": ms, "tflops": flops / ms / 1e9, "iters": iters}
+
+
+def weight_sets(set_bytes, world):
+    """Distinct copies of a rank's weight slice used in turn, so that a copy is read again only after more than twice the
+    L2's capacity of other weights has streamed through: one when the slice alone is that large, else a multiple of the
+    three products of a step."""
+    if world == 1 and set_bytes > 1.5 * L2_BYTES:
+        return 1
+    return len(MS) * max(1, math.ceil(2 * L2_BYTES / (len(MS) * set_bytes)))
 
 
 def main():
@@ -427,10 +692,13 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--no-extra", action="store_true", help="skip the large-m configurations")
-    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline")
-    ap.add_argument("--only", default=None, choices=["fp8", "fp8_big", "dyn4", "dyn4_decode", "int8_large_m", "int8_mid_m", "int8_stack", "bf16_mm"],
-                    help="run one large-m configuration a few times and exit (for profilers); prints its own JSON line")
+    ap.add_argument("--no-extra", action="store_true", help="skip the other configurations")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baselines")
+    ap.add_argument("--only", default=None,
+                    choices=["fp8", "fp8_big", "dyn4", "dyn4_decode", "int8_large_m", "int8_mid_m", "int8_stack", "bf16_mm", "config1",
+                             "int8_slice"],
+                    help="run one configuration a few times and exit (for profilers); prints its own JSON line")
+    ap.add_argument("--slice-world", type=int, default=8, help="--only int8_slice: the rank count whose weight slice is timed")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     rank = int(os.environ.get("RANK", "0"))
@@ -449,70 +717,104 @@ def main():
     tv.set_device(local_rank)
     dev = f"vk:{local_rank}"
     stream = tv.cuda_stream(local_rank)
+    timer = Timer(tv, stream, local_rank)
+    peaks = measured_peaks()
+    if world > 1 or torch.get_num_threads() < 2:
+        torch.set_num_threads(max(1, host_threads() // world))  # (torchrun gives every rank one thread; the checks use more)
     if args.only == "int8_stack":
-        print(json.dumps({"only": "int8_stack", **int8_stack(tv, stream)}), flush=True)
+        print(json.dumps({"only": "int8_stack", **int8_stack(tv, timer, peaks, cpu=False)}), flush=True)
         return
     if args.only is not None:
-        print(json.dumps(run_only(tv, stream, args.only, max(args.steps, 1) if args.steps != 200 else 3)), flush=True)
+        print(json.dumps(run_only(tv, timer, args.only, max(args.steps, 1) if args.steps != 200 else 3, args.slice_world)), flush=True)
         return
+    from torch_vulkan_b200 import shard
+
+    channel = None
     if world > 1:
         import torch.distributed as dist
 
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl")  # (no device_id: with "vk" registered, torch takes that for the accelerator)
-    peaks = measured_peaks()
+        objects = dist.new_group(backend="gloo")
+        if os.environ.get("TVB200_GATHER", "fused") == "fused":
+            channel = shard.PeerChannel(local_rank, objects)
 
-    # ---- inputs: this rank's slice of the weight rows (output columns); A replicated
+    # ---- inputs: this rank's slice of the weight rows (output columns), in `nsets` rotated copies; A replicated
     rows = N_OUT // world
+    nsets = weight_sets(rows * K_IN, world)
     a_host, w_full, s_full = make_inputs(N_OUT)
-    w = w_full[rank * rows:(rank + 1) * rows].contiguous().to(dev)
-    s = s_full[rank * rows:(rank + 1) * rows].contiguous().to(dev)
+    w_slice, s_slice = w_full[rank * rows:(rank + 1) * rows], s_full[rank * rows:(rank + 1) * rows]
+    shift = 16  # copy j holds the slice's rows rolled by 16 j: its output columns are rolled likewise
+    w_sets = [torch.roll(w_slice, shift * j, 0).contiguous().to(dev) for j in range(nsets)]
+    s_sets = [torch.roll(s_slice, shift * j, 0).contiguous().to(dev) for j in range(nsets)]
     a_dev = {m: a_host[m].to(dev) for m in MS}
     a_pinned = {m: a_host[m].pin_memory() for m in MS}
-    from torch_vulkan_b200 import shard
+    expected = {m: int8_expected(a_host[m], w_full, s_full) for m in MS}
+
+    def check(m, got, j, what):
+        """`got` [m, N] against the CPU product for weight copy j (every rank's slice of columns rolled by 16 j)."""
+        want, tol = expected[m]
+        want = torch.roll(want.view(m, world, rows), shift * j, 2).reshape(m, N_OUT)
+        tol = torch.roll(tol.view(m, world, rows), shift * j, 2).reshape(m, N_OUT)
+        if not ((got.float() - want.float()).abs() <= tol).all():
+            bad = int(((got.float() - want.float()).abs() > tol).sum())
+            raise SystemExit(f"bench.py: rank {rank}: {what}: {bad} outputs of the M={m} product outside the reference's bound")
 
     fused = None
-    if world > 1 and os.environ.get("TVB200_GATHER", "fused") == "fused":
-        import torch.distributed as dist
+    if channel is not None:
+        fused = {m: shard.GatheredOutputs(m, N_OUT, torch.bfloat16, channel) for m in MS}
 
-        objects = dist.new_group(backend="gloo")
-        fused = {m: shard.GatheredOutputs(m, N_OUT, torch.bfloat16, local_rank, objects) for m in MS}
-
-    def product(m, a):
+    def product(m, a, j, buf):
         if world == 1:
-            return torch._weight_int8pack_mm(a, w, s)
+            return torch._weight_int8pack_mm(a, w_sets[j], s_sets[j])
         if fused is not None:
-            # every rank's kernel stores its column slice into every rank's [m, N] buffer (peer stores over NVLink)
-            return fused[m].weight_int8pack_mm(a, w, s)
+            # every rank's kernel stores its column slice into every rank's [m, N] buffer (peer stores over NVLink); the
+            # three products of a step have nothing to do with each other: none waits for the ones before it in the step
+            return fused[m].weight_int8pack_mm(a, w_sets[j], s_sets[j], buf=buf, independent=MS.index(m))
         # every rank's column slice, then the NCCL all-gather into [m, N] (queued on the backend's stream)
-        return shard.weight_int8pack_mm(a, w, s)
+        return shard.weight_int8pack_mm(a, w_sets[j], s_sets[j])
 
-    def step_eager():
-        return [product(m, a_dev[m]) for m in MS]
+    # Step g of a cycle of `ngraphs` uses weight copies 3g .. 3g+2 (mod nsets) and output buffer set g % 2: a buffer is
+    # written again only a whole step after the step whose outputs it held.
+    ngraphs = 1 if world == 1 else (nsets // len(MS)) * (2 if (nsets // len(MS)) % 2 else 1)
 
-    # The step (three short kernels, plus the flag waits when sharded) is captured once into a CUDA graph and replayed:
-    # at 4 and 8 GPUs the kernels are shorter than the host's launch calls.
-    graph = None
-    if os.environ.get("TVB200_GRAPH", "1") != "0":
+    def step_sets(g):
+        return [(len(MS) * g + i) % nsets for i in range(len(MS))]
+
+    def step_eager(g):
+        outs = [product(m, a_dev[m], j, g % 2) for m, j in zip(MS, step_sets(g))]
+        if channel is not None:
+            channel.wait()  # the step ends when every rank holds every column
+        return outs
+
+    # ---- parity in the timed binary: every weight copy, every M, every rank's assembled output
+    for g in range(ngraphs):
+        for m, j, out in zip(MS, step_sets(g), step_eager(g)):
+            check(m, out.cpu(), j, "before timing")
+    if world > 1:
+        shard.barrier()
+
+    # The step (three short kernels, plus the wait when sharded) is captured into CUDA graphs and replayed: at 4 and 8 GPUs
+    # the kernels are shorter than the host's launch calls.
+    graphs = None
+    if os.environ.get("TVB200_GRAPH", "1") != "0" and (world == 1 or fused is not None):
         try:
-            graph = shard.StepGraph(step_eager, local_rank)
+            graphs = [shard.StepGraph(lambda g=g: step_eager(g), local_rank, warm=False) for g in range(ngraphs)]
         except Exception as exc:  # noqa: BLE001
             if rank == 0:
                 print(f"bench.py: graph capture failed ({exc}); launching eagerly", file=sys.stderr)
-            graph = None
+            graphs = None
 
     def step_plain(i):
-        if graph is not None:
-            graph.replay()
+        if graphs is not None:
+            graphs[i % ngraphs].replay()
         else:
-            step_eager()
+            step_eager(i % ngraphs)
 
     def barrier():
         tv.synchronize(local_rank)
         torch.cuda.synchronize()
         if world > 1:
-            import torch.distributed as dist
-
             shard.barrier()
 
     # ---- device-resident timing
@@ -522,22 +824,33 @@ def main():
         step_plain(i)
     barrier()
     launches_before = tv.dispatch_count()
-    start, end = time_steps(step_plain, args.steps, stream)
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record(stream)
+    for i in range(args.steps):
+        step_plain(args.warmup + i)
+    end.record(stream)
     barrier()
     launches = tv.dispatch_count() - launches_before
-    if graph is not None:
-        launches = args.steps * len(MS) * (2 if fused is not None else 1)  # replayed kernels are not re-counted by the runtime
+    per_step_launches = len(MS) + (1 if channel is not None else 0)
+    if graphs is not None:
+        launches = args.steps * per_step_launches  # replayed kernels are not re-counted by the runtime
     total_ms = start.elapsed_time(end)
+    if graphs is not None:  # what the last replays left in the output buffers
+        for g in range(ngraphs):
+            graphs[g].replay()
+            tv.synchronize(local_rank)
+            for m, j, out in zip(MS, step_sets(g), graphs[g].outputs):
+                check(m, out.cpu(), j, "after the timed replays")
+        barrier()
 
-    # ---- per-launch duration of the decode kernel (the roofline's numerator), same loop with an event pair per launch
-    pairs = []
-    for i in range(args.steps):
-        for m in MS:
-            s0, e0 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            s0.record(stream)
-            torch._weight_int8pack_mm(a_dev[m], w, s)
-            e0.record(stream)
-            pairs.append((m, s0, e0))
+    # ---- the decode kernel alone on this rank's slice (no exchange), per M: twelve launches per replayed graph
+    isolated_ms = {}
+    for m in MS:
+        reps = 4 * max(nsets, 3)
+        g_iso = shard.StepGraph(lambda: [torch._weight_int8pack_mm(a_dev[m], w_sets[i % nsets], s_sets[i % nsets]) for i in range(reps)],
+                                local_rank)
+        isolated_ms[m] = timer.median(g_iso.replay, 5) / reps
+        del g_iso
     barrier()
     # nvidia-smi needs a second or so of load to return samples: when the timed region was shorter than that, the
     # same steps keep running (untimed) until the sampling window is filled
@@ -545,63 +858,83 @@ def main():
         for i in range(20):
             step_plain(i)
         barrier()
-    clocks = sampler.stop() if sampler is not None else None
-    if clocks is not None:
-        clocks["window"] = "warm-up, timed region and per-launch pass, plus identical untimed steps up to 1.5 s"
-    isolated_ms = {m: statistics.median(s0.elapsed_time(e0) for mm, s0, e0 in pairs if mm == m) for m in MS}
     # average launch duration over the timed region: the region holds nothing but these launches, queued back to back
-    avg_launch_ms = total_ms / (args.steps * len(MS)) if world == 1 else statistics.mean(isolated_ms.values())
+    avg_launch_ms = total_ms / (args.steps * len(MS))
 
     # ---- end to end through the public API: A from pinned host memory, C back to the host, every call
     out_pinned = {m: torch.empty(m, N_OUT, dtype=torch.bfloat16).pin_memory() for m in MS}
 
-    def e2e_body():
+    def e2e_body(g):
         # every product's A goes up from page-locked memory and its C comes back into page-locked memory; the three
         # products of a step are queued back to back
         ups = [a_pinned[m].to(dev, non_blocking=True) for m in MS]
-        outs = [product(m, a) for m, a in zip(MS, ups)]
+        outs = [product(m, a, j, g % 2) for m, a, j in zip(MS, ups, step_sets(g))]
+        if channel is not None:
+            channel.wait()
         for m, c in zip(MS, outs):
             out_pinned[m].copy_(c, non_blocking=True)
         return ups, outs
 
+    e2e_steps = max(5, min(args.steps, 30))
+
     def time_e2e(step):
-        for _ in range(3):
-            step()
+        for i in range(3):
+            step(i)
         barrier()
         t0 = time.perf_counter()
-        for _ in range(e2e_steps):
-            step()
+        for i in range(e2e_steps):
+            step(3 + i)
         barrier()
         return (time.perf_counter() - t0) / e2e_steps
 
-    def step_e2e_eager():
-        e2e_body()
+    def step_e2e_eager(i):
+        e2e_body(i % ngraphs)
         tv.synchronize(local_rank)  # the step ends when all three results are on the host
 
-    e2e_steps = max(5, min(args.steps, 30))
     e2e_eager_s = time_e2e(step_e2e_eager)
     e2e_s, e2e_how = e2e_eager_s, "eager: every copy and product queued by its own call"
-    if graph is not None:
-        # the same copies and products recorded once (the host buffers are fixed; a caller rewrites A in place) and replayed
-        e2e_graph = shard.StepGraph(e2e_body, local_rank)
+    last_g = (3 + e2e_steps - 1) % ngraphs
+    if graphs is not None:
+        # the same copies and products recorded once per buffer set (the host buffers are fixed; a caller rewrites A in place)
+        e2e_graphs = [shard.StepGraph(lambda g=g: e2e_body(g), local_rank, warm=False) for g in range(ngraphs)]
 
-        def step_e2e_graph():
-            e2e_graph.replay()
+        def step_e2e_graph(i):
+            e2e_graphs[i % ngraphs].replay()
             tv.synchronize(local_rank)
 
         e2e_s, e2e_how = time_e2e(step_e2e_graph), "CUDA graph replay of the step's copies and products, then a stream synchronize"
-        for m in MS:  # what came back through the replayed copies is what the eager calls deliver
-            want = product(m, a_dev[m]).cpu() if world == 1 else None
-            if want is not None and not torch.equal(want.view(torch.int16), out_pinned[m].view(torch.int16)):
-                raise SystemExit("bench.py: the replayed end-to-end step returned different results")
+    for m, j in zip(MS, step_sets(last_g)):  # what came back to the host from the last end-to-end step
+        check(m, out_pinned[m], j, "end-to-end outputs on the host")
 
     # ---- max over ranks
     if world > 1:
         import torch.distributed as dist
 
-        t = torch.tensor([total_ms, e2e_s, avg_launch_ms, e2e_eager_s], dtype=torch.float64, device=torch.device("cuda", local_rank))
+        t = torch.tensor([total_ms, e2e_s, avg_launch_ms, e2e_eager_s] + [isolated_ms[m] for m in MS], dtype=torch.float64,
+                         device=torch.device("cuda", local_rank))
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        total_ms, e2e_s, avg_launch_ms, e2e_eager_s = t.tolist()
+        total_ms, e2e_s, avg_launch_ms, e2e_eager_s, *iso = t.tolist()
+        isolated_ms = dict(zip(MS, iso))
+
+    # ---- the other configurations (every rank takes part in the sharded ones)
+    extra = {}
+    if not args.no_extra:
+        del w_sets, s_sets
+        tv.empty_cache()
+        cpu = not args.no_cpu and rank == 0
+        if world == 1:
+            extra.update(extra_config1(tv, timer, peaks, cpu))
+            extra.update(extra_fp8(tv, timer, peaks, cpu, quick=False))
+            extra.update(extra_mm(tv, timer, peaks, quick=False))
+            extra.update(extra_dyn4(tv, timer, peaks, cpu, quick=False))
+            extra.update(int8_stack(tv, timer, peaks, cpu))
+        else:
+            if channel is not None:
+                extra.update(int8_stack_sharded(tv, timer, peaks, channel, rank, world, dev))
+            extra.update(fp8_sharded(tv, timer, peaks, rank, world, dev))
+    clocks = sampler.stop() if sampler is not None else None
+    if clocks is not None:
+        clocks["window"] = "warm-up, timed region, per-launch pass, end-to-end steps and the other configurations"
 
     if rank == 0:
         step_bytes = sum(algorithmic_bytes(m, N_OUT, K_IN) for m in MS)  # whole job, all ranks
@@ -609,38 +942,59 @@ def main():
         value = step_bytes / (ms_per_step * 1e-3) / 1e9
         launch_bytes = statistics.mean(algorithmic_bytes(m, rows, K_IN) for m in MS)  # one launch, this rank's slice
         achieved = launch_bytes / (avg_launch_ms * 1e-3) / 1e9
+        iso_mean = statistics.mean(isolated_ms.values())
+        streams = "each launch streams %.0f MB of weights" % (rows * K_IN / 1e6)
+        l2_note = ("no flush: " + streams + ", larger than the 126 MB L2") if nsets == 1 else \
+            ("no flush: %d distinct copies of the rank's weight slice are used in turn (%.0f MB, twice the 126 MB L2, between two "
+             "uses of a copy): %s from HBM" % (nsets, nsets * rows * K_IN / 1e6, streams))
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-            "dtype": "bf16 activations, int8 weights, float32 accumulation", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "sharding": f"weight rows / {world}" + ((" + fused peer-store gather of C" if fused is not None else " + NCCL all-gather of C") if world > 1 else ""),
-                       "l2": "no flush: each launch streams %.0f MB of weights, larger than the 126 MB L2" % (rows * K_IN / 1e6)
-                       if rows * K_IN > 126e6 else "weight slice of %.0f MB fits the 126 MB L2: launches after the first read it from L2" % (rows * K_IN / 1e6),
-                       "launches_per_step": len(MS), "launch": "CUDA graph replay of one step" if graph is not None else "eager"},
+            "dtype": DTYPE_NOTE, "data": "synthetic", "config": {"workload": WORKLOAD},
+            "details": {"sharding": f"weight rows / {world}" + ((" + fused peer-store gather of C (arrival counted per CTA, each product "
+                                                                 "waits for the one before)" if fused is not None else " + NCCL all-gather of C") if world > 1 else ""),
+                        "l2": l2_note, "weight_copies_per_rank": nsets, "launches_per_step": per_step_launches,
+                        "launch": f"CUDA graph replay, {ngraphs} recorded step(s) in turn" if graphs is not None else "eager",
+                        "parity": "every rank's assembled outputs checked against the CPU product (the reference's bound) for every weight "
+                                  "copy before timing, after the timed replays and after the end-to-end steps"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                          "frac": achieved / peaks["hbm_gbs"], "traffic": None, "peak_source": peaks["source"],
                          "kernel": "qmm8_skinny_kernel", "avg_launch_us": avg_launch_ms * 1e3,
-                         "avg_launch_how": "timed region / launches (launches queued back to back, as in decoding)",
-                         "isolated_launch_us_by_m": {str(m): isolated_ms[m] * 1e3 for m in MS}},
+                         "avg_launch_how": "timed region / product launches (launches queued back to back, as in decoding; with sharding "
+                                           "the region includes the exchange and one wait kernel per step)",
+                         "isolated_launch_us_by_m": {str(m): isolated_ms[m] * 1e3 for m in MS},
+                         "isolated_how": "the kernel alone on this rank's weight slice (no exchange), a replayed graph of launches over "
+                                         "the weight copies in turn",
+                         "isolated_frac": launch_bytes / (iso_mean * 1e-3) / 1e9 / peaks["hbm_gbs"]},
             "e2e": {"value": step_bytes / e2e_s / 1e9, "unit": UNIT,
                     "h2d_bytes_per_step": sum(2 * m * K_IN for m in MS), "d2h_bytes_per_step": sum(2 * m * N_OUT for m in MS),
                     "ms_per_step": e2e_s * 1e3, "how": e2e_how, "eager_value": step_bytes / e2e_eager_s / 1e9},
             "gpu_launches": int(launches),
             "clocks": clocks,
         }
+        if world > 1:
+            line["roofline"]["exchange_us_per_product"] = (avg_launch_ms - iso_mean) * 1e3
         if world == 1:
-            line["roofline"]["traffic"] = NCU_DRAM_BYTES_PER_LAUNCH
-            line["roofline"]["traffic_source"] = "ncu dram__bytes_read.sum + dram__bytes_write.sum, mean of the M = 1, 4, 16 launches (profiles/qmm8_skinny_config2.md)"
+            traffic = profiled_traffic()
+            line["roofline"]["traffic"] = traffic
+            line["roofline"]["traffic_source"] = ("ncu dram__bytes_read.sum + dram__bytes_write.sum, mean of the M = 1, 4, 16 launches, read "
+                                                  "from profiles/qmm8_skinny_config2.md")
         if not args.no_cpu and world == 1:
-            cpu_s, reps = cpu_reference_time(a_host, w_full, s_full, 8.0)
+            if torch.get_num_threads() < host_threads():
+                torch.set_num_threads(host_threads())
+
+            def cpu_step():
+                for m in MS:
+                    torch._weight_int8pack_mm(a_host[m], w_full, s_full)
+
+            cpu_s, reps = cpu_time(cpu_step, 8.0)
             line["cpu_baseline"] = {"value": step_bytes / cpu_s / 1e9, "unit": UNIT, "cores": torch.get_num_threads(),
                                     "kind": "reference",
                                     "sample": f"{reps} full steps (median): torch._weight_int8pack_mm on CPU tensors, the kernel "
                                               "the reference hands this op to without a GPU and checks its shader against",
                                     "ms_per_step": cpu_s * 1e3}
-        if not args.no_extra and world == 1:
-            del w_full
-            line["extra"] = extra_configs(tv, stream, peaks, quick=False)
+        if extra:
+            line["extra"] = extra
         print(json.dumps(line), flush=True)
     if world > 1:
         import torch.distributed as dist

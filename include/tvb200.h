@@ -79,7 +79,8 @@ TVB_API int tvb_empty_cache(int device);
 TVB_API void tvb_memory_stats(int device, uint64_t* allocated, uint64_t* reserved, uint64_t* blocks);
 /* The CUDA stream (cudaStream_t) that every launcher queues on for `device`. */
 TVB_API void* tvb_stream(int device);
-/* Replaces the device's stream with a caller-owned one (NULL restores the runtime's own). */
+/* Replaces the device's stream with a caller-owned one (NULL restores the runtime's own). The runtime's scratch is ordered
+ * by one stream per device at a time: the new stream is made to wait for what is already queued on the old one. */
 TVB_API int tvb_set_stream(int device, void* stream);
 /* Kernels launched so far (the reference's dispatch_count, crates/pyvk/src/lib.rs:112-116). */
 TVB_API uint64_t tvb_dispatch_count(void);
@@ -150,20 +151,38 @@ TVB_API int tvb_qmm8_widened(int device, const void* a, int dtype, int64_t a_sm,
  *      which has one device: crates/pyvk/csrc/backend.cpp:296) ----
  * Rank `rank` of `world` computes its n_local output columns and its kernel's epilogue stores them straight into
  * every rank's [m, n_local * world] output buffer at columns [rank * n_local, (rank + 1) * n_local): this GPU's own
- * memory and the peers' over NVLink (plain 16-byte stores to peer-mapped memory). c_ranks / flag_ranks: host arrays
- * of `world` device pointers, entry r being rank r's output buffer / its array of `world` uint32 flags, as mapped
- * into this process (tvb_ipc_export on the owner, tvb_ipc_import here). seq_counter: a uint32 in this rank's device
- * memory, 1 before the first product. When the last column is out, the kernel stores the counter's value into entry
- * `rank` of every rank's flag array (release, system scope). tvb_wait_flags queues a one-warp kernel that waits (bounded,
- * about two seconds) until every entry of this rank's own flag array has reached the counter's value, then adds one to
- * the counter; work queued after it may read the assembled output. The sequence number lives on the device so that a
- * captured CUDA graph of products can be replayed. Every rank must run the same sequence of products on a buffer, and a
- * buffer may be written again only after one other product (use two buffers alternately). 1 <= m <= 16, 16-bit A,
+ * memory and the peers' over NVLink (plain 16-byte stores to peer-mapped memory). c_ranks: host array of `world` device
+ * pointers, entry r being rank r's output buffer as mapped into this process (tvb_ipc_export on the owner,
+ * tvb_ipc_import here).
+ *
+ * Arrival is counted on a channel: every rank owns an array of `world` uint32 arrival counters, zero at the start
+ * (flag_ranks: host array of `world` device pointers, entry r being rank r's array as mapped here), and a uint32 product
+ * count in its own device memory, zero at the start (seq_counter). Every CTA of the product kernel, once its columns are
+ * stored on every rank, adds its share to entry `rank` of every rank's array (system scope, after a system-scope fence);
+ * a product adds 1024 in all, so rank r's slices of the first s products have arrived here when entry r of this rank's
+ * array has reached 1024 * s. The kernel's last CTA adds one to the product count.
+ *
+ * Ordering. Before it reads A or stores a column, a product kernel waits (bounded, see tvb_set_wait_limit_ms) until all
+ * ranks have delivered every earlier product of the channel; meanwhile its weights already stream into shared memory. So
+ * (1) the next sharded product may take a gathered output as its A without any call in between, and (2) an output buffer
+ * may be written again by the second product after the one that filled it (use two buffers in turn), provided that
+ * everything else that reads it on this rank was queued before this rank's next product. `independent` = i > 0 relaxes
+ * the wait to all but the latest i products of the channel (products of the same m, a pass per 16 rows counting as part
+ * of its product): for a product that neither reads the outputs of those i products nor writes a buffer that any rank
+ * may still be reading while they run. Work that is not a sharded
+ * product of the same channel (copies, other kernels) must be queued after tvb_wait_flags, which queues a one-warp
+ * kernel that waits in the same way for all products queued so far and changes nothing. The counts live on the device,
+ * so a captured CUDA graph of products can be replayed. Every rank must queue the same sequence of products on a channel.
+ * A wait that runs out sets the device's status word (tvb_synchronize then fails with "status 5") and the kernels go on
+ * without waiting again. 1 <= m <= 64 (16 rows of A per pass, every pass a product of its own on the channel), 16-bit A,
  * k a multiple of 128. */
 TVB_API int tvb_qmm8_gather(int device, const void* a, int dtype, int64_t a_sm, const int8_t* b, const void* scales,
                             void* const* c_ranks, uint32_t* const* flag_ranks, int world, int rank,
-                            const uint32_t* seq_counter, int64_t m, int64_t n_local, int64_t k);
-TVB_API int tvb_wait_flags(int device, const uint32_t* flags, int world, uint32_t* seq_counter);
+                            uint32_t* seq_counter, int independent, int64_t m, int64_t n_local, int64_t k);
+TVB_API int tvb_wait_flags(int device, const uint32_t* flags, int world, const uint32_t* seq_counter);
+/* How long the kernels above wait for peers before they give up (default about 2000 ms). Process-wide; applies to
+ * kernels launched (or captured) afterwards. 1 <= ms <= 60000. */
+TVB_API int tvb_set_wait_limit_ms(int ms);
 /* A device allocation as a 64-byte handle plus offset that another process of the node can map (cudaIpc*). */
 TVB_API int tvb_ipc_export(int device, const void* ptr, uint8_t* handle64, uint64_t* offset);
 TVB_API int tvb_ipc_import(int device, const uint8_t* handle64, uint64_t offset, void** out);
@@ -190,9 +209,14 @@ TVB_API int tvb_qmm8_linear(int device, const void* a, int dtype, int64_t a_sm, 
  * not used. The first call on a device looks the array's device address up (once, with that device current) and raises
  * the kernel's shared-memory limit; make that first call before any stream capture begins. Every call uses the one
  * array: it clears the counters it needs and then relies on stream order, so two calls that can overlap on the GPU
- * (different streams, no dependency between them) race on it and must be ordered by the caller. */
+ * (different streams, no dependency between them) race on it and must be ordered by the caller.
+ * How a failure surfaces: the kernel's waits are bounded; one that runs out leaves C incomplete and sets a status word
+ * inside the array (cleared at the start of every call). tvb_synchronize does not look at that word (it belongs to no
+ * runtime stream); tvb_qmm8_static_scratch_status does: it waits for `stream` and stores the word of the last call on
+ * `device` in *host_out (0: complete). It allocates nothing either. */
 TVB_API int tvb_qmm8_static_scratch(int device, const void* a, int dtype, int64_t a_sm, const int8_t* b, const void* scales,
                                     void* c, int64_t m, int64_t n, int64_t k, void* stream);
+TVB_API int tvb_qmm8_static_scratch_status(int device, void* stream, int* host_out);
 
 /* ---- aten::_dyn_quant_pack_4bit_weight (replaces the cat of three casts,
  *      quant.cpp:139-143) ----
@@ -245,8 +269,9 @@ TVB_API int tvb_qmm4_fast(int device, const void* inp, int dtype, const float* p
 
 /* ---- aten::_dyn_quant_matmul_4bit for at most 16 rows (decoding): the int4 weights streamed from HBM once, bit for bit
  *      the same results as tvb_qmm4 (replaces the two dispatches of crates/pyvk/csrc/quant.cpp:187-202 for small m) ----
- * tvb_qmm4_decode_usable: 1 when the kernel takes the shape (m <= 16, n % 8 == 0, k % 256 == 0, k <= 4096, bs % 32 == 0,
- * (k / 8) % bs == 0). tvb_qmm4_decode_prepare re-tiles the packed vector's weights and scales once per packed tensor
+ * tvb_qmm4_decode_usable: 1 when the kernel takes the shape (m <= 16, n % 8 == 0, k % 512 == 0, bs % 32 == 0,
+ * 512 % bs == 0, and k small enough, about 8192, for its activation fragments of 16 bytes per value of k to leave room for
+ * two weight records per warp in shared memory). tvb_qmm4_decode_prepare re-tiles the packed vector's weights and scales once per packed tensor
  * (0.5 byte per weight + 4 bytes per block scale; 16-byte aligned buffer of tvb_qmm4_decode_prepared_bytes). */
 TVB_API int tvb_qmm4_decode_usable(int64_t m, int64_t n, int64_t k, int64_t bs);
 TVB_API uint64_t tvb_qmm4_decode_prepared_bytes(int64_t n, int64_t k, int64_t bs);

@@ -1,5 +1,6 @@
 """One rank of the multi-GPU test (launched by torch.distributed.run from tests/test_multi_gpu.py): column-sharded
-products on device "vk" with the NCCL all-gather, compared with the single-GPU product and the reference's bound."""
+products on device "vk", with the fused peer-store gather and with the NCCL all-gather, compared with the single-GPU
+product and the reference's bound."""
 
 import os
 import sys
@@ -25,21 +26,74 @@ def main():
     dev = f"vk:{local}"
     objects = dist.new_group(backend="gloo")
     try:
-        # the fused product: every rank's kernel stores its columns into every rank's buffer, flags tell arrival
+        # the fused product: every rank's kernel stores its columns into every rank's buffer; arrival is counted per
+        # source rank, and every product kernel waits for the previous product of the channel by itself
+        channel = shard.PeerChannel(local, objects)
         for m in (1, 4, 16):
-            a, b, s = C.config_int8(m, 2048, 1024 * world, torch.bfloat16)
-            want, tol = C.int8_want(a, b, s)
-            outs = shard.GatheredOutputs(m, 1024 * world, torch.bfloat16, local, objects)
-            av, bv, sv = a.to(dev), shard.shard_rows(b, rank, world).to(dev), shard.shard_rows(s, rank, world).to(dev)
-            for rep in range(5):  # both buffers, several sequence numbers
-                got = outs.weight_int8pack_mm(av, bv, sv).cpu()
-                assert ((got.float() - want.float()).abs() <= tol).all(), f"rank {rank}: fused sharded product wrong (m={m}, rep={rep})"
-            # the same product captured in a CUDA graph and replayed (the sequence number lives on the device)
-            graph = shard.StepGraph(lambda: outs.weight_int8pack_mm(av, bv, sv), local)
-            for rep in range(3):
-                got = graph.replay().cpu()
+            n = 1024 * world
+            _, b, s = C.config_int8(m, 2048, n, torch.bfloat16)
+            bv, sv = shard.shard_rows(b, rank, world).to(dev), shard.shard_rows(s, rank, world).to(dev)
+            reps = 6
+            a_host = [torch.randn(m, 2048, generator=C.gen(100 + r)).to(torch.bfloat16) for r in range(reps)]
+            wants = [C.int8_want(a, b, s) for a in a_host]
+            outs = shard.GatheredOutputs(m, n, torch.bfloat16, channel)
+            av = a_host[0].to(dev)
+            for rep in range(reps):  # both buffers in turn, A rewritten in place: every product has its own expected value
+                av.copy_(a_host[rep].to(dev))
+                got = outs.weight_int8pack_mm(av, bv, sv)
+                channel.wait()
+                want, tol = wants[rep]
+                assert ((got.cpu().float() - want.float()).abs() <= tol).all(), f"rank {rank}: fused sharded product wrong (m={m}, rep={rep})"
+            # the same product recorded twice (one graph per output buffer) and replayed in turn
+            def body():
+                out = outs.weight_int8pack_mm(av, bv, sv)
+                channel.wait()
+                return out
+
+            graphs = [shard.StepGraph(body, local, warm=False) for _ in range(2)]
+            for rep in range(reps):
+                av.copy_(a_host[reps - 1 - rep].to(dev))
+                got = graphs[rep % 2].replay().cpu()
+                want, tol = wants[reps - 1 - rep]
                 assert ((got.float() - want.float()).abs() <= tol).all(), f"rank {rank}: graph replay wrong (m={m}, rep={rep})"
             shard.barrier(objects)
+
+        # a chain: each product takes the gathered output of the one before as its A, no call in between
+        m, k0, widths = 4, 2048, (1024 * world, 512 * world, 1024 * world)
+        layers, k = [], k0
+        for i, n in enumerate(widths):
+            _, b, s = C.config_int8(m, k, n, torch.bfloat16, seed=10 * i)
+            s = (s.float() / 30).to(torch.bfloat16)  # (keeps the chain's values near one)
+            layers.append((b, s, shard.shard_rows(b, rank, world).to(dev), shard.shard_rows(s, rank, world).to(dev),
+                           shard.GatheredOutputs(m, n, torch.bfloat16, channel, depth=1)))
+            k = n // 2  # the next product reads the first half of this one's columns
+        x_host = [torch.randn(m, k0, generator=C.gen(200 + r)).to(torch.bfloat16) for r in range(4)]
+        xv = x_host[0].to(dev)
+
+        def chain():
+            h, hs = xv, []
+            for b, s, bv, sv, outs in layers:
+                full = outs.weight_int8pack_mm(h, bv, sv)
+                hs.append(full)
+                h = full[:, : full.shape[1] // 2]
+            channel.wait()
+            return hs
+
+        def check_chain(hs, x, what):
+            h = x
+            for (b, s, _, _, _), got in zip(layers, hs):
+                got = got.cpu()
+                want, tol = C.int8_want(h, b, s)  # (from this device's own previous output: one product's bound per step)
+                assert ((got.float() - want.float()).abs() <= tol).all(), f"rank {rank}: chained sharded product wrong ({what})"
+                h = got[:, : got.shape[1] // 2]
+
+        check_chain(chain(), x_host[0], "eager")
+        graph = shard.StepGraph(chain, local, warm=False)
+        for rep in range(4):
+            xv.copy_(x_host[rep].to(dev))
+            check_chain(graph.replay(), x_host[rep], f"replay {rep}")
+        shard.barrier(objects)
+
         for m in (1, 4, 16):
             a, b, s = C.config_int8(m, 2048, 1024 * world, torch.bfloat16)
             want, tol = C.int8_want(a, b, s)

@@ -378,3 +378,79 @@ def test_qmm4_fast_route_flags_inexact_scales(abi):
     packed = dev(O.dyn_quant_pack_4bit_weight(w, sc, bvec, bs, k, n))
     _, inexact = abi.qmm4_fast_prepare(packed, n, k, bs)
     assert inexact == 1
+
+
+# ---------------------------------------------------------------- sharded product on one GPU, and a wait that runs out
+
+def test_gather_world1_counts_and_chains(abi):
+    """tvb_qmm8_gather with a world of one rank: the product lands in the rank's own buffer, every CTA's share adds up to
+    1024 per product in the arrival counter, the product count advances, and a second product takes the first one's
+    output as its A with no call in between."""
+    import ctypes
+
+    lib = abi.lib()
+    m, k, n = 4, 1024, 512
+    a, b, s = C.config_int8(m, k, n, torch.bfloat16, seed=5)
+    s = (s.float() / 20).to(torch.bfloat16)
+    _, b2, s2 = C.config_int8(m, n, 384, torch.bfloat16, seed=6)
+    da, db, ds, db2, ds2 = dev(a), dev(b), dev(s), dev(b2), dev(s2)
+    c1 = torch.zeros(m, n, dtype=torch.bfloat16, device="cuda")
+    c2 = torch.zeros(m, 384, dtype=torch.bfloat16, device="cuda")
+    state = torch.zeros(16, dtype=torch.int32, device="cuda")  # [0, 8): arrival counters; [8]: product count
+    torch.cuda.synchronize()
+    flags = (ctypes.c_void_p * 1)(state.data_ptr())
+    seq = state.data_ptr() + 32
+    for c, aa, bb, ss, nn, kk in ((c1, da, db, ds, n, k), (c2, c1, db2, ds2, 384, n)):
+        outs = (ctypes.c_void_p * 1)(c.data_ptr())
+        abi.check(lib.tvb_qmm8_gather(0, aa.data_ptr(), abi.BF16, aa.stride(0), bb.data_ptr(), ss.data_ptr(), outs, flags, 1, 0,
+                                      ctypes.c_void_p(seq), 0, m, nn, kk))
+    abi.check(lib.tvb_wait_flags(0, state.data_ptr(), 1, ctypes.c_void_p(seq)))
+    abi.synchronize()
+    st = state.cpu()
+    assert st[0].item() == 2 * 1024 and st[8].item() == 2
+    want1, tol1 = C.int8_want(a, b, s)
+    assert ((c1.cpu().float() - want1.float()).abs() <= tol1).all()
+    want2, tol2 = C.int8_want(c1.cpu(), b2, s2)
+    assert ((c2.cpu().float() - want2.float()).abs() <= tol2).all()
+
+
+def test_wait_for_peers_runs_out_and_is_reported(abi):
+    """A wait for a peer that never delivers gives up after the configured limit, without a fault: the host reads status 5
+    from tvb_synchronize, the runtime clears the status and the decode kernels' counters, and the next product is right."""
+    import ctypes
+    import time
+
+    lib = abi.lib()
+    abi.check(lib.tvb_set_wait_limit_ms(20))
+    try:
+        # a channel of two ranks whose other rank does not exist: one product counted, nothing ever arrives
+        state = torch.zeros(16, dtype=torch.int32, device="cuda")
+        state[8] = 1
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        abi.check(lib.tvb_wait_flags(0, state.data_ptr(), 2, ctypes.c_void_p(state.data_ptr() + 32)))
+        rc = lib.tvb_synchronize(0)
+        waited = time.perf_counter() - t0
+        assert rc == -1 and b"status 5" in lib.tvb_last_error()
+        assert waited < 1.0, f"the wait took {waited:.2f} s with a limit of 20 ms"
+        # a product kernel waiting for the previous product of such a channel gives up the same way, and still ends
+        m, k, n = 2, 512, 256
+        a, b, s = C.config_int8(m, k, n, torch.bfloat16, seed=9)
+        da, db, ds = dev(a), dev(b), dev(s)
+        mine = torch.zeros(m, 2 * n, dtype=torch.bfloat16, device="cuda")
+        theirs = torch.zeros(m, 2 * n, dtype=torch.bfloat16, device="cuda")  # (stands in for the missing peer's buffer)
+        their_state = torch.zeros(16, dtype=torch.int32, device="cuda")
+        torch.cuda.synchronize()
+        outs = (ctypes.c_void_p * 2)(mine.data_ptr(), theirs.data_ptr())
+        flags = (ctypes.c_void_p * 2)(state.data_ptr(), their_state.data_ptr())
+        abi.check(lib.tvb_qmm8_gather(0, da.data_ptr(), abi.BF16, da.stride(0), db.data_ptr(), ds.data_ptr(), outs, flags, 2, 0,
+                                      ctypes.c_void_p(state.data_ptr() + 32), 0, m, n, k))
+        assert lib.tvb_synchronize(0) == -1 and b"status 5" in lib.tvb_last_error()
+        assert lib.tvb_synchronize(0) == 0  # reported once, then cleared
+    finally:
+        abi.check(lib.tvb_set_wait_limit_ms(2000))
+    a, b, s = C.config_int8(16, 2048, 4099, torch.bfloat16, seed=3)
+    want, tol = C.int8_want(a, b, s)
+    got = abi.qmm8(dev(a), dev(b), dev(s), variant=2)
+    abi.synchronize()
+    assert ((got.cpu().float() - want.float()).abs() <= tol).all()

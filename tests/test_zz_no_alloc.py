@@ -40,6 +40,10 @@ def test_static_scratch_matches_allocating_entry_point(dtype, m, k, n):
         torch.cuda.synchronize()
         assert ((out.cpu().float() - ref.cpu().float()).abs() <= tol).all(), f"call {call}: differs from tvb_qmm8"
         assert ((out.cpu().float() - want.float()).abs() <= tol).all(), f"call {call}: differs from the expected product"
+        # how a bounded wait that ran out would surface: the call's status word, read back without any allocation
+        word = ctypes.c_int(-1)
+        assert lib.tvb_qmm8_static_scratch_status(0, ctypes.c_void_p(stream), ctypes.byref(word)) == 0, lib.tvb_last_error()
+        assert word.value == 0
 
 
 def test_static_scratch_rejects_what_it_cannot_hold():

@@ -56,8 +56,9 @@ SIGNATURES = {
     "tvb_addmm": (_i, [_i, _vp, _i, _i64, _i64, _vp, _i64, _i64, _vp, _i, _vp, _i, _i64, _vp, _i, _i64, _i64, _i64, _i]),
     "tvb_qmm8": (_i, [_i, _vp, _i, _i64, _vp, _vp, _vp, _i64, _i64, _i64, _i]),
     "tvb_qmm8_linear": (_i, [_i, _vp, _i, _i64, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64]),
-    "tvb_qmm8_gather": (_i, [_i, _vp, _i, _i64, _vp, _vp, _c.POINTER(_vp), _c.POINTER(_vp), _i, _i, _vp, _i64, _i64, _i64]),
+    "tvb_qmm8_gather": (_i, [_i, _vp, _i, _i64, _vp, _vp, _c.POINTER(_vp), _c.POINTER(_vp), _i, _i, _vp, _i, _i64, _i64, _i64]),
     "tvb_wait_flags": (_i, [_i, _vp, _i, _vp]),
+    "tvb_set_wait_limit_ms": (_i, [_i]),
     "tvb_graph_begin": (_i, [_i]),
     "tvb_graph_end": (_i, [_i, _c.POINTER(_vp)]),
     "tvb_graph_launch": (_i, [_i, _vp]),
@@ -65,6 +66,7 @@ SIGNATURES = {
     "tvb_ipc_export": (_i, [_i, _vp, _c.c_char_p, _c.POINTER(_u64)]),
     "tvb_ipc_import": (_i, [_i, _c.c_char_p, _u64, _c.POINTER(_vp)]),
     "tvb_qmm8_static_scratch": (_i, [_i, _vp, _i, _i64, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
+    "tvb_qmm8_static_scratch_status": (_i, [_i, _vp, _c.POINTER(_i)]),
     "tvb_qmm4_pack": (_i, [_i, _vp, _i64, _vp, _i, _i64, _vp, _i, _i64, _vp]),
     "tvb_qmm4_quantize": (_i, [_i, _vp, _i, _i64, _i64, _i, _vp, _vp, _vp]),
     "tvb_qmm4_matmul": (_i, [_i, _vp, _vp, _vp, _vp, _i, _vp, _i, _i64, _i64, _i64, _i64, _vp]),

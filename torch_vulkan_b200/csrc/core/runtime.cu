@@ -305,15 +305,22 @@ int tvb_synchronize(int device) {
   if (enter(device, &s) != 0) return -1;
   TVB_CUDA(cudaStreamSynchronize(s));
   int* status = nullptr;
+  void* counters = nullptr;
+  uint64_t counter_bytes = 0;
   {
     std::lock_guard<std::mutex> lock(g_mutex);
     status = g_devices[device].status;
+    counters = g_devices[device].ws[0];
+    counter_bytes = std::min<uint64_t>(g_devices[device].ws_size[0], 65536);
   }
   if (status != nullptr) {
     int code = 0;
     TVB_CUDA(cudaMemcpy(&code, status, sizeof(int), cudaMemcpyDeviceToHost));
     if (code != 0) {
       cudaMemset(status, 0, sizeof(int));
+      // The kernel that gave up left the decode kernels' tile and CTA counters (the head of workspace slot 0) wherever it
+      // stopped; they must read zero again before the next launch, or later launches would miscount arrivals.
+      if (counters != nullptr && counter_bytes != 0) cudaMemset(counters, 0, counter_bytes);
       return fail("a kernel gave up a bounded wait and left its result incomplete (status " + std::to_string(code) + ")");
     }
   }
@@ -364,7 +371,19 @@ int tvb_set_stream(int device, void* stream) {
   std::lock_guard<std::mutex> lock(g_mutex);
   DeviceState* d = nullptr;
   if (state_locked(device, &d) != 0) return -1;
-  d->stream = stream != nullptr ? static_cast<cudaStream_t>(stream) : d->own_stream;
+  cudaStream_t next = stream != nullptr ? static_cast<cudaStream_t>(stream) : d->own_stream;
+  if (next != d->stream) {
+    // The runtime's scratch (counters, partial sums, the status word, cached blocks) is ordered by one stream per device
+    // at a time: work queued on the new stream starts after everything already queued on the old one.
+    TVB_CUDA(cudaSetDevice(device));
+    cudaEvent_t ev = nullptr;
+    TVB_CUDA(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
+    cudaError_t err = cudaEventRecord(ev, d->stream);
+    if (err == cudaSuccess) err = cudaStreamWaitEvent(next, ev, 0);
+    cudaEventDestroy(ev);
+    if (err != cudaSuccess) return fail_cuda("tvb_set_stream: ordering the new stream after the old one", err);
+    d->stream = next;
+  }
   return 0;
 }
 

@@ -25,6 +25,7 @@
 //    output column, as the shader's matrix-vector path (qmm8.slang:78-111).
 #include <cuda.h>
 
+#include <atomic>
 #include <cstdlib>
 #include <mutex>
 
@@ -200,13 +201,22 @@ __device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a
 
 constexpr int kMaxRanks = 8;
 
+// SM cycles the waits for peers may take (tvb_set_wait_limit_ms; the default is about two seconds).
+std::atomic<long long> g_wait_limit_cycles{ptx::kWaitLimitCycles};
+
+// What one rank adds to its entry of every rank's arrival counters per sharded product, split over its CTAs (each CTA adds
+// its share when its own columns are out, so the sum is this constant whatever the grid).
+constexpr uint32_t kArriveWeight = 1024;
+
 struct SkinnyParams {
   const void* scales;
   void* c[kMaxRanks];        // output buffers [m, c_ld]: this GPU's, and with sharding every peer's (peer-mapped memory)
-  uint32_t* flags[kMaxRanks];  // with sharding: every rank's arrival-flag array (entry `rank` is this GPU's to write)
+  uint32_t* flags[kMaxRanks];  // with sharding: every rank's arrival counters (entry `rank` of each is this GPU's to add to)
   int* done;                 // with sharding: counter of finished CTAs (zero between launches)
   int nranks, rank;
-  const uint32_t* seq;       // with sharding: device counter whose value tells the peers this product's columns have arrived
+  uint32_t* seq;             // with sharding: device counter of the sharded products this rank has completed on the channel
+  uint32_t independent;      // with sharding: how many of the latest products of the channel this one need not wait for
+  long long wait_limit;      // with sharding: SM cycles after which the wait for the peers gives up
   int c_ld, c_col0;          // row length of the output buffers and first column of this GPU's slice
   float* partials;   // [grid][2][kPartialFloats]
   int* counters;     // [tiles], zero between launches
@@ -298,15 +308,15 @@ __global__ void __launch_bounds__((NWARPS + 2) * 32, 1)
 
   if (warp == NWARPS) {
     // ---------------- producer: one lane issues every TMA copy
+    const uint64_t stream_policy = ptx::policy_evict_first();  // weights are read once
+    const uint64_t keep_policy = ptx::policy_evict_last();     // every CTA re-reads A
+    const long long mine = u1 - u0;
+    const long long ahead = mine < Cfg::kStages ? mine : Cfg::kStages;
     if (lane == 0) {
       ptx::prefetch_tensormap(&map_w);
       ptx::prefetch_tensormap(&map_a);
-      const uint64_t stream_policy = ptx::policy_evict_first();  // weights are read once
-      const uint64_t keep_policy = ptx::policy_evict_last();     // every CTA re-reads A
       // The weights do not depend on earlier kernels of the stream: start streaming them at once, one ring's worth.
       // A (which an earlier kernel may have produced) is fetched only after the stream's earlier work has completed.
-      const long long mine = u1 - u0;
-      const long long ahead = mine < Cfg::kStages ? mine : Cfg::kStages;
       for (long long j = 0; j < ahead; j++) {
         const long long u = u0 + j;
         const int tile = unit_tile(u, p.chunks, small), chunk = static_cast<int>(u - static_cast<long long>(tile) * p.chunks);
@@ -314,6 +324,37 @@ __global__ void __launch_bounds__((NWARPS + 2) * 32, 1)
         ptx::mbar_expect_tx(full0 + 8 * static_cast<int>(j), Cfg::kStageBytes);
         ptx::tma_load_2d_hint(dst, &map_w, chunk * kChunkK, tile * Cfg::kRowsPerTile, full0 + 8 * static_cast<int>(j), stream_policy);
       }
+    }
+    if (p.done != nullptr) {
+      // Sharded product: before this CTA reads A or stores a column, every rank must have delivered the earlier products
+      // of the channel (all but the latest `independent` ones). The previous product's output may be this one's A; and a
+      // rank that has delivered has also finished reading its own A, which this product may be about to overwrite (two
+      // output buffers in turn). Lane r waits (bounded) for rank r's counter; the counters only grow, by kArriveWeight per
+      // product and rank.
+      ptx::grid_dependency_wait();  // (this rank's previous kernel has ended: the product count below is final)
+      if (lane < p.nranks) {
+        const uint32_t count = *reinterpret_cast<const volatile uint32_t*>(p.seq);
+        const uint32_t target = (count > p.independent ? count - p.independent : 0u) * kArriveWeight;
+        const uint32_t* mine_flag = p.flags[p.rank] + lane;
+        const long long start = clock64();
+        for (int spins = 0;; spins++) {
+          uint32_t v;
+          asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine_flag) : "memory");
+          if (static_cast<int32_t>(v - target) >= 0) break;
+          if ((spins & 63) == 63) {
+            // an earlier give-up (here or in an earlier kernel) is final: nobody waits the limit out a second time
+            if (*reinterpret_cast<volatile int*>(p.status) != 0) break;
+            if (clock64() - start > p.wait_limit) {
+              atomicExch(p.status, 5);
+              break;
+            }
+          }
+        }
+      }
+      __syncwarp();
+      asm volatile("fence.proxy.async.global;" ::: "memory");  // (the copies below read what the peers' stores delivered)
+    }
+    if (lane == 0) {
       ptx::grid_dependency_wait();
       for (long long j = 0; j < ahead; j++) {
         const int chunk = static_cast<int>(u0 + j - static_cast<long long>(unit_tile(u0 + j, p.chunks, small)) * p.chunks);
@@ -702,17 +743,19 @@ __global__ void __launch_bounds__((NWARPS + 2) * 32, 1)
     u += c1 - c0;
   }
   if (p.done != nullptr && ok) {
-    // Sharded product: when the last CTA has stored its columns everywhere, tell every rank (this one included) that
-    // this GPU's slice of product `seq` has arrived. The system-scope fence after the barrier covers the stores of
-    // all consumer threads of the CTA.
+    // Sharded product: this CTA's columns are stored everywhere (and it has read all of A it will ever read): add its
+    // share to this rank's arrival counter on every rank, this one included. The system-scope fence after the barrier
+    // covers the stores of all the CTA's threads; no CTA waits for another, and columns count as they land.
     ptx::named_bar_sync(2, (NWARPS + 1) * 32);  // (the agent warp arrives here too, after whatever it had to store)
     if (threadIdx.x == 0) {
       __threadfence_system();
+      const uint32_t share = (blockIdx.x + 1) * kArriveWeight / gridDim.x - blockIdx.x * kArriveWeight / gridDim.x;
+      for (int r = 0; r < p.nranks; r++)
+        asm volatile("red.relaxed.sys.global.add.u32 [%0], %1;" ::"l"(p.flags[r] + p.rank), "r"(share) : "memory");
+      // the last CTA to get here counts the product (the next kernel of the stream reads the count after this one has ended)
       if (atomicAdd(p.done, 1) == static_cast<int>(gridDim.x) - 1) {
         atomicExch(p.done, 0);
-        const uint32_t seq = *reinterpret_cast<const volatile uint32_t*>(p.seq);
-        for (int r = 0; r < p.nranks; r++)
-          asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.flags[r] + p.rank), "r"(seq) : "memory");
+        *reinterpret_cast<volatile uint32_t*>(p.seq) = *reinterpret_cast<const volatile uint32_t*>(p.seq) + 1u;
       }
     }
   }
@@ -739,7 +782,8 @@ struct GatherTargets {
   void* c[kMaxRanks];
   uint32_t* flags[kMaxRanks];
   int world, rank;
-  const uint32_t* seq;
+  uint32_t* seq;
+  uint32_t independent;
   int64_t n_total;
 };
 
@@ -748,10 +792,14 @@ int launch_skinny_cfg(int device, cudaStream_t stream, const void* a, int64_t a_
                       int m, int n, int k, int m0, const GatherTargets* gather = nullptr, const SkinnyAdds* adds = nullptr) {
   using Cfg = SkinnyCfg<NT, RW, NWARPS>;
   auto kernel = qmm8_skinny_kernel<DT, NT, RW, NWARPS, ADDS>;
-  static bool configured[64] = {};
-  if (!configured[device & 63]) {
-    TVB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
-    configured[device & 63] = true;
+  {
+    static std::mutex mutex;
+    static bool configured[64] = {};
+    std::lock_guard<std::mutex> lock(mutex);
+    if (!configured[device & 63]) {
+      TVB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+      configured[device & 63] = true;
+    }
   }
   CUtensorMap map_w, map_a;
   if (make_tensor_map_2d(&map_w, b, CU_TENSOR_MAP_DATA_TYPE_UINT8, k, n, k, kChunkK, Cfg::kRowsPerTile,
@@ -765,6 +813,7 @@ int launch_skinny_cfg(int device, cudaStream_t stream, const void* a, int64_t a_
   p.chunks = k / kChunkK;
   long long units = static_cast<long long>(p.tiles) * p.chunks;
   int grid = static_cast<int>(std::min<long long>(sm_count(device), units));
+  if (gather != nullptr && grid > static_cast<int>(kArriveWeight)) return fail("tvb_qmm8_gather: more than 1024 SMs");
   size_t partial_bytes = static_cast<size_t>(grid) * 2 * Cfg::kPartialFloats * sizeof(float);
   // Fixed layout, whatever the shape: 64 KB of tile counters (and, last, the finished-CTA counter), then the partial
   // sums. The counters must stay zero between launches, so no launch may ever use their bytes for anything else.
@@ -796,6 +845,8 @@ int launch_skinny_cfg(int device, cudaStream_t stream, const void* a, int64_t a_
     p.nranks = gather->world;
     p.rank = gather->rank;
     p.seq = gather->seq;
+    p.independent = gather->independent;
+    p.wait_limit = g_wait_limit_cycles.load();
     p.c_ld = static_cast<int>(gather->n_total);
     p.c_col0 = gather->rank * n;
     p.done = reinterpret_cast<int*>(static_cast<uint8_t*>(ws) + counter_bytes - sizeof(int));
@@ -836,31 +887,34 @@ bool skinny_ok(const void* a, int dtype, int64_t a_sm, const int8_t* b, int64_t 
 
 // ------------------------------------------------------------------ sharded product: waiting for the peers' columns
 
-// One thread per peer spins (bounded) until that peer's arrival flag reaches `seq`; a wait that runs out sets the status
-// word and returns. The flags are written with system-scope release stores by the peers' product kernels.
-__global__ void qmm8_wait_flags_kernel(const uint32_t* flags, int world, uint32_t* seq_counter, int* status) {
-  // Launched with programmatic stream serialization and transparent to it: the next product kernel of the stream may
-  // start streaming its weights at once; its own griddepcontrol.wait holds its use of A, the scratch and the outputs
-  // until this kernel, and with it the product whose flags it waits for (this rank's own flag comes last), has ended.
+// Lane r waits (bounded) until rank r's arrival counter covers every sharded product this rank has queued on the channel
+// so far; a wait that runs out sets the status word and returns. The counters are added to by the peers' product kernels
+// (and this rank's own) with system-scope reductions after a system-scope fence. Reads the product count, changes nothing:
+// waiting twice is harmless.
+__global__ void qmm8_wait_flags_kernel(const uint32_t* flags, int world, const uint32_t* seq_counter, int* status, long long limit) {
+  // Launched with programmatic stream serialization. The next kernel of the stream may start its prologue at once (a
+  // product kernel streams weights there); everything it does after its own griddepcontrol.wait comes after this kernel
+  // has ended. This kernel in turn reads the product count only after the stream's earlier kernels have ended: every
+  // kernel of such a chain waits, so "the previous kernel has ended" implies all earlier ones have.
   ptx::grid_launch_dependents();
+  ptx::grid_dependency_wait();
   const int r = threadIdx.x;
-  const uint32_t seq = *reinterpret_cast<volatile uint32_t*>(seq_counter);
   if (r < world) {
+    const uint32_t target = *reinterpret_cast<const volatile uint32_t*>(seq_counter) * kArriveWeight;
     const long long start = clock64();
-    for (;;) {
+    for (int spins = 0;; spins++) {
       uint32_t v;
       asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flags + r) : "memory");
-      if (static_cast<int32_t>(v - seq) >= 0) break;
-      if (clock64() - start > ptx::kWaitLimitCycles) {
-        atomicExch(status, 5);
-        break;
+      if (static_cast<int32_t>(v - target) >= 0) break;
+      if ((spins & 63) == 63) {
+        if (*reinterpret_cast<volatile int*>(status) != 0) break;
+        if (clock64() - start > limit) {
+          atomicExch(status, 5);
+          break;
+        }
       }
-      __nanosleep(100);
     }
   }
-  __syncwarp();
-  // every slice of product `seq` is here: the next product of this rank announces itself with seq + 1
-  if (r == 0) *reinterpret_cast<volatile uint32_t*>(seq_counter) = seq + 1;
 }
 
 // ------------------------------------------------------------------ the same kernel without any allocation
@@ -979,12 +1033,33 @@ extern "C" int tvb_qmm8_static_scratch(int device, const void* a, int dtype, int
   return 0;
 }
 
+extern "C" int tvb_qmm8_static_scratch_status(int device, void* stream_handle, int* host_out) {
+  TVB_REQUIRE(device >= 0 && device < 64, "tvb_qmm8_static_scratch_status: device index out of range");
+  TVB_REQUIRE(host_out != nullptr, "tvb_qmm8_static_scratch_status: NULL pointer");
+  TVB_CUDA(cudaSetDevice(device));
+  unsigned char* scratch = nullptr;
+  if (static_scratch_address(device, &scratch) != 0) return -1;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_handle);
+  int word = 0;
+  TVB_CUDA(cudaMemcpyAsync(&word, scratch + kStaticCounterBytes + kStaticPartialBytes, sizeof(int), cudaMemcpyDeviceToHost, stream));
+  TVB_CUDA(cudaStreamSynchronize(stream));
+  *host_out = word;
+  return 0;
+}
+
+extern "C" int tvb_set_wait_limit_ms(int ms) {
+  TVB_REQUIRE(ms >= 1 && ms <= 60000, "tvb_set_wait_limit_ms: 1 to 60000 milliseconds");
+  g_wait_limit_cycles.store(static_cast<long long>(ms) * 2000000ll);  // (at most ~2 GHz of SM clock)
+  return 0;
+}
+
 extern "C" int tvb_qmm8_gather(int device, const void* a, int dtype, int64_t a_sm, const int8_t* b, const void* scales,
-                               void* const* c_ranks, uint32_t* const* flag_ranks, int world, int rank, const uint32_t* seq_counter,
-                               int64_t m, int64_t n_local, int64_t k) {
+                               void* const* c_ranks, uint32_t* const* flag_ranks, int world, int rank, uint32_t* seq_counter,
+                               int independent, int64_t m, int64_t n_local, int64_t k) {
+  TVB_REQUIRE(independent >= 0 && independent <= 1024, "tvb_qmm8_gather: independent must be between 0 and 1024");
   TVB_REQUIRE(world >= 1 && world <= kMaxRanks && rank >= 0 && rank < world, "tvb_qmm8_gather: 1 to 8 ranks");
   TVB_REQUIRE(dtype == TVB_F16 || dtype == TVB_BF16, "tvb_qmm8_gather: A must be float16 or bfloat16");
-  TVB_REQUIRE(m >= 1 && m <= 16 && n_local >= 1 && k >= 1, "tvb_qmm8_gather: 1 <= m <= 16 (the decode kernel)");
+  TVB_REQUIRE(m >= 1 && m <= 64 && n_local >= 1 && k >= 1, "tvb_qmm8_gather: 1 <= m <= 64 (the decode kernel)");
   TVB_REQUIRE(a != nullptr && b != nullptr && scales != nullptr && c_ranks != nullptr && flag_ranks != nullptr &&
                   seq_counter != nullptr,
               "tvb_qmm8_gather: NULL pointer");
@@ -1002,16 +1077,27 @@ extern "C" int tvb_qmm8_gather(int device, const void* a, int dtype, int64_t a_s
   g.rank = rank;
   g.seq = seq_counter;
   g.n_total = n_local * world;
+  const int passes = static_cast<int>(ceil_div(m, 16));
   const int mi = static_cast<int>(m), ni = static_cast<int>(n_local), ki = static_cast<int>(k);
   const int64_t stride = m == 1 ? k : a_sm;
-  if (dtype == TVB_BF16)
-    return mi <= 8 ? launch_skinny<TVB_BF16, 1>(device, stream, a, stride, b, scales, g.c[rank], mi, ni, ki, 0, &g)
-                   : launch_skinny<TVB_BF16, 2>(device, stream, a, stride, b, scales, g.c[rank], mi, ni, ki, 0, &g);
-  return mi <= 8 ? launch_skinny<TVB_F16, 1>(device, stream, a, stride, b, scales, g.c[rank], mi, ni, ki, 0, &g)
-                 : launch_skinny<TVB_F16, 2>(device, stream, a, stride, b, scales, g.c[rank], mi, ni, ki, 0, &g);
+  // 16 rows of A per pass; every pass is a product of its own on the channel (it counts and is waited for like one)
+  for (int m0 = 0; m0 < mi; m0 += 16) {
+    const int rows = mi - m0;
+    // (the passes of one product do not depend on each other: pass i need not wait for the i passes before it either)
+    g.independent = static_cast<uint32_t>(independent * passes + m0 / 16);
+    int rc;
+    if (dtype == TVB_BF16)
+      rc = rows <= 8 ? launch_skinny<TVB_BF16, 1>(device, stream, a, stride, b, scales, g.c[rank], mi, ni, ki, m0, &g)
+                     : launch_skinny<TVB_BF16, 2>(device, stream, a, stride, b, scales, g.c[rank], mi, ni, ki, m0, &g);
+    else
+      rc = rows <= 8 ? launch_skinny<TVB_F16, 1>(device, stream, a, stride, b, scales, g.c[rank], mi, ni, ki, m0, &g)
+                     : launch_skinny<TVB_F16, 2>(device, stream, a, stride, b, scales, g.c[rank], mi, ni, ki, m0, &g);
+    if (rc != 0) return rc;
+  }
+  return 0;
 }
 
-extern "C" int tvb_wait_flags(int device, const uint32_t* flags, int world, uint32_t* seq_counter) {
+extern "C" int tvb_wait_flags(int device, const uint32_t* flags, int world, const uint32_t* seq_counter) {
   TVB_REQUIRE(flags != nullptr && seq_counter != nullptr && world >= 1 && world <= kMaxRanks, "tvb_wait_flags: bad arguments");
   cudaStream_t stream;
   if (enter(device, &stream) != 0) return -1;
@@ -1026,7 +1112,7 @@ extern "C" int tvb_wait_flags(int device, const uint32_t* flags, int world, uint
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  TVB_CUDA(cudaLaunchKernelEx(&cfg, qmm8_wait_flags_kernel, flags, world, seq_counter, status));
+  TVB_CUDA(cudaLaunchKernelEx(&cfg, qmm8_wait_flags_kernel, flags, world, seq_counter, status, g_wait_limit_cycles.load()));
   return launched("qmm8_wait_flags", dim3(1), dim3(32), 0, stream);
 }
 

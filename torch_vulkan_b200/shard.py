@@ -99,87 +99,109 @@ def barrier(group=None):
         dist.all_reduce(t, group=group)
 
 
-class GatheredOutputs:
-    """Output buffers for the fused sharded decode product (tvb_qmm8_gather): every rank holds a full [m, N] buffer
-    (two of them, used alternately) that all ranks' kernels write their column slices into directly, over NVLink for
-    the peers, plus per-buffer arrival flags. No collective call, no copy: the product kernel's epilogue is the gather.
+class PeerChannel:
+    """What the ranks of one node share for the fused sharded products: every rank's array of arrival counters (one
+    entry per source rank, added to by the product kernels of all ranks over NVLink) and, per rank, the device-resident
+    count of products queued so far. All sharded products of a process go through one channel and are totally ordered
+    on it: each product kernel waits for the previous one to have arrived from every rank before it reads its A or
+    stores a column (see tvb_qmm8_gather in include/tvb200.h).
 
-    `object_group` is a gloo group used once, to exchange the buffers' IPC handles.
+    `object_group` is a gloo group, used to exchange IPC handles. Construction is collective.
     """
 
-    def __init__(self, m, n_total, dtype, device_index, object_group, depth=2):
+    def __init__(self, device_index, object_group):
         import ctypes
 
         from . import cabi
 
         self._c, self._ct = cabi, ctypes
         self.world, self.rank = dist.get_world_size(), dist.get_rank()
-        self.dev, self.m, self.n_total, self.depth = device_index, m, n_total, depth
+        self.dev, self.group = device_index, object_group
         vk = torch.device("vk", device_index)
-        self.bufs = [torch.empty((m, n_total), dtype=dtype, device=vk) for _ in range(depth)]
-        self.flags = [torch.zeros(self.world, dtype=torch.int32, device=vk) for _ in range(depth)]
-        lib = cabi.lib()
-
-        def export(t):
-            handle, off = ctypes.create_string_buffer(64), ctypes.c_uint64(0)
-            cabi.check(lib.tvb_ipc_export(device_index, t.data_ptr(), handle, ctypes.byref(off)))
-            return handle.raw, off.value
-
-        mine = [(export(b), export(f)) for b, f in zip(self.bufs, self.flags)]
-        everyone = [None] * self.world
-        dist.all_gather_object(everyone, mine, group=object_group)
-
-        def import_(entry):
-            handle, off = entry
-            out = ctypes.c_void_p(0)
-            cabi.check(lib.tvb_ipc_import(device_index, handle, off, ctypes.byref(out)))
-            return out.value
-
-        self.c_ptrs, self.flag_ptrs = [], []
-        for d in range(depth):
-            cs, fs = [], []
-            for r in range(self.world):
-                if r == self.rank:
-                    cs.append(self.bufs[d].data_ptr())
-                    fs.append(self.flags[d].data_ptr())
-                else:
-                    cs.append(import_(everyone[r][d][0]))
-                    fs.append(import_(everyone[r][d][1]))
-            self.c_ptrs.append((ctypes.c_void_p * self.world)(*cs))
-            self.flag_ptrs.append((ctypes.c_void_p * self.world)(*fs))
-        self.calls = 0
-        self.seq_counter = torch.ones(1, dtype=torch.int32, device=vk)  # the sequence number lives on the device
-        cabi.check(lib.tvb_synchronize(device_index))  # the flags are zero before any peer may write them
+        self.state = torch.zeros(16, dtype=torch.int32, device=vk)  # [0, world): arrival counters; [8]: product count
+        self.flags, self.seq = self.state[:8], self.state[8:9]
+        cabi.check(cabi.lib().tvb_synchronize(device_index))  # the counters are zero before any peer may add to them
+        self.flag_ptrs = self.share(self.flags)
         barrier(object_group)
 
-    def weight_int8pack_mm(self, a, w_shard, scales_shard):
-        """The full [m, N] product on every rank; valid for work queued after this call on the backend's stream."""
-        cabi, lib = self._c, self._c.lib()
+    def share(self, tensor):
+        """Maps `tensor` (this rank's) and every peer's counterpart into this process: a ctypes array of `world`
+        device pointers, entry r being rank r's tensor. Collective; the tensor must stay alive."""
+        ctypes, cabi, lib = self._ct, self._c, self._c.lib()
+        handle, off = ctypes.create_string_buffer(64), ctypes.c_uint64(0)
+        cabi.check(lib.tvb_ipc_export(self.dev, tensor.data_ptr(), handle, ctypes.byref(off)))
+        everyone = [None] * self.world
+        dist.all_gather_object(everyone, (handle.raw, off.value), group=self.group)
+        ptrs = []
+        for r, (h, o) in enumerate(everyone):
+            if r == self.rank:
+                ptrs.append(tensor.data_ptr())
+            else:
+                out = ctypes.c_void_p(0)
+                cabi.check(lib.tvb_ipc_import(self.dev, h, o, ctypes.byref(out)))
+                ptrs.append(out.value)
+        return (ctypes.c_void_p * self.world)(*ptrs)
+
+    def wait(self):
+        """Queues the kernel that waits until every rank's slices of all products queued so far have arrived: what is
+        queued after it on the backend's stream (copies, any other kernel) may read the gathered outputs."""
+        self._c.check(self._c.lib().tvb_wait_flags(self.dev, self.flags.data_ptr(), self.world, self.seq.data_ptr()))
+
+
+class GatheredOutputs:
+    """Output buffers for the fused sharded decode product (tvb_qmm8_gather): every rank holds full [m, N] buffers
+    (`depth` of them, written in turn) that all ranks' kernels store their column slices into directly, over NVLink
+    for the peers. No collective call, no copy: the product kernel's epilogue is the gather.
+
+    A buffer returned by weight_int8pack_mm may be handed to the next sharded product of the channel as its A at once
+    (that kernel waits for the columns itself); anything else must be queued after channel.wait(). With two buffers a
+    buffer is rewritten by the second product after the one that filled it, which is safe as long as its other readers
+    on this rank were queued before this rank's next product. A CUDA graph freezes the buffer its products use: record
+    `depth` graphs in turn (or `depth` steps per graph) when the outputs of a step are read after the step.
+    """
+
+    def __init__(self, m, n_total, dtype, channel, depth=2):
+        self._c = channel._c
+        self.channel, self.m, self.n_total, self.depth = channel, m, n_total, depth
+        vk = torch.device("vk", channel.dev)
+        self.bufs = [torch.empty((m, n_total), dtype=dtype, device=vk) for _ in range(depth)]
+        self.c_ptrs = [channel.share(b) for b in self.bufs]
+        self.calls = 0
+        barrier(channel.group)
+
+    def weight_int8pack_mm(self, a, w_shard, scales_shard, buf=None, independent=0):
+        """Queues the product; returns the [m, N] buffer every rank's columns are stored into (`buf`: which of the
+        `depth` buffers, the same on every rank; default: in turn). `independent`: how many of the channel's latest
+        products this one has nothing to do with (it reads none of their outputs and writes no buffer a rank may still
+        be reading while they run): it then does not wait for them."""
+        cabi, lib, ch = self._c, self._c.lib(), self.channel
         m, k = a.shape
         n_local = w_shard.shape[0]
-        assert m == self.m and n_local * self.world == self.n_total and scales_shard.dtype == a.dtype
-        d = self.calls % self.depth
+        assert m == self.m and n_local * ch.world == self.n_total and scales_shard.dtype == a.dtype
+        d = self.calls % self.depth if buf is None else buf
         self.calls += 1
-        cabi.check(lib.tvb_qmm8_gather(self.dev, a.data_ptr(), cabi._dtype_code(a.dtype), a.stride(0), w_shard.data_ptr(),
-                                       scales_shard.data_ptr(), self.c_ptrs[d], self.flag_ptrs[d], self.world, self.rank,
-                                       self.seq_counter.data_ptr(), m, n_local, k))
-        cabi.check(lib.tvb_wait_flags(self.dev, self.flags[d].data_ptr(), self.world, self.seq_counter.data_ptr()))
+        cabi.check(lib.tvb_qmm8_gather(ch.dev, a.data_ptr(), cabi._dtype_code(a.dtype), a.stride(0), w_shard.data_ptr(),
+                                       scales_shard.data_ptr(), self.c_ptrs[d], ch.flag_ptrs, ch.world, ch.rank,
+                                       ch.seq.data_ptr(), independent, m, n_local, k))
         return self.bufs[d]
 
 
 class StepGraph:
     """A CUDA graph of whatever `fn` queues on the backend's stream (a decoding step: a handful of short kernels whose
-    launch cost would otherwise bound the step). `fn` is run once to warm up, once under capture; replay() queues the
-    recording. Tensors `fn` returns stay alive with the graph and are overwritten by every replay."""
+    launch cost would otherwise bound the step). `fn` is run once to warm up (`warm=False`: not at all, for a step
+    whose shapes have run before), then once under capture; replay() queues the recording. Tensors `fn` returns stay
+    alive with the graph and are overwritten by every replay. What `fn` decides on the host is frozen: a step that
+    alternates output buffers (GatheredOutputs) always replays into the buffers of the recorded call."""
 
-    def __init__(self, fn, device_index=0):
+    def __init__(self, fn, device_index=0, warm=True):
         import ctypes
 
         from . import cabi
 
         self._c, self.dev = cabi, device_index
         lib = cabi.lib()
-        fn()
+        if warm:
+            fn()
         cabi.check(lib.tvb_synchronize(device_index))
         cabi.check(lib.tvb_graph_begin(device_index))
         try:
