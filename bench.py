@@ -26,6 +26,7 @@ benchmark configurations, each with its own roofline and CPU baseline.
 """
 
 import argparse
+import datetime
 import json
 import math
 import os
@@ -401,10 +402,13 @@ STACK_SHAPES = [(6144, 4096), (4096, 4096), (28672, 4096), (4096, 14336)]  # qkv
 
 
 def stack_host_weights():
+    """The four weight matrices of a layer: uniform int8, and per-channel scales uniform in [0.5, 1.5] / (73.6 sqrt(k)) (73.6:
+    the root mean square of the weights), so that every product keeps the magnitude of its input and the activations of a
+    128-product chain stay finite and away from zero: the chain's outputs can be checked."""
     host = []
     for i, (n, k) in enumerate(STACK_SHAPES):
         w = torch.randint(-127, 128, (n, k), dtype=torch.int8, generator=gen(40 + i))
-        sc = (torch.rand(n, generator=gen(50 + i)) * 2e-3 + 1e-4).to(torch.bfloat16)
+        sc = ((torch.rand(n, generator=gen(50 + i)) + 0.5) / (73.6 * math.sqrt(k))).to(torch.bfloat16)
         host.append((w, sc))
     return host
 
@@ -734,7 +738,9 @@ def main():
         import torch.distributed as dist
 
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl")  # (no device_id: with "vk" registered, torch takes that for the accelerator)
+        # (no device_id: with "vk" registered, torch takes that for the accelerator; a short timeout: a rank that fell out must
+        # not hold the others for ten minutes)
+        dist.init_process_group("nccl", timeout=datetime.timedelta(seconds=180))
         objects = dist.new_group(backend="gloo")
         if os.environ.get("TVB200_GATHER", "fused") == "fused":
             channel = shard.PeerChannel(local_rank, objects)

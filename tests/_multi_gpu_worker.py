@@ -2,6 +2,7 @@
 products on device "vk", with the fused peer-store gather and with the NCCL all-gather, compared with the single-GPU
 product and the reference's bound."""
 
+import datetime
 import os
 import sys
 
@@ -22,7 +23,9 @@ def main():
 
     torch.cuda.set_device(local)
     tv.set_device(local)
-    dist.init_process_group("nccl")  # (no device_id: with "vk" registered, torch takes that for the accelerator)
+    # (no device_id: with "vk" registered, torch takes that for the accelerator; a short timeout: a rank that fell out must
+    # not hold the others for ten minutes)
+    dist.init_process_group("nccl", timeout=datetime.timedelta(seconds=180))
     dev = f"vk:{local}"
     objects = dist.new_group(backend="gloo")
     try:

@@ -62,7 +62,7 @@ def device_name(device=0):
 
 def _index(device):
     if device is None:
-        return 0
+        return _current[0]  # (as the CUDA module: no device named means the current one)
     if isinstance(device, int):
         return device
     d = torch.device(device)
