@@ -33,8 +33,12 @@
 #include "../core/tensormap.h"
 #include "numerics.cuh"
 #include "ptx.cuh"
+#include "qmm8_skinny.cuh"
 
 namespace tvb {
+
+// SM cycles the waits for peers may take (tvb_set_wait_limit_ms; the default is about two seconds).
+std::atomic<long long> g_wait_limit_cycles{ptx::kWaitLimitCycles};
 
 // The tcgen05 kernel for m > 16 (qmm8_tc.cu).
 bool qmm8_tc_usable(const void* a, int dtype, int64_t a_sm, const int8_t* b, int64_t m, int64_t n, int64_t k);
@@ -157,56 +161,6 @@ __global__ void __launch_bounds__(256) qmm8_f32_kernel(const float* __restrict__
 
 // ------------------------------------------------------------------ skinny kernel
 
-constexpr int kChunkK = 128;  // k values (= bytes of a weight row) per pipeline stage
-constexpr size_t kCounterBytes = 65536;                                   // scratch: tile counters first
-constexpr int kMaxTiles = static_cast<int>(kCounterBytes / sizeof(int)) - 1;  // (the last int counts finished CTAs)
-
-template <int NT, int RW, int NWARPS>
-struct SkinnyCfg {
-  static constexpr int kRowsPerTile = NWARPS * RW * 16;
-  static constexpr int kTokens = NT * 8;
-  static constexpr int kWeightBytes = kRowsPerTile * kChunkK;   // one TMA box
-  static constexpr int kTokenBoxBytes = kTokens * 128;          // 64 k of 16-bit values per row: two boxes per stage
-  static constexpr int kStageBytes = kWeightBytes + 2 * kTokenBoxBytes;
-  static constexpr int kStages = (224 * 1024 - kTokens * kRowsPerTile * 2) / kStageBytes < 8 ? (224 * 1024 - kTokens * kRowsPerTile * 2) / kStageBytes : 8;
-  static constexpr int kThreads = (NWARPS + 2) * 32;  // consumers, the producer warp, the agent warp
-  static constexpr int kOutTileBytes = kTokens * kRowsPerTile * 2;  // one tile's outputs, staged for coalesced stores
-  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /* alignment slack */ + 256 /* barriers */ + kOutTileBytes;
-  static constexpr int kPartialFloats = NWARPS * RW * NT * 32 * 4;  // one CTA's accumulators
-};
-
-// int8 x 4 (one 32-bit word, k ascending) -> two packed pairs of 16-bit floats, exactly.
-// bf16: the low 7 bits ride a 2^7 exponent (0x4300 | l = 128 + l); the same exponent with
-// the sign bit as its top mantissa bit is 128 or 256; their difference is the int8 value.
-// f16: 0x6400 | (x + 128) = 1024 + 128 + x; subtract 1152.
-template <int DT>
-__device__ __forceinline__ void widen_int8x4(uint32_t w, uint32_t& lo, uint32_t& hi) {
-  if (DT == TVB_BF16) {
-    uint32_t l = w & 0x7f7f7f7fu, s = w & 0x80808080u;
-    lo = ptx::sub_bf16x2(ptx::prmt(l, 0x43434343u, 0x4140u), ptx::prmt(s, 0x43434343u, 0x4140u));
-    hi = ptx::sub_bf16x2(ptx::prmt(l, 0x43434343u, 0x4342u), ptx::prmt(s, 0x43434343u, 0x4342u));
-  } else {
-    uint32_t u = w ^ 0x80808080u;
-    lo = ptx::sub_f16x2(ptx::prmt(u, 0x64646464u, 0x4140u), 0x64806480u);
-    hi = ptx::sub_f16x2(ptx::prmt(u, 0x64646464u, 0x4342u), 0x64806480u);
-  }
-}
-
-template <int DT>
-__device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
-                                          uint32_t b1) {
-  if (DT == TVB_BF16) ptx::mma_bf16_16816(d, a0, a1, a2, a3, b0, b1);
-  else ptx::mma_f16_16816(d, a0, a1, a2, a3, b0, b1);
-}
-
-constexpr int kMaxRanks = 8;
-
-// SM cycles the waits for peers may take (tvb_set_wait_limit_ms; the default is about two seconds).
-std::atomic<long long> g_wait_limit_cycles{ptx::kWaitLimitCycles};
-
-// What one rank adds to its entry of every rank's arrival counters per sharded product, split over its CTAs (each CTA adds
-// its share when its own columns are out, so the sum is this constant whatever the grid).
-constexpr uint32_t kArriveWeight = 1024;
 
 struct SkinnyParams {
   const void* scales;
@@ -232,39 +186,12 @@ struct SkinnyParams {
 // col], each sum rounded to the output type as the separate kernels would round it (so the fused result is bit for bit
 // that of product, add, add).
 template <int DT>
-__device__ __forceinline__ float half_bits_to_float(uint16_t h) {
-  return DT == TVB_BF16 ? __uint_as_float(static_cast<uint32_t>(h) << 16) : __half2float(__ushort_as_half(h));
-}
-template <int DT>
-__device__ __forceinline__ uint16_t float_to_half_bits(float v) {
-  return DT == TVB_BF16 ? f32_to_bf16_bits(v) : f32_to_f16_bits(v);
-}
-template <int DT>
 __device__ __forceinline__ uint16_t skinny_epilogue(const SkinnyParams& p, uint16_t bits, int token, int col) {
   if (p.bias != nullptr) bits = float_to_half_bits<DT>(half_bits_to_float<DT>(bits) + load_float<DT>(p.bias, col));
   if (p.residual != nullptr)
     bits = float_to_half_bits<DT>(half_bits_to_float<DT>(bits) +
                                   load_float<DT>(p.residual, static_cast<int64_t>(token) * p.c_ld + p.c_col0 + col));
   return bits;
-}
-
-// First unit of CTA c when `units` units are cut into `grid` contiguous ranges. (32-bit arithmetic whenever the products
-// fit, which the kernel checks once: 64-bit division is a long instruction sequence, and these run between segments.)
-__device__ __forceinline__ long long range_start(long long c, long long units, long long grid, bool small) {
-  if (small) return static_cast<unsigned>(c) * static_cast<unsigned>(units) / static_cast<unsigned>(grid);
-  return c * units / grid;
-}
-// The CTA whose range holds unit x.
-__device__ __forceinline__ int range_owner(long long x, long long units, long long grid, bool small) {
-  if (small)
-    return static_cast<int>((static_cast<unsigned>(x + 1) * static_cast<unsigned>(grid) + static_cast<unsigned>(units) - 1u) /
-                            static_cast<unsigned>(units)) - 1;
-  return static_cast<int>(((x + 1) * grid + units - 1) / units - 1);
-}
-
-// The tile that holds unit u.
-__device__ __forceinline__ int unit_tile(long long u, int chunks, bool small) {
-  return small ? static_cast<int>(static_cast<unsigned>(u) / static_cast<unsigned>(chunks)) : static_cast<int>(u / chunks);
 }
 
 // ADDS: the instantiation whose epilogue also adds a bias and a residual (tvb_qmm8_linear); the plain product carries no
