@@ -155,20 +155,20 @@ TVB_API int tvb_qmm8_widened(int device, const void* a, int dtype, int64_t a_sm,
  * pointers, entry r being rank r's output buffer as mapped into this process (tvb_ipc_export on the owner,
  * tvb_ipc_import here).
  *
- * Arrival is counted on a channel: every rank owns an array of `world` uint32 arrival counters, zero at the start
- * (flag_ranks: host array of `world` device pointers, entry r being rank r's array as mapped here), and a uint32 product
- * count in its own device memory, zero at the start (seq_counter). Every CTA of the product kernel, once its columns are
- * stored on every rank, adds its share to entry `rank` of every rank's array (system scope, after a system-scope fence);
- * a product adds 1024 in all, so rank r's slices of the first s products have arrived here when entry r of this rank's
- * array has reached 1024 * s. The kernel's last CTA adds one to the product count.
+ * Arrival is counted on a channel: every rank owns an array of 32 uint32 arrival counters ([4 slots][8 source ranks],
+ * 16-byte aligned), zero at the start (flag_ranks: host array of `world` device pointers, entry r being rank r's array as
+ * mapped here), and a uint32 product count in its own device memory, zero at the start (seq_counter). Product number q of
+ * the channel (counted from zero) is reported in slot q % 4: every CTA of the product kernel, once its columns are stored
+ * on every rank, adds its share to counter [q % 4][rank] of every rank's array (system scope, after a system-scope fence);
+ * a product adds 1024 in all, so rank r's slice of product q has arrived here when counter [q % 4][r] of this rank's array
+ * has reached 1024 * (q / 4 + 1). The kernel's last CTA adds one to the product count.
  *
  * Ordering. Before it reads A or stores a column, a product kernel waits (bounded, see tvb_set_wait_limit_ms) until all
  * ranks have delivered every earlier product of the channel; meanwhile its weights already stream into shared memory. So
  * (1) the next sharded product may take a gathered output as its A without any call in between, and (2) an output buffer
  * may be written again by the second product after the one that filled it (use two buffers in turn), provided that
- * everything else that reads it on this rank was queued before this rank's next product. `independent` = i > 0 relaxes
- * the wait to all but the latest i products of the channel (products of the same m, a pass per 16 rows counting as part
- * of its product): for a product that neither reads the outputs of those i products nor writes a buffer that any rank
+ * everything else that reads it on this rank was queued before this rank's next product. `independent` = i (1 to 3)
+ * relaxes the wait to all but the latest i products of the channel (a pass of 16 rows counts as a product here): for a product that neither reads the outputs of those i products nor writes a buffer that any rank
  * may still be reading while they run. Work that is not a sharded
  * product of the same channel (copies, other kernels) must be queued after tvb_wait_flags, which queues a one-warp
  * kernel that waits in the same way for all products queued so far and changes nothing. The counts live on the device,
@@ -183,6 +183,39 @@ TVB_API int tvb_wait_flags(int device, const uint32_t* flags, int world, const u
 /* How long the kernels above wait for peers before they give up (default about 2000 ms). Process-wide; applies to
  * kernels launched (or captured) afterwards. 1 <= ms <= 60000. */
 TVB_API int tvb_set_wait_limit_ms(int ms);
+/* ---- a list of decode products in one launch (no counterpart in the reference, which issues one dispatch per product:
+ *      crates/pyvk/csrc/quant.cpp:86-117) ----
+ * A chain is a fixed sequence of int8 weight-only products (the Linears of a decoder stack for one token step; the products
+ * of one decoding step) that one persistent kernel walks: the weights of the next products stream into shared memory while
+ * the current one is finished, so the start-up and wind-down of a launch, which cost more than a sharded decode product's
+ * streaming time, are paid once per chain. Results are bit for bit those of tvb_qmm8 (m <= 16 per pass) product by product.
+ *
+ * tvb_qmm8_chain_create records the products: all pointers are device pointers that must stay valid (and whose contents
+ * the caller may rewrite between runs); product i may take the output of product i - 1 as its A. c_ranks: host array of
+ * `world` pointers to every rank's [m, n_local * world] output buffer (world == 1: one pointer, the [m, n_local] output).
+ * `independent` as in tvb_qmm8_gather (0 to 3): a product starts when all earlier products of the chain, all but the latest
+ * `independent`, are complete on every rank. 1 <= m <= 64 (16 rows per pass), k a multiple of 128, A's rows and B 16-byte
+ * aligned; dtype TVB_F16 or TVB_BF16 for the whole chain. Sharded chains (world > 1) use the channel of tvb_qmm8_gather
+ * (flag_ranks, seq_counter), on which a chain of n passes counts as n products; every rank must run the same chains in the
+ * same order. With world == 1 both may be NULL (the chain then keeps counters of its own). wait_at_end != 0: the launch
+ * ends only when every rank's columns of the last product have arrived in this rank's buffers, so work queued after
+ * tvb_qmm8_chain_run may read them without tvb_wait_flags. tvb_qmm8_chain_run queues one cooperative launch on the device's
+ * stream (capturable in a CUDA graph). All waits inside are bounded (tvb_set_wait_limit_ms); one that runs out is reported
+ * by tvb_synchronize as status 5. tvb_qmm8_chain_destroy waits for the device's stream and frees the chain. */
+typedef struct TvbChainItem {
+  const void* a;
+  int64_t a_sm;
+  const int8_t* b;
+  const void* scales;
+  void* const* c_ranks;
+  int64_t m, n_local, k;
+  int32_t independent;
+  int32_t reserved;
+} TvbChainItem;
+TVB_API int tvb_qmm8_chain_create(int device, int dtype, const TvbChainItem* items, int count, uint32_t* const* flag_ranks,
+                                  int world, int rank, uint32_t* seq_counter, int wait_at_end, void** chain);
+TVB_API int tvb_qmm8_chain_run(int device, void* chain);
+TVB_API void tvb_qmm8_chain_destroy(void* chain);
 /* A device allocation as a 64-byte handle plus offset that another process of the node can map (cudaIpc*). */
 TVB_API int tvb_ipc_export(int device, const void* ptr, uint8_t* handle64, uint64_t* offset);
 TVB_API int tvb_ipc_import(int device, const uint8_t* handle64, uint64_t offset, void** out);

@@ -396,10 +396,10 @@ def test_gather_world1_counts_and_chains(abi):
     da, db, ds, db2, ds2 = dev(a), dev(b), dev(s), dev(b2), dev(s2)
     c1 = torch.zeros(m, n, dtype=torch.bfloat16, device="cuda")
     c2 = torch.zeros(m, 384, dtype=torch.bfloat16, device="cuda")
-    state = torch.zeros(16, dtype=torch.int32, device="cuda")  # [0, 8): arrival counters; [8]: product count
+    state = torch.zeros(64, dtype=torch.int32, device="cuda")  # [0, 32): arrival counters [slot][rank]; [32]: product count
     torch.cuda.synchronize()
     flags = (ctypes.c_void_p * 1)(state.data_ptr())
-    seq = state.data_ptr() + 32
+    seq = state.data_ptr() + 128
     for c, aa, bb, ss, nn, kk in ((c1, da, db, ds, n, k), (c2, c1, db2, ds2, 384, n)):
         outs = (ctypes.c_void_p * 1)(c.data_ptr())
         abi.check(lib.tvb_qmm8_gather(0, aa.data_ptr(), abi.BF16, aa.stride(0), bb.data_ptr(), ss.data_ptr(), outs, flags, 1, 0,
@@ -407,7 +407,7 @@ def test_gather_world1_counts_and_chains(abi):
     abi.check(lib.tvb_wait_flags(0, state.data_ptr(), 1, ctypes.c_void_p(seq)))
     abi.synchronize()
     st = state.cpu()
-    assert st[0].item() == 2 * 1024 and st[8].item() == 2
+    assert st[0].item() == 1024 and st[8].item() == 1024 and st[32].item() == 2  # products 0 and 1: slots 0 and 1
     want1, tol1 = C.int8_want(a, b, s)
     assert ((c1.cpu().float() - want1.float()).abs() <= tol1).all()
     want2, tol2 = C.int8_want(c1.cpu(), b2, s2)
@@ -424,11 +424,11 @@ def test_wait_for_peers_runs_out_and_is_reported(abi):
     abi.check(lib.tvb_set_wait_limit_ms(20))
     try:
         # a channel of two ranks whose other rank does not exist: one product counted, nothing ever arrives
-        state = torch.zeros(16, dtype=torch.int32, device="cuda")
-        state[8] = 1
+        state = torch.zeros(64, dtype=torch.int32, device="cuda")
+        state[32] = 1
         torch.cuda.synchronize()
         t0 = time.perf_counter()
-        abi.check(lib.tvb_wait_flags(0, state.data_ptr(), 2, ctypes.c_void_p(state.data_ptr() + 32)))
+        abi.check(lib.tvb_wait_flags(0, state.data_ptr(), 2, ctypes.c_void_p(state.data_ptr() + 128)))
         rc = lib.tvb_synchronize(0)
         waited = time.perf_counter() - t0
         assert rc == -1 and b"status 5" in lib.tvb_last_error()
@@ -439,12 +439,12 @@ def test_wait_for_peers_runs_out_and_is_reported(abi):
         da, db, ds = dev(a), dev(b), dev(s)
         mine = torch.zeros(m, 2 * n, dtype=torch.bfloat16, device="cuda")
         theirs = torch.zeros(m, 2 * n, dtype=torch.bfloat16, device="cuda")  # (stands in for the missing peer's buffer)
-        their_state = torch.zeros(16, dtype=torch.int32, device="cuda")
+        their_state = torch.zeros(64, dtype=torch.int32, device="cuda")
         torch.cuda.synchronize()
         outs = (ctypes.c_void_p * 2)(mine.data_ptr(), theirs.data_ptr())
         flags = (ctypes.c_void_p * 2)(state.data_ptr(), their_state.data_ptr())
         abi.check(lib.tvb_qmm8_gather(0, da.data_ptr(), abi.BF16, da.stride(0), db.data_ptr(), ds.data_ptr(), outs, flags, 2, 0,
-                                      ctypes.c_void_p(state.data_ptr() + 32), 0, m, n, k))
+                                      ctypes.c_void_p(state.data_ptr() + 128), 0, m, n, k))
         assert lib.tvb_synchronize(0) == -1 and b"status 5" in lib.tvb_last_error()
         assert lib.tvb_synchronize(0) == 0  # reported once, then cleared
     finally:
@@ -454,3 +454,51 @@ def test_wait_for_peers_runs_out_and_is_reported(abi):
     got = abi.qmm8(dev(a), dev(b), dev(s), variant=2)
     abi.synchronize()
     assert ((got.cpu().float() - want.float()).abs() <= tol).all()
+
+
+# ---------------------------------------------------------------- a list of products in one launch
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_chain_is_bit_for_bit_the_single_products(abi, dtype):
+    """tvb_qmm8_chain_*: products that feed one another, independent ones, a ragged one, one with several passes of 16 rows and
+    one with fewer units than CTAs, all in one persistent launch; every output equals tvb_qmm8's decode kernel on the same
+    inputs bit for bit, run after run, also after the inputs were rewritten in place."""
+    from torch_vulkan_b200 import shard
+
+    def weights(n, k, seed, shrink=1.0):
+        _, b, s = C.config_int8(1, k, n, dtype, seed=seed)
+        return dev(b), dev((s.float() * shrink).to(dtype))
+
+    x = dev(torch.randn(4, 1024, generator=C.gen(1)).to(dtype))
+    x2 = dev(torch.randn(16, 2048, generator=C.gen(2)).to(dtype))
+    x3 = dev(torch.randn(40, 256, generator=C.gen(3)).to(dtype))
+    x4 = dev(torch.randn(1, 8192, generator=C.gen(4)).to(dtype))
+    w1, s1 = weights(640, 1024, 11, 1 / 30)
+    w2, s2 = weights(384, 512, 12, 1 / 20)
+    w3, s3 = weights(4099, 2048, 13)
+    w4, s4 = weights(300, 256, 14)
+    w5, s5 = weights(3584, 8192, 15)
+    w6, s6 = weights(16, 128, 16)
+    h1 = torch.zeros(4, 640, dtype=dtype, device="cuda")
+    h2 = torch.zeros(4, 384, dtype=dtype, device="cuda")
+    h3 = torch.zeros(4, 16, dtype=dtype, device="cuda")
+    o3 = torch.zeros(16, 4099, dtype=dtype, device="cuda")
+    o4 = torch.zeros(40, 300, dtype=dtype, device="cuda")
+    o5 = torch.zeros(1, 3584, dtype=dtype, device="cuda")
+    torch.cuda.synchronize()
+    chain = shard.ProductChain([(x, w1, s1, h1), (h1[:, :512], w2, s2, h2), (x2, w3, s3, o3, 2), (h2[:, :128], w6, s6, h3, 1),
+                                (x3, w4, s4, o4, 1), (x4, w5, s5, o5, 3)])
+    for run in range(3):
+        if run == 2:
+            x.copy_(dev(torch.randn(4, 1024, generator=C.gen(9)).to(dtype)))
+            x4.mul_(0.5)
+            torch.cuda.synchronize()
+        chain.run()
+        abi.synchronize()
+        for a, w, s, got in ((x, w1, s1, h1), (h1[:, :512], w2, s2, h2), (x2, w3, s3, o3), (h2[:, :128], w6, s6, h3),
+                             (x3, w4, s4, o4), (x4, w5, s5, o5)):
+            want = abi.qmm8(a, w, s, variant=2)
+            abi.synchronize()
+            assert torch.equal(got.view(torch.int16), want.view(torch.int16)), f"run {run}: {tuple(a.shape)} x {tuple(w.shape)}"
+    want, tol = C.int8_want(x4.cpu(), w5.cpu(), s5.cpu())
+    assert ((o5.cpu().float() - want.float()).abs() <= tol).all()

@@ -22,6 +22,11 @@ class TvbAlloc(ctypes.Structure):
     _fields_ = [("handle", _vp), ("ptr", _vp), ("size", _u64), ("device", _c.c_int32), ("pad", _c.c_int32)]
 
 
+class TvbChainItem(ctypes.Structure):
+    _fields_ = [("a", _vp), ("a_sm", _i64), ("b", _vp), ("scales", _vp), ("c_ranks", _c.POINTER(_vp)), ("m", _i64),
+                ("n_local", _i64), ("k", _i64), ("independent", _c.c_int32), ("reserved", _c.c_int32)]
+
+
 # name -> (restype, argtypes): every entry point include/tvb200.h declares
 SIGNATURES = {
     "tvb_last_error": (_c.c_char_p, []),
@@ -59,6 +64,9 @@ SIGNATURES = {
     "tvb_qmm8_gather": (_i, [_i, _vp, _i, _i64, _vp, _vp, _c.POINTER(_vp), _c.POINTER(_vp), _i, _i, _vp, _i, _i64, _i64, _i64]),
     "tvb_wait_flags": (_i, [_i, _vp, _i, _vp]),
     "tvb_set_wait_limit_ms": (_i, [_i]),
+    "tvb_qmm8_chain_create": (_i, [_i, _i, _c.POINTER(TvbChainItem), _i, _c.POINTER(_vp), _i, _i, _vp, _i, _c.POINTER(_vp)]),
+    "tvb_qmm8_chain_run": (_i, [_i, _vp]),
+    "tvb_qmm8_chain_destroy": (None, [_vp]),
     "tvb_graph_begin": (_i, [_i]),
     "tvb_graph_end": (_i, [_i, _c.POINTER(_vp)]),
     "tvb_graph_launch": (_i, [_i, _vp]),

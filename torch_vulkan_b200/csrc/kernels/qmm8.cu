@@ -256,25 +256,21 @@ __global__ void __launch_bounds__((NWARPS + 2) * 32, 1)
       // Sharded product: before this CTA reads A or stores a column, every rank must have delivered the earlier products
       // of the channel (all but the latest `independent` ones). The previous product's output may be this one's A; and a
       // rank that has delivered has also finished reading its own A, which this product may be about to overwrite (two
-      // output buffers in turn). Lane r waits (bounded) for rank r's counter; the counters only grow, by kArriveWeight per
-      // product and rank.
+      // output buffers in turn). The warp waits (bounded), one arrival counter per lane.
       ptx::grid_dependency_wait();  // (this rank's previous kernel has ended: the product count below is final)
-      if (lane < p.nranks) {
-        const uint32_t count = *reinterpret_cast<const volatile uint32_t*>(p.seq);
-        const uint32_t target = (count > p.independent ? count - p.independent : 0u) * kArriveWeight;
-        const uint32_t* mine_flag = p.flags[p.rank] + lane;
+      {
+        const long long count = *reinterpret_cast<const volatile uint32_t*>(p.seq);
+        const long long upto = count - 1 - static_cast<long long>(p.independent);
         const long long start = clock64();
-        for (int spins = 0;; spins++) {
-          uint32_t v;
-          asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine_flag) : "memory");
-          if (static_cast<int32_t>(v - target) >= 0) break;
+        for (int spins = 0; !arrivals_complete_warp(p.flags[p.rank], p.nranks, upto); spins++) {
           if ((spins & 63) == 63) {
             // an earlier give-up (here or in an earlier kernel) is final: nobody waits the limit out a second time
-            if (*reinterpret_cast<volatile int*>(p.status) != 0) break;
-            if (clock64() - start > p.wait_limit) {
+            bool stop = *reinterpret_cast<volatile int*>(p.status) != 0;
+            if (!stop && clock64() - start > p.wait_limit) {
               atomicExch(p.status, 5);
-              break;
+              stop = true;
             }
+            if (__any_sync(0xffffffffu, stop)) break;
           }
         }
       }
@@ -676,9 +672,7 @@ __global__ void __launch_bounds__((NWARPS + 2) * 32, 1)
     ptx::named_bar_sync(2, (NWARPS + 1) * 32);  // (the agent warp arrives here too, after whatever it had to store)
     if (threadIdx.x == 0) {
       __threadfence_system();
-      const uint32_t share = (blockIdx.x + 1) * kArriveWeight / gridDim.x - blockIdx.x * kArriveWeight / gridDim.x;
-      for (int r = 0; r < p.nranks; r++)
-        asm volatile("red.relaxed.sys.global.add.u32 [%0], %1;" ::"l"(p.flags[r] + p.rank), "r"(share) : "memory");
+      arrive_publish(p.flags, p.nranks, p.rank, *reinterpret_cast<const volatile uint32_t*>(p.seq), arrive_share());
       // the last CTA to get here counts the product (the next kernel of the stream reads the count after this one has ended)
       if (atomicAdd(p.done, 1) == static_cast<int>(gridDim.x) - 1) {
         atomicExch(p.done, 0);
@@ -814,10 +808,10 @@ bool skinny_ok(const void* a, int dtype, int64_t a_sm, const int8_t* b, int64_t 
 
 // ------------------------------------------------------------------ sharded product: waiting for the peers' columns
 
-// Lane r waits (bounded) until rank r's arrival counter covers every sharded product this rank has queued on the channel
-// so far; a wait that runs out sets the status word and returns. The counters are added to by the peers' product kernels
-// (and this rank's own) with system-scope reductions after a system-scope fence. Reads the product count, changes nothing:
-// waiting twice is harmless.
+// One warp waits (bounded, one arrival counter per lane) until every sharded product this rank has queued on the channel so
+// far has arrived from every rank; a wait that runs out sets the status word and returns. The counters are added to by the
+// peers' product kernels (and this rank's own) with system-scope reductions after a system-scope fence. Reads the product
+// count, changes nothing: waiting twice is harmless.
 __global__ void qmm8_wait_flags_kernel(const uint32_t* flags, int world, const uint32_t* seq_counter, int* status, long long limit) {
   // Launched with programmatic stream serialization. The next kernel of the stream may start its prologue at once (a
   // product kernel streams weights there); everything it does after its own griddepcontrol.wait comes after this kernel
@@ -825,21 +819,16 @@ __global__ void qmm8_wait_flags_kernel(const uint32_t* flags, int world, const u
   // kernel of such a chain waits, so "the previous kernel has ended" implies all earlier ones have.
   ptx::grid_launch_dependents();
   ptx::grid_dependency_wait();
-  const int r = threadIdx.x;
-  if (r < world) {
-    const uint32_t target = *reinterpret_cast<const volatile uint32_t*>(seq_counter) * kArriveWeight;
-    const long long start = clock64();
-    for (int spins = 0;; spins++) {
-      uint32_t v;
-      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flags + r) : "memory");
-      if (static_cast<int32_t>(v - target) >= 0) break;
-      if ((spins & 63) == 63) {
-        if (*reinterpret_cast<volatile int*>(status) != 0) break;
-        if (clock64() - start > limit) {
-          atomicExch(status, 5);
-          break;
-        }
+  const long long upto = static_cast<long long>(*reinterpret_cast<const volatile uint32_t*>(seq_counter)) - 1;
+  const long long start = clock64();
+  for (int spins = 0; !arrivals_complete_warp(flags, world, upto); spins++) {
+    if ((spins & 63) == 63) {
+      bool stop = *reinterpret_cast<volatile int*>(status) != 0;
+      if (!stop && clock64() - start > limit) {
+        atomicExch(status, 5);
+        stop = true;
       }
+      if (__any_sync(0xffffffffu, stop)) break;
     }
   }
 }
@@ -983,7 +972,7 @@ extern "C" int tvb_set_wait_limit_ms(int ms) {
 extern "C" int tvb_qmm8_gather(int device, const void* a, int dtype, int64_t a_sm, const int8_t* b, const void* scales,
                                void* const* c_ranks, uint32_t* const* flag_ranks, int world, int rank, uint32_t* seq_counter,
                                int independent, int64_t m, int64_t n_local, int64_t k) {
-  TVB_REQUIRE(independent >= 0 && independent <= 1024, "tvb_qmm8_gather: independent must be between 0 and 1024");
+  TVB_REQUIRE(independent >= 0 && independent <= 3, "tvb_qmm8_gather: independent must be between 0 and 3");
   TVB_REQUIRE(world >= 1 && world <= kMaxRanks && rank >= 0 && rank < world, "tvb_qmm8_gather: 1 to 8 ranks");
   TVB_REQUIRE(dtype == TVB_F16 || dtype == TVB_BF16, "tvb_qmm8_gather: A must be float16 or bfloat16");
   TVB_REQUIRE(m >= 1 && m <= 64 && n_local >= 1 && k >= 1, "tvb_qmm8_gather: 1 <= m <= 64 (the decode kernel)");
@@ -1011,7 +1000,7 @@ extern "C" int tvb_qmm8_gather(int device, const void* a, int dtype, int64_t a_s
   for (int m0 = 0; m0 < mi; m0 += 16) {
     const int rows = mi - m0;
     // (the passes of one product do not depend on each other: pass i need not wait for the i passes before it either)
-    g.independent = static_cast<uint32_t>(independent * passes + m0 / 16);
+    g.independent = static_cast<uint32_t>(std::min(independent * passes + m0 / 16, kArriveSlots - 1));
     int rc;
     if (dtype == TVB_BF16)
       rc = rows <= 8 ? launch_skinny<TVB_BF16, 1>(device, stream, a, stride, b, scales, g.c[rank], mi, ni, ki, m0, &g)

@@ -58,9 +58,70 @@ __device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a
 
 constexpr int kMaxRanks = 8;
 
-// What one rank adds to its entry of every rank's arrival counters per sharded product, split over its CTAs (each CTA adds
-// its share when its own columns are out, so the sum is this constant whatever the grid).
+// Arrival counters of sharded products (and of the products of a chain). Every rank owns kArriveSlots x kMaxRanks
+// counters. Product number q of a channel (counted from zero, the same on every rank) is reported in slot q % 4: each CTA of
+// rank s, once its columns are stored on every rank, adds its share to counter [q % 4][s] of every rank; the shares of one
+// rank and product add up to kArriveWeight whatever the grid. So product q has arrived from rank s when counter [q % 4][s]
+// has reached (q / 4 + 1) * kArriveWeight. Slots keep products that may be in flight together apart: a product waits at
+// least for all products more than three before it, so a counter never holds shares of two unfinished products at once.
 constexpr uint32_t kArriveWeight = 1024;
+constexpr int kArriveSlots = 4;
+constexpr int kArriveWords = kArriveSlots * kMaxRanks;
+
+__device__ __forceinline__ uint32_t arrive_share() {
+  return (blockIdx.x + 1) * kArriveWeight / gridDim.x - blockIdx.x * kArriveWeight / gridDim.x;
+}
+
+// Adds `share` for product q to this rank's counters on every rank. The caller's earlier stores must be ordered before the
+// call by a system-scope fence of the calling thread.
+__device__ __forceinline__ void arrive_publish(uint32_t* const* flags, int nranks, int rank, uint32_t q, uint32_t share) {
+  const int index = static_cast<int>(q & 3u) * kMaxRanks + rank;
+  for (int r = 0; r < nranks; r++)
+    asm volatile("red.relaxed.sys.global.add.u32 [%0], %1;" ::"l"(flags[r] + index), "r"(share) : "memory");
+}
+
+// The product that slot `slot` must show for "all products up to number `upto` have arrived" (-1: none to show: those further
+// back are implied), and the counter value that shows it.
+__device__ __forceinline__ long long arrive_slot_product(long long upto, int slot) {
+  if (upto < 0) return -1;
+  return upto - ((upto - slot) & 3);
+}
+__device__ __forceinline__ uint32_t arrive_target(long long q) { return (static_cast<uint32_t>(q >> 2) + 1u) * kArriveWeight; }
+
+// One thread's check that all products up to number `upto` have arrived in `mine` (this rank's counters) from all ranks.
+// On success the thread has acquired what the arriving CTAs released.
+__device__ __forceinline__ bool arrivals_complete(const uint32_t* mine, int nranks, long long upto) {
+  bool all = true;
+#pragma unroll
+  for (int slot = 0; slot < kArriveSlots; slot++) {
+    const long long q = arrive_slot_product(upto, slot);
+    if (q < 0) continue;
+    const uint32_t target = arrive_target(q);
+    uint32_t v[kMaxRanks];
+    asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]) : "l"(mine + slot * kMaxRanks) : "memory");
+    asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]) : "l"(mine + slot * kMaxRanks + 4) : "memory");
+#pragma unroll
+    for (int r = 0; r < kMaxRanks; r++)
+      if (r < nranks) all = all && static_cast<int32_t>(v[r] - target) >= 0;
+  }
+  if (all) __threadfence_system();
+  return all;
+}
+
+// The same check by a whole warp, one counter per lane.
+__device__ __forceinline__ bool arrivals_complete_warp(const uint32_t* mine, int nranks, long long upto) {
+  const int lane = threadIdx.x & 31, slot = lane / kMaxRanks, r = lane % kMaxRanks;
+  const long long q = arrive_slot_product(upto, slot);
+  bool ok = true;
+  if (q >= 0 && r < nranks) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine + lane) : "memory");
+    ok = static_cast<int32_t>(v - arrive_target(q)) >= 0;
+  }
+  return __all_sync(0xffffffffu, ok);
+}
 
 template <int DT>
 __device__ __forceinline__ float half_bits_to_float(uint16_t h) {

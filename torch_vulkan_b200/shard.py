@@ -118,8 +118,8 @@ class PeerChannel:
         self.world, self.rank = dist.get_world_size(), dist.get_rank()
         self.dev, self.group = device_index, object_group
         vk = torch.device("vk", device_index)
-        self.state = torch.zeros(16, dtype=torch.int32, device=vk)  # [0, world): arrival counters; [8]: product count
-        self.flags, self.seq = self.state[:8], self.state[8:9]
+        self.state = torch.zeros(64, dtype=torch.int32, device=vk)  # [0, 32): arrival counters [slot][rank]; [32]: product count
+        self.flags, self.seq = self.state[:32], self.state[32:33]
         cabi.check(cabi.lib().tvb_synchronize(device_index))  # the counters are zero before any peer may add to them
         self.flag_ptrs = self.share(self.flags)
         barrier(object_group)
@@ -184,6 +184,61 @@ class GatheredOutputs:
                                        scales_shard.data_ptr(), self.c_ptrs[d], ch.flag_ptrs, ch.world, ch.rank,
                                        ch.seq.data_ptr(), independent, m, n_local, k))
         return self.bufs[d]
+
+
+class ProductChain:
+    """A fixed sequence of int8 weight-only decode products run by one persistent kernel (tvb_qmm8_chain_*): the weights
+    of the next products stream in while the current one is finished, and a product may take the output of the one
+    before it as its A. `products`: a list of (a, w, scales, out[, independent]) with a [m, k] (m <= 64; its buffer is
+    read at every run, so the caller rewrites it in place), w int8 [n_local, k], scales [n_local], and `out` either a
+    [m, n_local] tensor (one GPU) or a GatheredOutputs (sharded: every rank's columns land in every rank's buffer;
+    outputs[i] is then that buffer). `independent` (0 to 3): how many of the products just before it this one has nothing
+    to do with. With a channel the run ends only when the last product has arrived from every rank."""
+
+    def __init__(self, products, device_index=0, channel=None):
+        import ctypes
+
+        from . import cabi
+
+        self._c, self.dev, self.channel = cabi, device_index, channel
+        world = 1 if channel is None else channel.world
+        items = (cabi.TvbChainItem * len(products))()
+        self._keep, self.outputs = [], []
+        for i, prod in enumerate(products):
+            a, w, s, out = prod[:4]
+            m, k = a.shape
+            n_local = w.shape[0]
+            assert w.dtype == torch.int8 and w.is_contiguous() and s.dtype == a.dtype and a.stride(1) == 1
+            if isinstance(out, GatheredOutputs):
+                assert channel is not None and out.m == m and out.n_total == n_local * world
+                d = out.calls % out.depth
+                out.calls += 1
+                ptrs, buf = out.c_ptrs[d], out.bufs[d]
+            else:
+                assert world == 1 and tuple(out.shape) == (m, n_local) and out.is_contiguous() and out.dtype == a.dtype
+                ptrs, buf = (ctypes.c_void_p * 1)(out.data_ptr()), out
+            self._keep += [a, w, s, buf, ptrs]
+            self.outputs.append(buf)
+            items[i] = cabi.TvbChainItem(a.data_ptr(), a.stride(0), w.data_ptr(), s.data_ptr(), ptrs, m, n_local, k,
+                                         prod[4] if len(prod) > 4 else 0, 0)
+        handle = ctypes.c_void_p(0)
+        dtype = cabi._dtype_code(products[0][0].dtype)
+        if channel is None:
+            cabi.check(cabi.lib().tvb_qmm8_chain_create(device_index, dtype, items, len(products), None, 1, 0, None, 0, ctypes.byref(handle)))
+        else:
+            cabi.check(cabi.lib().tvb_qmm8_chain_create(device_index, dtype, items, len(products), channel.flag_ptrs, channel.world,
+                                                        channel.rank, channel.seq.data_ptr(), 1, ctypes.byref(handle)))
+        self.handle = handle
+
+    def run(self):
+        self._c.check(self._c.lib().tvb_qmm8_chain_run(self.dev, self.handle))
+        return self.outputs
+
+    def __del__(self):
+        try:
+            self._c.lib().tvb_qmm8_chain_destroy(self.handle)
+        except Exception:
+            pass
 
 
 class StepGraph:
