@@ -121,6 +121,12 @@ def profiled_traffic():
         return None
 
 
+def mark(what):
+    """Progress on stderr when TVB200_BENCH_TRACE is set (where a run that got stuck was)."""
+    if os.environ.get("TVB200_BENCH_TRACE"):
+        print(f"[bench {time.strftime('%H:%M:%S')}] {what}", file=sys.stderr, flush=True)
+
+
 def roof(bound, achieved, peak, unit, kernel, peak_note):
     return {"bound": bound, "achieved": achieved, "peak": peak, "unit": unit, "frac": achieved / peak, "kernel": kernel,
             "peak_source": peak_note}
@@ -413,6 +419,31 @@ def stack_host_weights():
     return host
 
 
+def check_last_layer(host, qkv, o, gu, h, what):
+    """The last layer's o, gate_up and down products (device results, already on the host) against the CPU product of their
+    own inputs, within the reference's bound."""
+    for got, a_in, (w, sc), name in ((o, qkv[:, :4096], host[1], "o"), (gu, o, host[2], "gate_up"), (h, gu[:, :14336], host[3], "down")):
+        want, tol = int8_expected(a_in.contiguous(), w, sc)
+        if not ((got.float() - want.float()).abs() <= tol).all():
+            raise SystemExit(f"bench.py: {what}: last layer's {name} product outside the reference's bound")
+
+
+def stack_chain(shard, weights, x, m, device_index, channel=None, gathered=None):
+    """The stack's 128 products as one chain (tvb_qmm8_chain_*): every product takes the previous one's output (its first 4096
+    or 14336 columns) as its A. Returns the chain and the last layer's four output buffers."""
+    prods, h, last = [], x, None
+    for layer in weights:
+        if channel is None:
+            bufs = [torch.empty(m, n, dtype=torch.bfloat16, device=x.device) for n, _ in STACK_SHAPES]
+            outs = bufs
+        else:
+            bufs, outs = [g.bufs[0] for g in gathered], [(g, 0) for g in gathered]
+        (wq, sq), (wo, so), (wg, sg), (wd, sd) = layer
+        prods += [(h, wq, sq, outs[0]), (bufs[0][:, :4096], wo, so, outs[1]), (bufs[1], wg, sg, outs[2]), (bufs[2][:, :14336], wd, sd, outs[3])]
+        h, last = bufs[3], bufs
+    return shard.ProductChain(prods, device_index, channel), last
+
+
 def int8_stack(tv, timer, peaks, cpu, ms_list=(1, 8, 64), layers=32):
     """Config 5 on one GPU: the int8 weight-only Linears of a 32-layer decoder (hidden 4096: qkv 6144, o 4096, gate_up 28672,
     down from 14336; 7 GB of weights, every layer its own buffers), decoded as one replayed graph of 128 products per step.
@@ -442,12 +473,23 @@ def int8_stack(tv, timer, peaks, cpu, ms_list=(1, 8, 64), layers=32):
         for _ in range(3):
             graph.replay()
         iters = 10
-        ms = timer.region(lambda i: graph.replay(), iters) / iters
+        ms_ops = timer.region(lambda i: graph.replay(), iters) / iters
+        del graph
+        # the same step as one launch of the persistent decode kernel (m > 16: one pass per 16 rows)
+        mark(f"int8 stack m={m}: per-product graph {ms_ops:.3f} ms; chain")
+        chain, last = stack_chain(shard, weights, x, m, timer.dev)
+        for _ in range(3):
+            chain.run()
+        ms_chain = timer.region(lambda i: chain.run(), iters) / iters
+        check_last_layer(host, *[t.cpu() for t in last], f"int8 stack as a chain (m={m})")
+        del chain, last
+        ms = min(ms_ops, ms_chain)
         gbs = wbytes / ms / 1e6
         entry = {"ms_per_token_step": ms, "weight_gbs": gbs, "products": 4 * layers, "weight_bytes": wbytes,
-                 "roofline": roof("hbm", gbs, peaks["hbm_gbs"], "GB/s", "qmm8_skinny_kernel" if m <= 32 else "qmm8 tcgen05 kernels",
+                 "one_launch_per_product_ms": ms_ops, "chain_ms": ms_chain,
+                 "roofline": roof("hbm", gbs, peaks["hbm_gbs"], "GB/s",
+                                  "qmm8_chain_kernel" if ms_chain <= ms_ops else ("qmm8_skinny_kernel" if m <= 32 else "qmm8 tcgen05 kernels"),
                                   peaks["source"] + " HBM copy bandwidth, weight bytes only")}
-        del graph
         if m == 1 or m == 16:
             # The same stack with its two residual additions (after o and after down): in the decode kernel's epilogue
             # (tvb_qmm8_linear, 128 launches per step) against a product and an add each (192 launches).
@@ -516,39 +558,50 @@ def int8_stack_sharded(tv, timer, peaks, channel, rank, world, dev, ms_list=(1, 
     for m in ms_list:
         x = torch.randn(m, 4096, generator=gen(60)).to(torch.bfloat16).to(dev)
         outs = [shard.GatheredOutputs(m, n, torch.bfloat16, channel, depth=1) for n, _ in STACK_SHAPES]
-
-        def step():
-            h = x
-            for (wq, sq), (wo, so), (wg, sg), (wd, sd) in weights:
-                qkv = outs[0].weight_int8pack_mm(h, wq, sq)
-                o = outs[1].weight_int8pack_mm(qkv[:, :4096], wo, so)
-                gu = outs[2].weight_int8pack_mm(o, wg, sg)
-                h = outs[3].weight_int8pack_mm(gu[:, :14336], wd, sd)
-            channel.wait()
-            return qkv, o, gu, h
-
-        graph = shard.StepGraph(step, channel.dev)
+        iters = 10
+        chain, last = stack_chain(shard, weights, x, m, channel.dev, channel, outs)
         for _ in range(3):
-            graph.replay()
+            chain.run()
         tv.synchronize(channel.dev)
         shard.barrier()
-        iters = 10
-        ms = timer.region(lambda i: graph.replay(), iters) / iters
-        qkv, o, gu, h = [t.cpu() for t in graph.outputs]
-        for got, a_in, (w, sc), name in ((o, qkv[:, :4096], host[1], "o"), (gu, o, host[2], "gate_up"), (h, gu[:, :14336], host[3], "down")):
-            want, tol = int8_expected(a_in.contiguous(), w, sc)
-            if not ((got.float() - want.float()).abs() <= tol).all():
-                raise SystemExit(f"bench.py: rank {rank}: sharded stack, last layer's {name} product outside the reference's bound (m={m})")
-        t = torch.tensor([ms], dtype=torch.float64, device=torch.device("cuda", channel.dev))
+        ms = timer.region(lambda i: chain.run(), iters) / iters
+        check_last_layer(host, *[t.cpu() for t in last], f"rank {rank}: sharded int8 stack as a chain (m={m})")
+        shard.barrier()
+        ms_ops = None
+        if m == 1:
+            # for comparison: one launch per product (tvb_qmm8_gather), each kernel waiting for the previous product's columns
+            def step():
+                h = x
+                for (wq, sq), (wo, so), (wg, sg), (wd, sd) in weights:
+                    qkv = outs[0].weight_int8pack_mm(h, wq, sq)
+                    o = outs[1].weight_int8pack_mm(qkv[:, :4096], wo, so)
+                    gu = outs[2].weight_int8pack_mm(o, wg, sg)
+                    h = outs[3].weight_int8pack_mm(gu[:, :14336], wd, sd)
+                channel.wait()
+                return qkv, o, gu, h
+
+            graph = shard.StepGraph(step, channel.dev)
+            for _ in range(3):
+                graph.replay()
+            tv.synchronize(channel.dev)
+            shard.barrier()
+            ms_ops = timer.region(lambda i: graph.replay(), iters) / iters
+            check_last_layer(host, *[t.cpu() for t in graph.outputs], f"rank {rank}: sharded int8 stack, one launch per product (m={m})")
+            del graph
+            shard.barrier()
+        t = torch.tensor([ms, ms_ops if ms_ops is not None else 0.0], dtype=torch.float64, device=torch.device("cuda", channel.dev))
         torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
-        ms = t.item()
+        ms_chain, ms_ops = t[0].item(), (t[1].item() if ms_ops is not None else None)
+        ms = ms_chain if ms_ops is None else min(ms_chain, ms_ops)
         gbs = wbytes / ms / 1e6
         out[f"int8_stack_32layers_m{m}_sharded"] = {
             "ms_per_token_step": ms, "weight_gbs": gbs, "products": 4 * layers, "weight_bytes": wbytes, "n_gpus": world,
-            "launches_per_step": 4 * layers * ((m + 15) // 16) + 1, "checked": "last layer's o, gate_up and down products on every rank",
-            "roofline": roof("hbm", gbs / world, peaks["hbm_gbs"], "GB/s", "qmm8_skinny_kernel (sharded, fused gather)",
+            "chain_ms": ms_chain, "one_launch_per_product_ms": ms_ops,
+            "checked": "last layer's o, gate_up and down products on every rank",
+            "roofline": roof("hbm", gbs / world, peaks["hbm_gbs"], "GB/s",
+                             ("qmm8_chain_kernel" if ms == ms_chain else "qmm8_skinny_kernel") + " (sharded, fused gather)",
                              peaks["source"] + " HBM copy bandwidth per GPU, weight bytes only")}
-        del graph, outs
+        del chain, last, outs
     del weights
     tv.empty_cache()
     return out
@@ -636,6 +689,24 @@ def run_only(tv, timer, which, iters, slice_world):
             del graph
         res["hbm_floor_us"] = rows * K_IN / 6543.1e3
         return res
+    elif which == "chain_probe":
+        # the persistent decode kernel on config 2's weights: one product, three independent ones, three that wait for one
+        # another, against one launch per product
+        from torch_vulkan_b200 import shard
+
+        w = torch.randint(-127, 128, (N_OUT, K_IN), dtype=torch.int8, generator=gen(2)).to("vk")
+        sv = (torch.rand(N_OUT, generator=gen(3)) * (2e-2 - 1e-3) + 1e-3).to(torch.bfloat16).to("vk")
+        a = {m: torch.randn(m, K_IN, generator=gen(1 + m)).to(torch.bfloat16).to("vk") for m in MS}
+        outs = {m: torch.empty(m, N_OUT, dtype=torch.bfloat16, device="vk") for m in MS}
+        res = {"only": which}
+        for label, prods in (("one_product_m16", [(a[16], w, sv, outs[16])]),
+                             ("three_independent", [(a[m], w, sv, outs[m], i) for i, m in enumerate(MS)]),
+                             ("three_in_sequence", [(a[m], w, sv, outs[m], 0) for m in MS])):
+            chain = shard.ProductChain(prods, timer.dev)
+            res[label + "_us"] = timer.median(chain.run, max(iters, 5)) * 1e3
+            del chain
+        res["one_launch_m16_us"] = timer.median(lambda: torch._weight_int8pack_mm(a[16], w, sv), max(iters, 5)) * 1e3
+        return res
     elif which == "dyn4_decode":
         # four weight sets in turn (147 MB of int4 data and scales in their decode form, more than the L2 holds)
         mm = 16
@@ -700,7 +771,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baselines")
     ap.add_argument("--only", default=None,
                     choices=["fp8", "fp8_big", "dyn4", "dyn4_decode", "int8_large_m", "int8_mid_m", "int8_stack", "bf16_mm", "config1",
-                             "int8_slice"],
+                             "int8_slice", "chain_probe"],
                     help="run one configuration a few times and exit (for profilers); prints its own JSON line")
     ap.add_argument("--slice-world", type=int, default=8, help="--only int8_slice: the rank count whose weight slice is timed")
     args = ap.parse_args()
@@ -755,7 +826,9 @@ def main():
     s_sets = [torch.roll(s_slice, shift * j, 0).contiguous().to(dev) for j in range(nsets)]
     a_dev = {m: a_host[m].to(dev) for m in MS}
     a_pinned = {m: a_host[m].pin_memory() for m in MS}
+    mark("expected values on the CPU")
     expected = {m: int8_expected(a_host[m], w_full, s_full) for m in MS}
+    mark("inputs ready")
 
     def check(m, got, j, what):
         """`got` [m, N] against the CPU product for weight copy j (every rank's slice of columns rolled by 16 j)."""
@@ -769,6 +842,7 @@ def main():
     fused = None
     if channel is not None:
         fused = {m: shard.GatheredOutputs(m, N_OUT, torch.bfloat16, channel) for m in MS}
+    plain_out = {m: [torch.empty(m, N_OUT, dtype=torch.bfloat16, device=dev) for _ in range(2)] for m in MS} if world == 1 else None
 
     def product(m, a, j, buf):
         if world == 1:
@@ -787,69 +861,110 @@ def main():
     def step_sets(g):
         return [(len(MS) * g + i) % nsets for i in range(len(MS))]
 
-    def step_eager(g):
-        outs = [product(m, a_dev[m], j, g % 2) for m, j in zip(MS, step_sets(g))]
-        if channel is not None:
-            channel.wait()  # the step ends when every rank holds every column
-        return outs
-
-    # ---- parity in the timed binary: every weight copy, every M, every rank's assembled output
-    for g in range(ngraphs):
-        for m, j, out in zip(MS, step_sets(g), step_eager(g)):
-            check(m, out.cpu(), j, "before timing")
-    if world > 1:
-        shard.barrier()
-
-    # The step (three short kernels, plus the wait when sharded) is captured into CUDA graphs and replayed: at 4 and 8 GPUs
-    # the kernels are shorter than the host's launch calls.
-    graphs = None
-    if os.environ.get("TVB200_GRAPH", "1") != "0" and (world == 1 or fused is not None):
-        try:
-            graphs = [shard.StepGraph(lambda g=g: step_eager(g), local_rank, warm=False) for g in range(ngraphs)]
-        except Exception as exc:  # noqa: BLE001
-            if rank == 0:
-                print(f"bench.py: graph capture failed ({exc}); launching eagerly", file=sys.stderr)
-            graphs = None
-
-    def step_plain(i):
-        if graphs is not None:
-            graphs[i % ngraphs].replay()
-        else:
-            step_eager(i % ngraphs)
-
     def barrier():
         tv.synchronize(local_rank)
         torch.cuda.synchronize()
         if world > 1:
             shard.barrier()
 
+    # Two ways to queue a step. "chain": the three products as one launch of the persistent decode kernel
+    # (tvb_qmm8_chain_*), which streams the next product's weights while the current one is finished and, sharded, ends when
+    # every rank's columns have arrived. "per_product": one launch per product through aten::_weight_int8pack_mm (sharded:
+    # tvb_qmm8_gather, then one wait kernel per step).
+    use_chain = os.environ.get("TVB200_CHAIN", "1") != "0" and (world == 1 or fused is not None)
+    chains = None
+    if use_chain:
+        chains = []
+        for g in range(ngraphs):
+            outs = [plain_out[m][g % 2] if world == 1 else (fused[m], g % 2) for m in MS]
+            chains.append(shard.ProductChain([(a_dev[m], w_sets[j], s_sets[j], out, i)
+                                              for i, (m, j, out) in enumerate(zip(MS, step_sets(g), outs))], local_rank, channel))
+
+    def step_fn(mode, g):
+        if mode == "chain":
+            return chains[g].run()
+        outs = [product(m, a_dev[m], j, g % 2) for m, j in zip(MS, step_sets(g))]
+        if channel is not None:
+            channel.wait()  # the step ends when every rank holds every column
+        return outs
+
+    def time_mode(mode, steps, warmup):
+        """Parity before, `steps` timed steps after `warmup`, parity after. Returns (ms of the timed region, replayable steps)."""
+        mark(f"{mode}: parity before timing")
+        for g in range(ngraphs):
+            for m, j, out in zip(MS, step_sets(g), step_fn(mode, g)):
+                check(m, out.cpu(), j, f"{mode}, before timing")
+        barrier()
+        # The step is captured into CUDA graphs and replayed: at 4 and 8 GPUs it is shorter than the host's launch calls.
+        graphs = None
+        mark(f"{mode}: capture")
+        if os.environ.get("TVB200_GRAPH", "1") != "0" and (world == 1 or fused is not None):
+            try:
+                graphs = [shard.StepGraph(lambda g=g: step_fn(mode, g), local_rank, warm=False) for g in range(ngraphs)]
+            except Exception as exc:  # noqa: BLE001
+                if rank == 0:
+                    print(f"bench.py: graph capture failed ({exc}); launching eagerly", file=sys.stderr)
+                try:
+                    tv.synchronize(local_rank)
+                except Exception:  # noqa: BLE001
+                    pass
+                graphs = None
+
+        def step(i):
+            if graphs is not None:
+                graphs[i % ngraphs].replay()
+            else:
+                step_fn(mode, i % ngraphs)
+
+        mark(f"{mode}: warm-up and timed steps")
+        for i in range(warmup):
+            step(i)
+        barrier()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record(stream)
+        for i in range(steps):
+            step(warmup + i)
+        end.record(stream)
+        barrier()
+        ms = start.elapsed_time(end)
+        for g in range(ngraphs):  # what a further run of every recorded step leaves in the output buffers
+            if graphs is not None:
+                graphs[g].replay()
+                outs = graphs[g].outputs
+            else:
+                outs = step_fn(mode, g)
+            tv.synchronize(local_rank)
+            for m, j, out in zip(MS, step_sets(g), outs):
+                check(m, out.cpu(), j, f"{mode}, after the timed steps")
+        barrier()
+        return ms, step, graphs is not None
+
     # ---- device-resident timing
     sampler = ClockSampler(local_rank) if rank == 0 else None
     sampler_t0 = time.perf_counter()
-    for i in range(args.warmup):
-        step_plain(i)
-    barrier()
-    launches_before = tv.dispatch_count()
-    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    start.record(stream)
-    for i in range(args.steps):
-        step_plain(args.warmup + i)
-    end.record(stream)
-    barrier()
-    launches = tv.dispatch_count() - launches_before
-    per_step_launches = len(MS) + (1 if channel is not None else 0)
-    if graphs is not None:
-        launches = args.steps * per_step_launches  # replayed kernels are not re-counted by the runtime
-    total_ms = start.elapsed_time(end)
-    if graphs is not None:  # what the last replays left in the output buffers
-        for g in range(ngraphs):
-            graphs[g].replay()
-            tv.synchronize(local_rank)
-            for m, j, out in zip(MS, step_sets(g), graphs[g].outputs):
-                check(m, out.cpu(), j, "after the timed replays")
-        barrier()
+    # both ways of queueing a step are timed; the faster one is the headline (and the end-to-end path), the other is reported
+    # beside it. (Every rank must pick the same one: the choice is made on the slowest rank's times.)
+    timed = {"per_product": time_mode("per_product", args.steps, args.warmup)}
+    if use_chain:
+        timed["chain"] = time_mode("chain", args.steps, args.warmup)
+    times = torch.tensor([timed[k][0] if k in timed else float("inf") for k in ("per_product", "chain")], dtype=torch.float64)
+    if world > 1:
+        import torch.distributed as dist
 
-    # ---- the decode kernel alone on this rank's slice (no exchange), per M: twelve launches per replayed graph
+        t = times.to(torch.device("cuda", local_rank))
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        times = t.cpu()
+    mode = "chain" if times[1] < times[0] else "per_product"
+    use_chain = mode == "chain"
+    total_ms, step_plain, replayed = timed[mode]
+    total_ms = float(times[1 if use_chain else 0])
+    other_mode = "per_product" if use_chain else "chain"
+    other_ms = float(times[0 if use_chain else 1]) if other_mode in timed else None
+    per_step_launches = 1 if use_chain else len(MS) + (1 if channel is not None else 0)
+    launches = args.steps * per_step_launches
+
+    # ---- the decode kernel alone on this rank's slice (no exchange), one launch per product, per M
+    mark("isolated launches")
     isolated_ms = {}
     for m in MS:
         reps = 4 * max(nsets, 3)
@@ -864,22 +979,21 @@ def main():
         for i in range(20):
             step_plain(i)
         barrier()
-    # average launch duration over the timed region: the region holds nothing but these launches, queued back to back
+    # average duration per product over the timed region: the region holds nothing but the steps, queued back to back
     avg_launch_ms = total_ms / (args.steps * len(MS))
 
-    # ---- end to end through the public API: A from pinned host memory, C back to the host, every call
+    # ---- end to end through the C ABI / the ops: A from pinned host memory, C back to the host, every step
     out_pinned = {m: torch.empty(m, N_OUT, dtype=torch.bfloat16).pin_memory() for m in MS}
 
     def e2e_body(g):
-        # every product's A goes up from page-locked memory and its C comes back into page-locked memory; the three
-        # products of a step are queued back to back
-        ups = [a_pinned[m].to(dev, non_blocking=True) for m in MS]
-        outs = [product(m, a, j, g % 2) for m, a, j in zip(MS, ups, step_sets(g))]
-        if channel is not None:
-            channel.wait()
+        # every product's A goes up from page-locked memory (into the buffers the step reads) and its C comes back into
+        # page-locked memory; copies and products are queued back to back
+        for m in MS:
+            a_dev[m].copy_(a_pinned[m], non_blocking=True)
+        outs = step_fn(mode, g)
         for m, c in zip(MS, outs):
             out_pinned[m].copy_(c, non_blocking=True)
-        return ups, outs
+        return outs
 
     e2e_steps = max(5, min(args.steps, 30))
 
@@ -897,11 +1011,13 @@ def main():
         e2e_body(i % ngraphs)
         tv.synchronize(local_rank)  # the step ends when all three results are on the host
 
+    mark("end to end, eager")
     e2e_eager_s = time_e2e(step_e2e_eager)
     e2e_s, e2e_how = e2e_eager_s, "eager: every copy and product queued by its own call"
     last_g = (3 + e2e_steps - 1) % ngraphs
-    if graphs is not None:
+    if replayed:
         # the same copies and products recorded once per buffer set (the host buffers are fixed; a caller rewrites A in place)
+        mark("end to end, replayed")
         e2e_graphs = [shard.StepGraph(lambda g=g: e2e_body(g), local_rank, warm=False) for g in range(ngraphs)]
 
         def step_e2e_graph(i):
@@ -916,14 +1032,14 @@ def main():
     if world > 1:
         import torch.distributed as dist
 
-        t = torch.tensor([total_ms, e2e_s, avg_launch_ms, e2e_eager_s] + [isolated_ms[m] for m in MS], dtype=torch.float64,
-                         device=torch.device("cuda", local_rank))
+        t = torch.tensor([e2e_s, e2e_eager_s] + [isolated_ms[m] for m in MS], dtype=torch.float64, device=torch.device("cuda", local_rank))
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        total_ms, e2e_s, avg_launch_ms, e2e_eager_s, *iso = t.tolist()
+        e2e_s, e2e_eager_s, *iso = t.tolist()
         isolated_ms = dict(zip(MS, iso))
 
     # ---- the other configurations (every rank takes part in the sharded ones)
     extra = {}
+    mark("other configurations")
     if not args.no_extra:
         del w_sets, s_sets
         tv.empty_cache()
@@ -957,17 +1073,19 @@ def main():
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": DTYPE_NOTE, "data": "synthetic", "config": {"workload": WORKLOAD},
-            "details": {"sharding": f"weight rows / {world}" + ((" + fused peer-store gather of C (arrival counted per CTA, each product "
-                                                                 "waits for the one before)" if fused is not None else " + NCCL all-gather of C") if world > 1 else ""),
+            "details": {"sharding": f"weight rows / {world}" + ((" + fused peer-store gather of C (arrival counted per CTA and source rank)" if fused is not None else " + NCCL all-gather of C") if world > 1 else ""),
                         "l2": l2_note, "weight_copies_per_rank": nsets, "launches_per_step": per_step_launches,
-                        "launch": f"CUDA graph replay, {ngraphs} recorded step(s) in turn" if graphs is not None else "eager",
+                        "step": ("one launch of the persistent decode kernel over the step's three products (tvb_qmm8_chain_run)" if use_chain
+                                 else "one launch per product (aten::_weight_int8pack_mm)" + (" and a wait kernel" if channel is not None else "")),
+                        "launch": f"CUDA graph replay, {ngraphs} recorded step(s) in turn" if replayed else "eager",
                         "parity": "every rank's assembled outputs checked against the CPU product (the reference's bound) for every weight "
                                   "copy before timing, after the timed replays and after the end-to-end steps"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                          "frac": achieved / peaks["hbm_gbs"], "traffic": None, "peak_source": peaks["source"],
-                         "kernel": "qmm8_skinny_kernel", "avg_launch_us": avg_launch_ms * 1e3,
-                         "avg_launch_how": "timed region / product launches (launches queued back to back, as in decoding; with sharding "
-                                           "the region includes the exchange and one wait kernel per step)",
+                         "kernel": "qmm8_chain_kernel" if use_chain else "qmm8_skinny_kernel", "avg_launch_us": avg_launch_ms * 1e3,
+                         "avg_launch_how": "timed region / products (steps queued back to back, as in decoding; a launch of the chain "
+                                           "kernel holds a step's three products and takes three times this; with sharding the region "
+                                           "includes the exchange)",
                          "isolated_launch_us_by_m": {str(m): isolated_ms[m] * 1e3 for m in MS},
                          "isolated_how": "the kernel alone on this rank's weight slice (no exchange), a replayed graph of launches over "
                                          "the weight copies in turn",
@@ -978,6 +1096,9 @@ def main():
             "gpu_launches": int(launches),
             "clocks": clocks,
         }
+        if other_ms is not None:
+            line["details"]["other_way"] = {"step": "one launch per product" if use_chain else "one launch of the persistent decode kernel per step",
+                                            "value": step_bytes / (other_ms / args.steps * 1e-3) / 1e9, "ms_per_step": other_ms / args.steps}
         if world > 1:
             line["roofline"]["exchange_us_per_product"] = (avg_launch_ms - iso_mean) * 1e3
         if world == 1:

@@ -671,7 +671,8 @@ __global__ void __launch_bounds__((NWARPS + 2) * 32, 1)
     // covers the stores of all the CTA's threads; no CTA waits for another, and columns count as they land.
     ptx::named_bar_sync(2, (NWARPS + 1) * 32);  // (the agent warp arrives here too, after whatever it had to store)
     if (threadIdx.x == 0) {
-      __threadfence_system();
+      if (p.nranks == 1) __threadfence();
+      else __threadfence_system();
       arrive_publish(p.flags, p.nranks, p.rank, *reinterpret_cast<const volatile uint32_t*>(p.seq), arrive_share());
       // the last CTA to get here counts the product (the next kernel of the stream reads the count after this one has ended)
       if (atomicAdd(p.done, 1) == static_cast<int>(gridDim.x) - 1) {

@@ -87,22 +87,11 @@ __device__ __forceinline__ ItemRange item_range(const ChainItemDev& d) {
 }
 
 // Adds this CTA's share of the completion of product number q to this rank's counters on every rank. Called by one thread
-// once everything the CTA stores for the product is ordered before it (barrier, then this thread's fence).
+// once everything the CTA stores for the product is ordered before it (the CTA's barriers, then this thread's fence).
 __device__ __forceinline__ void chain_publish(const ChainParams& p, uint32_t q) {
-  __threadfence_system();
+  if (p.nranks == 1) __threadfence();
+  else __threadfence_system();
   arrive_publish(p.flags, p.nranks, p.rank, q, arrive_share());
-}
-
-// One of the CTA's (up to) two parties of a product, the consumer warps and the agent warp, reports that its stores are
-// out; the second to report publishes.
-__device__ __forceinline__ void chain_party_done(const ChainParams& p, uint32_t q, int* pub_slot, bool two_parties) {
-  bool last = true;
-  if (two_parties) {
-    __threadfence_system();
-    last = atomicAdd(pub_slot, 1) == 1;
-    if (last) *reinterpret_cast<volatile int*>(pub_slot) = 0;
-  }
-  if (last) chain_publish(p, q);
 }
 
 struct ChainCursor {
@@ -152,11 +141,13 @@ __global__ void __launch_bounds__((NWARPS + 2) * 32, 1) qmm8_chain_kernel(const 
   uint64_t* bars = reinterpret_cast<uint64_t*>(base_ptr + Cfg::kStages * Cfg::kStageBytes);
   const uint32_t full0 = ptx::smem_u32(bars), empty0 = full0 + 8 * Cfg::kStages;
   const uint32_t agent_bar = empty0 + 8 * Cfg::kStages;  // the consumers have stored the partial sums of a segment they leave behind
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 2 * Cfg::kStages + 1);
+  const uint32_t item_bar = agent_bar + 8;               // the consumers have stored everything of a product
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 2 * Cfg::kStages + 2);
   int* last_flag = const_cast<int*>(abort_flag) + 1;  // two slots
   int* early_flag = last_flag + 2;  // set when every other contributor of the segment's tile was seen to have arrived
-  int* pub = early_flag + 1;        // kChainSets slots: parties of a product that have reported
-  static_assert((2 * Cfg::kStages + 1) * 8 + (1 + 2 + 1 + kChainSets) * 4 <= 256, "barrier area too small");
+  volatile int* agent_passed = early_flag + 1;  // how many of the consumers' hand-overs of a tile the agent warp has taken up
+  volatile int* agent_items = early_flag + 2;   // how many of the consumers' end-of-product reports it has taken up
+  static_assert((2 * Cfg::kStages + 2) * 8 + (1 + 2 + 1 + 2) * 4 <= 256, "barrier area too small");
   uint16_t* out_tile = reinterpret_cast<uint16_t*>(base_ptr + Cfg::kStages * Cfg::kStageBytes + 256);  // [tokens][rows of a tile]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -166,10 +157,12 @@ __global__ void __launch_bounds__((NWARPS + 2) * 32, 1) qmm8_chain_kernel(const 
       ptx::mbar_init(empty0 + 8 * s, NWARPS);
     }
     ptx::mbar_init(agent_bar, NWARPS);
+    ptx::mbar_init(item_bar, NWARPS);
     *abort_flag = 0;
     last_flag[0] = last_flag[1] = 0;
     *early_flag = 0;
-    for (int i = 0; i < kChainSets; i++) pub[i] = 0;
+    *agent_passed = 0;
+    *agent_items = 0;
     ptx::fence_mbar_init();
   }
   __syncthreads();
@@ -186,29 +179,10 @@ __global__ void __launch_bounds__((NWARPS + 2) * 32, 1) qmm8_chain_kernel(const 
       chain_enter(p, w);
       chain_enter(p, a);
       int ready_item = -1;  // the highest product known to be allowed to start
-      int mapped_item = -1; // the highest product whose tensor maps this lane has fetched
       long long idle_since = -1;
       bool ok = true;
       while (a.item < p.count) {
         bool progress = false;
-        // weights: as far ahead as the ring has room, whatever product they belong to
-        while (w.item < p.count) {
-          const int s = static_cast<int>(w.it % Cfg::kStages);
-          const uint32_t ph = static_cast<uint32_t>((w.it / Cfg::kStages) & 1);
-          if (!ptx::mbar_try_wait(empty0 + 8 * s, ph ^ 1u)) break;
-          if (w.item > mapped_item) {
-            // (the maps were written by the host before the launch; fetching them through the tensor-map proxy's acquire
-            // makes sure no stale copy of an earlier plan's map at the same address is used)
-            asm volatile("fence.proxy.tensormap::generic.acquire.gpu [%0], 128;" ::"l"(p.maps + 2 * w.item) : "memory");
-            asm volatile("fence.proxy.tensormap::generic.acquire.gpu [%0], 128;" ::"l"(p.maps + 2 * w.item + 1) : "memory");
-            mapped_item = w.item;
-          }
-          ptx::mbar_expect_tx(full0 + 8 * s, Cfg::kStageBytes);
-          ptx::tma_load_2d_hint(base + s * Cfg::kStageBytes, p.maps + 2 * w.item, w.chunk * kChunkK, w.tile * Cfg::kRowsPerTile,
-                                full0 + 8 * s, stream_policy);
-          chain_advance(p, w);
-          progress = true;
-        }
         // activations: only once their product may start
         if (a.it < w.it) {
           if (a.item > ready_item) {
@@ -221,15 +195,35 @@ __global__ void __launch_bounds__((NWARPS + 2) * 32, 1) qmm8_chain_kernel(const 
           while (a.item <= ready_item && a.it < w.it && a.item < p.count) {
             const int s = static_cast<int>(a.it % Cfg::kStages);
             const uint32_t dst = base + s * Cfg::kStageBytes + Cfg::kWeightBytes;
-            ptx::tma_load_2d_hint(dst, p.maps + 2 * a.item + 1, a.chunk * kChunkK, a.m0, full0 + 8 * s, keep_policy);
-            ptx::tma_load_2d_hint(dst + Cfg::kTokenBoxBytes, p.maps + 2 * a.item + 1, a.chunk * kChunkK + 64, a.m0, full0 + 8 * s, keep_policy);
+            const CUtensorMap* map_a = p.maps + 2 * a.item + 1;
+            ptx::tma_load_2d_hint(dst, map_a, a.chunk * kChunkK, a.m0, full0 + 8 * s, keep_policy);
+            ptx::tma_load_2d_hint(dst + Cfg::kTokenBoxBytes, map_a, a.chunk * kChunkK + 64, a.m0, full0 + 8 * s, keep_policy);
             chain_advance(p, a);
             progress = true;
           }
         }
+        // weights: as far ahead as the ring has room, whatever product they belong to
+        while (w.item < p.count) {
+          const int s = static_cast<int>(w.it % Cfg::kStages);
+          const uint32_t ph = static_cast<uint32_t>((w.it / Cfg::kStages) & 1);
+          if (!ptx::mbar_test_wait(empty0 + 8 * s, ph ^ 1u)) break;  // (a test, not a wait: the activations below must not be held up)
+          ptx::mbar_expect_tx(full0 + 8 * s, Cfg::kStageBytes);
+          ptx::tma_load_2d_hint(base + s * Cfg::kStageBytes, p.maps + 2 * w.item,
+                                w.chunk * kChunkK, w.tile * Cfg::kRowsPerTile, full0 + 8 * s, stream_policy);
+          chain_advance(p, w);
+          progress = true;
+        }
         if (progress) {
           idle_since = -1;
         } else {
+          // Nothing to issue right now. Sleep on the ring slot the next weights need (the usual thing to wait for; the
+          // thread is suspended, so it does not compete with the consumers for the shared-memory pipe) for at most half a
+          // microsecond, then look at both cursors again: activations may be waiting for other CTAs or ranks.
+          if (w.item < p.count)
+            ptx::mbar_try_wait_for(empty0 + 8 * static_cast<int>(w.it % Cfg::kStages), static_cast<uint32_t>((w.it / Cfg::kStages) & 1) ^ 1u,
+                                   a.it < w.it ? 100 : 500);
+          else
+            __nanosleep(200);
           if (*abort_flag != 0) { ok = false; break; }
           const long long now = clock64();
           if (idle_since < 0) idle_since = now;
@@ -246,8 +240,9 @@ __global__ void __launch_bounds__((NWARPS + 2) * 32, 1) qmm8_chain_kernel(const 
       while (a.it < w.it && a.item < p.count) {
         const int s = static_cast<int>(a.it % Cfg::kStages);
         const uint32_t dst = base + s * Cfg::kStageBytes + Cfg::kWeightBytes;
-        ptx::tma_load_2d_hint(dst, p.maps + 2 * a.item + 1, a.chunk * kChunkK, a.m0, full0 + 8 * s, keep_policy);
-        ptx::tma_load_2d_hint(dst + Cfg::kTokenBoxBytes, p.maps + 2 * a.item + 1, a.chunk * kChunkK + 64, a.m0, full0 + 8 * s, keep_policy);
+        const CUtensorMap* map_a = p.maps + 2 * a.item + 1;
+        ptx::tma_load_2d_hint(dst, map_a, a.chunk * kChunkK, a.m0, full0 + 8 * s, keep_policy);
+        ptx::tma_load_2d_hint(dst + Cfg::kTokenBoxBytes, map_a, a.chunk * kChunkK + 64, a.m0, full0 + 8 * s, keep_policy);
         chain_advance(p, a);
       }
       const long long first = w.it > Cfg::kStages ? w.it - Cfg::kStages : 0;
@@ -271,70 +266,105 @@ __global__ void __launch_bounds__((NWARPS + 2) * 32, 1) qmm8_chain_kernel(const 
   }
 
   if (warp == NWARPS + 1) {
-    // ---------------- agent: arrival (and, rarely, completion) of the tile that this CTA's first segment of a product shares
-    // A range that starts inside a tile and goes on beyond it leaves that tile's partial sums in scratch and moves on
+    // ---------------- agent: what would otherwise hold the consumers up between two products
+    // (Completing tiles here as a rule, so that the consumers never stop for one, was measured: one warp doing eight warps'
+    // additions is several times too slow.)
+    // (1) A range that starts inside a tile and goes on beyond it leaves that tile's partial sums in scratch and moves on
     // at once; this warp counts the arrival in the consumers' stead. Should it turn out to be the tile's last arrival
-    // (the other contributors normally come much later), this warp alone completes the tile.
-    int uses = 0;
+    // (the other contributors normally come much later), this warp alone completes the tile. (2) When the consumers have
+    // stored everything of a product, this warp orders those stores (a fence that takes microseconds while HBM is busy)
+    // and adds the CTA's share to the arrival counters. (3) For a product in which the CTA has no units it reports as
+    // soon as the product may start: a counter must never hold shares of products four apart.
+    int uses = 0, reports = 0;
     for (int item = 0; item < p.count; item++) {
       const ChainItemDev& d = p.items[item];
       const ItemRange rg_ = item_range(d);
-      if (!rg_.active) continue;
+      if (!rg_.active) {
+        bool go = true;
+        if (lane == 0) {
+          const long long upto = static_cast<long long>(seq0) + item - 1 - static_cast<long long>(d.independent);
+          const long long start = clock64();
+          for (int spins = 0; !arrivals_complete(p.flags[p.rank], p.nranks, upto); spins++) {
+            if ((spins & 15) == 15 && (*abort_flag != 0 || clock64() - start > p.wait_limit)) {
+              if (*abort_flag == 0) atomicExch(p.status, 5);
+              *abort_flag = 1;
+              go = false;
+              break;
+            }
+            __nanosleep(100);
+          }
+          if (go) chain_publish(p, seq0 + static_cast<uint32_t>(item));
+        }
+        if (!__shfl_sync(0xffffffffu, go, 0)) break;
+        continue;
+      }
       const bool small = rg_.small;
       const long long units = rg_.units, grid = rg_.g, u0 = rg_.u0, u1 = rg_.u1;
       const int tile = unit_tile(u0, d.chunks, small), c0 = static_cast<int>(u0 - static_cast<long long>(tile) * d.chunks);
       const int c1 = static_cast<int>(min(static_cast<long long>(d.chunks), c0 + (u1 - u0)));
       const bool left_behind = !(c0 == 0 && c1 == d.chunks) && u0 + (c1 - c0) < u1;
-      if (!left_behind) continue;
-      if (!ptx::mbar_wait(agent_bar, static_cast<uint32_t>(uses & 1), abort_flag)) break;
-      uses++;
-      int* counters = p.counters + (item % kChainSets) * kChainTileSlots;
-      const float* partials = p.partials + (item % kChainSets) * partial_set;
-      const long long tile_first_unit = static_cast<long long>(tile) * d.chunks;
-      const int cta_first = range_owner(tile_first_unit, units, grid, small);
-      const int cta_last = range_owner(tile_first_unit + d.chunks - 1, units, grid, small);
-      int last = 0;
-      if (lane == 0) {
-        __threadfence();  // (cumulative over the consumers' stores, which the barrier ordered before this)
-        last = atomicAdd(&counters[tile], 1) == cta_last - cta_first;
-        if (last) atomicExch(&counters[tile], 0);
-      }
-      last = __shfl_sync(0xffffffffu, last, 0);
-      if (last) {
-        __threadfence();
-        const int g = lane >> 2, t = lane & 3, rg = (g >> 1) | ((g & 1) << 2);
-        for (int w = 0; w < NWARPS; w++)  // this warp plays every consumer warp's part in turn
+      // Counts this CTA's arrival at `tile` and, should it be the tile's last, completes the tile.
+      auto see_to_tile = [&](int tile) {
+        int* counters = p.counters + (item % kChainSets) * kChainTileSlots;
+        const float* partials = p.partials + (item % kChainSets) * partial_set;
+        const long long tile_first_unit = static_cast<long long>(tile) * d.chunks;
+        const int cta_first = range_owner(tile_first_unit, units, grid, small);
+        const int cta_last = range_owner(tile_first_unit + d.chunks - 1, units, grid, small);
+        int last = 0;
+        if (lane == 0) {
+          __threadfence();  // (cumulative over the consumers' stores, which the barrier ordered before this)
+          last = atomicAdd(&counters[tile], 1) == cta_last - cta_first;
+          if (last) atomicExch(&counters[tile], 0);
+        }
+        last = __shfl_sync(0xffffffffu, last, 0);
+        if (last) {
+          __threadfence();
+          const int g = lane >> 2, t = lane & 3, rg = (g >> 1) | ((g & 1) << 2);
+          for (int w = 0; w < NWARPS; w++)  // this warp plays every consumer warp's part in turn
 #pragma unroll
-          for (int rb = 0; rb < RW; rb++)
+            for (int rb = 0; rb < RW; rb++)
 #pragma unroll
-            for (int nt = 0; nt < NT; nt++) {
-              float4 sum = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-              for (int cta = cta_last; cta >= cta_first; cta--) {  // the one fixed order of additions
-                const bool cta_first_segment = unit_tile(range_start(cta, units, grid, small), d.chunks, small) == tile;
-                const float4* theirs = reinterpret_cast<const float4*>(
-                    partials + (static_cast<size_t>(cta) * 2 + (cta_first_segment ? 0 : 1)) * Cfg::kPartialFloats);
-                const float4 v = __ldcg(&theirs[((w * RW + rb) * NT + nt) * 32 + lane]);
-                sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
-              }
-              const float vals[4] = {sum.x, sum.y, sum.z, sum.w};
+              for (int nt = 0; nt < NT; nt++) {
+                float4 sum = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                for (int cta = cta_last; cta >= cta_first; cta--) {  // the one fixed order of additions
+                  const bool cta_first_segment = unit_tile(range_start(cta, units, grid, small), d.chunks, small) == tile;
+                  const float4* theirs = reinterpret_cast<const float4*>(
+                      partials + (static_cast<size_t>(cta) * 2 + (cta_first_segment ? 0 : 1)) * Cfg::kPartialFloats);
+                  const float4 v = __ldcg(&theirs[((w * RW + rb) * NT + nt) * 32 + lane]);
+                  sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
+                }
+                const float vals[4] = {sum.x, sum.y, sum.z, sum.w};
 #pragma unroll
-              for (int half = 0; half < 2; half++) {
-                const int col = tile * Cfg::kRowsPerTile + (w * RW + rb) * 16 + rg + 8 * half;
-                if (col >= d.n) continue;
-                const float scale = load_float<DT>(d.scales, col);
+                for (int half = 0; half < 2; half++) {
+                  const int col = tile * Cfg::kRowsPerTile + (w * RW + rb) * 16 + rg + 8 * half;
+                  if (col >= d.n) continue;
+                  const float scale = load_float<DT>(d.scales, col);
 #pragma unroll
-                for (int i = 0; i < 2; i++) {
-                  const int token = d.m0 + nt * 8 + 2 * t + i;
-                  if (token >= d.m) continue;
-                  const uint16_t bits = float_to_half_bits<DT>(vals[2 * half + i] * scale);
-                  const int64_t off = static_cast<int64_t>(token) * d.c_ld + d.c_col0 + col;
-                  for (int r = 0; r < p.nranks; r++) static_cast<uint16_t*>(d.c[r])[off] = bits;
+                  for (int i = 0; i < 2; i++) {
+                    const int token = d.m0 + nt * 8 + 2 * t + i;
+                    if (token >= d.m) continue;
+                    const uint16_t bits = float_to_half_bits<DT>(vals[2 * half + i] * scale);
+                    const int64_t off = static_cast<int64_t>(token) * d.c_ld + d.c_col0 + col;
+                    for (int r = 0; r < p.nranks; r++) static_cast<uint16_t*>(d.c[r])[off] = bits;
+                  }
                 }
               }
-            }
+        }
+      };
+      if (left_behind) {
+        if (!ptx::mbar_wait(agent_bar, static_cast<uint32_t>(uses & 1), abort_flag)) break;
+        uses++;
+        if (lane == 0) *agent_passed = uses;  // (the consumers may now complete the barrier's next phase)
+        see_to_tile(tile);
       }
+      // the consumers' stores of this product are out (the barrier's release and acquire order them before the fence below)
+      if (!ptx::mbar_wait(item_bar, static_cast<uint32_t>(reports & 1), abort_flag)) break;
+      reports++;
       __syncwarp();
-      if (lane == 0) chain_party_done(p, seq0 + static_cast<uint32_t>(item), pub + (item % kChainSets), true);
+      if (lane == 0) {
+        *agent_items = reports;
+        chain_publish(p, seq0 + static_cast<uint32_t>(item));
+      }
     }
     return;
   }
@@ -348,39 +378,24 @@ __global__ void __launch_bounds__((NWARPS + 2) * 32, 1) qmm8_chain_kernel(const 
   long long it = 0;
   bool ok = true;
   int segment = 0;
+  int handovers = 0;  // tiles left to the agent warp so far
+  int reported = 0;   // products whose end was reported to the agent warp so far
   for (int item = 0; item < p.count && ok; item++) {
     const ChainItemDev& d = p.items[item];
     const ItemRange range = item_range(d);
-    int* pub_slot = pub + (item % kChainSets);
-    if (!range.active) {
-      // Nothing of this product is this CTA's: it has delivered (and read) all it ever will. It still reports only once
-      // the product may start, like the CTAs that work on it: a counter must never hold shares of products four apart.
-      if (threadIdx.x == 0) {
-        const long long upto = static_cast<long long>(seq0) + item - 1 - static_cast<long long>(d.independent);
-        const long long start = clock64();
-        for (int spins = 0; !arrivals_complete(p.flags[p.rank], p.nranks, upto); spins++) {
-          if ((spins & 15) == 15 && (*abort_flag != 0 || clock64() - start > p.wait_limit)) {
-            if (*abort_flag == 0) atomicExch(p.status, 5);
-            *abort_flag = 1;
-            break;
-          }
-        }
-        if (*abort_flag == 0) chain_publish(p, seq0 + static_cast<uint32_t>(item));
-      }
-      continue;
-    }
+    if (!range.active) continue;  // (the agent warp reports for the CTA)
     const bool small = range.small;
     const long long units = range.units, grid = range.g, u0 = range.u0, u1 = range.u1;
     const int chunks = d.chunks, n = d.n, m = d.m, m0 = d.m0;
     int* counters = p.counters + (item % kChainSets) * kChainTileSlots;
     float* partials = p.partials + (item % kChainSets) * partial_set;
-    bool left_behind = false;
     long long u = u0;
     while (u < u1 && ok) {
       const int tile = unit_tile(u, chunks, small), c0 = static_cast<int>(u - static_cast<long long>(tile) * chunks);
       const int c1 = static_cast<int>(min(static_cast<long long>(chunks), c0 + (u1 - u)));
       const bool first_segment = (u == u0);
       const bool whole_tile = c0 == 0 && c1 == chunks;
+      const bool hand_over = !whole_tile && u + (c1 - c0) < u1;  // (a first segment with more of the range to follow)
       // The ranges that share this tile (consecutive CTAs). Their partial sums are always added in descending CTA order.
       const long long tile_first_unit = static_cast<long long>(tile) * chunks;
       const int cta_first = whole_tile ? static_cast<int>(blockIdx.x) : range_owner(tile_first_unit, units, grid, small);
@@ -388,7 +403,7 @@ __global__ void __launch_bounds__((NWARPS + 2) * 32, 1) qmm8_chain_kernel(const 
       // A CTA that holds the tile's first k (the usual case for the last tile of its range) is added last. If, shortly
       // before its segment ends, it sees that all the others have already arrived, it is certain to finish the tile: it
       // then fetches their sums while its last chunks are in flight and skips the exchange through scratch altogether.
-      const bool may_be_early = !whole_tile && cta_first == static_cast<int>(blockIdx.x) && c1 - c0 >= 3;
+      const bool may_be_early = !whole_tile && !hand_over && cta_first == static_cast<int>(blockIdx.x) && c1 - c0 >= 3;
       bool early = false;
       int peeked = 0;
       float pre[RW][NT][4];
@@ -514,12 +529,24 @@ __global__ void __launch_bounds__((NWARPS + 2) * 32, 1) qmm8_chain_kernel(const 
           for (int nt = 0; nt < NT; nt++)
             __stcg(&mine[((warp * RW + rb) * NT + nt) * 32 + lane],
                    make_float4(acc[rb][nt][0], acc[rb][nt][1], acc[rb][nt][2], acc[rb][nt][3]));
-        if (u + (c1 - c0) < u1) {
+        if (hand_over) {
           // More of the range follows: leave the tile to the agent warp (which counts this arrival) and go on at once.
+          // (The agent must have seen the previous hand-over complete before this one may: a barrier tells two phases
+          // apart, not three. It almost always has.)
           __syncwarp();
-          if (lane == 0) ptx::mbar_arrive(agent_bar);
+          if (lane == 0) {
+            const long long start = clock64();
+            while (*agent_passed < handovers) {
+              if (*abort_flag != 0 || clock64() - start > p.wait_limit) {
+                *abort_flag = 1;
+                break;
+              }
+            }
+            ptx::mbar_arrive(agent_bar);
+          }
+          handovers++;
           finish = false;
-          left_behind = true;
+
         } else {
           // All consumer threads have stored their partial sums once they pass the barrier; one thread then publishes
           // them: its gpu-scope fence is cumulative over what the barrier ordered before it.
@@ -606,10 +633,21 @@ __global__ void __launch_bounds__((NWARPS + 2) * 32, 1) qmm8_chain_kernel(const 
       u += c1 - c0;
     }
     if (!ok) break;
-    // Everything this CTA's consumers store for the product is out (and they have read all of A they ever will): report,
-    // together with the agent warp where it had a tile to see to.
-    ptx::named_bar_sync(1, NWARPS * 32);
-    if (threadIdx.x == 0) chain_party_done(p, seq0 + static_cast<uint32_t>(item), pub_slot, left_behind);
+    // Everything this warp stores for the product is out (and it has read all of A it ever will): tell the agent warp, which
+    // reports for the CTA once all consumer warps have. (It must have taken up the previous product's report first: a
+    // barrier tells two phases apart, not three. It almost always has.)
+    __syncwarp();
+    if (lane == 0) {
+      const long long start = clock64();
+      while (*agent_items < reported) {
+        if (*abort_flag != 0 || clock64() - start > p.wait_limit) {
+          *abort_flag = 1;
+          break;
+        }
+      }
+      ptx::mbar_arrive(item_bar);
+    }
+    reported++;
   }
   if (ok && threadIdx.x == 0) {
     // the last CTA to get here counts the products (the next launch of the stream reads the count after this one has ended)

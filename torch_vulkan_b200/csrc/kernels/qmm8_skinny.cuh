@@ -73,9 +73,13 @@ __device__ __forceinline__ uint32_t arrive_share() {
 }
 
 // Adds `share` for product q to this rank's counters on every rank. The caller's earlier stores must be ordered before the
-// call by a system-scope fence of the calling thread.
+// call by a fence of the calling thread: system scope, or GPU scope when there is one rank.
 __device__ __forceinline__ void arrive_publish(uint32_t* const* flags, int nranks, int rank, uint32_t q, uint32_t share) {
   const int index = static_cast<int>(q & 3u) * kMaxRanks + rank;
+  if (nranks == 1) {
+    asm volatile("red.relaxed.gpu.global.add.u32 [%0], %1;" ::"l"(flags[0] + index), "r"(share) : "memory");
+    return;
+  }
   for (int r = 0; r < nranks; r++)
     asm volatile("red.relaxed.sys.global.add.u32 [%0], %1;" ::"l"(flags[r] + index), "r"(share) : "memory");
 }
@@ -89,7 +93,8 @@ __device__ __forceinline__ long long arrive_slot_product(long long upto, int slo
 __device__ __forceinline__ uint32_t arrive_target(long long q) { return (static_cast<uint32_t>(q >> 2) + 1u) * kArriveWeight; }
 
 // One thread's check that all products up to number `upto` have arrived in `mine` (this rank's counters) from all ranks.
-// On success the thread has acquired what the arriving CTAs released.
+// On success the thread has acquired what the arriving CTAs released. With one rank everything stays at GPU scope
+// (system-scope loads and fences are several times slower while HBM is busy).
 __device__ __forceinline__ bool arrivals_complete(const uint32_t* mine, int nranks, long long upto) {
   bool all = true;
 #pragma unroll
@@ -97,6 +102,12 @@ __device__ __forceinline__ bool arrivals_complete(const uint32_t* mine, int nran
     const long long q = arrive_slot_product(upto, slot);
     if (q < 0) continue;
     const uint32_t target = arrive_target(q);
+    if (nranks == 1) {
+      uint32_t v;
+      asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(mine + slot * kMaxRanks) : "memory");
+      all = all && static_cast<int32_t>(v - target) >= 0;
+      continue;
+    }
     uint32_t v[kMaxRanks];
     asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];"
                  : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]) : "l"(mine + slot * kMaxRanks) : "memory");
@@ -106,7 +117,10 @@ __device__ __forceinline__ bool arrivals_complete(const uint32_t* mine, int nran
     for (int r = 0; r < kMaxRanks; r++)
       if (r < nranks) all = all && static_cast<int32_t>(v[r] - target) >= 0;
   }
-  if (all) __threadfence_system();
+  if (all) {
+    if (nranks == 1) __threadfence();
+    else __threadfence_system();
+  }
   return all;
 }
 

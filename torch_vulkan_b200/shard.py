@@ -191,8 +191,8 @@ class ProductChain:
     of the next products stream in while the current one is finished, and a product may take the output of the one
     before it as its A. `products`: a list of (a, w, scales, out[, independent]) with a [m, k] (m <= 64; its buffer is
     read at every run, so the caller rewrites it in place), w int8 [n_local, k], scales [n_local], and `out` either a
-    [m, n_local] tensor (one GPU) or a GatheredOutputs (sharded: every rank's columns land in every rank's buffer;
-    outputs[i] is then that buffer). `independent` (0 to 3): how many of the products just before it this one has nothing
+    [m, n_local] tensor (one GPU) or a GatheredOutputs, alone or with the index of one of its buffers (sharded: every
+    rank's columns land in every rank's buffer; outputs[i] is then that buffer). `independent` (0 to 3): how many of the products just before it this one has nothing
     to do with. With a channel the run ends only when the last product has arrived from every rank."""
 
     def __init__(self, products, device_index=0, channel=None):
@@ -209,10 +209,12 @@ class ProductChain:
             m, k = a.shape
             n_local = w.shape[0]
             assert w.dtype == torch.int8 and w.is_contiguous() and s.dtype == a.dtype and a.stride(1) == 1
-            if isinstance(out, GatheredOutputs):
+            if isinstance(out, tuple) or isinstance(out, GatheredOutputs):
+                out, d = out if isinstance(out, tuple) else (out, None)  # (gathered outputs, which of its buffers)
                 assert channel is not None and out.m == m and out.n_total == n_local * world
-                d = out.calls % out.depth
-                out.calls += 1
+                if d is None:
+                    d = out.calls % out.depth
+                    out.calls += 1
                 ptrs, buf = out.c_ptrs[d], out.bufs[d]
             else:
                 assert world == 1 and tuple(out.shape) == (m, n_local) and out.is_contiguous() and out.dtype == a.dtype
