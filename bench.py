@@ -771,7 +771,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baselines")
     ap.add_argument("--only", default=None,
                     choices=["fp8", "fp8_big", "dyn4", "dyn4_decode", "int8_large_m", "int8_mid_m", "int8_stack", "bf16_mm", "config1",
-                             "int8_slice", "chain_probe"],
+                             "int8_slice", "chain_probe", "dyn4_all"],
                     help="run one configuration a few times and exit (for profilers); prints its own JSON line")
     ap.add_argument("--slice-world", type=int, default=8, help="--only int8_slice: the rank count whose weight slice is timed")
     args = ap.parse_args()
@@ -796,6 +796,10 @@ def main():
     peaks = measured_peaks()
     if world > 1 or torch.get_num_threads() < 2:
         torch.set_num_threads(max(1, host_threads() // world))  # (torchrun gives every rank one thread; the checks use more)
+    if args.only == "dyn4_all":
+        res = extra_dyn4(tv, timer, peaks, cpu=False, quick=False)
+        print(json.dumps({"only": "dyn4_all", **{k: {a: b for a, b in v.items() if a in ("tops", "ms", "us", "weight_gbs")} for k, v in res.items()}}), flush=True)
+        return
     if args.only == "int8_stack":
         print(json.dumps({"only": "int8_stack", **int8_stack(tv, timer, peaks, cpu=False)}), flush=True)
         return

@@ -96,6 +96,28 @@ def main():
             xv.copy_(x_host[rep].to(dev))
             check_chain(graph.replay(), x_host[rep], f"replay {rep}")
         shard.barrier(objects)
+        # the same chain as one launch of the persistent kernel (every product waits, inside the kernel, for the columns of the
+        # one before from all ranks; the launch ends when the last product has arrived from everywhere)
+        prods, h = [], xv
+        for b, s, bv, sv, outs in layers:
+            prods.append((h, bv, sv, outs))
+            h = outs.bufs[0][:, : outs.n_total // 2]
+        persistent = shard.ProductChain(prods, local, channel)
+        for rep in range(4):
+            xv.copy_(x_host[3 - rep].to(dev))
+            check_chain(persistent.run(), x_host[3 - rep], f"persistent kernel, run {rep}")
+        # and a step of products that have nothing to do with each other, m = 1, 4 and 16, in one launch
+        ind = []
+        for i, m_ in enumerate((1, 4, 16)):
+            a_, b_, s_ = C.config_int8(m_, 2048, 1024 * world, torch.bfloat16, seed=50 + i)
+            ind.append((a_, b_, s_, a_.to(dev), shard.shard_rows(b_, rank, world).to(dev), shard.shard_rows(s_, rank, world).to(dev),
+                        shard.GatheredOutputs(m_, 1024 * world, torch.bfloat16, channel, depth=1)))
+        step = shard.ProductChain([(av_, bv_, sv_, g_, i) for i, (_, _, _, av_, bv_, sv_, g_) in enumerate(ind)], local, channel)
+        for rep in range(3):
+            for (a_, b_, s_, *_), got in zip(ind, step.run()):
+                want, tol = C.int8_want(a_, b_, s_)
+                assert ((got.cpu().float() - want.float()).abs() <= tol).all(), f"rank {rank}: independent products in one launch wrong (run {rep})"
+        shard.barrier(objects)
 
         for m in (1, 4, 16):
             a, b, s = C.config_int8(m, 2048, 1024 * world, torch.bfloat16)

@@ -7,19 +7,22 @@
 //
 //   * Operands: the int4 weights unpacked once to int8 [n, k] (tvb_qmm4_prepare; the ATen layer caches it per
 //     packed tensor), the activations quantised to int8 [m, k] by PHASE 0 with 64 extra columns per row holding
-//     two halves o1 + o2 = -zero_point. (q - zp) does not fit int8, but q, o1 and o2 do, so a block sum is three
-//     MMAs into the same accumulator: W.q + W.o1 + W.o2 (exact integers, same value as the shader's loop).
+//     o1 + o2 = -zero_point. (q - zp) does not fit int8, but q and -zp do, except -zp = 128 (a row without negative
+//     values), which is stored as 64 + 64. A block sum is W.q + W.o1 into the same accumulator, plus W.o2 only for a
+//     tile of tokens in which some row needs it (exact integers, same value as the shader's loop).
 //   * Orientation: weight rows ride the MMA's 128 rows (TMEM lanes), tokens its 128 columns, so each draining
 //     thread owns one output column n and keeps that column's block scale in a register.
-//   * Drain: tcgen05.ld brings 64 int32 sums per thread; float(iacc) * scale costs one integer add and one FMA:
+//   * Drain: tcgen05.ld brings 32 int32 sums per thread; float(iacc) * scale costs one integer add and one FMA:
 //     bits(0x4B400000 + iacc) is the float 12582912 + iacc exactly, and fma(that, s, -12582912 s) rounds the exact
 //     product iacc * s once, which is fl(float(iacc) * s). (Needs 3 s exact in float32, true for scales that came
 //     from bfloat16; otherwise, or for blocks over 1024 values, a convert and a multiply are used.) One more add
-//     accumulates, as the reference does; the first block assigns.
+//     accumulates, as the reference does; the first block assigns. (Starting the accumulators at 0x4B400000, stored
+//     back by the draining warp with tcgen05.st so that the integer add disappears, was measured 2.5 times slower.)
 //   * Four TMEM accumulator buffers (4 x 128 columns) let the MMAs of the next blocks run under the drain.
 //
-// Warp roles: 0-7 drain and epilogue (two warps per TMEM lane quarter, one per half of the tokens), 8 TMA
-// producer, 9 MMA issuer and TMEM owner. Every wait is bounded.
+// Warp roles: 0-15 drain and epilogue (four warps per TMEM lane quarter, one per 32 tokens: four warps per scheduler
+// hide each other's tcgen05.ld and barrier waits, which two could not), 16 TMA producer, 17 MMA issuer and TMEM owner.
+// Every wait is bounded.
 #include <cuda.h>
 
 #include <cstdlib>
@@ -40,7 +43,8 @@ constexpr int kStages = 6;
 constexpr int kStageBytes = (kTileN + kTileM) * kStageK;  // 32 KB
 constexpr int kOTileBytes = kTileM * kStageK;             // 16 KB: the tokens' o1 / o2 columns
 constexpr int kAccBuffers = 4;
-constexpr int kThreads = 320;
+constexpr int kDrainWarps = 16;
+constexpr int kThreads = (kDrainWarps + 2) * 32;
 constexpr int kSmemBytes = kStages * kStageBytes + 2 * kOTileBytes + 1024 + 256;
 constexpr int kExtraCols = 64;  // per activation row: 32 x o1, 32 x o2
 
@@ -48,6 +52,7 @@ struct TcParams {
   const float* scales;   // [n, ndrains] (inside the packed vector)
   const float* bias;     // [n] or NULL
   const float* recip;    // [m]
+  const int32_t* neg_zp; // [m]
   const int* wide_scales;  // device flag: some scale has more than 22 significant bits
   void* out;             // [m, n] float32 or bfloat16
   int* status;
@@ -105,8 +110,8 @@ __global__ void __launch_bounds__(256) qmm4_quantize_tc_kernel(const void* __res
     q[qbase + kk] = static_cast<int8_t>(phase0_code(load_float<DT>(inp, base + kk), scale, zp));
   }
   if (t < kExtraCols) {
-    const int off = -zp;          // in [-127, 128]
-    const int o1 = off >> 1;      // both halves fit int8
+    const int off = -zp;                 // in [-127, 128]
+    const int o1 = off > 127 ? 64 : off;  // (128 does not fit int8: the one value that takes both halves)
     q[qbase + k + t] = static_cast<int8_t>(t < 32 ? o1 : off - o1);
   }
 }
@@ -151,17 +156,17 @@ template <bool WIDE>
 __device__ __forceinline__ void drain_tiles(const TcParams& p, const uint32_t tmem_base, const uint32_t tfull0,
                                             const uint32_t tempty0, volatile int* abort_flag, const int warp, const int lane) {
   const int tiles = p.tiles_m * p.tiles_n;
-  const int quarter = warp & 3, half = warp >> 2;
-  const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(half * 64);
+  const int quarter = warp & 3, group = warp >> 2;  // TMEM lanes 32 quarter ..., tokens 32 group ... of the tile
+  const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(group * 32);
   uint32_t buf = 0, buf_phase = 0;
   bool ok = true;
   for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
     const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
     const int col = tn * kTileN + quarter * 32 + lane;   // output column = weight row
     const int col_ld = min(col, p.n - 1);
-    const int tok0 = tm * kTileM + half * 64;
+    const int tok0 = tm * kTileM + group * 32;
     const float* srow = p.scales + static_cast<int64_t>(col_ld) * p.ndrains;
-    float acc0[32], acc1[32];   // tokens tok0 .. tok0+31 and tok0+32 .. tok0+63
+    float acc0[32];   // tokens tok0 .. tok0+31
     float s_next = __ldg(srow);
     for (int d = 0; d < p.ndrains && ok; d++) {
       const float s = s_next;
@@ -170,9 +175,8 @@ __device__ __forceinline__ void drain_tiles(const TcParams& p, const uint32_t tm
       ok = ptx::mbar_wait(tfull0 + 8 * buf, buf_phase, abort_flag);
       if (!ok) break;
       ptx::tc_fence_after();
-      uint32_t r0[32], r1[32];
+      uint32_t r0[32];
       ptx::tmem_ld_32x32(lane_base + buf * kTileM, r0);
-      ptx::tmem_ld_32x32(lane_base + buf * kTileM + 32, r1);
       ptx::tmem_ld_wait();
       ptx::tc_fence_before();
       __syncwarp();
@@ -181,23 +185,18 @@ __device__ __forceinline__ void drain_tiles(const TcParams& p, const uint32_t tm
         buf = 0;
         buf_phase ^= 1u;
       }
-      if (d == 0) {
-        fold_block<WIDE, true>(acc0, r0, s, t);
-        fold_block<WIDE, true>(acc1, r1, s, t);
-      } else {
-        fold_block<WIDE, false>(acc0, r0, s, t);
-        fold_block<WIDE, false>(acc1, r1, s, t);
-      }
+      if (d == 0) fold_block<WIDE, true>(acc0, r0, s, t);
+      else fold_block<WIDE, false>(acc0, r0, s, t);
     }
     if (!ok) break;
     if (col < p.n) {
       const float bias = p.bias != nullptr ? __ldg(p.bias + col) : 0.0f;
       const float hi = p.out_bf16 ? 3.38953139e38f : 3.40282347e38f;
 #pragma unroll
-      for (int i = 0; i < 64; i++) {
+      for (int i = 0; i < 32; i++) {
         const int tok = tok0 + i;
         if (tok < p.m) {
-          float v = __fmul_rn(i < 32 ? acc0[i & 31] : acc1[i & 31], __ldg(p.recip + tok));
+          float v = __fmul_rn(acc0[i], __ldg(p.recip + tok));
           if (p.bias != nullptr) v = __fadd_rn(v, bias);
           v = v < -hi ? -hi : v;  // (std::max / std::min: NaN passes)
           v = hi < v ? hi : v;
@@ -222,7 +221,8 @@ __global__ void __launch_bounds__(kThreads, 1)
   const uint32_t tfull0 = oempty0 + 16, tempty0 = tfull0 + 8 * kAccBuffers;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 4 + 2 * kAccBuffers);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  static_assert((2 * kStages + 4 + 2 * kAccBuffers) * 8 + 8 <= 256, "barrier area too small");
+  volatile int* needs_o2 = abort_flag + 1;  // per slot of the o tile: some token of the tile has -zero_point = 128
+  static_assert((2 * kStages + 4 + 2 * kAccBuffers) * 8 + 16 <= 256, "barrier area too small");
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
@@ -236,12 +236,12 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
     for (int b = 0; b < kAccBuffers; b++) {
       ptx::mbar_init(tfull0 + 8 * b, 1);
-      ptx::mbar_init(tempty0 + 8 * b, 8);
+      ptx::mbar_init(tempty0 + 8 * b, kDrainWarps);
     }
     *abort_flag = 0;
     ptx::fence_mbar_init();
   }
-  if (warp == 9) ptx::tmem_alloc(ptx::smem_u32(tmem_slot), 512);
+  if (warp == kDrainWarps + 1) ptx::tmem_alloc(ptx::smem_u32(tmem_slot), 512);
   ptx::tc_fence_before();
   __syncthreads();
   ptx::tc_fence_after();
@@ -250,42 +250,58 @@ __global__ void __launch_bounds__(kThreads, 1)
   const int nstages = (p.k + kStageK - 1) / kStageK;
   const int nsteps = p.k / 32;
 
-  if (warp == 8) {
+  if (warp == kDrainWarps) {
+    // ---------------- producer: lane 0 issues every TMA copy; the warp together looks at the tile's zero points
     if (lane == 0) {
       ptx::prefetch_tensormap(&map_w);
       ptx::prefetch_tensormap(&map_q);
-      long long it = 0;
-      int ti = 0;
-      bool ok = true;
-      for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ti++) {
-        const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
-        const int slot = ti & 1;
+    }
+    long long it = 0;
+    int ti = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ti++) {
+      const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
+      const int slot = ti & 1;
+      // does a token of this tile carry -zero_point = 128 (then the MMA lane adds the W.o2 term)? four tokens per lane
+      bool wide_row = false;
+      for (int i = lane; i < kTileM; i += 32) {
+        const int tok = tm * kTileM + i;
+        wide_row = wide_row || (tok < p.m && __ldg(p.neg_zp + tok) == 128);
+      }
+      wide_row = __any_sync(0xffffffffu, wide_row);
+      if (lane == 0) {
         ok = ptx::mbar_wait(oempty0 + 8 * slot, static_cast<uint32_t>(((ti >> 1) & 1) ^ 1), abort_flag);
-        if (!ok) break;
-        ptx::mbar_expect_tx(ofull0 + 8 * slot, kOTileBytes);
-        ptx::tma_load_2d(otile0 + slot * kOTileBytes, &map_q, p.k, tm * kTileM, ofull0 + 8 * slot);
-        for (int kb = 0; kb < nstages; kb++, it++) {
-          const int s = static_cast<int>(it % kStages);
-          ok = ptx::mbar_wait(empty0 + 8 * s, static_cast<uint32_t>(((it / kStages) & 1) ^ 1), abort_flag);
-          if (!ok) break;
-          const uint32_t dst = base + s * kStageBytes;
-          ptx::mbar_expect_tx(full0 + 8 * s, kStageBytes);
-          ptx::tma_load_2d(dst, &map_w, kb * kStageK, tn * kTileN, full0 + 8 * s);
-          ptx::tma_load_2d(dst + kTileN * kStageK, &map_q, kb * kStageK, tm * kTileM, full0 + 8 * s);
+        if (ok) {
+          needs_o2[slot] = wide_row ? 1 : 0;  // (ordered before the MMA lane's read by the barrier it waits on)
+          ptx::mbar_expect_tx(ofull0 + 8 * slot, kOTileBytes);
+          ptx::tma_load_2d(otile0 + slot * kOTileBytes, &map_q, p.k, tm * kTileM, ofull0 + 8 * slot);
+          for (int kb = 0; kb < nstages; kb++, it++) {
+            const int s = static_cast<int>(it % kStages);
+            ok = ptx::mbar_wait(empty0 + 8 * s, static_cast<uint32_t>(((it / kStages) & 1) ^ 1), abort_flag);
+            if (!ok) break;
+            const uint32_t dst = base + s * kStageBytes;
+            ptx::mbar_expect_tx(full0 + 8 * s, kStageBytes);
+            ptx::tma_load_2d(dst, &map_w, kb * kStageK, tn * kTileN, full0 + 8 * s);
+            ptx::tma_load_2d(dst + kTileN * kStageK, &map_q, kb * kStageK, tm * kTileM, full0 + 8 * s);
+          }
         }
       }
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+    }
+    if (lane == 0) {
+      // no copy may still be in flight when the CTA's shared memory is released
       const long long first = it > kStages ? it - kStages : 0;
       for (long long j = first; j < it; j++) {
         volatile int never = 0;
         ptx::mbar_wait(full0 + 8 * static_cast<int>(j % kStages), static_cast<uint32_t>((j / kStages) & 1), &never);
       }
-      if (ti > 0) {
+      if (ti > 0 && ok) {
         volatile int never = 0;
         ptx::mbar_wait(ofull0 + 8 * ((ti - 1) & 1), static_cast<uint32_t>(((ti - 1) >> 1) & 1), &never);
       }
     }
     __syncwarp();
-  } else if (warp == 9) {
+  } else if (warp == kDrainWarps + 1) {
     if (lane == 0) {
       // int32 accumulators, signed 8-bit operands, both K-major, 128 x 128
       const uint32_t idesc = ptx::tc_instr_desc(2, 1, 1, kTileN, kTileM);
@@ -302,6 +318,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         ok = ptx::mbar_wait(ofull0 + 8 * slot, static_cast<uint32_t>((ti >> 1) & 1), abort_flag);
         if (!ok) break;
         const uint64_t o_desc = ptx::tc_smem_desc_sw128(otile0 + slot * kOTileBytes);
+        const bool with_o2 = needs_o2[slot] != 0;
         int steps_left = nsteps;
         for (int kb = 0; kb < nstages && ok; kb++) {
           ok = ptx::mbar_wait(full0 + 8 * stage, stage_phase, abort_flag);
@@ -320,8 +337,8 @@ __global__ void __launch_bounds__(kThreads, 1)
             }
             const uint32_t d_tmem = tmem_base + buf * kTileM;
             ptx::tc_mma<1>(d_tmem, w_desc, q_desc, idesc, in_drain != 0 ? 1u : 0u);
-            ptx::tc_mma<1>(d_tmem, w_desc, o_desc, idesc, 1u);      // + W . o1
-            ptx::tc_mma<1>(d_tmem, w_desc, o_desc + 2, idesc, 1u);  // + W . o2
+            ptx::tc_mma<1>(d_tmem, w_desc, o_desc, idesc, 1u);                   // + W . o1
+            if (with_o2) ptx::tc_mma<1>(d_tmem, w_desc, o_desc + 2, idesc, 1u);  // + W . o2 (a row with -zero_point = 128)
             w_desc += 2;  // the next 32 bytes of k, in the descriptor's 16-byte units
             q_desc += 2;
             if (++in_drain == spd) {
@@ -351,7 +368,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   ptx::tc_fence_before();
   __syncthreads();
   if (threadIdx.x == 0 && *abort_flag != 0) atomicExch(p.status, 3);
-  if (warp == 9) {
+  if (warp == kDrainWarps + 1) {
     ptx::tc_fence_after();
     ptx::tmem_dealloc(tmem_base, 512);
   }
@@ -463,6 +480,7 @@ extern "C" int tvb_qmm4_tc(int device, const void* inp, int dtype, const float* 
   p.scales = packed + wcount;
   p.bias = has_bias ? packed + wcount + n * p.ndrains : nullptr;
   p.recip = recip;
+  p.neg_zp = neg_zp;
   p.wide_scales = static_cast<const int*>(prepared);
   p.out = out;
   if (status_word(device, &p.status) != 0) return -1;
