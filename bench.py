@@ -287,7 +287,7 @@ def extra_config1(tv, timer, peaks, cpu):
         out[label] = {"us_per_product": us, "weight_gbs": nbytes / us / 1e3}
         del graph
     res = {"workload": "config1: _weight_int8pack_mm f32 A[32,4096] x int8 W[4096,4096] + f32 scales[4096]", **out,
-           "roofline": roof("hbm", out["hbm_streaming"]["weight_gbs"], peaks["hbm_gbs"], "GB/s", "qmm8_f32split_tc_kernel",
+           "roofline": roof("hbm", out["hbm_streaming"]["weight_gbs"], peaks["hbm_gbs"], "GB/s", "qmm8_f32_tc_kernel",
                             peaks["source"] + " HBM copy bandwidth; 17.84 MB per product, twelve weight copies in turn")}
     if cpu:
         sec, reps = cpu_time(lambda: torch._weight_int8pack_mm(a, w, s), 2.0)
@@ -665,13 +665,15 @@ def run_only(tv, timer, which, iters, slice_world):
         w = torch.randint(-127, 128, (n, k), dtype=torch.int8, generator=gen(2))
         sv = (torch.rand(n, generator=gen(3)) * (2e-2 - 1e-3) + 1e-3).to("vk")
         copies = [torch.roll(w, 16 * i, 0).to("vk") for i in range(12)]
-        state = {"i": 0}
+        from torch_vulkan_b200 import shard
 
-        def fn():
-            state["i"] += 1
-            return torch._weight_int8pack_mm(av, copies[state["i"] % 12], sv)
-
-        flops = 2.0 * m * n * k
+        graph = shard.StepGraph(lambda: [torch._weight_int8pack_mm(av, copies[i], sv) for i in range(12)])
+        us = timer.median(graph.replay, max(iters, 5)) / 12 * 1e3
+        graph1 = shard.StepGraph(lambda: [torch._weight_int8pack_mm(av, copies[0], sv) for i in range(12)])
+        us1 = timer.median(graph1.replay, max(iters, 5)) / 12 * 1e3
+        single = timer.median(lambda: torch._weight_int8pack_mm(av, copies[0], sv), 10) * 1e3
+        return {"only": which, "us_per_product_hbm_streaming": us, "weight_gbs": algorithmic_bytes(m, n, k, 4) / us / 1e3,
+                "us_per_product_l2_resident": us1, "us_single_eager_launch": single}
     elif which == "int8_slice":
         # the weight slice one rank of `slice_world` owns in config 2, on one GPU: enough copies in turn to stream from HBM
         rows = N_OUT // slice_world

@@ -132,7 +132,8 @@ TVB_API int tvb_add_rowvec(int device, void* c, int c_dtype, int64_t c_sm, const
  * dtype; B and C are contiguous. variant: 0 automatic, 1 the plain CUDA-core kernel,
  * 2 the TMA-fed skinny kernel (m <= 64, 16-bit A, k % 128 == 0), 3 the tcgen05 kernel that widens the weights in
  * its main loop, 4 the weights widened once into runtime-owned scratch (2 bytes per weight) and the 16-bit tcgen05
- * GEMM over them (chosen from m = 1024 on). */
+ * GEMM over them (chosen from m = 1024 on), 5 float32 A on tcgen05 through an exact split of every value into three
+ * bfloat16 terms (at most 256 rows, k a multiple of 64, B 16-byte aligned; chosen whenever it applies). */
 TVB_API int tvb_qmm8(int device, const void* a, int dtype, int64_t a_sm, const int8_t* b, const void* scales, void* c,
              int64_t m, int64_t n, int64_t k, int variant);
 

@@ -502,3 +502,43 @@ def test_chain_is_bit_for_bit_the_single_products(abi, dtype):
             assert torch.equal(got.view(torch.int16), want.view(torch.int16)), f"run {run}: {tuple(a.shape)} x {tuple(w.shape)}"
     want, tol = C.int8_want(x4.cpu(), w5.cpu(), s5.cpu())
     assert ((o5.cpu().float() - want.float()).abs() <= tol).all()
+
+
+# ---------------------------------------------------------------- float32 activations on the tensor cores
+
+@pytest.mark.parametrize("m,k,n", [(1, 64, 17), (8, 4096, 300), (32, 4096, 4096), (33, 1088, 128), (100, 256, 515), (256, 2048, 1000),
+                                   (32, 8192, 640)])
+def test_qmm8_float32_tensor_core_split(abi, m, k, n):
+    """variant 5: float32 A as three bfloat16 terms on tcgen05 (k split over several CTAs for small matrices), against the
+    reference's bound for float32 and against the CUDA-core kernel."""
+    a, b, s = C.config_int8(m, k, n, torch.float32, seed=m + n)
+    want, tol = C.int8_want(a, b, s)
+    got = abi.qmm8(dev(a), dev(b), dev(s), variant=5)
+    again = abi.qmm8(dev(a), dev(b), dev(s), variant=5)
+    plain = abi.qmm8(dev(a), dev(b), dev(s), variant=1)
+    abi.synchronize()
+    err = (got.cpu() - want).abs()
+    assert (err <= tol).all(), f"max excess {(err - tol).max()}"
+    assert torch.equal(got, again)  # (the slices of k are added in a fixed order)
+    assert ((got.cpu() - plain.cpu()).abs() <= 2 * tol).all()
+    # against the float64 product: the error stays a small multiple of float32's rounding of the magnitude sum
+    ref64, mag = O.weight_int8pack_mm_f64(a, b, s)
+    assert ((got.cpu().double() - ref64).abs() <= torch.finfo(torch.float32).eps * ref64.abs() + 2.0 ** -21 * mag).all()
+
+
+def test_qmm8_float32_tensor_core_special_values(abi):
+    """Infinities and NaNs in A come out as the CUDA-core kernel gives them; rows of A further apart than k are fine."""
+    a, b, s = C.config_int8(6, 128, 64, torch.float32, seed=3)
+    a[0, 5] = float("inf")
+    a[1, 7] = float("nan")
+    a[2, :] = 0.0
+    a[4, 1] = 1.0e-38
+    wide = torch.zeros(6, 200)
+    wide[:, :128] = a
+    got = abi.qmm8(dev(wide)[:, :128], dev(b), dev(s), variant=5).cpu()
+    plain = abi.qmm8(dev(a), dev(b), dev(s), variant=1).cpu()
+    abi.synchronize()
+    assert torch.equal(torch.isnan(got), torch.isnan(plain)) and torch.equal(torch.isinf(got), torch.isinf(plain))
+    finite = torch.isfinite(plain)
+    _, tol = C.int8_want(torch.nan_to_num(a, nan=0.0, posinf=0.0, neginf=0.0), b, s)
+    assert ((got[finite] - plain[finite]).abs() <= 2 * tol[finite] + 1e-30).all()

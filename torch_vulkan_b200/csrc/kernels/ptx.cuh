@@ -91,6 +91,23 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   }
 }
 
+// The same wait by polling (mbarrier.test_wait, which never suspends the thread): for hand-overs that recur every few
+// hundred clocks, where the time a suspended thread takes to be woken would set the pace.
+__device__ __forceinline__ bool mbar_wait_spin(uint32_t bar, uint32_t parity, volatile int* abort) {
+  if (mbar_test_wait(bar, parity)) return true;
+  long long start = clock64();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 256; i++)
+      if (mbar_test_wait(bar, parity)) return true;
+    if (*abort != 0) return false;
+    if (clock64() - start > kWaitLimitCycles) {
+      *abort = 1;
+      return false;
+    }
+  }
+}
+
 // 2-D tiled TMA load into this CTA's shared memory, completion on `bar`.
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
   asm volatile(

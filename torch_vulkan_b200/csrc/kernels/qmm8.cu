@@ -49,6 +49,11 @@ bool qmm8_widen_gemm_usable(const void* a, int dtype, int64_t a_sm, const int8_t
 int qmm8_widen_gemm(int device, cudaStream_t stream, const void* a, int dtype, int64_t a_sm, const int8_t* b, const void* scales,
                     void* c, int64_t m, int64_t n, int64_t k);
 
+// float32 A on the tensor cores through an exact three-term bfloat16 split (qmm8_f32_tc.cu).
+bool qmm8_f32_tc_usable(const void* a, int dtype, int64_t a_sm, const int8_t* b, int64_t m, int64_t n, int64_t k);
+int qmm8_f32_tc(int device, cudaStream_t stream, const float* a, int64_t a_sm, const int8_t* b, const float* scales, float* c, int64_t m,
+                int64_t n, int64_t k);
+
 namespace {
 
 // ------------------------------------------------------------------ plain kernel
@@ -1065,7 +1070,12 @@ extern "C" int tvb_qmm8(int device, const void* a, int dtype, int64_t a_sm, cons
   bool can_skinny = skinny_ok(a, dtype, a_sm, b, m, n, k);
   TVB_REQUIRE(variant != 2 || can_skinny,
               "tvb_qmm8: the skinny kernel needs 16-bit A, m <= 64, k a multiple of 128, 16-byte aligned rows");
-  TVB_REQUIRE(variant >= 0 && variant <= 4, "tvb_qmm8: unknown kernel variant");
+  TVB_REQUIRE(variant >= 0 && variant <= 5, "tvb_qmm8: unknown kernel variant");
+  const bool can_f32_tc = qmm8_f32_tc_usable(a, dtype, a_sm, b, m, n, k);
+  TVB_REQUIRE(variant != 5 || can_f32_tc,
+              "tvb_qmm8: the float32 tensor-core kernel needs float32 A, at most 256 rows, k a multiple of 64, 16-byte aligned B");
+  if (variant == 5 || (variant == 0 && can_f32_tc))
+    return qmm8_f32_tc(device, stream, static_cast<const float*>(a), a_sm, b, static_cast<const float*>(scales), static_cast<float*>(c), m, n, k);
   const bool can_tc = qmm8_tc_usable(a, dtype, a_sm, b, m, n, k);
   TVB_REQUIRE(variant != 3 || can_tc, "tvb_qmm8: the tcgen05 kernel needs 16-bit A, k a multiple of 16, 16-byte aligned rows");
   const bool can_widen = qmm8_widen_gemm_usable(a, dtype, a_sm, b, m, n, k);
