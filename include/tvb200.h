@@ -329,6 +329,20 @@ TVB_API int tvb_scaled_mm(int device, const void* a, int a_dtype, int64_t a_s0, 
                   const void* bias, int bias_dtype, const float* scale_result, void* out, int out_dtype, int64_t m,
                   int64_t n, int64_t k, int variant);
 
+/* The same product with B's columns sharded over the GPUs of one node (no counterpart in the reference, which has one
+ * device: crates/pyvk/csrc/backend.cpp:296): rank `rank` of `world` multiplies by its [k, n_local] slice of B (and its
+ * n_local values of a row-wise scale_b and of the bias) and the tcgen05 kernel's epilogue stores the tile rows straight
+ * into every rank's [m, n_local * world] output at columns [rank * n_local, (rank + 1) * n_local): this GPU's memory and
+ * the peers' over NVLink, tile by tile while the other tiles are still being multiplied. Arrival is counted on the channel
+ * of tvb_qmm8_gather (c_ranks, flag_ranks, seq_counter, independent as there; one product = one count): the kernel waits
+ * for the channel's earlier products before its first store, and work that is not a sharded product of the channel must
+ * be queued after tvb_wait_flags. Needs the layout of the tcgen05 kernel (K-major operands, 16-byte aligned rows). */
+TVB_API int tvb_scaled_mm_gather(int device, const void* a, int a_dtype, int64_t a_s0, int64_t a_s1, const void* b, int b_dtype,
+                                 int64_t b_s0, int64_t b_s1, const float* scale_a, const float* scale_b, int rowwise,
+                                 const void* bias, int bias_dtype, const float* scale_result, void* const* c_ranks, int out_dtype,
+                                 uint32_t* const* flag_ranks, int world, int rank, uint32_t* seq_counter, int independent,
+                                 int64_t m, int64_t n_local, int64_t k);
+
 /* ---- aten::mm / aten::addmm for float32, float16 and bfloat16 (replaces the reference's gemm dispatches,
  *      crates/pyvk/csrc/linalg.cpp:227-321, for the matrices either side of the quantised products) ----
  * out[m, n] = A[m, k] @ B[k, n] (+ bias[n]), float32 accumulation, one rounding to out_dtype. A and B have one dtype;

@@ -142,6 +142,17 @@ def main():
         bsh, sbsh = shard.shard_scaled_mm_b(fb, sb, rank, world)
         got8 = shard.scaled_mm(fa.to(dev), bsh.t().contiguous().to(dev).t(), sa.to(dev), sbsh.to(dev), out_dtype=torch.bfloat16).cpu()
         assert ((got8.float() - want8.float()).abs() <= tol8).all(), f"rank {rank}: sharded float8 product outside the bound"
+        # float8 with the gather fused into the tcgen05 epilogue: a shape the tensor-core kernel takes, ragged in m, both scale modes
+        for rowwise in (True, False):
+            fa, fb, sa, sb = C.config_fp8(300, 1024, 512 * world, rowwise)
+            want8, tol8 = C.scaled_want(fa, fb, sa, sb, None, None, torch.bfloat16)
+            bsh, sbsh = shard.shard_scaled_mm_b(fb, sb, rank, world)
+            fav, bshv, sav, sbv = fa.to(dev), bsh.t().contiguous().to(dev).t(), sa.to(dev), sbsh.to(dev)
+            outs8 = shard.GatheredOutputs(300, 512 * world, torch.bfloat16, channel)
+            for rep in range(3):
+                got8 = outs8.scaled_mm(fav, bshv, sav, sbv)
+                channel.wait()
+                assert ((got8.cpu().float() - want8.float()).abs() <= tol8).all(), f"rank {rank}: fused sharded float8 product wrong (rep {rep})"
         tv.synchronize(local)
         shard.barrier()
         if rank == 0:

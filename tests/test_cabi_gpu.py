@@ -542,3 +542,28 @@ def test_qmm8_float32_tensor_core_special_values(abi):
     finite = torch.isfinite(plain)
     _, tol = C.int8_want(torch.nan_to_num(a, nan=0.0, posinf=0.0, neginf=0.0), b, s)
     assert ((got[finite] - plain[finite]).abs() <= 2 * tol[finite] + 1e-30).all()
+
+
+def test_scaled_mm_gather_world1(abi):
+    """tvb_scaled_mm_gather with a world of one rank equals tvb_scaled_mm's tensor-core kernel bit for bit, counts one product
+    on the channel, and runs twice in a row (the second waits for the first)."""
+    import ctypes
+
+    lib = abi.lib()
+    fa, fb, sa, sb = C.config_fp8(300, 512, 768, True)
+    da, db = dev(fa), dev(fb.t().contiguous()).t()
+    dsa, dsb = dev(sa.reshape(-1)), dev(sb.reshape(-1))
+    want = abi.scaled_mm(da, db, dev(sa), dev(sb), out_dtype=torch.bfloat16, variant=2)
+    state = torch.zeros(64, dtype=torch.int32, device="cuda")
+    out = torch.zeros(300, 768, dtype=torch.bfloat16, device="cuda")
+    torch.cuda.synchronize()
+    outs, flags = (ctypes.c_void_p * 1)(out.data_ptr()), (ctypes.c_void_p * 1)(state.data_ptr())
+    for _ in range(2):
+        abi.check(lib.tvb_scaled_mm_gather(0, da.data_ptr(), abi.E4M3, da.stride(0), da.stride(1), db.data_ptr(), abi.E4M3, db.stride(0),
+                                           db.stride(1), dsa.data_ptr(), dsb.data_ptr(), 1, None, abi.F32, None, outs, abi.BF16, flags, 1, 0,
+                                           ctypes.c_void_p(state.data_ptr() + 128), 0, 300, 768, 512))
+    abi.check(lib.tvb_wait_flags(0, state.data_ptr(), 1, ctypes.c_void_p(state.data_ptr() + 128)))
+    abi.synchronize()
+    assert torch.equal(out.view(torch.int16), want.view(torch.int16))
+    st = state.cpu()
+    assert st[0].item() == 1024 and st[8].item() == 1024 and st[32].item() == 2

@@ -93,6 +93,8 @@ SIGNATURES = {
     "tvb_qmm4_fast_prepare": (_i, [_i, _vp, _i64, _i64, _i64, _vp, _u64, _c.POINTER(_i)]),
     "tvb_qmm4_fast_workspace_bytes": (_u64, [_i64, _i64]),
     "tvb_qmm4_fast": (_i, [_i, _vp, _i, _vp, _i, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _u64]),
+    "tvb_scaled_mm_gather": (_i, [_i, _vp, _i, _i64, _i64, _vp, _i, _i64, _i64, _vp, _vp, _i, _vp, _i, _vp, _c.POINTER(_vp), _i,
+                                  _c.POINTER(_vp), _i, _i, _vp, _i, _i64, _i64, _i64]),
     "tvb_scaled_mm": (_i, [_i, _vp, _i, _i64, _i64, _vp, _i, _i64, _i64, _vp, _vp, _i, _vp, _i, _vp, _vp, _i, _i64, _i64,
                            _i64, _i]),
 }

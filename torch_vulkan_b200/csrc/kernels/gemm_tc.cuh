@@ -76,6 +76,9 @@ __device__ __forceinline__ void gemm_tile_coords(int tile, int tiles_m, int tile
 //   __device__ static void store(const Params&, const uint8_t* smem, int row, int col_tile0, int col_off,
 //                                const uint32_t (&acc)[32], int m, int n);
 //       thread `row`'s 32 accumulators for columns col_tile0 + col_off ... + 31
+//   __device__ static void kernel_begin(const Params&, int tid);  __device__ static void kernel_end(const Params&, int tid, bool ok);
+//       called by all epilogue threads before the first tile and after the last (what a sharded product does around its
+//       stores: wait for the channel's earlier products, report this CTA's columns as delivered)
 template <int KIND, int BN, class Epi, int BM = 128>
 __global__ void __launch_bounds__((BM / 32 + 2) * 32, 1)
     gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmTcShape sh,
@@ -178,6 +181,7 @@ __global__ void __launch_bounds__((BM / 32 + 2) * 32, 1)
   } else {
     int titer = 0;
     bool ok = true;
+    Epi::kernel_begin(ep, threadIdx.x);
     for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, titer++) {
       int tm, tn;
       gemm_tile_coords(tile, sh.tiles_m, sh.tiles_n, BM == 128 ? 16 : 12, tm, tn);
@@ -202,6 +206,7 @@ __global__ void __launch_bounds__((BM / 32 + 2) * 32, 1)
       ptx::tc_fence_before();
       ptx::mbar_arrive(tempty0 + 8 * acc);
     }
+    Epi::kernel_end(ep, threadIdx.x, ok);
   }
   ptx::tc_fence_before();
   __syncthreads();

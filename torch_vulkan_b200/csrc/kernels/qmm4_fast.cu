@@ -120,6 +120,8 @@ struct FastEpilogue {
     int out_bf16, vector_ok;
   };
   static constexpr int kSmemBytes = 4 * kBN * 2 * 4;  // per epilogue warp: the tile's biases and column factors
+  __device__ static void kernel_begin(const Params&, int) {}
+  __device__ static void kernel_end(const Params&, int, bool) {}
 
   __device__ static void begin_tile(const Params& p, uint8_t* smem, int row0, int col0, int m, int n, int tid) {
     const int warp = tid >> 5, lane = tid & 31;

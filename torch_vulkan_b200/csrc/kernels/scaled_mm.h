@@ -8,6 +8,17 @@
 
 namespace tvb {
 
+// A product whose output columns are one rank's slice of a [m, n_total] output kept on every rank of a node: the epilogue
+// stores into every rank's buffer and reports on the channel of tvb_qmm8_gather.
+struct ScaledMmGather {
+  void* out[8];          // every rank's [m, n_total] buffer (this rank's own included)
+  uint32_t* flags[8];    // every rank's arrival counters
+  int world, rank;
+  uint32_t* seq;         // this rank's product count
+  uint32_t independent;
+  int64_t n_total;
+};
+
 struct ScaledMmParams {
   const void* a;         // [m, k]: element (i, kk) at a[i * a_s0 + kk * a_s1]
   const void* b;         // [k, n]: element (kk, j) at b[kk * b_s0 + j * b_s1]
@@ -21,6 +32,7 @@ struct ScaledMmParams {
   int64_t a_s0, a_s1, b_s0, b_s1;
   int64_t residual_ld;
   int a_dtype, b_dtype, bias_dtype, out_dtype, rowwise, residual_dtype;
+  const ScaledMmGather* gather = nullptr;  // sharded output (float8 operands on the tcgen05 kernel only)
 };
 
 int scaled_mm_plain(cudaStream_t stream, const ScaledMmParams& p);

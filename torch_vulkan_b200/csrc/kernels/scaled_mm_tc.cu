@@ -8,6 +8,7 @@
 // a cast, seven dispatches in all. Float8 products are exact in float32, so
 // (sum a*b) * scale_a[i] * scale_b[j] differs from sum (a*scale_a)(b*scale_b) only by
 // float32 roundings, inside the bound the reference's test uses (tests/python/test_quant.py:124-128).
+#include <atomic>
 #include <cstdlib>
 
 #include <cuda_bf16.h>
@@ -17,15 +18,22 @@
 #include "../core/tensormap.h"
 #include "gemm_tc.cuh"
 #include "numerics.cuh"
+#include "qmm8_skinny.cuh"
 #include "scaled_mm.h"
 
 namespace tvb {
+
+extern std::atomic<long long> g_wait_limit_cycles;  // (qmm8.cu; tvb_set_wait_limit_ms)
+
 namespace {
 
 constexpr int kBN = 256;
 
 // RES: the instantiation that also adds a residual matrix (aten::addmm with a full `self`); the others carry no code for it.
-template <int WARPS, bool RES>
+// GATHER: the instantiation of a sharded product (tvb_scaled_mm_gather): the tile's rows go into every rank's [m, n_total]
+// buffer at this rank's columns (plain 16-byte stores, to peer memory over NVLink), and around its stores the CTA waits for
+// the channel's earlier products and reports its own columns, as the sharded decode kernel does (qmm8.cu).
+template <int WARPS, bool RES, bool GATHER = false>
 struct ScaledEpilogueT {
   struct Params {
     const float* scale_a;
@@ -36,8 +44,56 @@ struct ScaledEpilogueT {
     int64_t residual_ld;
     void* out;
     int bias_dtype, out_dtype, rowwise, vector_ok, residual_dtype, residual_vector_ok;
+    // sharded output
+    void* outs[kMaxRanks];
+    uint32_t* flags[kMaxRanks];
+    uint32_t* seq;
+    int* done;
+    int* status;
+    long long wait_limit;
+    int64_t out_ld, out_col0;
+    int nranks, rank;
+    uint32_t independent;
   };
   static constexpr int kSmemBytes = WARPS * kBN * 2 * 4;  // per epilogue warp: column scales and biases of the tile
+
+  __device__ static void kernel_begin(const Params& p, int tid) {
+    if constexpr (GATHER) {
+      // before a column is stored: every rank has delivered the channel's earlier products (and so has finished reading
+      // what this product may be about to overwrite); one warp waits, bounded, one arrival counter per lane
+      if (tid < 32) {
+        const long long upto = static_cast<long long>(*reinterpret_cast<const volatile uint32_t*>(p.seq)) - 1 - static_cast<long long>(p.independent);
+        const long long start = clock64();
+        for (int spins = 0; !arrivals_complete_warp(p.flags[p.rank], p.nranks, upto); spins++) {
+          if ((spins & 63) == 63) {
+            bool stop = *reinterpret_cast<volatile int*>(p.status) != 0;
+            if (!stop && clock64() - start > p.wait_limit) {
+              atomicExch(p.status, 5);
+              stop = true;
+            }
+            if (__any_sync(0xffffffffu, stop)) break;
+          }
+        }
+      }
+      ptx::named_bar_sync(1, WARPS * 32);
+    }
+  }
+
+  __device__ static void kernel_end(const Params& p, int tid, bool ok) {
+    if constexpr (GATHER) {
+      ptx::named_bar_sync(1, WARPS * 32);  // (every epilogue thread's stores come before the report)
+      if (tid == 0 && ok) {
+        if (p.nranks == 1) __threadfence();
+        else __threadfence_system();
+        arrive_publish(p.flags, p.nranks, p.rank, *reinterpret_cast<const volatile uint32_t*>(p.seq), arrive_share());
+        // the last CTA to get here counts the product (the next kernel of the stream reads the count after this one has ended)
+        if (atomicAdd(p.done, 1) == static_cast<int>(gridDim.x) - 1) {
+          atomicExch(p.done, 0);
+          *reinterpret_cast<volatile uint32_t*>(p.seq) = *reinterpret_cast<const volatile uint32_t*>(p.seq) + 1u;
+        }
+      }
+    }
+  }
 
   __device__ static void begin_tile(const Params& p, uint8_t* smem, int row0, int col0, int m, int n, int tid) {
     const int warp = tid >> 5, lane = tid & 31;
@@ -109,6 +165,33 @@ struct ScaledEpilogueT {
       v[i] = f8_out ? x * inv : x;
     }
     const int col = col_tile0 + col_off;
+    if constexpr (GATHER) {
+      // this rank's columns of every rank's [m, n_total] buffer
+      const int64_t og = static_cast<int64_t>(row) * p.out_ld + p.out_col0 + col;
+      if (p.vector_ok && col + 32 <= n && p.out_dtype == TVB_BF16) {
+        uint4 packed[4];
+#pragma unroll
+        for (int q = 0; q < 4; q++) {
+          uint32_t w[4];
+#pragma unroll
+          for (int j = 0; j < 4; j++) {
+            __nv_bfloat162 h = __floats2bfloat162_rn(v[q * 8 + 2 * j], v[q * 8 + 2 * j + 1]);
+            w[j] = *reinterpret_cast<uint32_t*>(&h);
+          }
+          packed[q] = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+        for (int r = 0; r < p.nranks; r++) {
+          uint4* dst = reinterpret_cast<uint4*>(static_cast<uint16_t*>(p.outs[r]) + og);
+#pragma unroll
+          for (int q = 0; q < 4; q++) dst[q] = packed[q];
+        }
+        return;
+      }
+      for (int r = 0; r < p.nranks; r++)
+        for (int i = 0; i < 32; i++)
+          if (col + i < n) store_float_rt(p.outs[r], og + i, p.out_dtype, v[i]);
+      return;
+    }
     const int64_t o = static_cast<int64_t>(row) * n + col;
     if constexpr (RES) add_residual(p, row, col, n, inv, v);
     if (p.vector_ok && col + 32 <= n) {
@@ -149,9 +232,9 @@ bool scaled_mm_tc_usable(const ScaledMmParams& p) {
          p.k < (int64_t(1) << 30);
 }
 
-template <int KIND, int BM, bool RES>
+template <int KIND, int BM, bool RES, bool GATHER = false>
 int scaled_mm_tc_tile(int device, cudaStream_t stream, const ScaledMmParams& p) {
-  using ScaledEpilogue = ScaledEpilogueT<BM / 32, RES>;
+  using ScaledEpilogue = ScaledEpilogueT<BM / 32, RES, GATHER>;
   using Cfg = GemmTcCfg<kBN, ScaledEpilogue::kSmemBytes, BM>;
   auto kernel = gemm_tc_kernel<KIND, kBN, ScaledEpilogue, BM>;
   static bool configured[64] = {};
@@ -184,6 +267,29 @@ int scaled_mm_tc_tile(int device, cudaStream_t stream, const ScaledMmParams& p) 
   ep.out_dtype = p.out_dtype;
   ep.rowwise = p.rowwise;
   ep.vector_ok = (reinterpret_cast<uintptr_t>(p.out) & 15u) == 0 && (p.n * dtype_size(p.out_dtype)) % 16 == 0;
+  int* status = nullptr;
+  if (status_word(device, &status) != 0) return -1;
+  if constexpr (GATHER) {
+    const ScaledMmGather& g = *p.gather;
+    const int64_t es_out = dtype_size(p.out_dtype);
+    ep.vector_ok = (g.n_total * es_out) % 16 == 0 && (g.rank * p.n * es_out) % 16 == 0;
+    for (int r = 0; r < g.world; r++) {
+      ep.outs[r] = g.out[r];
+      ep.flags[r] = g.flags[r];
+      ep.vector_ok = ep.vector_ok && (reinterpret_cast<uintptr_t>(g.out[r]) & 15u) == 0;
+    }
+    ep.nranks = g.world;
+    ep.rank = g.rank;
+    ep.seq = g.seq;
+    ep.independent = g.independent;
+    ep.out_ld = g.n_total;
+    ep.out_col0 = static_cast<int64_t>(g.rank) * p.n;
+    ep.status = status;
+    ep.wait_limit = g_wait_limit_cycles.load();
+    void* ws = nullptr;  // the counter of finished CTAs (zero between launches)
+    if (workspace(device, 3, 256, &ws) != 0) return -1;
+    ep.done = static_cast<int*>(ws);
+  }
   ep.residual = p.residual;
   ep.residual_ld = p.residual_ld;
   ep.residual_dtype = p.residual_dtype;
@@ -193,8 +299,6 @@ int scaled_mm_tc_tile(int device, cudaStream_t stream, const ScaledMmParams& p) 
   const uint32_t fa = KIND == 0 ? (p.a_dtype == TVB_E4M3 ? 0 : 1) : (p.a_dtype == TVB_F16 ? 0 : 1);
   const uint32_t fb = KIND == 0 ? (p.b_dtype == TVB_E4M3 ? 0 : 1) : (p.b_dtype == TVB_F16 ? 0 : 1);
   const uint32_t idesc = ptx::tc_instr_desc(1, fa, fb, 128, kBN);  // (every MMA covers 128 rows of the tile)
-  int* status = nullptr;
-  if (status_word(device, &status) != 0) return -1;
   const int grid = static_cast<int>(std::min<int64_t>(sm_count(device), static_cast<int64_t>(sh.tiles_m) * sh.tiles_n));
   kernel<<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(map_a, map_b, sh, idesc, ep, status);
   return launched(KIND == 0 ? "scaled_mm_tc" : "mm_tc", dim3(grid), dim3(Cfg::kThreads), Cfg::kSmemBytes, stream);
@@ -221,6 +325,11 @@ int scaled_mm_tc_kind(int device, cudaStream_t stream, const ScaledMmParams& p) 
       return big ? scaled_mm_tc_tile<KIND, 256, true>(device, stream, p) : scaled_mm_tc_tile<KIND, 128, true>(device, stream, p);
   }
   if (p.residual != nullptr) return fail("scaled_mm_tc: a residual goes with 16-bit operands only");
+  if constexpr (KIND == 0) {
+    if (p.gather != nullptr)
+      return big ? scaled_mm_tc_tile<KIND, 256, false, true>(device, stream, p) : scaled_mm_tc_tile<KIND, 128, false, true>(device, stream, p);
+  }
+  if (p.gather != nullptr) return fail("scaled_mm_tc: a sharded output goes with float8 operands only");
   return big ? scaled_mm_tc_tile<KIND, 256, false>(device, stream, p) : scaled_mm_tc_tile<KIND, 128, false>(device, stream, p);
 }
 
@@ -259,6 +368,44 @@ extern "C" int tvb_scaled_mm(int device, const void* a, int a_dtype, int64_t a_s
   const bool big = m * n >= int64_t(128) * 256 * 8 && k >= 128;
   if (variant == 2 || (variant == 0 && usable && big)) return scaled_mm_tc(device, stream, p);
   return scaled_mm_plain(stream, p);
+}
+
+extern "C" int tvb_scaled_mm_gather(int device, const void* a, int a_dtype, int64_t a_s0, int64_t a_s1, const void* b, int b_dtype,
+                                    int64_t b_s0, int64_t b_s1, const float* scale_a, const float* scale_b, int rowwise,
+                                    const void* bias, int bias_dtype, const float* scale_result, void* const* c_ranks, int out_dtype,
+                                    uint32_t* const* flag_ranks, int world, int rank, uint32_t* seq_counter, int independent,
+                                    int64_t m, int64_t n_local, int64_t k) {
+  TVB_REQUIRE((a_dtype == TVB_E4M3 || a_dtype == TVB_E5M2) && (b_dtype == TVB_E4M3 || b_dtype == TVB_E5M2),
+              "tvb_scaled_mm_gather: operands must be float8_e4m3fn or float8_e5m2");
+  TVB_REQUIRE(out_dtype == TVB_F32 || out_dtype == TVB_F16 || out_dtype == TVB_BF16 || out_dtype == TVB_E4M3 || out_dtype == TVB_E5M2,
+              "tvb_scaled_mm_gather: unsupported output dtype");
+  TVB_REQUIRE(world >= 1 && world <= kMaxRanks && rank >= 0 && rank < world, "tvb_scaled_mm_gather: 1 to 8 ranks");
+  TVB_REQUIRE(independent >= 0 && independent <= kArriveSlots - 1, "tvb_scaled_mm_gather: independent must be between 0 and 3");
+  TVB_REQUIRE(m >= 1 && n_local >= 1 && k >= 1, "tvb_scaled_mm_gather: empty product");
+  TVB_REQUIRE(a != nullptr && b != nullptr && scale_a != nullptr && scale_b != nullptr && c_ranks != nullptr && flag_ranks != nullptr &&
+                  seq_counter != nullptr,
+              "tvb_scaled_mm_gather: NULL pointer");
+  cudaStream_t stream;
+  if (enter(device, &stream) != 0) return -1;
+  ScaledMmGather g{};
+  for (int r = 0; r < world; r++) {
+    TVB_REQUIRE(c_ranks[r] != nullptr && flag_ranks[r] != nullptr, "tvb_scaled_mm_gather: NULL buffer of a rank");
+    g.out[r] = c_ranks[r];
+    g.flags[r] = flag_ranks[r];
+  }
+  g.world = world;
+  g.rank = rank;
+  g.seq = seq_counter;
+  g.independent = static_cast<uint32_t>(independent);
+  g.n_total = n_local * world;
+  ScaledMmParams p{};
+  p.a = a; p.b = b; p.scale_a = scale_a; p.scale_b = scale_b; p.bias = bias; p.scale_result = scale_result; p.out = c_ranks[rank];
+  p.m = m; p.n = n_local; p.k = k;
+  p.a_s0 = a_s0; p.a_s1 = a_s1; p.b_s0 = b_s0; p.b_s1 = b_s1;
+  p.a_dtype = a_dtype; p.b_dtype = b_dtype; p.bias_dtype = bias_dtype; p.out_dtype = out_dtype; p.rowwise = rowwise;
+  p.gather = &g;
+  TVB_REQUIRE(scaled_mm_tc_usable(p), "tvb_scaled_mm_gather: needs K-major operands with 16-byte aligned rows (the tcgen05 kernel)");
+  return scaled_mm_tc(device, stream, p);
 }
 
 extern "C" int tvb_addmm(int device, const void* a, int dtype, int64_t a_s0, int64_t a_s1, const void* b, int64_t b_s0,

@@ -186,6 +186,30 @@ class GatheredOutputs:
         return self.bufs[d]
 
 
+    def scaled_mm(self, a, b_shard, scale_a, scale_b_shard, bias_shard=None, buf=None, independent=0):
+        """aten::_scaled_mm with B's columns sharded, the gather fused into the tcgen05 kernel's epilogue
+        (tvb_scaled_mm_gather): float8 a [m, k] row-major, b_shard [k, n_local] column-major, float32 scales (one value
+        each, or [m, 1] and this rank's [1, n_local]); returns the [m, N] buffer (of this object's dtype) that every
+        rank's columns are stored into. Valid for the channel's next sharded product at once, for anything else after
+        channel.wait()."""
+        cabi, lib, ch = self._c, self._c.lib(), self.channel
+        m, k = a.shape
+        n_local = b_shard.shape[1]
+        assert m == self.m and n_local * ch.world == self.n_total
+        rowwise = 0 if (scale_a.numel() == 1 and scale_b_shard.numel() == 1) else 1
+        sa, sb = scale_a.contiguous().reshape(-1), scale_b_shard.contiguous().reshape(-1)
+        d = self.calls % self.depth if buf is None else buf
+        self.calls += 1
+        self._keep = (sa, sb)  # (alive until the next call: the kernel reads them)
+        cabi.check(lib.tvb_scaled_mm_gather(ch.dev, a.data_ptr(), cabi._dtype_code(a.dtype), a.stride(0), a.stride(1), b_shard.data_ptr(),
+                                            cabi._dtype_code(b_shard.dtype), b_shard.stride(0), b_shard.stride(1), sa.data_ptr(),
+                                            sb.data_ptr(), rowwise, bias_shard.data_ptr() if bias_shard is not None else None,
+                                            cabi._dtype_code(bias_shard.dtype) if bias_shard is not None else cabi.F32, None,
+                                            self.c_ptrs[d], cabi._dtype_code(self.bufs[d].dtype), ch.flag_ptrs, ch.world, ch.rank,
+                                            ch.seq.data_ptr(), independent, m, n_local, k))
+        return self.bufs[d]
+
+
 class ProductChain:
     """A fixed sequence of int8 weight-only decode products run by one persistent kernel (tvb_qmm8_chain_*): the weights
     of the next products stream in while the current one is finished, and a product may take the output of the one
