@@ -43,7 +43,8 @@ struct GemmTcCfg {
   static constexpr int kHalves = BM / 128;        // MMAs per k step (one per 128 rows)
   static constexpr int kEpiWarps = BM / 32;
   static constexpr int kStageA = kBM * kGemmStageK, kStageB = BN * kGemmStageK, kStage = kStageA + kStageB;
-  static constexpr int kBudget = (BM == 128 ? 200 : 224) * 1024 - EPI_SMEM;
+  // (an epilogue's shared memory beyond 8 KB comes on top of the budget: the 128-row configuration has room to spare)
+  static constexpr int kBudget = (BM == 128 ? 200 : 224) * 1024 - (EPI_SMEM < 8192 ? EPI_SMEM : 8192);
   static constexpr int kStages = kBudget / kStage < 8 ? kBudget / kStage : 8;
   static constexpr int kThreads = (kEpiWarps + 2) * 32;
   static constexpr int kAccCols = kHalves * BN;   // TMEM columns of one tile's accumulators
@@ -53,6 +54,7 @@ struct GemmTcCfg {
   static_assert(kWant <= 512, "the accumulators do not fit the tensor memory");
   static constexpr int kBarBytes = 256;
   static constexpr int kSmemBytes = kStages * kStage + 1024 + kBarBytes + EPI_SMEM;
+  static_assert(kSmemBytes <= 227 * 1024, "more shared memory than a CTA may have");
 };
 
 // Tile order: bands of `band` tile rows, walked column by column, so that the ~148 tiles in flight at any time cover a

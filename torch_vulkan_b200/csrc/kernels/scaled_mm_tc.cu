@@ -55,7 +55,9 @@ struct ScaledEpilogueT {
     int nranks, rank;
     uint32_t independent;
   };
-  static constexpr int kSmemBytes = WARPS * kBN * 2 * 4;  // per epilogue warp: column scales and biases of the tile
+  static constexpr int kScaleBytes = WARPS * kBN * 2 * 4;  // per epilogue warp: column scales and biases of the tile
+  static constexpr int kStageBytes = GATHER ? WARPS * 32 * 128 : 0;  // sharded: per warp 32 rows x 64 columns of bfloat16 on their way out
+  static constexpr int kSmemBytes = kScaleBytes + kStageBytes;
 
   __device__ static void kernel_begin(const Params& p, int tid) {
     if constexpr (GATHER) {
@@ -151,11 +153,11 @@ struct ScaledEpilogueT {
 
   __device__ static void store(const Params& p, const uint8_t* smem, int row, int col_tile0, int col_off,
                                const uint32_t (&acc)[32], int m, int n) {
-    if (row >= m) return;
+    if (!GATHER && row >= m) return;  // (a sharded product's warps stay together: they exchange rows through shared memory)
     const int warp = (threadIdx.x >> 5) % WARPS;
     const float* cs = reinterpret_cast<const float*>(smem) + warp * 2 * kBN + col_off;
     const float* cb = cs + kBN;
-    const float sa = p.scale_a == nullptr ? 1.0f : (p.rowwise ? p.scale_a[row] : p.scale_a[0]);
+    const float sa = p.scale_a == nullptr ? 1.0f : (p.rowwise ? p.scale_a[row < m ? row : m - 1] : p.scale_a[0]);
     const bool f8_out = p.out_dtype == TVB_E4M3 || p.out_dtype == TVB_E5M2;
     const float inv = f8_out && p.scale_result != nullptr ? 1.0f / p.scale_result[0] : 1.0f;
     float v[32];
@@ -166,10 +168,14 @@ struct ScaledEpilogueT {
     }
     const int col = col_tile0 + col_off;
     if constexpr (GATHER) {
-      // this rank's columns of every rank's [m, n_total] buffer
-      const int64_t og = static_cast<int64_t>(row) * p.out_ld + p.out_col0 + col;
-      if (p.vector_ok && col + 32 <= n && p.out_dtype == TVB_BF16) {
-        uint4 packed[4];
+      // This rank's columns of every rank's [m, n_total] buffer. A thread holds 64 bytes of one row; stored as they are, a
+      // warp's stores would be 32 scattered 16-byte pieces per instruction, which NVLink carries at a fraction of its
+      // rate. So the warp collects 64 columns of its 32 rows in shared memory and writes them out as 128-byte row
+      // segments: eight lanes per row, four rows per instruction.
+      if (p.vector_ok && p.out_dtype == TVB_BF16) {
+        const int lane = threadIdx.x & 31;
+        const uint32_t stage = ptx::smem_u32(smem) + kScaleBytes + warp * (32 * 128);
+        const int half = (col_off >> 5) & 1;
 #pragma unroll
         for (int q = 0; q < 4; q++) {
           uint32_t w[4];
@@ -178,15 +184,29 @@ struct ScaledEpilogueT {
             __nv_bfloat162 h = __floats2bfloat162_rn(v[q * 8 + 2 * j], v[q * 8 + 2 * j + 1]);
             w[j] = *reinterpret_cast<uint32_t*>(&h);
           }
-          packed[q] = make_uint4(w[0], w[1], w[2], w[3]);
+          asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(stage + lane * 128 + (((half * 4 + q) ^ (lane & 7)) << 4)), "r"(w[0]),
+                       "r"(w[1]), "r"(w[2]), "r"(w[3])
+                       : "memory");
         }
-        for (int r = 0; r < p.nranks; r++) {
-          uint4* dst = reinterpret_cast<uint4*>(static_cast<uint16_t*>(p.outs[r]) + og);
+        if (half == 1) {
+          __syncwarp();
+          const int row0 = row - lane, c = lane & 7;
+          const int colg = col_tile0 + col_off - 32 + c * 8;
 #pragma unroll
-          for (int q = 0; q < 4; q++) dst[q] = packed[q];
+          for (int it = 0; it < 8; it++) {
+            const int r = it * 4 + (lane >> 3);
+            if (row0 + r < m && colg + 8 <= n) {
+              const uint4 val = ptx::lds128(stage + r * 128 + ((c ^ (r & 7)) << 4));
+              const int64_t og = static_cast<int64_t>(row0 + r) * p.out_ld + p.out_col0 + colg;
+              for (int rk = 0; rk < p.nranks; rk++) *reinterpret_cast<uint4*>(static_cast<uint16_t*>(p.outs[rk]) + og) = val;
+            }
+          }
+          __syncwarp();  // (the staging rows are free again)
         }
         return;
       }
+      if (row >= m) return;
+      const int64_t og = static_cast<int64_t>(row) * p.out_ld + p.out_col0 + col;
       for (int r = 0; r < p.nranks; r++)
         for (int i = 0; i < 32; i++)
           if (col + i < n) store_float_rt(p.outs[r], og + i, p.out_dtype, v[i]);
@@ -272,7 +292,7 @@ int scaled_mm_tc_tile(int device, cudaStream_t stream, const ScaledMmParams& p) 
   if constexpr (GATHER) {
     const ScaledMmGather& g = *p.gather;
     const int64_t es_out = dtype_size(p.out_dtype);
-    ep.vector_ok = (g.n_total * es_out) % 16 == 0 && (g.rank * p.n * es_out) % 16 == 0;
+    ep.vector_ok = (g.n_total * es_out) % 16 == 0 && (p.n * es_out) % 16 == 0;
     for (int r = 0; r < g.world; r++) {
       ep.outs[r] = g.out[r];
       ep.flags[r] = g.flags[r];
@@ -326,8 +346,10 @@ int scaled_mm_tc_kind(int device, cudaStream_t stream, const ScaledMmParams& p) 
   }
   if (p.residual != nullptr) return fail("scaled_mm_tc: a residual goes with 16-bit operands only");
   if constexpr (KIND == 0) {
+    // A sharded product takes 128-row tiles whatever the shape: with their two accumulator buffers the epilogue, whose
+    // stores to the peers are paced by NVLink, runs under the next tile's MMAs (256-row tiles have one buffer).
     if (p.gather != nullptr)
-      return big ? scaled_mm_tc_tile<KIND, 256, false, true>(device, stream, p) : scaled_mm_tc_tile<KIND, 128, false, true>(device, stream, p);
+      return scaled_mm_tc_tile<KIND, 128, false, true>(device, stream, p);
   }
   if (p.gather != nullptr) return fail("scaled_mm_tc: a sharded output goes with float8 operands only");
   return big ? scaled_mm_tc_tile<KIND, 256, false>(device, stream, p) : scaled_mm_tc_tile<KIND, 128, false>(device, stream, p);
