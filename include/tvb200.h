@@ -46,7 +46,9 @@ enum TvbDtype {
   TVB_I64 = 8,
   TVB_F64 = 9,
   TVB_BOOL = 10,
-  TVB_I16 = 11
+  TVB_I16 = 11,
+  TVB_E4M3FNUZ = 12, /* float8_e4m3fnuz: bias 8, no infinities, no negative zero, NaN = 0x80 */
+  TVB_E5M2FNUZ = 13  /* float8_e5m2fnuz: bias 16, likewise */
 };
 
 /* An allocation as seen by the host (replaces VktAlloc, vk.h:50-55: on CUDA
@@ -217,6 +219,28 @@ TVB_API int tvb_qmm8_chain_create(int device, int dtype, const TvbChainItem* ite
                                   int world, int rank, uint32_t* seq_counter, int wait_at_end, void** chain);
 TVB_API int tvb_qmm8_chain_run(int device, void* chain);
 TVB_API void tvb_qmm8_chain_destroy(void* chain);
+/* ---- collectives for hosts without PyTorch (no counterpart in the reference: one device, crates/pyvk/csrc/backend.cpp:296) ----
+ * The all-gather that assembles the column slices of any sharded product (tvb_qmm4*, tvb_scaled_mm, tvb_qmm8 at any m) on
+ * every rank, over NCCL (looked up at run time: TVB200_NCCL_LIB, else the process's libnccl.so.2; -1 with a message where
+ * there is none). One process per GPU: rank 0 makes an id (tvb_comm_unique_id, 128 bytes), the host carries it to the other
+ * ranks by its own means, and every rank calls tvb_comm_init_rank. A single process that drives several GPUs calls
+ * tvb_comm_init_all instead (comms_out: `ndev` handles, entry i for devices[i]). Communicators are non-blocking and every
+ * call is bounded on the host: a call that gets no answer within its time limit (timeout_ms; 0: 30 s) aborts the
+ * communicator and returns -1 instead of hanging, after which only tvb_comm_abort / tvb_comm_destroy may be called on it.
+ * tvb_all_gather queues rank r's `nbytes` into recv[r * nbytes ...) on the device's stream; tvb_all_gather_columns does
+ * the same for a [m, n_local] slice and leaves the row-major [m, n_local * world] matrix in c_full (the ranks' slices
+ * interleaved by a small kernel; scratch is the runtime's). tvb_comm_wait waits for the device's stream with a limit and
+ * aborts the communicator if the collective does not finish (a peer that has gone), which also lets the stream drain.
+ * tvb_comm_abort frees a communicator without waiting for anybody; tvb_comm_destroy waits for queued work first. */
+TVB_API int tvb_comm_unique_id(uint8_t* id128);
+TVB_API int tvb_comm_init_rank(int device, const uint8_t* id128, int world, int rank, int timeout_ms, void** comm);
+TVB_API int tvb_comm_init_all(const int* devices, int ndev, void** comms_out);
+TVB_API int tvb_all_gather(void* comm, const void* send, void* recv, uint64_t nbytes);
+TVB_API int tvb_all_gather_columns(void* comm, const void* c_local, void* c_full, int dtype, int64_t m, int64_t n_local);
+TVB_API int tvb_comm_wait(void* comm, int timeout_ms);
+TVB_API int tvb_comm_abort(void* comm);
+TVB_API int tvb_comm_destroy(void* comm);
+
 /* A device allocation as a 64-byte handle plus offset that another process of the node can map (cudaIpc*). */
 TVB_API int tvb_ipc_export(int device, const void* ptr, uint8_t* handle64, uint64_t* offset);
 TVB_API int tvb_ipc_import(int device, const uint8_t* handle64, uint64_t offset, void** out);
@@ -320,10 +344,12 @@ TVB_API int tvb_qmm4_decode(int device, const void* inp, int dtype, const float*
  * out[m, n] = cast((a * scale_a) @ (b * scale_b) + bias) (float8 outputs: times
  * 1 / *scale_result). a: float8 [m, k], element (i, kk) at a[i * a_s0 + kk * a_s1];
  * b: float8 [k, n], element (kk, j) at b[kk * b_s0 + j * b_s1] (strides in elements).
- * a_dtype / b_dtype: TVB_E4M3 or TVB_E5M2. scale_a / scale_b: device float32, one element
+ * a_dtype / b_dtype: TVB_E4M3 or TVB_E5M2 (the tensor cores' own formats), or the fnuz formats TVB_E4M3FNUZ / TVB_E5M2FNUZ,
+ * which the reference tabulates as well (crates/pyvk/csrc/backend.cpp:471-477,486-534) and which run on the plain kernel
+ * (decoded in the loop; the tensor cores have no such operand format). scale_a / scale_b: device float32, one element
  * (rowwise 0) or m / n elements (rowwise 1). bias: n elements of bias_dtype, or NULL.
  * scale_result: device float32 or NULL. out: contiguous [m, n] of out_dtype (F32, F16,
- * BF16, E4M3, E5M2). variant: 0 automatic, 1 the plain kernel, 2 the tcgen05 kernel. */
+ * BF16, E4M3, E5M2, E4M3FNUZ, E5M2FNUZ). variant: 0 automatic, 1 the plain kernel, 2 the tcgen05 kernel. */
 TVB_API int tvb_scaled_mm(int device, const void* a, int a_dtype, int64_t a_s0, int64_t a_s1, const void* b, int b_dtype,
                   int64_t b_s0, int64_t b_s1, const float* scale_a, const float* scale_b, int rowwise,
                   const void* bias, int bias_dtype, const float* scale_result, void* out, int out_dtype, int64_t m,

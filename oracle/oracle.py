@@ -23,8 +23,9 @@ _LIB_PATH = os.path.join(_HERE, "_build", "liboracle.so")
 _lib = None
 
 _DT = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}
-_F8 = {torch.float8_e4m3fn: 0, torch.float8_e5m2: 1}
-_OUT = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2, torch.float8_e4m3fn: 3, torch.float8_e5m2: 4}
+_F8 = {torch.float8_e4m3fn: 0, torch.float8_e5m2: 1, torch.float8_e4m3fnuz: 2, torch.float8_e5m2fnuz: 3}
+_OUT = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2, torch.float8_e4m3fn: 3, torch.float8_e5m2: 4,
+        torch.float8_e4m3fnuz: 5, torch.float8_e5m2fnuz: 6}
 
 
 def build(force=False):

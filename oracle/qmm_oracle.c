@@ -78,11 +78,14 @@ uint16_t oracle_f32_to_f16(float f) {
 /* ---- float8 (c10's conversions: the reference builds its tables from them,
  *      backend.cpp:486-534) ------------------------------------------------ */
 
-/* kind 0: e4m3fn (bias 7, no inf, NaN 0x7f), kind 1: e5m2 (IEEE-like). */
+/* kind 0: e4m3fn (bias 7, no inf, NaN 0x7f), kind 1: e5m2 (IEEE-like), kind 2: e4m3fnuz (bias 8), kind 3: e5m2fnuz
+ * (bias 16). The fnuz formats have no infinities and no negative zero; their one NaN is 0x80 (backend.cpp:471-477). */
 float oracle_f8_to_f32(uint8_t c, int kind) {
-  int ebits = kind == 0 ? 4 : 5, mbits = 7 - ebits, bias = kind == 0 ? 7 : 15;
+  int fnuz = kind >= 2, ebits = (kind & 1) == 0 ? 4 : 5, mbits = 7 - ebits;
+  int bias = (ebits == 4 ? 7 : 15) + fnuz;
   int sign = c >> 7, e = (c >> mbits) & ((1 << ebits) - 1), m = c & ((1 << mbits) - 1);
   float v;
+  if (fnuz && c == 0x80) return NAN;
   if (kind == 0 && (c & 0x7f) == 0x7f) v = NAN;
   else if (kind == 1 && e == 31) v = m ? NAN : INFINITY;
   else if (e == 0) v = ldexpf((float)m, 1 - bias - mbits);
@@ -91,25 +94,31 @@ float oracle_f8_to_f32(uint8_t c, int kind) {
 }
 
 uint8_t oracle_f32_to_f8(float f, int kind) {
-  int ebits = kind == 0 ? 4 : 5, mbits = 7 - ebits, bias = kind == 0 ? 7 : 15;
+  int fnuz = kind >= 2, ebits = (kind & 1) == 0 ? 4 : 5, mbits = 7 - ebits;
+  int bias = (ebits == 4 ? 7 : 15) + fnuz;
   uint32_t u = f32_bits(f);
   uint8_t sign = (uint8_t)((u >> 24) & 0x80u);
   uint32_t mag = u & 0x7fffffffu;
+  if (fnuz && mag >= 0x7f800000u) return 0x80;                          /* NaN and infinities: the one NaN */
   if (mag > 0x7f800000u) return (uint8_t)(sign | 0x7f);                 /* NaN */
   if (mag == 0x7f800000u) return (uint8_t)(sign | (kind == 0 ? 0x7f : 0x7c));
-  if (mag == 0) return sign;
+  if (mag == 0) return fnuz ? 0 : sign;
   int e = (int)(mag >> 23) - 127;
   uint64_t m = (mag & 0x7fffffu) | 0x800000u;           /* value = m * 2^(e-23) */
   if (mag < 0x00800000u) { e = -126; m = mag; }          /* float32 denormal */
   int emin = 1 - bias;
   int shift = 23 - mbits + (e < emin ? emin - e : 0);
-  if (shift > 40) return sign;
+  if (shift > 40) return fnuz ? 0 : sign;
   uint64_t half = 1ull << (shift - 1);
   uint64_t r = m >> shift, rem = m & ((1ull << shift) - 1);
   if (rem > half || (rem == half && (r & 1u))) r++;
   uint32_t code;
   if (e < emin) code = (uint32_t)r;                      /* denormal (may round up to the first normal) */
   else code = ((uint32_t)(e - emin + 1) << mbits) + (uint32_t)(r - (1u << mbits));
+  if (fnuz) {
+    if (code > 0x7f) return 0x80;                        /* beyond the largest value: NaN (no saturation) */
+    return code == 0 ? 0 : (uint8_t)(sign | code);       /* no negative zero */
+  }
   if (kind == 0) { if (code > 0x7e) code = 0x7f; }       /* beyond 448: NaN (no saturation) */
   else { if (code > 0x7c) code = 0x7c; }                 /* beyond 57344: inf */
   return (uint8_t)(sign | code);
@@ -268,7 +277,7 @@ void oracle_qmm4_matmul(const int32_t* q, const float* recip, const int32_t* neg
  * scale_a / scale_b: one float (rowwise 0) or m / n floats (rowwise 1).
  * bias: n floats (already widened) or NULL. inv_scale_result: multiplies the
  * sum when the output is float8 (1 / scale_result), else pass 1.
- * out_kind: 0 float32, 1 float16, 2 bfloat16, 3 e4m3fn, 4 e5m2.
+ * out_kind: 0 float32, 1 float16, 2 bfloat16, 3 e4m3fn, 4 e5m2, 5 e4m3fnuz, 6 e5m2fnuz.
  * acc64: 0 accumulates in float32 (k ascending), 1 in float64 and also stores
  * the unrounded sum in ref64 (optional) for the ulp check. */
 void oracle_scaled_mm(const uint8_t* a, int a_kind, int64_t a_s0, int64_t a_s1,
@@ -304,7 +313,9 @@ void oracle_scaled_mm(const uint8_t* a, int a_kind, int64_t a_s0, int64_t a_s1,
         case 1: ((uint16_t*)out)[o] = oracle_f32_to_f16(r); break;
         case 2: ((uint16_t*)out)[o] = oracle_f32_to_bf16(r); break;
         case 3: ((uint8_t*)out)[o] = oracle_f32_to_f8(r, 0); break;
-        default: ((uint8_t*)out)[o] = oracle_f32_to_f8(r, 1); break;
+        case 4: ((uint8_t*)out)[o] = oracle_f32_to_f8(r, 1); break;
+        case 5: ((uint8_t*)out)[o] = oracle_f32_to_f8(r, 2); break;
+        default: ((uint8_t*)out)[o] = oracle_f32_to_f8(r, 3); break;
       }
     }
 }

@@ -153,6 +153,22 @@ def main():
                 got8 = outs8.scaled_mm(fav, bshv, sav, sbv)
                 channel.wait()
                 assert ((got8.cpu().float() - want8.float()).abs() <= tol8).all(), f"rank {rank}: fused sharded float8 product wrong (rep {rep})"
+        # the C ABI's own communicator: the slices of the dyn-int4 and float8 products assembled without torch.distributed
+        comm = shard.AbiComm(local, objects)
+        part4 = torch._dyn_quant_matmul_4bit(x.to(dev), mine, bs, k, n // world)
+        full4 = comm.all_gather_columns(part4)
+        comm.wait()
+        assert torch.equal(full4.cpu(), want4), f"rank {rank}: tvb_all_gather_columns (dyn-int4) differs"
+        fa, fb, sa, sb = C.config_fp8(256, 1024, 512 * world, True)
+        want8, tol8 = C.scaled_want(fa, fb, sa, sb, None, None, torch.bfloat16)
+        bsh, sbsh = shard.shard_scaled_mm_b(fb, sb, rank, world)
+        part8 = torch._scaled_mm(fa.to(dev), bsh.t().contiguous().to(dev).t(), sa.to(dev), sbsh.to(dev), out_dtype=torch.bfloat16)
+        full8 = comm.all_gather_columns(part8)
+        one_row = comm.all_gather_columns(part8[:1])
+        comm.wait()
+        assert ((full8.cpu().float() - want8.float()).abs() <= tol8).all(), f"rank {rank}: tvb_all_gather_columns (float8) differs"
+        assert torch.equal(one_row.cpu(), full8[:1].cpu())
+        comm.destroy()
         tv.synchronize(local)
         shard.barrier()
         if rank == 0:

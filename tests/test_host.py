@@ -91,3 +91,26 @@ def test_decode_kernel_work_split(tiles, chunks, grid):
                 assert (starts[c + 1] - 1) // chunks == t
             assert (c, slot) not in slots
             slots.add((c, slot))
+
+
+def test_comm_entry_points_fail_cleanly_without_a_gpu():
+    """The collective entry points: an id can be made wherever NCCL can be loaded; joining a communicator without a usable
+    GPU returns -1 with a message instead of crashing (the multi-rank path itself is covered on GPUs and, for the host
+    logic of assembling column slices, by the gloo ranks of test_shard.py)."""
+    import ctypes
+
+    import torch
+
+    from torch_vulkan_b200 import cabi
+
+    lib = cabi.lib()
+    ident = ctypes.create_string_buffer(128)
+    rc = lib.tvb_comm_unique_id(ident)
+    assert rc in (0, -1)
+    if rc == -1:
+        assert b"NCCL" in lib.tvb_last_error()
+    if not torch.cuda.is_available():
+        handle = ctypes.c_void_p(0)
+        assert lib.tvb_comm_init_rank(0, ident.raw, 1, 0, 100, ctypes.byref(handle)) == -1
+        assert len(lib.tvb_last_error()) > 0
+    assert lib.tvb_comm_abort(None) == 0 and lib.tvb_comm_destroy(None) == 0

@@ -211,3 +211,41 @@ def test_device_round_trips_and_casts():
     import torch_vulkan_b200 as tv
     stats = tv.memory_stats()
     assert stats["reserved_bytes"] >= stats["allocated_bytes"] > 0
+
+
+FNUZ = [torch.float8_e4m3fnuz, torch.float8_e5m2fnuz]
+
+
+def test_fnuz_float8_casts_match_c10():
+    """The fnuz formats the reference tabulates as well (crates/pyvk/csrc/backend.cpp:471-477): every code decodes, and a
+    spread of values encodes, exactly as c10 does (no infinities, no negative zero, the one NaN 0x80, overflow to NaN)."""
+    for f8 in FNUZ:
+        codes = torch.arange(256, dtype=torch.int32).to(torch.uint8).view(f8)
+        got, want = codes.to("vk").float().cpu(), codes.float()
+        assert torch.equal(got.isnan(), want.isnan()) and torch.equal(got[~want.isnan()], want[~want.isnan()])
+        vals = want[~want.isnan()].sort().values
+        mid = (vals[1:] + vals[:-1]) / 2  # halfway cases: ties to even
+        probes = torch.cat([vals, mid, torch.nextafter(mid, torch.tensor(float("inf"))), torch.nextafter(mid, torch.tensor(-float("inf"))),
+                            torch.randn(4000, generator=C.gen(8)) * 300, torch.randn(4000, generator=C.gen(9)) * 1e-3,
+                            torch.tensor([0.0, -0.0, float("inf"), -float("inf"), float("nan"), 1e-12, -1e-12, 1e9, -1e9])])
+        got, want = probes.to("vk").to(f8).cpu().view(torch.uint8), probes.to(f8).view(torch.uint8)
+        assert torch.equal(got, want)
+
+
+@pytest.mark.parametrize("fa,fb", [(FNUZ[0], FNUZ[0]), (FNUZ[1], FNUZ[0]), (FNUZ[0], C.FLOAT8[0])])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32, torch.float8_e4m3fnuz])
+@pytest.mark.parametrize("rowwise", [False, True])
+def test_scaled_mm_fnuz(fa, fb, out_dtype, rowwise):
+    """_scaled_mm with fnuz operands and outputs against the reference's emulated formula (crates/pyvk/csrc/quant.cpp:283-299)."""
+    a, b, sa, sb, bias, _ = C.scaled_case(fa, fb, out_dtype, rowwise, m=40, k=96, n=72)
+    scale_result = torch.tensor(2.0) if out_dtype in FNUZ else None
+    want, tol = C.scaled_want(a, b, sa, sb, bias, scale_result, out_dtype)
+    if out_dtype in FNUZ:  # (scaled_want's formula, with the division the fnuz output takes as well)
+        af, bf = a.float() * sa, b.float() * sb
+        want = ((af @ bf) * 0.5).to(out_dtype)
+        tol = torch.finfo(out_dtype).eps * want.float().abs() + 2**-20 * (af.abs() @ bf.abs()) * 0.5
+    kw = dict(bias=bias.to("vk") if bias is not None else None, out_dtype=out_dtype,
+              scale_result=scale_result.to("vk") if scale_result is not None else None)
+    with on_gpu():
+        got = torch._scaled_mm(a.to("vk"), b.to("vk"), sa.to("vk"), sb.to("vk"), **kw)
+    assert got.dtype == want.dtype and ((got.cpu().float() - want.float()).abs() <= tol).all()

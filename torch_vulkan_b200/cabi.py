@@ -12,7 +12,7 @@ import os
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "lib", "libtvb200.so")
 
-F32, F16, BF16, E4M3, E5M2, I8, U8, I32, I64, F64, BOOL, I16 = range(12)
+F32, F16, BF16, E4M3, E5M2, I8, U8, I32, I64, F64, BOOL, I16, E4M3FNUZ, E5M2FNUZ = range(14)
 
 _c = ctypes
 _vp, _i, _i64, _u64, _u32 = _c.c_void_p, _c.c_int, _c.c_int64, _c.c_uint64, _c.c_uint32
@@ -67,6 +67,14 @@ SIGNATURES = {
     "tvb_qmm8_chain_create": (_i, [_i, _i, _c.POINTER(TvbChainItem), _i, _c.POINTER(_vp), _i, _i, _vp, _i, _c.POINTER(_vp)]),
     "tvb_qmm8_chain_run": (_i, [_i, _vp]),
     "tvb_qmm8_chain_destroy": (None, [_vp]),
+    "tvb_comm_unique_id": (_i, [_c.c_char_p]),
+    "tvb_comm_init_rank": (_i, [_i, _c.c_char_p, _i, _i, _i, _c.POINTER(_vp)]),
+    "tvb_comm_init_all": (_i, [_c.POINTER(_i), _i, _c.POINTER(_vp)]),
+    "tvb_all_gather": (_i, [_vp, _vp, _vp, _u64]),
+    "tvb_all_gather_columns": (_i, [_vp, _vp, _vp, _i, _i64, _i64]),
+    "tvb_comm_wait": (_i, [_vp, _i]),
+    "tvb_comm_abort": (_i, [_vp]),
+    "tvb_comm_destroy": (_i, [_vp]),
     "tvb_graph_begin": (_i, [_i]),
     "tvb_graph_end": (_i, [_i, _c.POINTER(_vp)]),
     "tvb_graph_launch": (_i, [_i, _vp]),
@@ -131,7 +139,7 @@ def _dtype_code(dtype):
 
     return {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16, torch.float8_e4m3fn: E4M3, torch.float8_e5m2: E5M2,
             torch.int8: I8, torch.uint8: U8, torch.int32: I32, torch.int64: I64, torch.float64: F64, torch.bool: BOOL,
-            torch.int16: I16}[dtype]
+            torch.int16: I16, torch.float8_e4m3fnuz: E4M3FNUZ, torch.float8_e5m2fnuz: E5M2FNUZ}[dtype]
 
 
 def _ptr(t):

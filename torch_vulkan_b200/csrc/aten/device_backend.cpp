@@ -30,6 +30,8 @@ int dtype_code(at::ScalarType t) {
     case at::kBFloat16: return TVB_BF16;
     case at::kFloat8_e4m3fn: return TVB_E4M3;
     case at::kFloat8_e5m2: return TVB_E5M2;
+    case at::kFloat8_e4m3fnuz: return TVB_E4M3FNUZ;
+    case at::kFloat8_e5m2fnuz: return TVB_E5M2FNUZ;
     case at::kChar: return TVB_I8;
     case at::kByte: return TVB_U8;
     case at::kInt: return TVB_I32;

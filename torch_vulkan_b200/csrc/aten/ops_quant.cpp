@@ -412,9 +412,9 @@ at::Tensor& scaled_mm_out(const at::Tensor& mat1, const at::Tensor& mat2, const 
   at::native::resize_output(out, {M, N});
   if (out.numel() == 0) return out;
   const int ad = dtype_code(mat1.scalar_type()), bd = dtype_code(mat2.scalar_type()), od = dtype_code(out.scalar_type());
-  if ((ad != TVB_E4M3 && ad != TVB_E5M2) || (bd != TVB_E4M3 && bd != TVB_E5M2))
-    no_fallback("aten::_scaled_mm", "only float8_e4m3fn and float8_e5m2 operands have kernels");
-  if (od != TVB_F32 && od != TVB_F16 && od != TVB_BF16 && od != TVB_E4M3 && od != TVB_E5M2)
+  auto is_f8 = [](int dt) { return dt == TVB_E4M3 || dt == TVB_E5M2 || dt == TVB_E4M3FNUZ || dt == TVB_E5M2FNUZ; };
+  if (!is_f8(ad) || !is_f8(bd)) no_fallback("aten::_scaled_mm", "only the four float8 formats have kernels");
+  if (od != TVB_F32 && od != TVB_F16 && od != TVB_BF16 && !is_f8(od))
     no_fallback("aten::_scaled_mm", std::string("no kernel writes ") + c10::toString(out.scalar_type()));
   // The kernels write a contiguous [M, N]; any other `out` receives a copy of one.
   at::Tensor dst = out.is_contiguous() ? out : at::empty({M, N}, out.options());

@@ -31,7 +31,7 @@ inline int dtype_size(int dtype) {
     case TVB_F64: case TVB_I64: return 8;
     case TVB_F32: case TVB_I32: return 4;
     case TVB_F16: case TVB_BF16: case TVB_I16: return 2;
-    case TVB_E4M3: case TVB_E5M2: case TVB_I8: case TVB_U8: case TVB_BOOL: return 1;
+    case TVB_E4M3: case TVB_E5M2: case TVB_E4M3FNUZ: case TVB_E5M2FNUZ: case TVB_I8: case TVB_U8: case TVB_BOOL: return 1;
     default: return 0;
   }
 }

@@ -33,7 +33,9 @@ __device__ __forceinline__ Value load_value(const void* p, int64_t idx, int dtyp
   switch (dtype) {
     case TVB_F32: v.d = static_cast<const float*>(p)[idx]; break;
     case TVB_F64: v.d = static_cast<const double*>(p)[idx]; break;
-    case TVB_F16: case TVB_BF16: case TVB_E4M3: case TVB_E5M2: v.d = load_float_rt(p, idx, dtype); break;
+    case TVB_F16: case TVB_BF16: case TVB_E4M3: case TVB_E5M2: case TVB_E4M3FNUZ: case TVB_E5M2FNUZ:
+      v.d = load_float_rt(p, idx, dtype);
+      break;
     case TVB_I8: v.i = static_cast<const int8_t*>(p)[idx]; v.is_int = true; break;
     case TVB_U8: v.i = static_cast<const uint8_t*>(p)[idx]; v.is_int = true; break;
     case TVB_BOOL: v.i = static_cast<const uint8_t*>(p)[idx] != 0; v.is_int = true; break;
@@ -48,7 +50,7 @@ __device__ __forceinline__ Value load_value(const void* p, int64_t idx, int dtyp
 __device__ __forceinline__ void store_value(void* p, int64_t idx, int dtype, const Value& v) {
   switch (dtype) {
     case TVB_F64: static_cast<double*>(p)[idx] = v.is_int ? static_cast<double>(v.i) : v.d; break;
-    case TVB_F32: case TVB_F16: case TVB_BF16: case TVB_E4M3: case TVB_E5M2: {
+    case TVB_F32: case TVB_F16: case TVB_BF16: case TVB_E4M3: case TVB_E5M2: case TVB_E4M3FNUZ: case TVB_E5M2FNUZ: {
       float f = v.is_int ? static_cast<float>(v.i) : static_cast<float>(v.d);
       store_float_rt(p, idx, dtype, f);
       break;

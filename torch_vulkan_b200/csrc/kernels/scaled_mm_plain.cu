@@ -68,7 +68,7 @@ __global__ void __launch_bounds__(256) scaled_mm_plain_kernel(const ScaledMmPara
     }
   }
 
-  const bool f8_out = p.out_dtype == TVB_E4M3 || p.out_dtype == TVB_E5M2;
+  const bool f8_out = p.out_dtype == TVB_E4M3 || p.out_dtype == TVB_E5M2 || p.out_dtype == TVB_E4M3FNUZ || p.out_dtype == TVB_E5M2FNUZ;
   const float inv = f8_out && p.scale_result != nullptr ? 1.0f / p.scale_result[0] : 1.0f;
 #pragma unroll
   for (int i = 0; i < 4; i++) {

@@ -367,11 +367,13 @@ extern "C" int tvb_scaled_mm(int device, const void* a, int a_dtype, int64_t a_s
                              int64_t b_s0, int64_t b_s1, const float* scale_a, const float* scale_b, int rowwise,
                              const void* bias, int bias_dtype, const float* scale_result, void* out, int out_dtype, int64_t m,
                              int64_t n, int64_t k, int variant) {
-  TVB_REQUIRE((a_dtype == TVB_E4M3 || a_dtype == TVB_E5M2) && (b_dtype == TVB_E4M3 || b_dtype == TVB_E5M2),
-              "tvb_scaled_mm: operands must be float8_e4m3fn or float8_e5m2");
-  TVB_REQUIRE(out_dtype == TVB_F32 || out_dtype == TVB_F16 || out_dtype == TVB_BF16 || out_dtype == TVB_E4M3 ||
-                  out_dtype == TVB_E5M2,
+  auto is_f8 = [](int dt) { return dt == TVB_E4M3 || dt == TVB_E5M2 || dt == TVB_E4M3FNUZ || dt == TVB_E5M2FNUZ; };
+  TVB_REQUIRE(is_f8(a_dtype) && is_f8(b_dtype), "tvb_scaled_mm: operands must be float8 (e4m3fn, e5m2, e4m3fnuz or e5m2fnuz)");
+  TVB_REQUIRE(out_dtype == TVB_F32 || out_dtype == TVB_F16 || out_dtype == TVB_BF16 || is_f8(out_dtype),
               "tvb_scaled_mm: unsupported output dtype");
+  // the tensor cores take e4m3fn and e5m2 operands; the fnuz formats (operands or output) are decoded / encoded by the plain kernel
+  const bool hw_formats = (a_dtype == TVB_E4M3 || a_dtype == TVB_E5M2) && (b_dtype == TVB_E4M3 || b_dtype == TVB_E5M2) &&
+                          out_dtype != TVB_E4M3FNUZ && out_dtype != TVB_E5M2FNUZ;
   TVB_REQUIRE(m >= 0 && n >= 0 && k >= 0, "tvb_scaled_mm: negative size");
   TVB_REQUIRE(variant >= 0 && variant <= 2, "tvb_scaled_mm: unknown kernel variant");
   if (m == 0 || n == 0) return 0;
@@ -384,8 +386,8 @@ extern "C" int tvb_scaled_mm(int device, const void* a, int a_dtype, int64_t a_s
   p.m = m; p.n = n; p.k = k;
   p.a_s0 = a_s0; p.a_s1 = a_s1; p.b_s0 = b_s0; p.b_s1 = b_s1;
   p.a_dtype = a_dtype; p.b_dtype = b_dtype; p.bias_dtype = bias_dtype; p.out_dtype = out_dtype; p.rowwise = rowwise;
-  const bool usable = scaled_mm_tc_usable(p);
-  TVB_REQUIRE(variant != 2 || usable, "tvb_scaled_mm: the tcgen05 kernel needs K-major operands with 16-byte aligned rows");
+  const bool usable = hw_formats && scaled_mm_tc_usable(p);
+  TVB_REQUIRE(variant != 2 || usable, "tvb_scaled_mm: the tcgen05 kernel needs e4m3fn / e5m2 K-major operands with 16-byte aligned rows");
   // small problems do not fill one wave of 128 x 256 tiles: the plain kernel's 64 x 64 tiles spread them wider
   const bool big = m * n >= int64_t(128) * 256 * 8 && k >= 128;
   if (variant == 2 || (variant == 0 && usable && big)) return scaled_mm_tc(device, stream, p);

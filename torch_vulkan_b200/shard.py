@@ -99,6 +99,45 @@ def barrier(group=None):
         dist.all_reduce(t, group=group)
 
 
+class AbiComm:
+    """The C ABI's own communicator (tvb_comm_*: NCCL behind the library, for hosts that bind it without PyTorch): rank 0
+    makes the id, the object group carries it, every rank joins. all_gather_columns assembles [m, N/G] slices into [m, N]
+    on the backend's stream; wait() bounds the wait on the host and aborts the communicator instead of hanging."""
+
+    def __init__(self, device_index, object_group, timeout_ms=30000):
+        import ctypes
+
+        from . import cabi
+
+        self._c, self._ct, self.dev = cabi, ctypes, device_index
+        self.world, self.rank = dist.get_world_size(), dist.get_rank()
+        ident = ctypes.create_string_buffer(128)
+        if self.rank == 0:
+            cabi.check(cabi.lib().tvb_comm_unique_id(ident))
+        box = [ident.raw]
+        dist.broadcast_object_list(box, src=0, group=object_group)
+        handle = ctypes.c_void_p(0)
+        cabi.check(cabi.lib().tvb_comm_init_rank(device_index, box[0], self.world, self.rank, timeout_ms, ctypes.byref(handle)))
+        self.handle = handle
+
+    def all_gather_columns(self, c_local):
+        m, n_local = c_local.shape
+        c_local = c_local.contiguous()
+        out = torch.empty((m, n_local * self.world), dtype=c_local.dtype, device=c_local.device)
+        self._c.check(self._c.lib().tvb_all_gather_columns(self.handle, c_local.data_ptr(), out.data_ptr(), self._c._dtype_code(c_local.dtype),
+                                                           m, n_local))
+        self._keep = c_local  # (alive until the next call: the collective reads it on the stream)
+        return out
+
+    def wait(self, timeout_ms=30000):
+        self._c.check(self._c.lib().tvb_comm_wait(self.handle, timeout_ms))
+
+    def destroy(self):
+        if self.handle:
+            self._c.lib().tvb_comm_destroy(self.handle)
+            self.handle = None
+
+
 class PeerChannel:
     """What the ranks of one node share for the fused sharded products: every rank's array of arrival counters (one
     entry per source rank, added to by the product kernels of all ranks over NVLink) and, per rank, the device-resident
