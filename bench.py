@@ -568,8 +568,9 @@ def int8_stack_sharded(tv, timer, peaks, channel, rank, world, dev, ms_list=(1, 
         check_last_layer(host, *[t.cpu() for t in last], f"rank {rank}: sharded int8 stack as a chain (m={m})")
         shard.barrier()
         ms_ops = None
-        if m == 1:
-            # for comparison: one launch per product (tvb_qmm8_gather), each kernel waiting for the previous product's columns
+        if True:
+            # the other way: one launch per product (tvb_qmm8_gather; a pass per 16 rows), each kernel waiting for the previous
+            # product's columns
             def step():
                 h = x
                 for (wq, sq), (wo, so), (wg, sg), (wd, sd) in weights:

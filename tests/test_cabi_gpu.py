@@ -44,7 +44,8 @@ def test_qmm8_reference_cases(abi, dtype, m, k, n):
 @pytest.mark.parametrize("variant", [1, 2])
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("m,k,n", [(1, 128, 8), (1, 256, 257), (3, 1024, 255), (8, 4096, 300), (9, 512, 1000), (16, 2048, 4099),
-                                   (13, 8192, 520), (33, 256, 77), (64, 384, 513)])
+                                   (13, 8192, 520), (33, 256, 77), (64, 384, 513), (17, 1024, 300), (32, 4096, 1000), (40, 2048, 3001),
+                                   (64, 8192, 1024), (50, 128, 40)])
 def test_qmm8_kernel_variants(abi, variant, dtype, m, k, n):
     a, b, s = C.config_int8(m, k, n, dtype, seed=m + n)
     want, tol = C.int8_want(a, b, s)

@@ -121,10 +121,11 @@ at::Tensor weight_int8pack_mm(const at::Tensor& A, const at::Tensor& B, const at
   at::Tensor s = scales.to(A.scalar_type()).contiguous();  // (the CPU reads the scales in A's dtype)
   const int dev = enter_device(A);
   const int dt = dtype_code(A.scalar_type());
-  // More than 32 rows, 16-bit A, aligned rows: the GEMM over cached widened weights (keyed on the caller's own scales
-  // tensor, so only when no converted copy of it was needed). It is faster than widening in the main loop at every such m
-  // (37 against 50 us at m = 64 on a 14336 x 4096 layer, 62 against 95 us at m = 512).
-  if (M > 32 && (dt == TVB_BF16 || dt == TVB_F16) && K % 16 == 0 && A.stride(0) % 8 == 0 && A.stride(0) >= K &&
+  // More rows than one pass of the decode kernel takes (64, when k is a multiple of 128; else 32), 16-bit A, aligned rows: the
+  // GEMM over cached widened weights (keyed on the caller's own scales tensor, so only when no converted copy of it was
+  // needed). It is faster than widening in the main loop at every such m (62 against 95 us at m = 512 on a 14336 x 4096
+  // layer).
+  if (M > (K % 128 == 0 ? 64 : 32) && (dt == TVB_BF16 || dt == TVB_F16) && K % 16 == 0 && A.stride(0) % 8 == 0 && A.stride(0) >= K &&
       (reinterpret_cast<uintptr_t>(gpu_address(A)) & 15u) == 0 && (reinterpret_cast<uintptr_t>(gpu_address(B)) & 15u) == 0 &&
       s.is_same(scales)) {
     at::Tensor widened = widened_weights(B, s, dev, dt, N, K);

@@ -798,12 +798,19 @@ int launch_skinny(int device, cudaStream_t stream, const void* a, int64_t a_sm, 
   // Small weight matrices (a decoder's qkv, o and down projections) are cut into 128-row tiles: twice as many tiles, so half
   // as many CTAs share each and the completion of shared tiles, which dominates such short launches, is shorter. Large ones
   // keep 256-row tiles (fewer token fragments read per weight). Measured on a 32-layer stack: 4-6 % per decoding step.
-  const bool small = static_cast<int64_t>(n) * k < (int64_t(64) << 20);
-  if (adds != nullptr && gather == nullptr)
-    return small ? launch_skinny_cfg<DT, NT, 1, 8, true>(device, stream, a, a_sm, b, scales, c, m, n, k, m0, nullptr, adds)
-                 : launch_skinny_cfg<DT, NT, 2, 8, true>(device, stream, a, a_sm, b, scales, c, m, n, k, m0, nullptr, adds);
-  if (small) return launch_skinny_cfg<DT, NT, 1, 8>(device, stream, a, a_sm, b, scales, c, m, n, k, m0, gather);
-  return launch_skinny_cfg<DT, NT, 2, 8>(device, stream, a, a_sm, b, scales, c, m, n, k, m0, gather);
+  if constexpr (NT > 2) {
+    // 32 or 64 rows of A in one pass (the weights streamed once): 128-row tiles whatever the matrix's size, which is what
+    // the token fragments leave room for in registers and shared memory. (Bias and residual keep to passes of 16 rows.)
+    if (adds != nullptr) return fail("tvb_qmm8: internal: wide passes carry no adds");
+    return launch_skinny_cfg<DT, NT, 1, 8>(device, stream, a, a_sm, b, scales, c, m, n, k, m0, gather);
+  } else {
+    const bool small = static_cast<int64_t>(n) * k < (int64_t(64) << 20);
+    if (adds != nullptr && gather == nullptr)
+      return small ? launch_skinny_cfg<DT, NT, 1, 8, true>(device, stream, a, a_sm, b, scales, c, m, n, k, m0, nullptr, adds)
+                   : launch_skinny_cfg<DT, NT, 2, 8, true>(device, stream, a, a_sm, b, scales, c, m, n, k, m0, nullptr, adds);
+    if (small) return launch_skinny_cfg<DT, NT, 1, 8>(device, stream, a, a_sm, b, scales, c, m, n, k, m0, gather);
+    return launch_skinny_cfg<DT, NT, 2, 8>(device, stream, a, a_sm, b, scales, c, m, n, k, m0, gather);
+  }
 }
 
 bool skinny_ok(const void* a, int dtype, int64_t a_sm, const int8_t* b, int64_t m, int64_t n, int64_t k) {
@@ -975,6 +982,19 @@ extern "C" int tvb_set_wait_limit_ms(int ms) {
   return 0;
 }
 
+// One pass of the decode kernel over `rows` rows of A from row m0 on (rows <= 8, 16, 32, 64 pick the token count).
+template <int DT>
+static int skinny_pass(int device, cudaStream_t stream, const void* a, int64_t stride, const int8_t* b, const void* scales, void* c,
+                       int mi, int ni, int ki, int m0, int rows, const GatherTargets* gather, const SkinnyAdds* adds) {
+  if (rows <= 8) return launch_skinny<DT, 1>(device, stream, a, stride, b, scales, c, mi, ni, ki, m0, gather, adds);
+  if (rows <= 16) return launch_skinny<DT, 2>(device, stream, a, stride, b, scales, c, mi, ni, ki, m0, gather, adds);
+  if (rows <= 32) return launch_skinny<DT, 4>(device, stream, a, stride, b, scales, c, mi, ni, ki, m0, gather, adds);
+  return launch_skinny<DT, 8>(device, stream, a, stride, b, scales, c, mi, ni, ki, m0, gather, adds);
+}
+
+// Rows of A per pass: 16 with bias or residual in the epilogue, else up to 64 (one pass streams the weights once).
+static int pass_rows(int m, const SkinnyAdds* adds) { return adds != nullptr || m <= 16 ? 16 : 64; }
+
 extern "C" int tvb_qmm8_gather(int device, const void* a, int dtype, int64_t a_sm, const int8_t* b, const void* scales,
                                void* const* c_ranks, uint32_t* const* flag_ranks, int world, int rank, uint32_t* seq_counter,
                                int independent, int64_t m, int64_t n_local, int64_t k) {
@@ -999,21 +1019,17 @@ extern "C" int tvb_qmm8_gather(int device, const void* a, int dtype, int64_t a_s
   g.rank = rank;
   g.seq = seq_counter;
   g.n_total = n_local * world;
-  const int passes = static_cast<int>(ceil_div(m, 16));
   const int mi = static_cast<int>(m), ni = static_cast<int>(n_local), ki = static_cast<int>(k);
   const int64_t stride = m == 1 ? k : a_sm;
-  // 16 rows of A per pass; every pass is a product of its own on the channel (it counts and is waited for like one)
-  for (int m0 = 0; m0 < mi; m0 += 16) {
-    const int rows = mi - m0;
+  // up to 64 rows of A per pass; every pass is a product of its own on the channel (it counts and is waited for like one)
+  const int step = pass_rows(mi, nullptr);
+  const int passes = static_cast<int>(ceil_div(mi, step));
+  for (int m0 = 0, pass = 0; m0 < mi; m0 += step, pass++) {
+    const int rows = std::min(step, mi - m0);
     // (the passes of one product do not depend on each other: pass i need not wait for the i passes before it either)
-    g.independent = static_cast<uint32_t>(std::min(independent * passes + m0 / 16, kArriveSlots - 1));
-    int rc;
-    if (dtype == TVB_BF16)
-      rc = rows <= 8 ? launch_skinny<TVB_BF16, 1>(device, stream, a, stride, b, scales, g.c[rank], mi, ni, ki, m0, &g)
-                     : launch_skinny<TVB_BF16, 2>(device, stream, a, stride, b, scales, g.c[rank], mi, ni, ki, m0, &g);
-    else
-      rc = rows <= 8 ? launch_skinny<TVB_F16, 1>(device, stream, a, stride, b, scales, g.c[rank], mi, ni, ki, m0, &g)
-                     : launch_skinny<TVB_F16, 2>(device, stream, a, stride, b, scales, g.c[rank], mi, ni, ki, m0, &g);
+    g.independent = static_cast<uint32_t>(std::min(independent * passes + pass, kArriveSlots - 1));
+    const int rc = dtype == TVB_BF16 ? skinny_pass<TVB_BF16>(device, stream, a, stride, b, scales, g.c[rank], mi, ni, ki, m0, rows, &g, nullptr)
+                                     : skinny_pass<TVB_F16>(device, stream, a, stride, b, scales, g.c[rank], mi, ni, ki, m0, rows, &g, nullptr);
     if (rc != 0) return rc;
   }
   return 0;
@@ -1038,19 +1054,15 @@ extern "C" int tvb_wait_flags(int device, const uint32_t* flags, int world, cons
   return launched("qmm8_wait_flags", dim3(1), dim3(32), 0, stream);
 }
 
-// The decode kernel over all rows of A, 16 per pass.
+// The decode kernel over all rows of A.
 static int skinny_passes(int device, cudaStream_t stream, const void* a, int dtype, int64_t a_sm, const int8_t* b, const void* scales,
                          void* c, int mi, int ni, int ki, const SkinnyAdds* adds) {
   const int64_t stride = mi == 1 ? ki : a_sm;  // (one row: any stride will do for the map)
-  for (int m0 = 0; m0 < mi; m0 += 16) {
-    const int rows = mi - m0;
-    int rc;
-    if (dtype == TVB_BF16)
-      rc = rows <= 8 ? launch_skinny<TVB_BF16, 1>(device, stream, a, stride, b, scales, c, mi, ni, ki, m0, nullptr, adds)
-                     : launch_skinny<TVB_BF16, 2>(device, stream, a, stride, b, scales, c, mi, ni, ki, m0, nullptr, adds);
-    else
-      rc = rows <= 8 ? launch_skinny<TVB_F16, 1>(device, stream, a, stride, b, scales, c, mi, ni, ki, m0, nullptr, adds)
-                     : launch_skinny<TVB_F16, 2>(device, stream, a, stride, b, scales, c, mi, ni, ki, m0, nullptr, adds);
+  const int step = pass_rows(mi, adds);
+  for (int m0 = 0; m0 < mi; m0 += step) {
+    const int rows = std::min(step, mi - m0);
+    const int rc = dtype == TVB_BF16 ? skinny_pass<TVB_BF16>(device, stream, a, stride, b, scales, c, mi, ni, ki, m0, rows, nullptr, adds)
+                                     : skinny_pass<TVB_F16>(device, stream, a, stride, b, scales, c, mi, ni, ki, m0, rows, nullptr, adds);
     if (rc != 0) return rc;
   }
   return 0;
@@ -1083,9 +1095,10 @@ extern "C" int tvb_qmm8(int device, const void* a, int dtype, int64_t a_sm, cons
   // the extra pass over the weights pays for itself from about 730 rows on (874 against 1237 TFLOP/s, 3 bytes per weight)
   if (variant == 4 || (variant == 0 && can_widen && m >= 1024))
     return qmm8_widen_gemm(device, stream, a, dtype, a_sm, b, scales, c, m, n, k);
-  // 17-32 rows: two passes of the decode kernel stream the weights twice and still beat one 128-row tensor-core tile
-  const bool two_passes = can_skinny && m <= 32;
-  if (variant == 3 || (variant == 0 && can_tc && m > 16 && !two_passes))
+  // up to 64 rows: one pass of the decode kernel (32 or 64 token columns per MMA row block) streams the weights once and
+  // beats a 128-row tensor-core tile, which is mostly padding at these sizes
+  const bool decode_pass = can_skinny && m <= 64;
+  if (variant == 3 || (variant == 0 && can_tc && m > 16 && !decode_pass))
     return qmm8_tc(device, stream, a, dtype, m == 1 ? k : a_sm, b, scales, c, m, n, k);
   if (variant == 2 || (variant == 0 && can_skinny)) return skinny_passes(device, stream, a, dtype, a_sm, b, scales, c, mi, ni, ki, nullptr);
   if (dtype == TVB_F32 && variant == 0 && k % 16 == 0 && (a_sm % 4 == 0 || m == 1) && (reinterpret_cast<uintptr_t>(a) & 15u) == 0 &&
