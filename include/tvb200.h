@@ -105,6 +105,13 @@ TVB_API int tvb_memcpy_d2d(int device, void* dst, const void* src, uint64_t nbyt
 /* Device -> page-locked host memory without waiting: the bytes are there after tvb_synchronize (or any later
  * waiting call) on the device. */
 TVB_API int tvb_memcpy_d2h_async(int device, void* dst, const void* src, uint64_t nbytes);
+/* The same copy on a second stream of the runtime's (the copy-out lane): it starts when everything queued on the device's
+ * stream so far has run, and what is queued afterwards does not wait for it, so a result travels to the host under the
+ * next kernels. The caller leaves `src` unwritten until the lane is joined. tvb_join_copies makes the device's stream wait
+ * for the lane; tvb_synchronize and tvb_graph_end join by themselves (a recorded step holds its copies). No counterpart
+ * in the reference, whose stream is one queue (crates/vkcore/src/stream.rs). */
+TVB_API int tvb_memcpy_d2h_overlapped(int device, void* dst, const void* src, uint64_t nbytes);
+TVB_API int tvb_join_copies(int device);
 
 /* Page-locked host memory (replaces the reference's pinned allocator, crates/pyvk/csrc/backend.cpp:313-340):
  * copies from and to it are asynchronous. tvb_host_is_pinned: 1 if `ptr` lies in page-locked memory, else 0. */
@@ -349,7 +356,8 @@ TVB_API int tvb_qmm4_decode(int device, const void* inp, int dtype, const float*
  * (decoded in the loop; the tensor cores have no such operand format). scale_a / scale_b: device float32, one element
  * (rowwise 0) or m / n elements (rowwise 1). bias: n elements of bias_dtype, or NULL.
  * scale_result: device float32 or NULL. out: contiguous [m, n] of out_dtype (F32, F16,
- * BF16, E4M3, E5M2, E4M3FNUZ, E5M2FNUZ). variant: 0 automatic, 1 the plain kernel, 2 the tcgen05 kernel. */
+ * BF16, E4M3, E5M2, E4M3FNUZ, E5M2FNUZ). variant: 0 automatic, 1 the plain kernel, 2 the tcgen05 kernels, 3 among
+ * those the one that puts a pair of CTAs (tcgen05 cta_group::2) on each 256 x 256 tile, whatever the shape. */
 TVB_API int tvb_scaled_mm(int device, const void* a, int a_dtype, int64_t a_s0, int64_t a_s1, const void* b, int b_dtype,
                   int64_t b_s0, int64_t b_s1, const float* scale_a, const float* scale_b, int rowwise,
                   const void* bias, int bias_dtype, const float* scale_result, void* out, int out_dtype, int64_t m,
@@ -373,8 +381,8 @@ TVB_API int tvb_scaled_mm_gather(int device, const void* a, int a_dtype, int64_t
  *      crates/pyvk/csrc/linalg.cpp:227-321, for the matrices either side of the quantised products) ----
  * out[m, n] = A[m, k] @ B[k, n] (+ bias[n]), float32 accumulation, one rounding to out_dtype. A and B have one dtype;
  * element (i, kk) of A at a[i * a_s0 + kk * a_s1], element (kk, j) of B at b[kk * b_s0 + j * b_s1]; out contiguous.
- * variant: 0 automatic, 1 the plain CUDA-core kernel (any strides, float32 included), 2 the tcgen05 kernel (16-bit
- * operands, both K-major: a_s1 == 1 and b_s0 == 1, rows 16-byte aligned). */
+ * variant: 0 automatic, 1 the plain CUDA-core kernel (any strides, float32 included), 2 the tcgen05 kernels (16-bit
+ * operands, both K-major: a_s1 == 1 and b_s0 == 1, rows 16-byte aligned), 3 among those the kernel of CTA pairs. */
 TVB_API int tvb_mm(int device, const void* a, int dtype, int64_t a_s0, int64_t a_s1, const void* b, int64_t b_s0, int64_t b_s1,
            const void* bias, int bias_dtype, void* out, int out_dtype, int64_t m, int64_t n, int64_t k, int variant);
 

@@ -261,6 +261,26 @@ def test_scaled_mm_tcgen05(abi, fa, fb, out_dtype, rowwise, m, k, n):
         assert ok.all(), f"max excess {(err - tol).max()} at {(err - tol).argmax()}"
 
 
+@pytest.mark.parametrize("fa,fb", [(C.FLOAT8[0], C.FLOAT8[0]), (C.FLOAT8[1], C.FLOAT8[0])])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32, torch.float8_e4m3fn])
+@pytest.mark.parametrize("rowwise", [False, True])
+@pytest.mark.parametrize("m,k,n", [(256, 128, 256), (130, 144, 264), (257, 1024, 511), (384, 4096 + 32, 768), (1100, 512, 1300)])
+def test_scaled_mm_cta_pairs(abi, fa, fb, out_dtype, rowwise, m, k, n):
+    """The kernel that puts a pair of CTAs on each 256 x 256 tile (variant 3), ragged edges in both dimensions included."""
+    a, b, sa, sb, bias, sr = C.scaled_case(fa, fb, out_dtype, rowwise, m=m, k=k, n=n)
+    want, tol = C.scaled_want(a, b, sa, sb, bias, sr, out_dtype)
+    got = abi.scaled_mm(dev(a), dev(b), dev(sa), dev(sb), dev(bias), dev(sr), out_dtype, variant=3)
+    abi.synchronize()
+    err = (got.cpu().float() - want.float()).abs()
+    ok = err <= tol
+    if out_dtype in C.FLOAT8:
+        assert ok.float().mean() > 0.999
+        up = (want.float().abs() * 2**-2).clamp_min(2**-9)
+        assert (err <= up + tol).all()
+    else:
+        assert ok.all(), f"max excess {(err - tol).max()} at {(err - tol).argmax()}"
+
+
 def test_scaled_mm_config4_sample(abi):
     for rowwise in (False, True):
         a, b, sa, sb = C.config_fp8(512, 8192, 1024, rowwise)

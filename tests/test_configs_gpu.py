@@ -100,3 +100,46 @@ def test_config5_layer_shapes(m):
         got = torch._weight_int8pack_mm(inp.to("vk"), b.to("vk"), s.to("vk")).cpu()
         assert got.shape == (m, n)
         assert ((got.float() - want.float()).abs() <= tol).all(), name
+
+
+def test_results_copied_out_beside_the_next_products(tv):
+    """copy_to_host_overlapped: each product's result leaves on the second stream while the next product runs; eager and
+    as a recorded step replayed with new inputs. Every result is compared with the CPU product."""
+    from torch_vulkan_b200 import shard
+
+    ms = [16, 4, 1]
+    a_cpu = {m: C.config_int8(m, 1024, 4096, torch.bfloat16)[0] for m in ms}
+    _, b, s = C.config_int8(1, 1024, 4096, torch.bfloat16)
+    bv, sv = b.to("vk"), s.to("vk")
+    a_pin = {m: a_cpu[m].clone().pin_memory() for m in ms}
+    a_dev = {m: torch.empty_like(a_cpu[m], device="vk") for m in ms}
+    out_pin = {m: torch.zeros(m, 4096, dtype=torch.bfloat16).pin_memory() for m in ms}
+
+    def step():
+        outs = []
+        for m in ms:
+            a_dev[m].copy_(a_pin[m], non_blocking=True)
+        for m in ms:
+            c = torch._weight_int8pack_mm(a_dev[m], bv, sv)
+            tv.copy_to_host_overlapped(out_pin[m], c)
+            outs.append(c)
+        return outs
+
+    def check(scale):
+        for m in ms:
+            want, tol = C.int8_want(a_cpu[m] * scale, b, s)
+            assert ((out_pin[m].float() - want.float()).abs() <= tol).all()
+
+    step()
+    tv.synchronize()
+    check(1.0)
+    graph = shard.StepGraph(step, 0, warm=False)
+    for scale in (2.0, -0.5):
+        for m in ms:
+            a_pin[m].copy_(a_cpu[m] * scale)
+            out_pin[m].zero_()
+        graph.replay()
+        tv.synchronize()
+        check(scale)
+    with pytest.raises(ValueError):
+        tv.copy_to_host_overlapped(torch.zeros(1, 4096, dtype=torch.bfloat16), graph.outputs[-1])

@@ -50,6 +50,21 @@ def test_tvb_mm_tensor_core_kernel(dtype, m, k, n):
     assert ((plain.double() - want).abs() <= tol).all()
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("m,k,n", [(256, 64, 256), (300, 520, 1000), (1100, 256, 1300)])
+def test_tvb_mm_cta_pairs(dtype, m, k, n):
+    """Variant 3: a pair of CTAs on each 256 x 256 tile (tcgen05 cta_group::2), bias and residual included."""
+    a = torch.randn(m, k, generator=gen(1)).to(dtype)
+    w = torch.randn(n, k, generator=gen(2)).to(dtype)
+    bias = torch.randn(n, generator=gen(3)).to(dtype)
+    res = torch.randn(m, n, generator=gen(4)).to(dtype)
+    want, tol = bound(a, w.t(), dtype)
+    got = raw_mm(a.to("vk"), w.to("vk").t(), bias.to("vk"), 3)
+    assert ((got.double() - (want + bias.double())).abs() <= tol + EPS[dtype] * bias.double().abs()).all()
+    got_r = raw_addmm(a.to("vk"), w.to("vk").t(), res.to("vk"), 3)
+    assert ((got_r.double() - (want + res.double())).abs() <= tol + EPS[dtype] * (want + res.double()).abs()).all()
+
+
 def raw_addmm(a, b, residual, variant, out=None):
     m, k = a.shape
     n = b.shape[1]

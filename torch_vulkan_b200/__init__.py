@@ -70,8 +70,32 @@ def _index(device):
 
 
 def synchronize(device=None):
-    """Waits for all queued GPU work on the device."""
-    _native.synchronize(_index(device))
+    """Waits for all queued GPU work on the device (the copy-out lane of copy_to_host_overlapped included)."""
+    try:
+        _native.synchronize(_index(device))
+    finally:
+        _copied_out.clear()
+
+
+_copied_out = []  # sources of overlapped copies: kept alive (and out of the allocator's pool) until the next synchronize
+
+
+def copy_to_host_overlapped(dst, src):
+    """Copies the "vk" tensor `src` into the page-locked CPU tensor `dst` on the runtime's second stream: the copy starts
+    when everything queued so far has run, and kernels queued afterwards run beside it (a step's results travel to the host
+    under the step's remaining products). The bytes are in `dst` after synchronize(). Do not write to `src` before that.
+    Inside a recorded step (shard.StepGraph) the recording holds the copy; return `src` from the step so that it lives
+    as long as the recording. The reference has one queue per device (crates/vkcore/src/stream.rs): no counterpart."""
+    from . import cabi
+
+    if src.device.type != "vk" or dst.device.type != "cpu" or not dst.is_pinned():
+        raise ValueError("copy_to_host_overlapped: from a \"vk\" tensor into a page-locked CPU tensor")
+    if src.dtype != dst.dtype or src.shape != dst.shape or not src.is_contiguous() or not dst.is_contiguous():
+        raise ValueError("copy_to_host_overlapped: contiguous tensors of one dtype and shape")
+    idx = src.device.index or 0
+    cabi.check(cabi.lib().tvb_memcpy_d2h_overlapped(idx, dst.data_ptr(), src.data_ptr(), src.numel() * src.element_size()))
+    _copied_out.append(src)
+    return dst
 
 
 def memory_stats(device=None):

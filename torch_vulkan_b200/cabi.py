@@ -51,6 +51,8 @@ SIGNATURES = {
     "tvb_memcpy_d2h": (_i, [_i, _vp, _vp, _u64]),
     "tvb_memcpy_d2d": (_i, [_i, _vp, _vp, _u64]),
     "tvb_memcpy_d2h_async": (_i, [_i, _vp, _vp, _u64]),
+    "tvb_memcpy_d2h_overlapped": (_i, [_i, _vp, _vp, _u64]),
+    "tvb_join_copies": (_i, [_i]),
     "tvb_copy_strided": (_i, [_i, _vp, _i, _c.POINTER(_i64), _vp, _i, _c.POINTER(_i64), _c.POINTER(_i64), _i]),
     "tvb_fill_strided": (_i, [_i, _vp, _i, _u64, _c.POINTER(_i64), _c.POINTER(_i64), _i]),
     "tvb_add_rowvec": (_i, [_i, _vp, _i, _i64, _vp, _i, _i64, _i64]),

@@ -44,6 +44,11 @@ struct DeviceState {
   void* ws[4] = {nullptr, nullptr, nullptr, nullptr};
   uint64_t ws_size[4] = {0, 0, 0, 0};
   int* status = nullptr;
+  // the copy-out lane of tvb_memcpy_d2h_overlapped: a second stream, the event that forks it off the main stream and
+  // the event that the main stream waits for when the lane is joined
+  cudaStream_t copy_stream = nullptr;
+  cudaEvent_t fork_event = nullptr, join_event = nullptr;
+  bool copies_pending = false;
 };
 
 std::mutex g_mutex;
@@ -300,9 +305,24 @@ void tvb_free(void* handle) {
   delete b;
 }
 
+int tvb_join_copies(int device) {
+  cudaStream_t s;
+  if (enter(device, &s) != 0) return -1;
+  cudaEvent_t join = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    DeviceState& d = g_devices[device];
+    if (d.copies_pending) join = d.join_event;
+    d.copies_pending = false;
+  }
+  if (join != nullptr) TVB_CUDA(cudaStreamWaitEvent(s, join, 0));
+  return 0;
+}
+
 int tvb_synchronize(int device) {
   cudaStream_t s;
   if (enter(device, &s) != 0) return -1;
+  if (tvb_join_copies(device) != 0) return -1;
   TVB_CUDA(cudaStreamSynchronize(s));
   int* status = nullptr;
   void* counters = nullptr;
@@ -409,6 +429,13 @@ void tvb_shutdown(void) {
     }
     if (d.status != nullptr) cudaFree(d.status);
     d.status = nullptr;
+    if (d.copy_stream != nullptr) {
+      cudaStreamSynchronize(d.copy_stream);
+      cudaStreamDestroy(d.copy_stream);
+      cudaEventDestroy(d.fork_event);
+      cudaEventDestroy(d.join_event);
+      d.copy_stream = nullptr;
+    }
     cudaStreamDestroy(d.own_stream);
     d.own_stream = d.stream = nullptr;
   }
@@ -456,6 +483,7 @@ int tvb_graph_end(int device, void** graph_exec) {
   TVB_REQUIRE(graph_exec != nullptr, "tvb_graph_end: NULL pointer");
   cudaStream_t s;
   if (enter(device, &s) != 0) return -1;
+  if (tvb_join_copies(device) != 0) return -1;  // a recording cannot end with the copy-out lane still forked off
   cudaGraph_t graph = nullptr;
   TVB_CUDA(cudaStreamEndCapture(s, &graph));
   cudaGraphExec_t exec = nullptr;
@@ -549,6 +577,34 @@ int tvb_memcpy_d2h_async(int device, void* dst, const void* src, uint64_t nbytes
   if (nbytes == 0) return 0;
   TVB_REQUIRE(tvb_host_is_pinned(dst) != 0, "tvb_memcpy_d2h_async: the destination must be page-locked host memory");
   TVB_CUDA(cudaMemcpyAsync(dst, src, nbytes, cudaMemcpyDeviceToHost, s));
+  return 0;
+}
+
+int tvb_memcpy_d2h_overlapped(int device, void* dst, const void* src, uint64_t nbytes) {
+  cudaStream_t s;
+  if (enter(device, &s) != 0) return -1;
+  if (nbytes == 0) return 0;
+  TVB_REQUIRE(tvb_host_is_pinned(dst) != 0, "tvb_memcpy_d2h_overlapped: the destination must be page-locked host memory");
+  cudaStream_t lane = nullptr;
+  cudaEvent_t fork = nullptr, join = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    DeviceState& d = g_devices[device];
+    if (d.copy_stream == nullptr) {
+      TVB_CUDA(cudaStreamCreateWithFlags(&d.copy_stream, cudaStreamNonBlocking));
+      TVB_CUDA(cudaEventCreateWithFlags(&d.fork_event, cudaEventDisableTiming));
+      TVB_CUDA(cudaEventCreateWithFlags(&d.join_event, cudaEventDisableTiming));
+    }
+    lane = d.copy_stream;
+    fork = d.fork_event;
+    join = d.join_event;
+    d.copies_pending = true;
+  }
+  // the lane takes up where the main stream stands now (inside a recording this is what makes it part of the recording)
+  TVB_CUDA(cudaEventRecord(fork, s));
+  TVB_CUDA(cudaStreamWaitEvent(lane, fork, 0));
+  TVB_CUDA(cudaMemcpyAsync(dst, src, nbytes, cudaMemcpyDeviceToHost, lane));
+  TVB_CUDA(cudaEventRecord(join, lane));
   return 0;
 }
 

@@ -30,6 +30,7 @@ struct GemmTcShape {
   int kblocks;       // ceil(k bytes / kGemmStageK)
   int k_elems_per_block;  // kGemmStageK for 8-bit operands, half of it for 16-bit
   int tiles_m, tiles_n;
+  int band;           // tile rows per band of the tile order (gemm_tile_coords)
 };
 
 // Bytes of k per shared-memory stage: 128 (128-byte swizzle, four MMAs per stage). 64 (64-byte swizzle, twice as many
@@ -127,7 +128,7 @@ __global__ void __launch_bounds__((BM / 32 + 2) * 32, 1)
       bool ok = true;
       for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
         int tm, tn;
-        gemm_tile_coords(tile, sh.tiles_m, sh.tiles_n, BM == 128 ? 16 : 12, tm, tn);
+        gemm_tile_coords(tile, sh.tiles_m, sh.tiles_n, sh.band, tm, tn);
         for (int kb = 0; kb < sh.kblocks; kb++, it++) {
           const int s = static_cast<int>(it % Cfg::kStages);
           const uint32_t ph = static_cast<uint32_t>((it / Cfg::kStages) & 1);
@@ -186,7 +187,7 @@ __global__ void __launch_bounds__((BM / 32 + 2) * 32, 1)
     Epi::kernel_begin(ep, threadIdx.x);
     for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, titer++) {
       int tm, tn;
-      gemm_tile_coords(tile, sh.tiles_m, sh.tiles_n, BM == 128 ? 16 : 12, tm, tn);
+      gemm_tile_coords(tile, sh.tiles_m, sh.tiles_n, sh.band, tm, tn);
       const int acc = titer % Cfg::kAccBufs;
       const uint32_t aph = static_cast<uint32_t>((titer / Cfg::kAccBufs) & 1);
       Epi::begin_tile(ep, epi_smem, tm * Cfg::kBM, tn * BN, sh.m, sh.n, threadIdx.x);

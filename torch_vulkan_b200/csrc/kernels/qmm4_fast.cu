@@ -251,6 +251,7 @@ extern "C" int tvb_qmm4_fast(int device, const void* inp, int dtype, const float
   sh.k_elems_per_block = kGemmStageK / 2;
   sh.tiles_m = static_cast<int>(ceil_div(m, Cfg::kBM));
   sh.tiles_n = static_cast<int>(ceil_div(n, kBN));
+  sh.band = Cfg::kBM == 128 ? 16 : 12;
   FastEpilogue::Params ep{};
   const int64_t wcount = n * k / 2, nblocks = k / bs;
   ep.recip = recip;

@@ -33,6 +33,7 @@ struct ScaledMmParams {
   int64_t residual_ld;
   int a_dtype, b_dtype, bias_dtype, out_dtype, rowwise, residual_dtype;
   const ScaledMmGather* gather = nullptr;  // sharded output (float8 operands on the tcgen05 kernel only)
+  int pair = 0;          // 1: the kernel of CTA pairs whatever the shape (variant 3 of the entry points)
 };
 
 int scaled_mm_plain(cudaStream_t stream, const ScaledMmParams& p);

@@ -10,6 +10,7 @@
 // float32 roundings, inside the bound the reference's test uses (tests/python/test_quant.py:124-128).
 #include <atomic>
 #include <cstdlib>
+#include <mutex>
 
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -17,6 +18,7 @@
 #include "../core/common.h"
 #include "../core/tensormap.h"
 #include "gemm_tc.cuh"
+#include "gemm_tc2.cuh"
 #include "numerics.cuh"
 #include "qmm8_skinny.cuh"
 #include "scaled_mm.h"
@@ -277,6 +279,7 @@ int scaled_mm_tc_tile(int device, cudaStream_t stream, const ScaledMmParams& p) 
   sh.k_elems_per_block = k_per_stage;
   sh.tiles_m = static_cast<int>(ceil_div(p.m, Cfg::kBM));
   sh.tiles_n = static_cast<int>(ceil_div(p.n, kBN));
+  sh.band = BM == 128 ? 16 : 12;
   typename ScaledEpilogue::Params ep{};
   ep.scale_a = p.scale_a;
   ep.scale_b = p.scale_b;
@@ -324,6 +327,81 @@ int scaled_mm_tc_tile(int device, cudaStream_t stream, const ScaledMmParams& p) 
   return launched(KIND == 0 ? "scaled_mm_tc" : "mm_tc", dim3(grid), dim3(Cfg::kThreads), Cfg::kSmemBytes, stream);
 }
 
+// The pair kernel (gemm_tc2.cuh): two CTAs per 256 x 256 tile. How many pairs the device holds at once is asked of the
+// runtime once per device (a pair needs both SMs of a TPC).
+template <int KIND, bool RES>
+int scaled_mm_tc_pair(int device, cudaStream_t stream, const ScaledMmParams& p) {
+  using ScaledEpilogue = ScaledEpilogueT<4, RES, false>;
+  using Cfg = GemmTc2Cfg<ScaledEpilogue::kSmemBytes>;
+  auto kernel = gemm_tc2_kernel<KIND, ScaledEpilogue>;
+  static std::mutex mutex;
+  static int max_pairs[64] = {};
+  const int es = static_cast<int>(dtype_size(p.a_dtype));
+  const CUtensorMapDataType dt = es == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+                                         : (p.a_dtype == TVB_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16);
+  const int k_per_stage = kGemmStageK / es;
+  CUtensorMap map_a, map_b;
+  if (make_tensor_map_2d(&map_a, p.a, dt, p.k, p.m, p.a_s0 * es, k_per_stage, Cfg::kRows, CU_TENSOR_MAP_SWIZZLE_128B) != 0) return -1;
+  if (make_tensor_map_2d(&map_b, p.b, dt, p.k, p.n, p.b_s1 * es, k_per_stage, Cfg::kRows, CU_TENSOR_MAP_SWIZZLE_128B) != 0) return -1;
+  GemmTcShape sh{};
+  sh.m = static_cast<int>(p.m);
+  sh.n = static_cast<int>(p.n);
+  sh.kblocks = static_cast<int>(ceil_div(p.k, k_per_stage));
+  sh.k_elems_per_block = k_per_stage;
+  sh.tiles_m = static_cast<int>(ceil_div(p.m, Cfg::kTile));
+  sh.tiles_n = static_cast<int>(ceil_div(p.n, Cfg::kTile));
+  static const int band_forced = [] { const char* v = std::getenv("TVB200_GEMM_BAND"); return v != nullptr ? std::atoi(v) : 0; }();
+  sh.band = band_forced > 0 ? band_forced : 16;
+  typename ScaledEpilogue::Params ep{};
+  ep.scale_a = p.scale_a;
+  ep.scale_b = p.scale_b;
+  ep.bias = p.bias;
+  ep.scale_result = p.scale_result;
+  ep.out = p.out;
+  ep.bias_dtype = p.bias_dtype;
+  ep.out_dtype = p.out_dtype;
+  ep.rowwise = p.rowwise;
+  ep.vector_ok = (reinterpret_cast<uintptr_t>(p.out) & 15u) == 0 && (p.n * dtype_size(p.out_dtype)) % 16 == 0;
+  ep.residual = p.residual;
+  ep.residual_ld = p.residual_ld;
+  ep.residual_dtype = p.residual_dtype;
+  ep.residual_vector_ok = p.residual != nullptr && (reinterpret_cast<uintptr_t>(p.residual) & 15u) == 0 &&
+                          (p.residual_ld * dtype_size(p.residual_dtype)) % 16 == 0;
+  int* status = nullptr;
+  if (status_word(device, &status) != 0) return -1;
+  const uint32_t fa = KIND == 0 ? (p.a_dtype == TVB_E4M3 ? 0 : 1) : (p.a_dtype == TVB_F16 ? 0 : 1);
+  const uint32_t fb = KIND == 0 ? (p.b_dtype == TVB_E4M3 ? 0 : 1) : (p.b_dtype == TVB_F16 ? 0 : 1);
+  const uint32_t idesc = ptx::tc_instr_desc(1, fa, fb, Cfg::kTile, Cfg::kTile);  // (one instruction covers the pair's 256 rows)
+  cudaLaunchConfig_t cfg{};
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.blockDim = dim3(Cfg::kThreads);
+  cfg.dynamicSmemBytes = Cfg::kSmemBytes;
+  cfg.stream = stream;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  int pairs_max = 0;
+  {
+    std::lock_guard<std::mutex> lock(mutex);
+    if (max_pairs[device & 63] == 0) {
+      TVB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+      cfg.gridDim = dim3(2 * static_cast<unsigned>(sm_count(device) / 2));
+      int clusters = 0;
+      TVB_CUDA(cudaOccupancyMaxActiveClusters(&clusters, kernel, &cfg));
+      TVB_REQUIRE(clusters >= 1, "scaled_mm_tc: the device holds no pair of CTAs of the tile kernel");
+      max_pairs[device & 63] = clusters;
+    }
+    pairs_max = max_pairs[device & 63];
+  }
+  const int pairs = static_cast<int>(std::min<int64_t>(pairs_max, static_cast<int64_t>(sh.tiles_m) * sh.tiles_n));
+  cfg.gridDim = dim3(2 * pairs);
+  TVB_CUDA(cudaLaunchKernelEx(&cfg, kernel, map_a, map_b, sh, idesc, ep, status));
+  return launched(KIND == 0 ? "scaled_mm_tc2" : "mm_tc2", dim3(2 * pairs), dim3(Cfg::kThreads), Cfg::kSmemBytes, stream);
+}
+
 // 256-row tiles keep the tensor pipe fed, but their read-back is not overlapped and there are half as many of them.
 // Measured against 128-row tiles (8192 x 8192 outputs): +14 % from 16 KB of k per row on, +6 % at 8 KB, -8 % at 2 KB. They
 // are taken when k is long enough and the tiles still fill the SMs as evenly.
@@ -340,6 +418,19 @@ int scaled_mm_tc_kind(int device, cudaStream_t stream, const ScaledMmParams& p) 
   bool big = p.m > 128 && waves_cost(256) < waves_cost(128);
   if (forced == 128) big = false;
   if (forced == 256) big = true;
+  // The pair kernel (two CTAs per 256 x 256 tile). Measured against the better of the single-CTA tilings, float8: +3 % at
+  // 8192^3, +8 % at 4096^3 and at 2048 x 14336 x 4096, +7 % at 16384 x 8192 x 2048, level at 1024 x 8192 x 8192; bfloat16:
+  // +3 to +10 % on the same shapes except those with 16 KB of k per row (8192^3, 1024 x 8192 x 8192: -5 %), which keep the
+  // single-CTA 256-row tiles.
+  static const int pair_forced = [] { const char* v = std::getenv("TVB200_GEMM_PAIR"); return v != nullptr ? std::atoi(v) : -1; }();
+  const bool pair_suits = p.m > 256 && p.n >= 512 && (KIND == 0 || k_bytes < 16384);
+  const bool pair = p.gather == nullptr && (p.pair != 0 || (pair_forced >= 0 ? pair_forced != 0 && p.m > 128 : pair_suits));
+  if (pair) {
+    if constexpr (KIND == 2) {
+      if (p.residual != nullptr) return scaled_mm_tc_pair<KIND, true>(device, stream, p);
+    }
+    if (p.residual == nullptr) return scaled_mm_tc_pair<KIND, false>(device, stream, p);
+  }
   if constexpr (KIND == 2) {  // (only aten::addmm passes a residual, and only 16-bit operands come with one)
     if (p.residual != nullptr)
       return big ? scaled_mm_tc_tile<KIND, 256, true>(device, stream, p) : scaled_mm_tc_tile<KIND, 128, true>(device, stream, p);
@@ -375,7 +466,7 @@ extern "C" int tvb_scaled_mm(int device, const void* a, int a_dtype, int64_t a_s
   const bool hw_formats = (a_dtype == TVB_E4M3 || a_dtype == TVB_E5M2) && (b_dtype == TVB_E4M3 || b_dtype == TVB_E5M2) &&
                           out_dtype != TVB_E4M3FNUZ && out_dtype != TVB_E5M2FNUZ;
   TVB_REQUIRE(m >= 0 && n >= 0 && k >= 0, "tvb_scaled_mm: negative size");
-  TVB_REQUIRE(variant >= 0 && variant <= 2, "tvb_scaled_mm: unknown kernel variant");
+  TVB_REQUIRE(variant >= 0 && variant <= 3, "tvb_scaled_mm: unknown kernel variant");
   if (m == 0 || n == 0) return 0;
   TVB_REQUIRE(out != nullptr && scale_a != nullptr && scale_b != nullptr && (k == 0 || (a != nullptr && b != nullptr)),
               "tvb_scaled_mm: NULL pointer");
@@ -387,10 +478,11 @@ extern "C" int tvb_scaled_mm(int device, const void* a, int a_dtype, int64_t a_s
   p.a_s0 = a_s0; p.a_s1 = a_s1; p.b_s0 = b_s0; p.b_s1 = b_s1;
   p.a_dtype = a_dtype; p.b_dtype = b_dtype; p.bias_dtype = bias_dtype; p.out_dtype = out_dtype; p.rowwise = rowwise;
   const bool usable = hw_formats && scaled_mm_tc_usable(p);
-  TVB_REQUIRE(variant != 2 || usable, "tvb_scaled_mm: the tcgen05 kernel needs e4m3fn / e5m2 K-major operands with 16-byte aligned rows");
+  TVB_REQUIRE(variant < 2 || usable, "tvb_scaled_mm: the tcgen05 kernels need e4m3fn / e5m2 K-major operands with 16-byte aligned rows");
+  p.pair = variant == 3;
   // small problems do not fill one wave of 128 x 256 tiles: the plain kernel's 64 x 64 tiles spread them wider
   const bool big = m * n >= int64_t(128) * 256 * 8 && k >= 128;
-  if (variant == 2 || (variant == 0 && usable && big)) return scaled_mm_tc(device, stream, p);
+  if (variant >= 2 || (variant == 0 && usable && big)) return scaled_mm_tc(device, stream, p);
   return scaled_mm_plain(stream, p);
 }
 
@@ -441,7 +533,7 @@ extern "C" int tvb_addmm(int device, const void* a, int dtype, int64_t a_s0, int
   TVB_REQUIRE(residual == nullptr || (is_float(residual_dtype) && residual_ld >= n),
               "tvb_addmm: the residual must be float32, float16 or bfloat16 with rows at least n apart");
   TVB_REQUIRE(m >= 0 && n >= 0 && k >= 0, "tvb_mm: negative size");
-  TVB_REQUIRE(variant >= 0 && variant <= 2, "tvb_mm: unknown kernel variant");
+  TVB_REQUIRE(variant >= 0 && variant <= 3, "tvb_mm: unknown kernel variant");
   if (m == 0 || n == 0) return 0;
   TVB_REQUIRE(out != nullptr && (k == 0 || (a != nullptr && b != nullptr)), "tvb_mm: NULL pointer");
   cudaStream_t stream;
@@ -453,9 +545,10 @@ extern "C" int tvb_addmm(int device, const void* a, int dtype, int64_t a_s0, int
   p.a_s0 = a_s0; p.a_s1 = a_s1; p.b_s0 = b_s0; p.b_s1 = b_s1;
   p.a_dtype = dtype; p.b_dtype = dtype; p.bias_dtype = bias_dtype; p.out_dtype = out_dtype;
   const bool usable = dtype != TVB_F32 && scaled_mm_tc_usable(p);
-  TVB_REQUIRE(variant != 2 || usable, "tvb_mm: the tcgen05 kernel needs 16-bit K-major operands with 16-byte aligned rows");
+  TVB_REQUIRE(variant < 2 || usable, "tvb_mm: the tcgen05 kernels need 16-bit K-major operands with 16-byte aligned rows");
+  p.pair = variant == 3;
   const bool big = m * n >= int64_t(128) * 256 * 8 && k >= 64;
-  if (variant == 2 || (variant == 0 && usable && big)) return scaled_mm_tc(device, stream, p);
+  if (variant >= 2 || (variant == 0 && usable && big)) return scaled_mm_tc(device, stream, p);
   return scaled_mm_plain(stream, p);
 }
 
