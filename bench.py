@@ -851,8 +851,14 @@ def main():
     shift = 16  # copy j holds the slice's rows rolled by 16 j: its output columns are rolled likewise
     w_sets = [torch.roll(w_slice, shift * j, 0).contiguous().to(dev) for j in range(nsets)]
     s_sets = [torch.roll(s_slice, shift * j, 0).contiguous().to(dev) for j in range(nsets)]
-    a_dev = {m: a_host[m].to(dev) for m in MS}
-    a_pinned = {m: a_host[m].pin_memory() for m in MS}
+    # the step's activations lie one after the other in one device buffer and in one page-locked host buffer (a caller
+    # that knows the step's products in advance lays them out so): one copy takes all of them up
+    a_all_pinned = torch.cat([a_host[m] for m in MS]).pin_memory()
+    a_all_dev = a_all_pinned.to(dev)
+    a_dev, row = {}, 0
+    for m in MS:
+        a_dev[m] = a_all_dev[row:row + m]
+        row += m
     mark("expected values on the CPU")
     expected = {m: int8_expected(a_host[m], w_full, s_full) for m in MS}
     mark("inputs ready")
@@ -871,13 +877,13 @@ def main():
         fused = {m: shard.GatheredOutputs(m, N_OUT, torch.bfloat16, channel) for m in MS}
     plain_out = {m: [torch.empty(m, N_OUT, dtype=torch.bfloat16, device=dev) for _ in range(2)] for m in MS} if world == 1 else None
 
-    def product(m, a, j, buf):
+    def product(m, a, j, buf, pos=None):
         if world == 1:
             return torch._weight_int8pack_mm(a, w_sets[j], s_sets[j])
         if fused is not None:
             # every rank's kernel stores its column slice into every rank's [m, N] buffer (peer stores over NVLink); the
             # three products of a step have nothing to do with each other: none waits for the ones before it in the step
-            return fused[m].weight_int8pack_mm(a, w_sets[j], s_sets[j], buf=buf, independent=MS.index(m))
+            return fused[m].weight_int8pack_mm(a, w_sets[j], s_sets[j], buf=buf, independent=MS.index(m) if pos is None else pos)
         # every rank's column slice, then the NCCL all-gather into [m, N] (queued on the backend's stream)
         return shard.weight_int8pack_mm(a, w_sets[j], s_sets[j])
 
@@ -1014,13 +1020,24 @@ def main():
 
     def e2e_body(g):
         # every product's A goes up from page-locked memory (into the buffers the step reads) and its C comes back into
-        # page-locked memory; copies and products are queued back to back
-        for m in MS:
-            a_dev[m].copy_(a_pinned[m], non_blocking=True)
-        outs = step_fn(mode, g)
-        for m, c in zip(MS, outs):
-            out_pinned[m].copy_(c, non_blocking=True)
-        return outs
+        # page-locked memory
+        a_all_dev.copy_(a_all_pinned, non_blocking=True)
+        if mode == "chain":
+            outs = step_fn(mode, g)
+            for m, c in zip(MS, outs):
+                out_pinned[m].copy_(c, non_blocking=True)
+            return outs
+        # one launch per product: each result leaves on the runtime's second stream as soon as it is complete, under the
+        # products that follow (largest first, so that the copy left over at the end of the step is the smallest)
+        sets = dict(zip(MS, step_sets(g)))
+        outs = {}
+        for pos, m in enumerate(sorted(MS, reverse=True)):
+            c = product(m, a_dev[m], sets[m], g % 2, pos)
+            if channel is not None:
+                channel.wait()  # every rank's columns of this product have arrived
+            tv.copy_to_host_overlapped(out_pinned[m], c)
+            outs[m] = c
+        return [outs[m] for m in MS]
 
     e2e_steps = max(5, min(args.steps, 30))
 
@@ -1051,7 +1068,7 @@ def main():
             e2e_graphs[i % ngraphs].replay()
             tv.synchronize(local_rank)
 
-        e2e_s, e2e_how = time_e2e(step_e2e_graph), "CUDA graph replay of the step's copies and products, then a stream synchronize"
+        e2e_s, e2e_how = time_e2e(step_e2e_graph), "CUDA graph replay of the step's copies and products (results copied out beside the following products), then a stream synchronize"
     for m, j in zip(MS, step_sets(last_g)):  # what came back to the host from the last end-to-end step
         check(m, out_pinned[m], j, "end-to-end outputs on the host")
 

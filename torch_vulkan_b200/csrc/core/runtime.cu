@@ -44,6 +44,7 @@ struct DeviceState {
   void* ws[4] = {nullptr, nullptr, nullptr, nullptr};
   uint64_t ws_size[4] = {0, 0, 0, 0};
   int* status = nullptr;
+  int* status_host = nullptr;  // page-locked copy of the status word, filled by a copy queued ahead of each wait
   // the copy-out lane of tvb_memcpy_d2h_overlapped: a second stream, the event that forks it off the main stream and
   // the event that the main stream waits for when the lane is joined
   cudaStream_t copy_stream = nullptr;
@@ -184,6 +185,8 @@ int status_word(int device, int** out) {
     TVB_CUDA(cudaSetDevice(device));
     TVB_CUDA(cudaMalloc(&d->status, 256));
     TVB_CUDA(cudaMemsetAsync(d->status, 0, 256, d->stream));
+    TVB_CUDA(cudaHostAlloc(reinterpret_cast<void**>(&d->status_host), 256, cudaHostAllocDefault));
+    *d->status_host = 0;
   }
   *out = d->status;
   return 0;
@@ -323,19 +326,22 @@ int tvb_synchronize(int device) {
   cudaStream_t s;
   if (enter(device, &s) != 0) return -1;
   if (tvb_join_copies(device) != 0) return -1;
-  TVB_CUDA(cudaStreamSynchronize(s));
   int* status = nullptr;
+  int* status_host = nullptr;
   void* counters = nullptr;
   uint64_t counter_bytes = 0;
   {
     std::lock_guard<std::mutex> lock(g_mutex);
     status = g_devices[device].status;
+    status_host = g_devices[device].status_host;
     counters = g_devices[device].ws[0];
     counter_bytes = std::min<uint64_t>(g_devices[device].ws_size[0], 65536);
   }
+  // the status word travels behind the queued work, so the wait below is the only round trip to the device
+  if (status != nullptr) TVB_CUDA(cudaMemcpyAsync(status_host, status, sizeof(int), cudaMemcpyDeviceToHost, s));
+  TVB_CUDA(cudaStreamSynchronize(s));
   if (status != nullptr) {
-    int code = 0;
-    TVB_CUDA(cudaMemcpy(&code, status, sizeof(int), cudaMemcpyDeviceToHost));
+    const int code = *static_cast<volatile int*>(status_host);
     if (code != 0) {
       cudaMemset(status, 0, sizeof(int));
       // The kernel that gave up left the decode kernels' tile and CTA counters (the head of workspace slot 0) wherever it
@@ -428,7 +434,9 @@ void tvb_shutdown(void) {
       d.ws_size[w] = 0;
     }
     if (d.status != nullptr) cudaFree(d.status);
+    if (d.status_host != nullptr) cudaFreeHost(d.status_host);
     d.status = nullptr;
+    d.status_host = nullptr;
     if (d.copy_stream != nullptr) {
       cudaStreamSynchronize(d.copy_stream);
       cudaStreamDestroy(d.copy_stream);
