@@ -190,6 +190,30 @@ TVB_API int tvb_qmm8_gather(int device, const void* a, int dtype, int64_t a_sm, 
                             void* const* c_ranks, uint32_t* const* flag_ranks, int world, int rank,
                             uint32_t* seq_counter, int independent, int64_t m, int64_t n_local, int64_t k);
 TVB_API int tvb_wait_flags(int device, const uint32_t* flags, int world, const uint32_t* seq_counter);
+
+/* Several decode products of one shape in ONE launch of the decode kernel (no counterpart in the reference, which
+ * dispatches once per product, crates/pyvk/csrc/quant.cpp:86-117): products that do not depend on each other, such as
+ * the requests of one decoding step against different weights, or q, k, v of one layer. Product g is
+ * C_g[m_g, n] = A_g[m_g, k] . B_g[n, k]^T * scales_g[n] with 1 <= m_g <= 16; n, k and the dtype (TVB_F16 / TVB_BF16)
+ * are shared; k % 128 == 0, rows of A and B 16-byte aligned. The kernel numbers its tiles through all products and cuts
+ * the whole list into one range per SM, so the launch costs one start and one end whatever `count` (1 to 4) is. Results
+ * are those of tvb_qmm8 within one rounding of the float32 sums (the same products, summed over differently cut ranges of
+ * k); a launch repeats its own results bit for bit.
+ * c_ranks: tvb_qmm8_group reads c_ranks[0], the contiguous [m, n] output. tvb_qmm8_group_gather is the sharded form
+ * (see tvb_qmm8_gather): n_local rows of every B on this rank, c_ranks = every rank's [m, n_local * world] buffer for that
+ * product; the launch takes `count` consecutive product numbers on the channel and waits, before it reads any A, for
+ * all earlier products but the latest `independent` (independent + count <= 4). */
+typedef struct TvbGroupItem {
+  const void* a;
+  int64_t a_sm;
+  const int8_t* b;
+  const void* scales;
+  void* const* c_ranks;
+  int64_t m;
+} TvbGroupItem;
+TVB_API int tvb_qmm8_group(int device, int dtype, const TvbGroupItem* items, int count, int64_t n, int64_t k);
+TVB_API int tvb_qmm8_group_gather(int device, int dtype, const TvbGroupItem* items, int count, uint32_t* const* flag_ranks, int world,
+                          int rank, uint32_t* seq_counter, int independent, int64_t n_local, int64_t k);
 /* How long the kernels above wait for peers before they give up (default about 2000 ms). Process-wide; applies to
  * kernels launched (or captured) afterwards. 1 <= ms <= 60000. */
 TVB_API int tvb_set_wait_limit_ms(int ms);

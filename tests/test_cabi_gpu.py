@@ -435,6 +435,94 @@ def test_gather_world1_counts_and_chains(abi):
     assert ((c2.cpu().float() - want2.float()).abs() <= tol2).all()
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("ms,k,n", [((1, 4, 16), 1024, 4096), ((3, 8), 512, 1000), ((16, 16, 16, 16), 256, 136), ((2,), 8192, 12288),
+                                    ((1, 4, 16), 4096, 18432)])
+def test_group_products_in_one_launch(abi, dtype, ms, k, n):
+    """tvb_qmm8_group: several products of one shape in one launch of the decode kernel. Every product within the reference's
+    bound of the CPU result and of tvb_qmm8's; a second launch repeats the first bit for bit."""
+    import ctypes
+
+    lib = abi.lib()
+    cases = [C.config_int8(m, k, n, dtype, seed=40 + i) for i, m in enumerate(ms)]
+    devs = [(dev(a), dev(b), dev(s)) for a, b, s in cases]
+    outs = [torch.zeros(m, n, dtype=dtype, device="cuda") for m in ms]
+    items = (abi.TvbGroupItem * len(ms))()
+    keep = []
+    for i, ((da, db, ds), out) in enumerate(zip(devs, outs)):
+        ptrs = (ctypes.c_void_p * 1)(out.data_ptr())
+        keep.append(ptrs)
+        items[i].a, items[i].a_sm, items[i].b, items[i].scales = da.data_ptr(), da.stride(0), db.data_ptr(), ds.data_ptr()
+        items[i].c_ranks, items[i].m = ctypes.cast(ptrs, ctypes.POINTER(ctypes.c_void_p)), ms[i]
+    torch.cuda.synchronize()
+    code = abi.BF16 if dtype == torch.bfloat16 else abi.F16
+    abi.check(lib.tvb_qmm8_group(0, code, items, len(ms), n, k))
+    abi.synchronize()
+    first = [o.clone() for o in outs]
+    for o in outs:
+        o.zero_()
+    torch.cuda.synchronize()
+    abi.check(lib.tvb_qmm8_group(0, code, items, len(ms), n, k))
+    abi.synchronize()
+    eps = torch.finfo(dtype).eps
+    for (a, b, s), (da, db, ds), out, f in zip(cases, devs, outs, first):
+        want, tol = C.int8_want(a, b, s)
+        assert ((out.cpu().float() - want.float()).abs() <= tol).all()
+        assert torch.equal(out, f)
+        single = abi.qmm8(da, db, ds)
+        abi.synchronize()
+        # (one step of the output type where the sum is not small against its terms; float32 rounding of the terms otherwise)
+        assert ((out.float() - single.float()).abs().cpu() <= eps * single.float().abs().cpu() + tol).all()
+    # what the entry point refuses
+    items[0].m = 17
+    assert lib.tvb_qmm8_group(0, code, items, len(ms), n, k) == -1 and b"m <= 16" in lib.tvb_last_error()
+    items[0].m = ms[0]
+    assert lib.tvb_qmm8_group(0, code, items, 5, n, k) == -1
+
+
+def test_group_gather_world1_counts(abi):
+    """tvb_qmm8_group_gather with a world of one rank: three products land in the rank's own buffers, take three product
+    numbers on the channel (every CTA reports its share of each), and a following sharded product waits for all three."""
+    import ctypes
+
+    lib = abi.lib()
+    ms, k, n = (1, 4, 16), 1024, 2048
+    cases = [C.config_int8(m, k, n, torch.bfloat16, seed=60 + i) for i, m in enumerate(ms)]
+    devs = [(dev(a), dev(b), dev(s)) for a, b, s in cases]
+    outs = [torch.zeros(m, n, dtype=torch.bfloat16, device="cuda") for m in ms]
+    state = torch.zeros(64, dtype=torch.int32, device="cuda")
+    items = (abi.TvbGroupItem * 3)()
+    keep = []
+    for i, ((da, db, ds), out) in enumerate(zip(devs, outs)):
+        ptrs = (ctypes.c_void_p * 1)(out.data_ptr())
+        keep.append(ptrs)
+        items[i].a, items[i].a_sm, items[i].b, items[i].scales = da.data_ptr(), da.stride(0), db.data_ptr(), ds.data_ptr()
+        items[i].c_ranks, items[i].m = ctypes.cast(ptrs, ctypes.POINTER(ctypes.c_void_p)), ms[i]
+    torch.cuda.synchronize()
+    flags = (ctypes.c_void_p * 1)(state.data_ptr())
+    seq = ctypes.c_void_p(state.data_ptr() + 128)
+    for _ in range(2):  # two launches: products 0-2, then 3-5 (slots 3, 0, 1), the second waiting for the first
+        abi.check(lib.tvb_qmm8_group_gather(0, abi.BF16, items, 3, flags, 1, 0, seq, 0, n, k))
+    # a single sharded product after them, taking the last group's m = 16 output... as its A would need k == n; use its own A
+    a4, b4, s4 = C.config_int8(4, k, 256, torch.bfloat16, seed=70)
+    c4 = torch.zeros(4, 256, dtype=torch.bfloat16, device="cuda")
+    d4 = (dev(a4), dev(b4), dev(s4))
+    torch.cuda.synchronize()
+    abi.check(lib.tvb_qmm8_gather(0, d4[0].data_ptr(), abi.BF16, d4[0].stride(0), d4[1].data_ptr(), d4[2].data_ptr(),
+                                  (ctypes.c_void_p * 1)(c4.data_ptr()), flags, 1, 0, seq, 0, 4, 256, k))
+    abi.check(lib.tvb_wait_flags(0, state.data_ptr(), 1, seq))
+    abi.synchronize()
+    st = state.cpu()
+    # products 0..6: slot q % 4 holds 1024 per product reported there
+    assert [st[8 * slot].item() for slot in range(4)] == [2048, 2048, 2048, 1024] and st[32].item() == 7
+    for (a, b, s), out in zip(cases, outs):
+        want, tol = C.int8_want(a, b, s)
+        assert ((out.cpu().float() - want.float()).abs() <= tol).all()
+    want, tol = C.int8_want(a4, b4, s4)
+    assert ((c4.cpu().float() - want.float()).abs() <= tol).all()
+    assert lib.tvb_qmm8_group_gather(0, abi.BF16, items, 3, flags, 1, 0, seq, 2, n, k) == -1  # independent + count > 4
+
+
 def test_wait_for_peers_runs_out_and_is_reported(abi):
     """A wait for a peer that never delivers gives up after the configured limit, without a fault: the host reads status 5
     from tvb_synchronize, the runtime clears the status and the decode kernels' counters, and the next product is right."""

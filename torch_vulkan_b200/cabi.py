@@ -27,6 +27,10 @@ class TvbChainItem(ctypes.Structure):
                 ("n_local", _i64), ("k", _i64), ("independent", _c.c_int32), ("reserved", _c.c_int32)]
 
 
+class TvbGroupItem(ctypes.Structure):
+    _fields_ = [("a", _vp), ("a_sm", _i64), ("b", _vp), ("scales", _vp), ("c_ranks", _c.POINTER(_vp)), ("m", _i64)]
+
+
 # name -> (restype, argtypes): every entry point include/tvb200.h declares
 SIGNATURES = {
     "tvb_last_error": (_c.c_char_p, []),
@@ -66,6 +70,8 @@ SIGNATURES = {
     "tvb_qmm8_gather": (_i, [_i, _vp, _i, _i64, _vp, _vp, _c.POINTER(_vp), _c.POINTER(_vp), _i, _i, _vp, _i, _i64, _i64, _i64]),
     "tvb_wait_flags": (_i, [_i, _vp, _i, _vp]),
     "tvb_set_wait_limit_ms": (_i, [_i]),
+    "tvb_qmm8_group": (_i, [_i, _i, _c.POINTER(TvbGroupItem), _i, _i64, _i64]),
+    "tvb_qmm8_group_gather": (_i, [_i, _i, _c.POINTER(TvbGroupItem), _i, _c.POINTER(_vp), _i, _i, _vp, _i, _i64, _i64]),
     "tvb_qmm8_chain_create": (_i, [_i, _i, _c.POINTER(TvbChainItem), _i, _c.POINTER(_vp), _i, _i, _vp, _i, _c.POINTER(_vp)]),
     "tvb_qmm8_chain_run": (_i, [_i, _vp]),
     "tvb_qmm8_chain_destroy": (None, [_vp]),

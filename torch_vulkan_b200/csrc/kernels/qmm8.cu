@@ -187,6 +187,22 @@ struct SkinnyParams {
   const void* residual;  // [m, c_ld] of A's dtype, laid out like the output, added after the bias (rounded again), or NULL
 };
 
+// Several products of one shape in one launch (tvb_qmm8_group): product g has its own activations, weights, scales and
+// outputs; n, k and the tiling are shared. The kernel's tiles are numbered through all products (tile = g * tiles + its
+// tile within product g), so the list of (tile, chunk) units, cut into one contiguous range per CTA, runs across them: a
+// CTA shares at most the two tiles at its range's ends with other CTAs however many products the launch holds.
+constexpr int kMaxGroup = 4;
+struct SkinnyGroup {
+  CUtensorMap map_w[kMaxGroup], map_a[kMaxGroup];
+  const void* scales[kMaxGroup];
+  void* c[kMaxGroup][kMaxRanks];
+  int m[kMaxGroup];
+  int count;
+};
+struct NoGroup {};
+template <bool GROUP> struct GroupArg { using type = NoGroup; };
+template <> struct GroupArg<true> { using type = SkinnyGroup; };
+
 // What a Linear does after the product, in the thread that holds the finished value: + bias[col], then + residual[token,
 // col], each sum rounded to the output type as the separate kernels would round it (so the fused result is bit for bit
 // that of product, add, add).
@@ -201,11 +217,44 @@ __device__ __forceinline__ uint16_t skinny_epilogue(const SkinnyParams& p, uint1
 
 // ADDS: the instantiation whose epilogue also adds a bias and a residual (tvb_qmm8_linear); the plain product carries no
 // code for them (with it in one kernel, behind a test of the two pointers, every launch was 0.65 us slower).
-template <int DT, int NT, int RW, int NWARPS, bool ADDS = false>
+template <int DT, int NT, int RW, int NWARPS, bool ADDS = false, bool GROUP = false>
 __global__ void __launch_bounds__((NWARPS + 2) * 32, 1)
     qmm8_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
-                       const SkinnyParams p) {
+                       const SkinnyParams p, const __grid_constant__ typename GroupArg<GROUP>::type group) {
   using Cfg = SkinnyCfg<NT, RW, NWARPS>;
+  static_assert(!(ADDS && GROUP), "grouped products carry no adds");
+  // product g of a grouped launch (g = 0 otherwise): which product a tile belongs to, and that product's operands
+  auto split = [&](int tile, int& g, int& lt) {
+    if constexpr (GROUP) {
+      g = tile / p.tiles;
+      lt = tile - g * p.tiles;
+    } else {
+      g = 0;
+      lt = tile;
+    }
+  };
+  auto weights_of = [&](int g) -> const CUtensorMap* {
+    if constexpr (GROUP) return &group.map_w[g];
+    else return &map_w;
+  };
+  auto tokens_of = [&](int g) -> const CUtensorMap* {
+    if constexpr (GROUP) return &group.map_a[g];
+    else return &map_a;
+  };
+  auto scales_of = [&](int g) -> const void* {
+    if constexpr (GROUP) return group.scales[g];
+    else return p.scales;
+  };
+  auto rows_of = [&](int g) -> int {
+    if constexpr (GROUP) return group.m[g];
+    else return p.m;
+  };
+  auto out_of = [&](int g, int r) -> void* {
+    if constexpr (GROUP) return group.c[g][r];
+    else return p.c[r];
+  };
+  int products = 1;
+  if constexpr (GROUP) products = group.count;
   extern __shared__ uint8_t smem_raw[];
   // stages need 1024-byte alignment for the 128-byte swizzle pattern
   uint32_t base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -233,7 +282,7 @@ __global__ void __launch_bounds__((NWARPS + 2) * 32, 1)
   __syncthreads();
   ptx::grid_launch_dependents();  // the next kernel of the stream may take SMs as this one's CTAs retire
 
-  const long long units = static_cast<long long>(p.tiles) * p.chunks;
+  const long long units = static_cast<long long>(p.tiles) * products * p.chunks;
   const long long grid = gridDim.x;
   const bool small = (units + 1) * (grid + 1) < (1ll << 31);
   const long long u0 = range_start(blockIdx.x, units, grid, small), u1 = range_start(blockIdx.x + 1, units, grid, small);
@@ -245,16 +294,20 @@ __global__ void __launch_bounds__((NWARPS + 2) * 32, 1)
     const long long mine = u1 - u0;
     const long long ahead = mine < Cfg::kStages ? mine : Cfg::kStages;
     if (lane == 0) {
-      ptx::prefetch_tensormap(&map_w);
-      ptx::prefetch_tensormap(&map_a);
+      for (int g = 0; g < products; g++) {
+        ptx::prefetch_tensormap(weights_of(g));
+        ptx::prefetch_tensormap(tokens_of(g));
+      }
       // The weights do not depend on earlier kernels of the stream: start streaming them at once, one ring's worth.
       // A (which an earlier kernel may have produced) is fetched only after the stream's earlier work has completed.
       for (long long j = 0; j < ahead; j++) {
         const long long u = u0 + j;
         const int tile = unit_tile(u, p.chunks, small), chunk = static_cast<int>(u - static_cast<long long>(tile) * p.chunks);
+        int g, lt;
+        split(tile, g, lt);
         const uint32_t dst = base + static_cast<int>(j) * Cfg::kStageBytes;
         ptx::mbar_expect_tx(full0 + 8 * static_cast<int>(j), Cfg::kStageBytes);
-        ptx::tma_load_2d_hint(dst, &map_w, chunk * kChunkK, tile * Cfg::kRowsPerTile, full0 + 8 * static_cast<int>(j), stream_policy);
+        ptx::tma_load_2d_hint(dst, weights_of(g), chunk * kChunkK, lt * Cfg::kRowsPerTile, full0 + 8 * static_cast<int>(j), stream_policy);
       }
     }
     if (p.done != nullptr) {
@@ -285,19 +338,27 @@ __global__ void __launch_bounds__((NWARPS + 2) * 32, 1)
     if (lane == 0) {
       ptx::grid_dependency_wait();
       for (long long j = 0; j < ahead; j++) {
-        const int chunk = static_cast<int>(u0 + j - static_cast<long long>(unit_tile(u0 + j, p.chunks, small)) * p.chunks);
+        const int tile_j = unit_tile(u0 + j, p.chunks, small);
+        const int chunk = static_cast<int>(u0 + j - static_cast<long long>(tile_j) * p.chunks);
+        int g, lt;
+        split(tile_j, g, lt);
         const uint32_t dst = base + static_cast<int>(j) * Cfg::kStageBytes + Cfg::kWeightBytes;
-        ptx::tma_load_2d_hint(dst, &map_a, chunk * kChunkK, p.m0, full0 + 8 * static_cast<int>(j), keep_policy);
-        ptx::tma_load_2d_hint(dst + Cfg::kTokenBoxBytes, &map_a, chunk * kChunkK + 64, p.m0, full0 + 8 * static_cast<int>(j), keep_policy);
+        ptx::tma_load_2d_hint(dst, tokens_of(g), chunk * kChunkK, p.m0, full0 + 8 * static_cast<int>(j), keep_policy);
+        ptx::tma_load_2d_hint(dst + Cfg::kTokenBoxBytes, tokens_of(g), chunk * kChunkK + 64, p.m0, full0 + 8 * static_cast<int>(j), keep_policy);
       }
       long long it = ahead;
       bool ok = true;
-      int tile = unit_tile(u0 + ahead, p.chunks, small);
-      int chunk = static_cast<int>(u0 + ahead - static_cast<long long>(tile) * p.chunks);
+      int tile, g;
+      split(unit_tile(u0 + ahead, p.chunks, small), g, tile);  // (`tile` counts within product g from here on)
+      int chunk = static_cast<int>(u0 + ahead - static_cast<long long>(unit_tile(u0 + ahead, p.chunks, small)) * p.chunks);
       for (long long u = u0 + ahead; u < u1 && ok; u++, it++, chunk++) {
         if (chunk == p.chunks) {
           chunk = 0;
           tile++;
+          if (GROUP && tile == p.tiles) {
+            tile = 0;
+            g++;
+          }
         }
         int s = static_cast<int>(it % Cfg::kStages);
         uint32_t ph = static_cast<uint32_t>((it / Cfg::kStages) & 1);
@@ -305,9 +366,9 @@ __global__ void __launch_bounds__((NWARPS + 2) * 32, 1)
         if (!ok) break;
         uint32_t dst = base + s * Cfg::kStageBytes;
         ptx::mbar_expect_tx(full0 + 8 * s, Cfg::kStageBytes);
-        ptx::tma_load_2d_hint(dst, &map_w, chunk * kChunkK, tile * Cfg::kRowsPerTile, full0 + 8 * s, stream_policy);
-        ptx::tma_load_2d_hint(dst + Cfg::kWeightBytes, &map_a, chunk * kChunkK, p.m0, full0 + 8 * s, keep_policy);
-        ptx::tma_load_2d_hint(dst + Cfg::kWeightBytes + Cfg::kTokenBoxBytes, &map_a, chunk * kChunkK + 64, p.m0,
+        ptx::tma_load_2d_hint(dst, weights_of(g), chunk * kChunkK, tile * Cfg::kRowsPerTile, full0 + 8 * s, stream_policy);
+        ptx::tma_load_2d_hint(dst + Cfg::kWeightBytes, tokens_of(g), chunk * kChunkK, p.m0, full0 + 8 * s, keep_policy);
+        ptx::tma_load_2d_hint(dst + Cfg::kWeightBytes + Cfg::kTokenBoxBytes, tokens_of(g), chunk * kChunkK + 64, p.m0,
                               full0 + 8 * s, keep_policy);
       }
       // Leave no copy in flight behind: every stage that was armed has landed before the CTA ends.
@@ -345,6 +406,8 @@ __global__ void __launch_bounds__((NWARPS + 2) * 32, 1)
       last = __shfl_sync(0xffffffffu, last, 0);
       if (last) {
         __threadfence();
+        int product, lt;
+        split(tile, product, lt);
         const int g = lane >> 2, t = lane & 3, rg = (g >> 1) | ((g & 1) << 2);
         for (int w = 0; w < NWARPS; w++)  // this warp plays every consumer warp's part in turn
 #pragma unroll
@@ -362,18 +425,18 @@ __global__ void __launch_bounds__((NWARPS + 2) * 32, 1)
               const float vals[4] = {sum.x, sum.y, sum.z, sum.w};
 #pragma unroll
               for (int half = 0; half < 2; half++) {
-                const int col = tile * Cfg::kRowsPerTile + (w * RW + rb) * 16 + rg + 8 * half;
+                const int col = lt * Cfg::kRowsPerTile + (w * RW + rb) * 16 + rg + 8 * half;
                 if (col >= p.n) continue;
-                const float scale = load_float<DT>(p.scales, col);
+                const float scale = load_float<DT>(scales_of(product), col);
 #pragma unroll
                 for (int i = 0; i < 2; i++) {
                   const int token = p.m0 + nt * 8 + 2 * t + i;
-                  if (token >= p.m) continue;
+                  if (token >= rows_of(product)) continue;
                   const float v = vals[2 * half + i] * scale;
                   uint16_t bits = DT == TVB_BF16 ? f32_to_bf16_bits(v) : f32_to_f16_bits(v);
                   if constexpr (ADDS) bits = skinny_epilogue<DT>(p, bits, token, col);
                   const int64_t off = static_cast<int64_t>(token) * p.c_ld + p.c_col0 + col;
-                  for (int r = 0; r < p.nranks; r++) static_cast<uint16_t*>(p.c[r])[off] = bits;
+                  for (int r = 0; r < p.nranks; r++) static_cast<uint16_t*>(out_of(product, r))[off] = bits;
                 }
               }
             }
@@ -409,6 +472,9 @@ __global__ void __launch_bounds__((NWARPS + 2) * 32, 1)
     // before its segment ends, it sees that all the others have already arrived, it is certain to finish the tile: it
     // then fetches their sums while its last chunks are in flight and skips the exchange through scratch altogether.
     const bool may_be_early = !whole_tile && cta_first == static_cast<int>(blockIdx.x) && c1 - c0 >= 3;
+    int product, lt;  // the product the tile belongs to and the tile's index within it
+    split(tile, product, lt);
+    const int m_rows = rows_of(product);
     bool early = false;
     int peeked = 0;
     float pre[RW][NT][4];
@@ -426,8 +492,8 @@ __global__ void __launch_bounds__((NWARPS + 2) * 32, 1)
     for (int rb = 0; rb < RW; rb++)
 #pragma unroll
       for (int half = 0; half < 2; half++) {
-        const int col = tile * Cfg::kRowsPerTile + (warp * RW + rb) * 16 + rg + 8 * half;
-        scale_pre[rb][half] = col < p.n ? load_float<DT>(p.scales, col) : 0.0f;
+        const int col = lt * Cfg::kRowsPerTile + (warp * RW + rb) * 16 + rg + 8 * half;
+        scale_pre[rb][half] = col < p.n ? load_float<DT>(scales_of(product), col) : 0.0f;
       }
     float bias_pre[ADDS ? RW : 1][2];
     uint32_t residual_pre[ADDS ? RW : 1][NT][2];  // [..][half]: the values of tokens 2t (low 16 bits) and 2t + 1
@@ -447,7 +513,7 @@ __global__ void __launch_bounds__((NWARPS + 2) * 32, 1)
       for (int rb = 0; rb < RW; rb++)
 #pragma unroll
         for (int half = 0; half < 2; half++) {
-          const int col = tile * Cfg::kRowsPerTile + (warp * RW + rb) * 16 + rg + 8 * half;
+          const int col = lt * Cfg::kRowsPerTile + (warp * RW + rb) * 16 + rg + 8 * half;
           bias_pre[rb][half] = p.bias != nullptr && col < p.n ? load_float<DT>(p.bias, col) : 0.0f;
 #pragma unroll
           for (int nt = 0; nt < NT; nt++) {
@@ -624,7 +690,6 @@ __global__ void __launch_bounds__((NWARPS + 2) * 32, 1)
 #pragma unroll
         for (int half = 0; half < 2; half++) {
           const int lcol = lrow0 + 8 * half;                       // column within the tile (weight row = output column)
-          const int col = tile * Cfg::kRowsPerTile + lcol;
           const float scale = scale_pre[rb][half];
 #pragma unroll
           for (int nt = 0; nt < NT; nt++)
@@ -642,17 +707,17 @@ __global__ void __launch_bounds__((NWARPS + 2) * 32, 1)
         }
       }
       ptx::named_bar_sync(1, NWARPS * 32);
-      const int col_base = tile * Cfg::kRowsPerTile;
+      const int col_base = lt * Cfg::kRowsPerTile;
       const bool vec = (p.c_ld % 8 == 0) && (p.c_col0 % 8 == 0);
       for (int v = threadIdx.x; v < Cfg::kTokens * (Cfg::kRowsPerTile / 8); v += NWARPS * 32) {
         const int tok = v / (Cfg::kRowsPerTile / 8), chunk = v % (Cfg::kRowsPerTile / 8);
         const int token = p.m0 + tok, col = col_base + chunk * 8;
-        if (token >= p.m || col >= p.n) continue;
+        if (token >= m_rows || col >= p.n) continue;
         const uint4 val = *reinterpret_cast<const uint4*>(out_tile + tok * Cfg::kRowsPerTile + chunk * 8);
         const int64_t off = static_cast<int64_t>(token) * p.c_ld + p.c_col0 + col;
         if (vec && col + 8 <= p.n) {
           for (int r = 0; r < p.nranks; r++) {
-            uint16_t* dst = static_cast<uint16_t*>(p.c[r]) + off;
+            uint16_t* dst = static_cast<uint16_t*>(out_of(product, r)) + off;
             if ((reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
               *reinterpret_cast<uint4*>(dst) = val;
             } else {
@@ -663,7 +728,7 @@ __global__ void __launch_bounds__((NWARPS + 2) * 32, 1)
         } else {
           const uint16_t* e = reinterpret_cast<const uint16_t*>(&val);
           for (int r = 0; r < p.nranks; r++)
-            for (int j = 0; j < 8 && col + j < p.n; j++) (static_cast<uint16_t*>(p.c[r]) + off)[j] = e[j];
+            for (int j = 0; j < 8 && col + j < p.n; j++) (static_cast<uint16_t*>(out_of(product, r)) + off)[j] = e[j];
         }
       }
       ptx::named_bar_sync(1, NWARPS * 32);  // (the staging tile is free again)
@@ -678,11 +743,14 @@ __global__ void __launch_bounds__((NWARPS + 2) * 32, 1)
     if (threadIdx.x == 0) {
       if (p.nranks == 1) __threadfence();
       else __threadfence_system();
-      arrive_publish(p.flags, p.nranks, p.rank, *reinterpret_cast<const volatile uint32_t*>(p.seq), arrive_share());
-      // the last CTA to get here counts the product (the next kernel of the stream reads the count after this one has ended)
+      // (a grouped launch holds `products` products of the channel: the CTA reports its share of each, whichever tiles
+      // it had, since the counters say "every CTA of the launch is past its stores")
+      const uint32_t first = *reinterpret_cast<const volatile uint32_t*>(p.seq);
+      for (int q = 0; q < products; q++) arrive_publish(p.flags, p.nranks, p.rank, first + static_cast<uint32_t>(q), arrive_share());
+      // the last CTA to get here counts the products (the next kernel of the stream reads the count after this one has ended)
       if (atomicAdd(p.done, 1) == static_cast<int>(gridDim.x) - 1) {
         atomicExch(p.done, 0);
-        *reinterpret_cast<volatile uint32_t*>(p.seq) = *reinterpret_cast<const volatile uint32_t*>(p.seq) + 1u;
+        *reinterpret_cast<volatile uint32_t*>(p.seq) = first + static_cast<uint32_t>(products);
       }
     }
   }
@@ -788,7 +856,7 @@ int launch_skinny_cfg(int device, cudaStream_t stream, const void* a, int64_t a_
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  TVB_CUDA(cudaLaunchKernelEx(&cfg, kernel, map_w, map_a, p));
+  TVB_CUDA(cudaLaunchKernelEx(&cfg, kernel, map_w, map_a, p, NoGroup{}));
   return launched("qmm8_skinny", dim3(grid), dim3(Cfg::kThreads), Cfg::kSmemBytes, stream);
 }
 
@@ -811,6 +879,105 @@ int launch_skinny(int device, cudaStream_t stream, const void* a, int64_t a_sm, 
     if (small) return launch_skinny_cfg<DT, NT, 1, 8>(device, stream, a, a_sm, b, scales, c, m, n, k, m0, gather);
     return launch_skinny_cfg<DT, NT, 2, 8>(device, stream, a, a_sm, b, scales, c, m, n, k, m0, gather);
   }
+}
+
+// One product of a grouped launch as the host hands it over.
+struct GroupItem {
+  const void* a;
+  int64_t a_sm;
+  const int8_t* b;
+  const void* scales;
+  void* c[kMaxRanks];
+  int m;
+};
+
+// Several products of one shape (n, k) in one launch of the decode kernel, at most 16 rows of A each. `gather` as in
+// launch_skinny_cfg (its c[] is not used: every item brings its own outputs); its products take consecutive numbers on
+// the channel.
+template <int DT, int NT, int RW>
+int launch_skinny_group(int device, cudaStream_t stream, const GroupItem* items, int count, int n, int k, const GatherTargets* gather) {
+  constexpr int NWARPS = 8;
+  using Cfg = SkinnyCfg<NT, RW, NWARPS>;
+  auto kernel = qmm8_skinny_kernel<DT, NT, RW, NWARPS, false, true>;
+  {
+    static std::mutex mutex;
+    static bool configured[64] = {};
+    std::lock_guard<std::mutex> lock(mutex);
+    if (!configured[device & 63]) {
+      TVB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+      configured[device & 63] = true;
+    }
+  }
+  SkinnyGroup group{};
+  group.count = count;
+  const int nranks = gather != nullptr ? gather->world : 1;
+  for (int g = 0; g < count; g++) {
+    if (make_tensor_map_2d(&group.map_w[g], items[g].b, CU_TENSOR_MAP_DATA_TYPE_UINT8, k, n, k, kChunkK, Cfg::kRowsPerTile,
+                           CU_TENSOR_MAP_SWIZZLE_128B) != 0)
+      return -1;
+    if (make_tensor_map_2d(&group.map_a[g], items[g].a, DT == TVB_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+                           k, items[g].m, items[g].a_sm * 2, 64, Cfg::kTokens, CU_TENSOR_MAP_SWIZZLE_128B) != 0)
+      return -1;
+    group.scales[g] = items[g].scales;
+    group.m[g] = items[g].m;
+    for (int r = 0; r < nranks; r++) group.c[g][r] = items[g].c[r];
+  }
+  SkinnyParams p{};
+  p.tiles = static_cast<int>(ceil_div(n, Cfg::kRowsPerTile));
+  p.chunks = k / kChunkK;
+  const long long units = static_cast<long long>(p.tiles) * count * p.chunks;
+  const int grid = static_cast<int>(std::min<long long>(sm_count(device), units));
+  if (gather != nullptr && grid > static_cast<int>(kArriveWeight)) return fail("tvb_qmm8_group_gather: more than 1024 SMs");
+  if (static_cast<long long>(p.tiles) * count > kMaxTiles) return fail("tvb_qmm8_group: more than 4 million output columns in all");
+  const size_t partial_bytes = static_cast<size_t>(grid) * 2 * Cfg::kPartialFloats * sizeof(float);
+  void* ws = nullptr;
+  if (workspace(device, 0, kCounterBytes + partial_bytes, &ws) != 0) return -1;
+  p.counters = static_cast<int*>(ws);
+  p.partials = reinterpret_cast<float*>(static_cast<uint8_t*>(ws) + kCounterBytes);
+  if (status_word(device, &p.status) != 0) return -1;
+  p.nranks = 1;
+  p.c_ld = n;
+  p.c_col0 = 0;
+  p.n = n;
+  p.k = k;
+  p.m0 = 0;
+  if (gather != nullptr) {
+    for (int r = 0; r < gather->world; r++) p.flags[r] = gather->flags[r];
+    p.nranks = gather->world;
+    p.rank = gather->rank;
+    p.seq = gather->seq;
+    p.independent = gather->independent;
+    p.wait_limit = g_wait_limit_cycles.load();
+    p.c_ld = static_cast<int>(gather->n_total);
+    p.c_col0 = gather->rank * n;
+    p.done = reinterpret_cast<int*>(static_cast<uint8_t*>(ws) + kCounterBytes - sizeof(int));
+  }
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(Cfg::kThreads);
+  cfg.dynamicSmemBytes = Cfg::kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  CUtensorMap unused{};
+  TVB_CUDA(cudaLaunchKernelEx(&cfg, kernel, unused, unused, p, group));
+  return launched("qmm8_skinny(group)", dim3(grid), dim3(Cfg::kThreads), Cfg::kSmemBytes, stream);
+}
+
+template <int DT>
+int launch_group(int device, cudaStream_t stream, const GroupItem* items, int count, int n, int k, const GatherTargets* gather) {
+  int rows = 0;
+  for (int g = 0; g < count; g++) rows = std::max(rows, items[g].m);
+  // tile height as for single products: by the size of one product's weights
+  const bool small = static_cast<int64_t>(n) * k < (int64_t(64) << 20);
+  if (rows <= 8)
+    return small ? launch_skinny_group<DT, 1, 1>(device, stream, items, count, n, k, gather)
+                 : launch_skinny_group<DT, 1, 2>(device, stream, items, count, n, k, gather);
+  return small ? launch_skinny_group<DT, 2, 1>(device, stream, items, count, n, k, gather)
+               : launch_skinny_group<DT, 2, 2>(device, stream, items, count, n, k, gather);
 }
 
 bool skinny_ok(const void* a, int dtype, int64_t a_sm, const int8_t* b, int64_t m, int64_t n, int64_t k) {
@@ -913,7 +1080,7 @@ int launch_skinny_static(int device, int sms, cudaStream_t stream, unsigned char
   p.n = n;
   p.k = k;
   p.m0 = m0;
-  kernel<<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(map_w, map_a, p);
+  kernel<<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(map_w, map_a, p, NoGroup{});
   return launched("qmm8_skinny(static scratch)", dim3(grid), dim3(Cfg::kThreads), Cfg::kSmemBytes, stream);
 }
 
@@ -1033,6 +1200,62 @@ extern "C" int tvb_qmm8_gather(int device, const void* a, int dtype, int64_t a_s
     if (rc != 0) return rc;
   }
   return 0;
+}
+
+// ------------------------------------------------------------------ several products of one shape in one launch
+
+static int group_products(const char* who, int device, int dtype, const TvbGroupItem* items, int count, uint32_t* const* flag_ranks,
+                          int world, int rank, uint32_t* seq_counter, int independent, int64_t n, int64_t k, bool sharded) {
+  TVB_REQUIRE(items != nullptr && count >= 1 && count <= kMaxGroup, std::string(who) + ": 1 to 4 products");
+  TVB_REQUIRE(dtype == TVB_F16 || dtype == TVB_BF16, std::string(who) + ": A must be float16 or bfloat16");
+  TVB_REQUIRE(n >= 1 && k >= 1 && n * world < (int64_t(1) << 31), std::string(who) + ": bad sizes");
+  cudaStream_t stream;
+  if (enter(device, &stream) != 0) return -1;
+  GroupItem host[kMaxGroup] = {};
+  for (int g = 0; g < count; g++) {
+    const TvbGroupItem& it = items[g];
+    TVB_REQUIRE(it.m >= 1 && it.m <= 16, std::string(who) + ": 1 <= m <= 16 for every product");
+    TVB_REQUIRE(it.a != nullptr && it.b != nullptr && it.scales != nullptr && it.c_ranks != nullptr, std::string(who) + ": NULL pointer");
+    TVB_REQUIRE(skinny_ok(it.a, dtype, it.a_sm, it.b, it.m, n, k), std::string(who) + ": needs k a multiple of 128 and 16-byte aligned A rows and B");
+    host[g].a = it.a;
+    host[g].a_sm = it.m == 1 ? k : it.a_sm;
+    host[g].b = it.b;
+    host[g].scales = it.scales;
+    host[g].m = static_cast<int>(it.m);
+    for (int r = 0; r < world; r++) {
+      TVB_REQUIRE(it.c_ranks[r] != nullptr, std::string(who) + ": NULL output buffer");
+      host[g].c[r] = it.c_ranks[r];
+    }
+  }
+  GatherTargets gt{};
+  if (sharded) {
+    // the launch's products and the `independent` products before them report in different slots of the channel
+    TVB_REQUIRE(independent >= 0 && independent + count <= kArriveSlots, std::string(who) + ": independent + count must not exceed 4");
+    for (int r = 0; r < world; r++) {
+      TVB_REQUIRE(flag_ranks[r] != nullptr, std::string(who) + ": NULL counters of a rank");
+      gt.flags[r] = flag_ranks[r];
+    }
+    gt.world = world;
+    gt.rank = rank;
+    gt.seq = seq_counter;
+    gt.independent = static_cast<uint32_t>(independent);
+    gt.n_total = n * world;
+  }
+  const int ni = static_cast<int>(n), ki = static_cast<int>(k);
+  return dtype == TVB_BF16 ? launch_group<TVB_BF16>(device, stream, host, count, ni, ki, sharded ? &gt : nullptr)
+                           : launch_group<TVB_F16>(device, stream, host, count, ni, ki, sharded ? &gt : nullptr);
+}
+
+extern "C" int tvb_qmm8_group(int device, int dtype, const TvbGroupItem* items, int count, int64_t n, int64_t k) {
+  return group_products("tvb_qmm8_group", device, dtype, items, count, nullptr, 1, 0, nullptr, 0, n, k, false);
+}
+
+extern "C" int tvb_qmm8_group_gather(int device, int dtype, const TvbGroupItem* items, int count, uint32_t* const* flag_ranks, int world,
+                                     int rank, uint32_t* seq_counter, int independent, int64_t n_local, int64_t k) {
+  TVB_REQUIRE(world >= 1 && world <= kMaxRanks && rank >= 0 && rank < world, "tvb_qmm8_group_gather: 1 to 8 ranks");
+  TVB_REQUIRE(flag_ranks != nullptr && seq_counter != nullptr, "tvb_qmm8_group_gather: NULL pointer");
+  return group_products("tvb_qmm8_group_gather", device, dtype, items, count, flag_ranks, world, rank, seq_counter, independent, n_local,
+                        k, true);
 }
 
 extern "C" int tvb_wait_flags(int device, const uint32_t* flags, int world, const uint32_t* seq_counter) {

@@ -249,6 +249,53 @@ class GatheredOutputs:
         return self.bufs[d]
 
 
+def weight_int8pack_mm_group(activations, weights, scales, outs=None, device_index=None, bufs=None, independent=0):
+    """Up to four int8 weight-only decode products of one shape in ONE launch (tvb_qmm8_group / tvb_qmm8_group_gather):
+    products that do not depend on each other, such as one decoding step's requests against different weights. Product i is
+    activations[i] [m_i, k] (m_i <= 16) times weights[i] [n, k] int8 with scales[i] [n]; n, k and the dtype are shared.
+
+    One GPU: `outs` are the [m_i, n] output tensors (made when None); returns them. Sharded: `outs` are GatheredOutputs
+    of one channel, one per product (weights[i] being this rank's rows), `bufs` which buffer of each to write (default: in
+    turn); returns the [m_i, N] buffers, valid for the channel's next sharded product at once and for anything else after
+    channel.wait(). `independent`: as for GatheredOutputs.weight_int8pack_mm, counted before the launch's first product."""
+    import ctypes
+
+    from . import cabi
+
+    lib, count = cabi.lib(), len(activations)
+    assert 1 <= count <= 4 and len(weights) == count and len(scales) == count
+    n, k = weights[0].shape
+    dtype = activations[0].dtype
+    items = (cabi.TvbGroupItem * count)()
+    sharded = outs is not None and isinstance(outs[0], GatheredOutputs)
+    keep, results = [], []
+    if outs is None:
+        outs = [torch.empty((a.shape[0], n), dtype=dtype, device=a.device) for a in activations]
+    for i, (a, w, s, out) in enumerate(zip(activations, weights, scales, outs)):
+        assert tuple(w.shape) == (n, k) and w.dtype == torch.int8 and w.is_contiguous() and a.shape[1] == k and a.stride(1) == 1
+        assert a.dtype == dtype and s.dtype == dtype and s.numel() == n
+        if sharded:
+            assert out.m == a.shape[0] and out.n_total == n * out.channel.world and out.channel is outs[0].channel
+            d = (out.calls % out.depth) if bufs is None else bufs[i]
+            out.calls += 1
+            ptrs, buf = out.c_ptrs[d], out.bufs[d]
+        else:
+            assert tuple(out.shape) == (a.shape[0], n) and out.is_contiguous() and out.dtype == dtype
+            ptrs, buf = (ctypes.c_void_p * 1)(out.data_ptr()), out
+        keep.append(ptrs)
+        items[i].a, items[i].a_sm, items[i].b, items[i].scales = a.data_ptr(), a.stride(0), w.data_ptr(), s.data_ptr()
+        items[i].c_ranks, items[i].m = ctypes.cast(ptrs, ctypes.POINTER(ctypes.c_void_p)), a.shape[0]
+        results.append(buf)
+    if sharded:
+        ch = outs[0].channel
+        cabi.check(lib.tvb_qmm8_group_gather(ch.dev, cabi._dtype_code(dtype), items, count, ch.flag_ptrs, ch.world, ch.rank,
+                                             ch.seq.data_ptr(), independent, n, k))
+    else:
+        dev = device_index if device_index is not None else (activations[0].device.index or 0)
+        cabi.check(lib.tvb_qmm8_group(dev, cabi._dtype_code(dtype), items, count, n, k))
+    return results
+
+
 class ProductChain:
     """A fixed sequence of int8 weight-only decode products run by one persistent kernel (tvb_qmm8_chain_*): the weights
     of the next products stream in while the current one is finished, and a product may take the output of the one
