@@ -118,6 +118,34 @@ def main():
                 want, tol = C.int8_want(a_, b_, s_)
                 assert ((got.cpu().float() - want.float()).abs() <= tol).all(), f"rank {rank}: independent products in one launch wrong (run {rep})"
         shard.barrier(objects)
+        # the same three products as one launch of the decode kernel (tvb_qmm8_group_gather), eager and replayed with A
+        # rewritten; a sharded product queued right behind the group takes the m = 4 output as its A
+        _, b_n, s_n = C.config_int8(4, 1024 * world, 512 * world, torch.bfloat16, seed=77)
+        s_n = (s_n.float() / 30).to(torch.bfloat16)
+        bv_n, sv_n = shard.shard_rows(b_n, rank, world).to(dev), shard.shard_rows(s_n, rank, world).to(dev)
+        after = shard.GatheredOutputs(4, 512 * world, torch.bfloat16, channel, depth=1)
+        acts = [x[3] for x in ind]
+
+        def grouped():
+            outs = shard.weight_int8pack_mm_group(acts, [x[4] for x in ind], [x[5] for x in ind], outs=[x[6] for x in ind], bufs=[0, 0, 0])
+            nxt = after.weight_int8pack_mm(outs[1], bv_n, sv_n, buf=0)
+            channel.wait()
+            return outs + [nxt]
+
+        grouped_graph = None
+        for rep in range(5):
+            scale = (1.0, -2.0, 0.5, 4.0, -1.0)[rep]
+            for (a_, *_), av_ in zip(ind, acts):
+                av_.copy_((a_ * scale).to(dev))
+            if rep == 2:
+                grouped_graph = shard.StepGraph(grouped, local, warm=False)
+            res = grouped() if grouped_graph is None else grouped_graph.replay()
+            for (a_, b_, s_, *_), got in zip(ind, res):
+                want, tol = C.int8_want(a_ * scale, b_, s_)
+                assert ((got.cpu().float() - want.float()).abs() <= tol).all(), f"rank {rank}: grouped sharded products wrong (rep {rep})"
+            want, tol = C.int8_want(res[1].cpu(), b_n, s_n)
+            assert ((res[3].cpu().float() - want.float()).abs() <= tol).all(), f"rank {rank}: product behind the group wrong (rep {rep})"
+        shard.barrier(objects)
 
         for m in (1, 4, 16):
             a, b, s = C.config_int8(m, 2048, 1024 * world, torch.bfloat16)
