@@ -110,12 +110,14 @@ def measured_peaks():
     return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
 
 
-def profiled_traffic():
-    """DRAM bytes per decode launch from the committed ncu summary (its `roofline.traffic` line), or None."""
+def profiled_traffic(grouped=False):
+    """DRAM bytes per decode launch (one product, or a grouped launch of the step's three) from the committed ncu summary
+    (its `roofline.traffic` lines), or None."""
     path = os.path.join(ROOT, "profiles", "qmm8_skinny_config2.md")
     try:
         with open(path) as f:
-            found = re.search(r"([0-9.]+) MB \(the figure `bench\.py` reports as `roofline\.traffic`\)", f.read())
+            found = re.search(r"([0-9.]+) MB \(the figure `bench\.py` reports as `roofline\.traffic`" + (" for a grouped step" if grouped else "") + r"\)",
+                              f.read())
         return float(found.group(1)) * 1e6 if found else None
     except OSError:
         return None
@@ -1176,10 +1178,12 @@ def main():
         if world > 1:
             line["roofline"]["exchange_us_per_product"] = (avg_launch_ms - iso_mean) * 1e3
         if world == 1:
-            traffic = profiled_traffic()
+            traffic = profiled_traffic(grouped=mode == "group")
             line["roofline"]["traffic"] = traffic
-            line["roofline"]["traffic_source"] = ("ncu dram__bytes_read.sum + dram__bytes_write.sum, mean of the M = 1, 4, 16 launches, read "
-                                                  "from profiles/qmm8_skinny_config2.md")
+            line["roofline"]["traffic_source"] = ("ncu dram__bytes_read.sum + dram__bytes_write.sum per launch (" +
+                                                  ("a grouped launch holds the step's three products: compare with three times the bytes of a product" if mode == "group"
+                                                   else "mean of the M = 1, 4, 16 launches") + "), read from profiles/qmm8_skinny_config2.md")
+            line["roofline"]["bytes_per_launch"] = step_bytes if mode != "per_product" else step_bytes / len(MS)
         if not args.no_cpu and world == 1:
             if torch.get_num_threads() < host_threads():
                 torch.set_num_threads(host_threads())
