@@ -1039,6 +1039,12 @@ def main():
         # every product's A goes up from page-locked memory (into the buffers the step reads) and its C comes back into
         # page-locked memory
         a_all_dev.copy_(a_all_pinned, non_blocking=True)
+        if mode == "group" and world == 1:
+            # the grouped launch stores its results straight into the page-locked host buffers: the kernel's stores are
+            # the copy down
+            sets = step_sets(g)
+            return shard.weight_int8pack_mm_group([a_dev[m] for m in MS], [w_sets[j] for j in sets], [s_sets[j] for j in sets],
+                                                  outs=[out_pinned[m] for m in MS], device_index=local_rank)
         if mode in ("chain", "group"):
             outs = step_fn(mode, g)
             for m, c in zip(MS, outs):
@@ -1093,7 +1099,9 @@ def main():
 
             best_s = time_e2e(step_e2e_graph)
             how = ("CUDA graph replay of the step's copies and products" +
-                   (" (results copied out beside the following products)" if em == "per_product" else "") + ", then a stream synchronize")
+                   (" (results copied out beside the following products)" if em == "per_product" else
+                    " (the kernel stores its results into the page-locked host buffers)" if em == "group" and world == 1 else "") +
+                   ", then a stream synchronize")
             del e2e_graphs
         for m, j in zip(MS, step_sets(last_g)):  # what came back to the host from the last end-to-end step
             check(m, out_pinned[m], j, f"end-to-end outputs on the host ({em})")

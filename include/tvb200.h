@@ -199,7 +199,9 @@ TVB_API int tvb_wait_flags(int device, const uint32_t* flags, int world, const u
  * the whole list into one range per SM, so the launch costs one start and one end whatever `count` (1 to 4) is. Results
  * are those of tvb_qmm8 within one rounding of the float32 sums (the same products, summed over differently cut ranges of
  * k); a launch repeats its own results bit for bit.
- * c_ranks: tvb_qmm8_group reads c_ranks[0], the contiguous [m, n] output. tvb_qmm8_group_gather is the sharded form
+ * c_ranks: tvb_qmm8_group reads c_ranks[0], the contiguous [m, n] output; it may lie in page-locked host memory
+ * (tvb_host_alloc, cudaHostAlloc), in which case the kernel's stores are the copy to the host: the result is there after
+ * tvb_synchronize and no tvb_memcpy_d2h is needed. tvb_qmm8_group_gather is the sharded form
  * (see tvb_qmm8_gather): n_local rows of every B on this rank, c_ranks = every rank's [m, n_local * world] buffer for that
  * product; the launch takes `count` consecutive product numbers on the channel and waits, before it reads any A, for
  * all earlier products but the latest `independent` (independent + count <= 4). */

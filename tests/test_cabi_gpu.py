@@ -480,6 +480,25 @@ def test_group_products_in_one_launch(abi, dtype, ms, k, n):
     assert lib.tvb_qmm8_group(0, code, items, 5, n, k) == -1
 
 
+def test_group_products_into_host_memory(abi):
+    """The grouped launch with page-locked host tensors as outputs: the kernel's stores are the copy to the host."""
+    from torch_vulkan_b200 import shard
+
+    ms, k, n = (1, 4, 16), 2048, 6144
+    cases = [C.config_int8(m, k, n, torch.bfloat16, seed=80 + i) for i, m in enumerate(ms)]
+    outs = [torch.zeros(m, n, dtype=torch.bfloat16).pin_memory() for m in ms]
+    devs = [(dev(a), dev(b), dev(s)) for a, b, s in cases]
+    torch.cuda.synchronize()
+    for rep in range(2):
+        for o in outs:
+            o.zero_()
+        got = shard.weight_int8pack_mm_group([d[0] for d in devs], [d[1] for d in devs], [d[2] for d in devs], outs=outs, device_index=0)
+        abi.synchronize()
+        for (a, b, s), o in zip(cases, got):
+            want, tol = C.int8_want(a, b, s)
+            assert ((o.float() - want.float()).abs() <= tol).all()
+
+
 def test_group_gather_world1_counts(abi):
     """tvb_qmm8_group_gather with a world of one rank: three products land in the rank's own buffers, take three product
     numbers on the channel (every CTA reports its share of each), and a following sharded product waits for all three."""

@@ -254,7 +254,9 @@ def weight_int8pack_mm_group(activations, weights, scales, outs=None, device_ind
     products that do not depend on each other, such as one decoding step's requests against different weights. Product i is
     activations[i] [m_i, k] (m_i <= 16) times weights[i] [n, k] int8 with scales[i] [n]; n, k and the dtype are shared.
 
-    One GPU: `outs` are the [m_i, n] output tensors (made when None); returns them. Sharded: `outs` are GatheredOutputs
+    One GPU: `outs` are the [m_i, n] output tensors (made when None); returns them. An output may also be a page-locked
+    CPU tensor (`pin_memory()`): the kernel then stores that product's columns straight into host memory as they are
+    finished, and no copy is needed to bring the result down (it is there after synchronize()). Sharded: `outs` are GatheredOutputs
     of one channel, one per product (weights[i] being this rank's rows), `bufs` which buffer of each to write (default: in
     turn); returns the [m_i, N] buffers, valid for the channel's next sharded product at once and for anything else after
     channel.wait(). `independent`: as for GatheredOutputs.weight_int8pack_mm, counted before the launch's first product."""
@@ -281,6 +283,7 @@ def weight_int8pack_mm_group(activations, weights, scales, outs=None, device_ind
             ptrs, buf = out.c_ptrs[d], out.bufs[d]
         else:
             assert tuple(out.shape) == (a.shape[0], n) and out.is_contiguous() and out.dtype == dtype
+            assert out.device.type != "cpu" or out.is_pinned(), "a host output must be page-locked"
             ptrs, buf = (ctypes.c_void_p * 1)(out.data_ptr()), out
         keep.append(ptrs)
         items[i].a, items[i].a_sm, items[i].b, items[i].scales = a.data_ptr(), a.stride(0), w.data_ptr(), s.data_ptr()
