@@ -370,10 +370,14 @@ def extra_dyn4(tv, timer, peaks, cpu, quick):
     for mm in ((128,) if quick else (128, 512, 2048)):
         xv = torch.randn(mm, k, generator=gen(11)).to("vk")
         for mode in ("exact", "fast"):  # exact: bit for bit (the default); fast: TORCH_VK_QMM4=fast, rtol 1e-5
+            before = os.environ.get("TORCH_VK_QMM4")
             if mode == "fast":
                 os.environ["TORCH_VK_QMM4"] = "fast"
             ms = timer.median(lambda: torch._dyn_quant_matmul_4bit(xv, packed, bs, k, n), 5)
-            os.environ.pop("TORCH_VK_QMM4", None)
+            if mode == "fast":
+                os.environ.pop("TORCH_VK_QMM4", None)
+                if before is not None:
+                    os.environ["TORCH_VK_QMM4"] = before
             tops = 2.0 * mm * n * k / ms / 1e9
             entry = {"tops": tops, "ms": ms, "frac_of_2x_measured_bf16": tops / peak,
                      "roofline": roof("tensor", tops, peak, "TOP/s",

@@ -346,6 +346,20 @@ TVB_API uint64_t tvb_qmm4_tc_workspace_bytes(int64_t m, int64_t k);
 TVB_API int tvb_qmm4_tc(int device, const void* inp, int dtype, const float* packed, int has_bias, const void* prepared,
                         void* out, int64_t m, int64_t n, int64_t k, int64_t bs, void* workspace, uint64_t workspace_bytes);
 
+/* The float16 form of tvb_qmm4_tc, bit for bit as well (tcgen05 kind::f16 over float16 copies of the integers: q - zero_point
+ * and the weights; block sums below 2^24 are exact in the float32 accumulators). Where a block holds 32 values and every
+ * scale came from bfloat16 (what the op's groupwise form is given), float(block sum) * scale is exact, so the reference's
+ * multiply and add per output and block is one fma with the same single rounding: the per-block drain, which bounds both
+ * forms, is a third of the int8 form's. Other scales (found when the weights are prepared) take multiply and add. `prepared`
+ * comes from tvb_qmm4_prepare16 (tvb_qmm4_prepared16_bytes(n, k) bytes: two per weight). k and bs multiples of 32,
+ * bs <= 8192. workspace: tvb_qmm4_tc16_workspace_bytes(m, k). */
+TVB_API uint64_t tvb_qmm4_prepared16_bytes(int64_t n, int64_t k);
+TVB_API int tvb_qmm4_prepare16(int device, const float* packed, int64_t n, int64_t k, int64_t bs, void* prepared,
+                               uint64_t prepared_bytes);
+TVB_API uint64_t tvb_qmm4_tc16_workspace_bytes(int64_t m, int64_t k);
+TVB_API int tvb_qmm4_tc16(int device, const void* inp, int dtype, const float* packed, int has_bias, const void* prepared,
+                          void* out, int64_t m, int64_t n, int64_t k, int64_t bs, void* workspace, uint64_t workspace_bytes);
+
 /* The opt-in fast route of the same op (no counterpart in the reference): one float16 GEMM on tcgen05 over exact
  * operands, (q - zero_point) and weight * block scale, accumulated over the whole of k in float32. Outputs differ from the
  * exact routes by float32 accumulation order only (not bit for bit). tvb_qmm4_fast_prepare writes the float16 weights

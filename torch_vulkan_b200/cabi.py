@@ -105,6 +105,10 @@ SIGNATURES = {
     "tvb_qmm4_decode_workspace_bytes": (_u64, [_i64, _i64]),
     "tvb_qmm4_decode": (_i, [_i, _vp, _i, _vp, _i, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _u64]),
     "tvb_qmm4_tc": (_i, [_i, _vp, _i, _vp, _i, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _u64]),
+    "tvb_qmm4_prepared16_bytes": (_u64, [_i64, _i64]),
+    "tvb_qmm4_prepare16": (_i, [_i, _vp, _i64, _i64, _i64, _vp, _u64]),
+    "tvb_qmm4_tc16_workspace_bytes": (_u64, [_i64, _i64]),
+    "tvb_qmm4_tc16": (_i, [_i, _vp, _i, _vp, _i, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _u64]),
     "tvb_qmm4_fast_prepared_bytes": (_u64, [_i64, _i64]),
     "tvb_qmm4_fast_prepare": (_i, [_i, _vp, _i64, _i64, _i64, _vp, _u64, _c.POINTER(_i)]),
     "tvb_qmm4_fast_workspace_bytes": (_u64, [_i64, _i64]),
@@ -264,6 +268,29 @@ def qmm4_tc(x, packed, prepared, bs, k, n):
     ws = torch.empty(max(nbytes, 1), dtype=torch.uint8, device=x.device)
     check(lib().tvb_qmm4_tc(_dev(x), _ptr(x), _dtype_code(x.dtype), _ptr(packed), has_bias, _ptr(prepared), _ptr(out), m, n, k,
                             bs, _ptr(ws), nbytes))
+    return out
+
+
+def qmm4_prepare16(packed, n, k, bs):
+    import torch
+
+    nbytes = lib().tvb_qmm4_prepared16_bytes(n, k)
+    prepared = torch.empty(nbytes, dtype=torch.uint8, device=packed.device)
+    check(lib().tvb_qmm4_prepare16(_dev(packed), _ptr(packed), n, k, bs, _ptr(prepared), nbytes))
+    return prepared
+
+
+def qmm4_tc16(x, packed, prepared, bs, k, n):
+    import torch
+
+    m = x.shape[0]
+    nblocks = (k + bs - 1) // bs
+    has_bias = 1 if packed.numel() - (n * k // 2 + n * nblocks) else 0
+    out = torch.empty((m, n), dtype=x.dtype, device=x.device)
+    nbytes = lib().tvb_qmm4_tc16_workspace_bytes(m, k)
+    ws = torch.empty(max(nbytes, 1), dtype=torch.uint8, device=x.device)
+    check(lib().tvb_qmm4_tc16(_dev(x), _ptr(x), _dtype_code(x.dtype), _ptr(packed), has_bias, _ptr(prepared), _ptr(out), m, n, k,
+                              bs, _ptr(ws), nbytes))
     return out
 
 

@@ -217,7 +217,7 @@ struct PreparedWeights {
   int64_t numel, n, k, bs;
   uint32_t version;
   int kind;       // 0: int8 weights for the exact tensor-core kernel; 1: float16 weight * scale for the fast route;
-                  // 2: nibbles and scales tiled for the decode kernel
+                  // 2: nibbles and scales tiled for the decode kernel; 3: float16 weights for the float16 form of the exact kernel
   int inexact;    // kind 1: some weight * scale product is not exact in float16 (the fast route must not be used)
   at::Tensor prepared;
 };
@@ -245,13 +245,16 @@ at::Tensor prepared_weights(const at::Tensor& packed, int dev, int64_t n, int64_
     ++it;
   }
   const uint64_t bytes = kind == 0 ? tvb_qmm4_prepared_bytes(n, k)
-                                   : (kind == 1 ? tvb_qmm4_fast_prepared_bytes(n, k) : tvb_qmm4_decode_prepared_bytes(n, k, bs));
+                                   : (kind == 1 ? tvb_qmm4_fast_prepared_bytes(n, k)
+                                                : (kind == 2 ? tvb_qmm4_decode_prepared_bytes(n, k, bs) : tvb_qmm4_prepared16_bytes(n, k)));
   at::Tensor prepared = at::empty({static_cast<int64_t>(bytes)}, packed.options().dtype(at::kByte));
   int flag = 0;
   if (kind == 0)
     check(tvb_qmm4_prepare(dev, static_cast<const float*>(gpu_address(packed)), n, k, bs, gpu_address_out(prepared), bytes));
   else if (kind == 2)
     check(tvb_qmm4_decode_prepare(dev, static_cast<const float*>(gpu_address(packed)), n, k, bs, gpu_address_out(prepared), bytes));
+  else if (kind == 3)
+    check(tvb_qmm4_prepare16(dev, static_cast<const float*>(gpu_address(packed)), n, k, bs, gpu_address_out(prepared), bytes));
   else
     check(tvb_qmm4_fast_prepare(dev, static_cast<const float*>(gpu_address(packed)), n, k, bs, gpu_address_out(prepared), bytes, &flag));
   if (inexact != nullptr) *inexact = flag;
@@ -319,6 +322,17 @@ at::Tensor dyn_quant_matmul_4bit(const at::Tensor& inp, const at::Tensor& packed
                             bias_elements != 0 ? 1 : 0, gpu_address(prepared), gpu_address_out(outr), rows, N, K, block_size,
                             gpu_address_out(dws), dbytes));
     }
+    return out;
+  }
+  if (!force_plain && mode != "i8" && block_size == 32 && K % 32 == 0 && packed.is_same(packed_weights)) {
+    // Blocks of 32 values (the groupwise form the op is usually given, its scales from bfloat16): the float16 form of the
+    // exact kernel, whose per-block drain is one fma per output. Same bits as the int8 form (TORCH_VK_QMM4=i8 keeps that).
+    at::Tensor prepared = prepared_weights(packed_weights, dev, N, K, block_size, 3, nullptr);
+    const uint64_t tc_bytes = tvb_qmm4_tc16_workspace_bytes(M, K);
+    at::Tensor tc_ws = at::empty({static_cast<int64_t>(tc_bytes)}, inp.options().dtype(at::kByte));
+    check(tvb_qmm4_tc16(dev, gpu_address(x), dtype_code(x.scalar_type()), static_cast<const float*>(gpu_address(packed)),
+                        bias_elements != 0 ? 1 : 0, gpu_address(prepared), gpu_address_out(out), M, N, K, block_size,
+                        gpu_address_out(tc_ws), tc_bytes));
     return out;
   }
   if (!force_plain && K % 32 == 0 && block_size % 32 == 0) {
