@@ -215,6 +215,43 @@ __device__ __forceinline__ uint16_t skinny_epilogue(const SkinnyParams& p, uint1
   return bits;
 }
 
+// acc += the partial sums that CTAs hi, hi - 1, ..., lo left in scratch for `tile`, in that order (the one fixed order of
+// additions). The addresses of a few contributors are worked out first and their loads issued together: with one
+// contributor at a time, each one's index arithmetic (two divisions) and its trip to the L2 came one after the other, and
+// the CTA that finishes a shared tile was the last of its launch to end by about 3 us.
+template <class Cfg, int RW, int NT>
+__device__ __forceinline__ void add_partials(float (&acc)[RW][NT][4], const float* partials, const int hi, const int lo, const int tile,
+                                             const long long units, const long long grid, const bool small, const int chunks,
+                                             const int warp, const int lane) {
+  constexpr int kBatch = RW * NT <= 2 ? 4 : (RW * NT <= 4 ? 2 : 1);
+  for (int top = hi; top >= lo; top -= kBatch) {
+    const float4* theirs[kBatch];
+#pragma unroll
+    for (int j = 0; j < kBatch; j++) {
+      const int cta = top - j >= lo ? top - j : lo;  // (past the end: a valid address whose values are not added)
+      const bool cta_first_segment = unit_tile(range_start(cta, units, grid, small), chunks, small) == tile;
+      theirs[j] = reinterpret_cast<const float4*>(partials + (static_cast<size_t>(cta) * 2 + (cta_first_segment ? 0 : 1)) * Cfg::kPartialFloats);
+    }
+    float4 v[kBatch][RW][NT];
+#pragma unroll
+    for (int j = 0; j < kBatch; j++)
+#pragma unroll
+      for (int rb = 0; rb < RW; rb++)
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++) v[j][rb][nt] = __ldcg(&theirs[j][((warp * RW + rb) * NT + nt) * 32 + lane]);
+#pragma unroll
+    for (int j = 0; j < kBatch; j++) {
+      if (top - j < lo) break;
+#pragma unroll
+      for (int rb = 0; rb < RW; rb++)
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++) {
+          acc[rb][nt][0] += v[j][rb][nt].x; acc[rb][nt][1] += v[j][rb][nt].y; acc[rb][nt][2] += v[j][rb][nt].z; acc[rb][nt][3] += v[j][rb][nt].w;
+        }
+    }
+  }
+}
+
 // ADDS: the instantiation whose epilogue also adds a bias and a residual (tvb_qmm8_linear); the plain product carries no
 // code for them (with it in one kernel, behind a test of the two pointers, every launch was 0.65 us slower).
 template <int DT, int NT, int RW, int NWARPS, bool ADDS = false, bool GROUP = false>
@@ -611,18 +648,7 @@ __global__ void __launch_bounds__((NWARPS + 2) * 32, 1)
         for (int nt = 0; nt < NT; nt++)
 #pragma unroll
           for (int i = 0; i < 4; i++) pre[rb][nt][i] = 0.0f + pre[rb][nt][i];
-      for (int cta = cta_last - 1; cta > cta_first; cta--) {
-        const bool cta_first_segment = unit_tile(range_start(cta, units, grid, small), p.chunks, small) == tile;
-        const float4* theirs = reinterpret_cast<const float4*>(
-            p.partials + (static_cast<size_t>(cta) * 2 + (cta_first_segment ? 0 : 1)) * Cfg::kPartialFloats);
-#pragma unroll
-        for (int rb = 0; rb < RW; rb++)
-#pragma unroll
-          for (int nt = 0; nt < NT; nt++) {
-            float4 v = __ldcg(&theirs[((warp * RW + rb) * NT + nt) * 32 + lane]);
-            pre[rb][nt][0] += v.x; pre[rb][nt][1] += v.y; pre[rb][nt][2] += v.z; pre[rb][nt][3] += v.w;
-          }
-      }
+      add_partials<Cfg, RW, NT>(pre, p.partials, cta_last - 1, cta_first + 1, tile, units, grid, small, p.chunks, warp, lane);
 #pragma unroll
       for (int rb = 0; rb < RW; rb++)
 #pragma unroll
@@ -666,18 +692,8 @@ __global__ void __launch_bounds__((NWARPS + 2) * 32, 1)
             for (int nt = 0; nt < NT; nt++)
 #pragma unroll
               for (int i = 0; i < 4; i++) acc[rb][nt][i] = 0.0f;
-          for (int cta = cta_last; cta >= cta_first; cta--) {  // fixed order: the sum does not depend on who came last
-            const bool cta_first_segment = unit_tile(range_start(cta, units, grid, small), p.chunks, small) == tile;
-            const float4* theirs = reinterpret_cast<const float4*>(
-                p.partials + (static_cast<size_t>(cta) * 2 + (cta_first_segment ? 0 : 1)) * Cfg::kPartialFloats);
-#pragma unroll
-            for (int rb = 0; rb < RW; rb++)
-#pragma unroll
-              for (int nt = 0; nt < NT; nt++) {
-                float4 v = __ldcg(&theirs[((warp * RW + rb) * NT + nt) * 32 + lane]);
-                acc[rb][nt][0] += v.x; acc[rb][nt][1] += v.y; acc[rb][nt][2] += v.z; acc[rb][nt][3] += v.w;
-              }
-          }
+          // fixed order: the sum does not depend on who came last
+          add_partials<Cfg, RW, NT>(acc, p.partials, cta_last, cta_first, tile, units, grid, small, p.chunks, warp, lane);
         }
       }
     }
