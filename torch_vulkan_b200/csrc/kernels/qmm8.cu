@@ -223,7 +223,9 @@ template <class Cfg, int RW, int NT>
 __device__ __forceinline__ void add_partials(float (&acc)[RW][NT][4], const float* partials, const int hi, const int lo, const int tile,
                                              const long long units, const long long grid, const bool small, const int chunks,
                                              const int warp, const int lane) {
-  constexpr int kBatch = RW * NT <= 2 ? 4 : (RW * NT <= 4 ? 2 : 1);
+  // (the configurations of large matrices and wide passes keep one contributor at a time: their registers are spoken for,
+  // and a launch of theirs is long against its finish)
+  constexpr int kBatch = RW * NT <= 2 ? 4 : 1;
   for (int top = hi; top >= lo; top -= kBatch) {
     const float4* theirs[kBatch];
 #pragma unroll
