@@ -31,7 +31,8 @@
 // drain, the limit of both forms, does not feel.
 //
 // Warp roles: 0-15 drain and epilogue (four warps per TMEM lane quarter, one per 32 tokens: four warps per scheduler
-// hide each other's tcgen05.ld and barrier waits, which two could not), 16 TMA producer, 17 MMA issuer and TMEM owner.
+// hide each other's tcgen05.ld and barrier waits, which two could not), 16 TMA producer, 17 and 18 MMA issuers (17 owns the
+// tensor memory allocation).
 // Every wait is bounded.
 #include <cuda.h>
 #include <cuda_fp16.h>
