@@ -1038,6 +1038,8 @@ def main():
 
     # ---- end to end through the C ABI / the ops: A from pinned host memory, C back to the host, every step
     out_pinned = {m: torch.empty(m, N_OUT, dtype=torch.bfloat16).pin_memory() for m in MS}
+    host_gathered = ({m: shard.HostGathered(m, N_OUT, torch.bfloat16, channel) for m in MS}
+                     if fused is not None and "group" in timed and os.environ.get("TVB200_HOST_GATHER", "1") != "0" else None)
 
     def e2e_body(g, mode):
         # every product's A goes up from page-locked memory (into the buffers the step reads) and its C comes back into
@@ -1049,6 +1051,14 @@ def main():
             sets = step_sets(g)
             return shard.weight_int8pack_mm_group([a_dev[m] for m in MS], [w_sets[j] for j in sets], [s_sets[j] for j in sets],
                                                   outs=[out_pinned[m] for m in MS], device_index=local_rank)
+        if mode == "group" and host_gathered is not None:
+            # sharded: every rank's kernel also stores its columns into page-locked host memory that all ranks of the node
+            # map (one shared segment): the whole result is on the host, once, when every rank's columns have arrived
+            sets = step_sets(g)
+            outs = shard.weight_int8pack_mm_group([a_dev[m] for m in MS], [w_sets[j] for j in sets], [s_sets[j] for j in sets],
+                                                  outs=[fused[m] for m in MS], bufs=[g % 2] * len(MS), host_outs=[host_gathered[m] for m in MS])
+            channel.wait()
+            return outs
         if mode in ("chain", "group"):
             outs = step_fn(mode, g)
             for m, c in zip(MS, outs):
@@ -1104,11 +1114,15 @@ def main():
             best_s = time_e2e(step_e2e_graph)
             how = ("CUDA graph replay of the step's copies and products" +
                    (" (results copied out beside the following products)" if em == "per_product" else
-                    " (the kernel stores its results into the page-locked host buffers)" if em == "group" and world == 1 else "") +
+                    " (the kernel stores its results into the page-locked host buffers)" if em == "group" and world == 1 else
+                    " (every rank's kernel stores its columns into one page-locked host buffer that all ranks map)" if em == "group" and host_gathered is not None else "") +
                    ", then a stream synchronize")
             del e2e_graphs
+        if world > 1:
+            shard.barrier()  # (a shared host buffer is complete for everyone when every rank's step has ended)
         for m, j in zip(MS, step_sets(last_g)):  # what came back to the host from the last end-to-end step
-            check(m, out_pinned[m], j, f"end-to-end outputs on the host ({em})")
+            on_host = host_gathered[m].tensors[last_g % 2] if em == "group" and host_gathered is not None else out_pinned[m]
+            check(m, on_host, j, f"end-to-end outputs on the host ({em})")
         if world > 1:  # (every rank must pick the same way: the slowest rank's times decide)
             import torch.distributed as dist
 
@@ -1181,6 +1195,8 @@ def main():
                          "isolated_frac": launch_bytes / (iso_mean * 1e-3) / 1e9 / peaks["hbm_gbs"]},
             "e2e": {"value": step_bytes / e2e_s / 1e9, "unit": UNIT,
                     "h2d_bytes_per_step": sum(2 * m * K_IN for m in MS), "d2h_bytes_per_step": sum(2 * m * N_OUT for m in MS),
+                    "d2h_how": ("every rank stores its own columns into one host buffer shared by the node's ranks: the figure is the whole node's"
+                                if e2e_mode == "group" and host_gathered is not None else "every rank brings the whole result down"),
                     "ms_per_step": e2e_s * 1e3, "how": e2e_how, "eager_value": step_bytes / e2e_eager_s / 1e9},
             "gpu_launches": int(launches),
             "clocks": clocks,

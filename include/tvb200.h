@@ -118,6 +118,10 @@ TVB_API int tvb_join_copies(int device);
 TVB_API int tvb_host_alloc(uint64_t nbytes, void** out);
 TVB_API void tvb_host_free(void* ptr);
 TVB_API int tvb_host_is_pinned(const void* ptr);
+/* Page-locks host memory the caller owns (for instance a shared-memory segment mapped by every process of a node) and
+ * returns the address under which kernels reach it. tvb_host_unregister before the memory is unmapped. */
+TVB_API int tvb_host_register(void* ptr, uint64_t nbytes, void** device_ptr);
+TVB_API int tvb_host_unregister(void* ptr);
 
 /* ---- data movement kernels (the slice of the reference's cast / move / fill
  *      kernels that the four ops and their tests need: cast.slang, move.slang) */
@@ -212,6 +216,11 @@ typedef struct TvbGroupItem {
   const void* scales;
   void* const* c_ranks;
   int64_t m;
+  void* c_host;  /* NULL, or one more destination for this product's columns: page-locked host memory that the device can
+                  * address (tvb_host_alloc, or any host memory after tvb_host_register), laid out like the c_ranks buffers.
+                  * Sharded, the ranks of a node may all pass one buffer in shared memory: every rank's kernel stores its own
+                  * columns there, and after tvb_wait_flags + tvb_synchronize every process reads the whole result with no
+                  * copy. Either every product of a launch has one or none. */
 } TvbGroupItem;
 TVB_API int tvb_qmm8_group(int device, int dtype, const TvbGroupItem* items, int count, int64_t n, int64_t k);
 TVB_API int tvb_qmm8_group_gather(int device, int dtype, const TvbGroupItem* items, int count, uint32_t* const* flag_ranks, int world,

@@ -132,6 +132,27 @@ def main():
             channel.wait()
             return outs + [nxt]
 
+        hosts = [shard.HostGathered(x[6].m, x[6].n_total, torch.bfloat16, channel, depth=1) for x in ind]
+
+        def grouped_to_host():
+            outs = shard.weight_int8pack_mm_group(acts, [x[4] for x in ind], [x[5] for x in ind], outs=[x[6] for x in ind], bufs=[0, 0, 0],
+                                                  host_outs=hosts)
+            channel.wait()
+            return outs
+
+        for rep in range(3):  # the same launch also storing every rank's columns into host memory that all ranks map
+            scale = (1.0, -2.0, 0.5)[rep]
+            for (a_, *_), av_ in zip(ind, acts):
+                av_.copy_((a_ * scale).to(dev))
+            for h in hosts:
+                h.tensors[0].zero_()
+            shard.barrier(objects)
+            grouped_to_host()
+            tv.synchronize()
+            for (a_, b_, s_, *_), h in zip(ind, hosts):
+                want, tol = C.int8_want(a_ * scale, b_, s_)
+                assert ((h.tensors[0].float() - want.float()).abs() <= tol).all(), f"rank {rank}: results delivered to the host wrong (rep {rep})"
+            shard.barrier(objects)
         grouped_graph = None
         for rep in range(5):
             scale = (1.0, -2.0, 0.5, 4.0, -1.0)[rep]

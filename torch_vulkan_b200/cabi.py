@@ -28,7 +28,7 @@ class TvbChainItem(ctypes.Structure):
 
 
 class TvbGroupItem(ctypes.Structure):
-    _fields_ = [("a", _vp), ("a_sm", _i64), ("b", _vp), ("scales", _vp), ("c_ranks", _c.POINTER(_vp)), ("m", _i64)]
+    _fields_ = [("a", _vp), ("a_sm", _i64), ("b", _vp), ("scales", _vp), ("c_ranks", _c.POINTER(_vp)), ("m", _i64), ("c_host", _vp)]
 
 
 # name -> (restype, argtypes): every entry point include/tvb200.h declares
@@ -51,6 +51,8 @@ SIGNATURES = {
     "tvb_host_alloc": (_i, [_u64, _c.POINTER(_vp)]),
     "tvb_host_free": (None, [_vp]),
     "tvb_host_is_pinned": (_i, [_vp]),
+    "tvb_host_register": (_i, [_vp, _u64, _c.POINTER(_vp)]),
+    "tvb_host_unregister": (_i, [_vp]),
     "tvb_memcpy_h2d": (_i, [_i, _vp, _vp, _u64]),
     "tvb_memcpy_d2h": (_i, [_i, _vp, _vp, _u64]),
     "tvb_memcpy_d2d": (_i, [_i, _vp, _vp, _u64]),

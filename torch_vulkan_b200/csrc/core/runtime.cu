@@ -466,6 +466,27 @@ void tvb_host_free(void* ptr) {
   if (ptr != nullptr && cudaFreeHost(ptr) != cudaSuccess) cudaGetLastError();
 }
 
+int tvb_host_register(void* ptr, uint64_t nbytes, void** device_ptr) {
+  TVB_REQUIRE(ptr != nullptr && nbytes != 0 && device_ptr != nullptr, "tvb_host_register: NULL pointer or empty range");
+  cudaStream_t s;
+  if (enter(tvb_current_device(), &s) != 0) return -1;
+  TVB_CUDA(cudaHostRegister(ptr, nbytes, cudaHostRegisterPortable | cudaHostRegisterMapped));
+  void* dev = nullptr;
+  cudaError_t err = cudaHostGetDevicePointer(&dev, ptr, 0);
+  if (err != cudaSuccess) {
+    cudaHostUnregister(ptr);
+    return fail_cuda("cudaHostGetDevicePointer", err);
+  }
+  *device_ptr = dev;
+  return 0;
+}
+
+int tvb_host_unregister(void* ptr) {
+  TVB_REQUIRE(ptr != nullptr, "tvb_host_unregister: NULL pointer");
+  TVB_CUDA(cudaHostUnregister(ptr));
+  return 0;
+}
+
 int tvb_host_is_pinned(const void* ptr) {
   if (ptr == nullptr) return 0;
   {

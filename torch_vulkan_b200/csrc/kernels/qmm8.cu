@@ -169,7 +169,9 @@ __global__ void __launch_bounds__(256) qmm8_f32_kernel(const float* __restrict__
 
 struct SkinnyParams {
   const void* scales;
-  void* c[kMaxRanks];        // output buffers [m, c_ld]: this GPU's, and with sharding every peer's (peer-mapped memory)
+  void* c[kMaxRanks + 1];    // output buffers [m, c_ld]: this GPU's, and with sharding every peer's (peer-mapped memory); a
+                             // grouped launch may add one in page-locked host memory
+  int ndest;                 // how many of them (nranks, or nranks + 1 with the host's)
   uint32_t* flags[kMaxRanks];  // with sharding: every rank's arrival counters (entry `rank` of each is this GPU's to add to)
   int* done;                 // with sharding: counter of finished CTAs (zero between launches)
   int nranks, rank;
@@ -195,7 +197,7 @@ constexpr int kMaxGroup = 4;
 struct SkinnyGroup {
   CUtensorMap map_w[kMaxGroup], map_a[kMaxGroup];
   const void* scales[kMaxGroup];
-  void* c[kMaxGroup][kMaxRanks];
+  void* c[kMaxGroup][kMaxRanks + 1];
   int m[kMaxGroup];
   int count;
 };
@@ -475,7 +477,7 @@ __global__ void __launch_bounds__((NWARPS + 2) * 32, 1)
                   uint16_t bits = DT == TVB_BF16 ? f32_to_bf16_bits(v) : f32_to_f16_bits(v);
                   if constexpr (ADDS) bits = skinny_epilogue<DT>(p, bits, token, col);
                   const int64_t off = static_cast<int64_t>(token) * p.c_ld + p.c_col0 + col;
-                  for (int r = 0; r < p.nranks; r++) static_cast<uint16_t*>(out_of(product, r))[off] = bits;
+                  for (int r = 0; r < p.ndest; r++) static_cast<uint16_t*>(out_of(product, r))[off] = bits;
                 }
               }
             }
@@ -734,7 +736,7 @@ __global__ void __launch_bounds__((NWARPS + 2) * 32, 1)
         const uint4 val = *reinterpret_cast<const uint4*>(out_tile + tok * Cfg::kRowsPerTile + chunk * 8);
         const int64_t off = static_cast<int64_t>(token) * p.c_ld + p.c_col0 + col;
         if (vec && col + 8 <= p.n) {
-          for (int r = 0; r < p.nranks; r++) {
+          for (int r = 0; r < p.ndest; r++) {
             uint16_t* dst = static_cast<uint16_t*>(out_of(product, r)) + off;
             if ((reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
               *reinterpret_cast<uint4*>(dst) = val;
@@ -745,7 +747,7 @@ __global__ void __launch_bounds__((NWARPS + 2) * 32, 1)
           }
         } else {
           const uint16_t* e = reinterpret_cast<const uint16_t*>(&val);
-          for (int r = 0; r < p.nranks; r++)
+          for (int r = 0; r < p.ndest; r++)
             for (int j = 0; j < 8 && col + j < p.n; j++) (static_cast<uint16_t*>(out_of(product, r)) + off)[j] = e[j];
         }
       }
@@ -759,7 +761,7 @@ __global__ void __launch_bounds__((NWARPS + 2) * 32, 1)
     // covers the stores of all the CTA's threads; no CTA waits for another, and columns count as they land.
     ptx::named_bar_sync(2, (NWARPS + 1) * 32);  // (the agent warp arrives here too, after whatever it had to store)
     if (threadIdx.x == 0) {
-      if (p.nranks == 1) __threadfence();
+      if (p.nranks == 1 && p.ndest == 1) __threadfence();
       else __threadfence_system();
       // (a grouped launch holds `products` products of the channel: the CTA reports its share of each, whichever tiles
       // it had, since the counters say "every CTA of the launch is past its stores")
@@ -864,6 +866,7 @@ int launch_skinny_cfg(int device, cudaStream_t stream, const void* a, int64_t a_
     p.c_col0 = gather->rank * n;
     p.done = reinterpret_cast<int*>(static_cast<uint8_t*>(ws) + counter_bytes - sizeof(int));
   }
+  p.ndest = p.nranks;
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(grid);
   cfg.blockDim = dim3(Cfg::kThreads);
@@ -906,6 +909,7 @@ struct GroupItem {
   const int8_t* b;
   const void* scales;
   void* c[kMaxRanks];
+  void* c_host;   // or NULL: one more destination, in page-locked host memory, laid out like the others
   int m;
 };
 
@@ -939,7 +943,11 @@ int launch_skinny_group(int device, cudaStream_t stream, const GroupItem* items,
     group.scales[g] = items[g].scales;
     group.m[g] = items[g].m;
     for (int r = 0; r < nranks; r++) group.c[g][r] = items[g].c[r];
+    group.c[g][nranks] = items[g].c_host;
   }
+  bool to_host = items[0].c_host != nullptr;
+  for (int g = 0; g < count; g++)
+    if ((items[g].c_host != nullptr) != to_host) return fail("tvb_qmm8_group: either every product has a host destination or none");
   SkinnyParams p{};
   p.tiles = static_cast<int>(ceil_div(n, Cfg::kRowsPerTile));
   p.chunks = k / kChunkK;
@@ -970,6 +978,7 @@ int launch_skinny_group(int device, cudaStream_t stream, const GroupItem* items,
     p.c_col0 = gather->rank * n;
     p.done = reinterpret_cast<int*>(static_cast<uint8_t*>(ws) + kCounterBytes - sizeof(int));
   }
+  p.ndest = p.nranks + (to_host ? 1 : 0);
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(grid);
   cfg.blockDim = dim3(Cfg::kThreads);
@@ -1092,6 +1101,7 @@ int launch_skinny_static(int device, int sms, cudaStream_t stream, unsigned char
   p.scales = scales;
   p.c[0] = c;
   p.nranks = 1;
+  p.ndest = 1;
   p.c_ld = n;
   p.c_col0 = 0;
   p.m = m;
@@ -1240,6 +1250,7 @@ static int group_products(const char* who, int device, int dtype, const TvbGroup
     host[g].b = it.b;
     host[g].scales = it.scales;
     host[g].m = static_cast<int>(it.m);
+    host[g].c_host = it.c_host;
     for (int r = 0; r < world; r++) {
       TVB_REQUIRE(it.c_ranks[r] != nullptr, std::string(who) + ": NULL output buffer");
       host[g].c[r] = it.c_ranks[r];

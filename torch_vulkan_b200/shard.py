@@ -249,7 +249,55 @@ class GatheredOutputs:
         return self.bufs[d]
 
 
-def weight_int8pack_mm_group(activations, weights, scales, outs=None, device_index=None, bufs=None, independent=0):
+class HostGathered:
+    """[m, n_total] result buffers (`depth` of them, used in turn) in page-locked host memory that every rank of the node
+    maps: one shared-memory segment, registered with CUDA in every process. A grouped sharded launch given such buffers
+    (`weight_int8pack_mm_group(..., host_outs=...)`) stores each rank's columns straight into them, so after channel.wait()
+    and synchronize() every process reads the whole result from `tensors[buf]` with no copy down: a node delivers a result
+    to its host once, not once per rank. Collective: every rank of the channel constructs it."""
+
+    def __init__(self, m, n_total, dtype, channel, depth=2):
+        import ctypes
+        import os
+
+        from . import cabi
+
+        self._c, self.channel, self.m, self.n_total, self.depth = cabi, channel, m, n_total, depth
+        esize = torch.empty((), dtype=dtype).element_size()
+        each = (m * n_total * esize + 4095) // 4096 * 4096
+        names = [None]
+        if channel.rank == 0:
+            names[0] = f"/dev/shm/tvb200_{os.getpid()}_{id(self):x}"
+        dist.broadcast_object_list(names, src=dist.get_global_rank(channel.group, 0) if channel.group is not None else 0, group=channel.group)
+        self.path = names[0]
+        if channel.rank == 0:
+            self._file = torch.from_file(self.path, shared=True, size=each * depth, dtype=torch.uint8)
+        barrier(channel.group)
+        if channel.rank != 0:
+            self._file = torch.from_file(self.path, shared=True, size=each * depth, dtype=torch.uint8)
+        barrier(channel.group)
+        if channel.rank == 0:
+            os.unlink(self.path)  # (the mappings keep the memory)
+        dev = ctypes.c_void_p(0)
+        cabi.check(cabi.lib().tvb_host_register(self._file.data_ptr(), each * depth, ctypes.byref(dev)))
+        self._registered = self._file.data_ptr()
+        self.tensors = [self._file[i * each:i * each + m * n_total * esize].view(dtype).view(m, n_total) for i in range(depth)]
+        self.dev_ptrs = [dev.value + i * each for i in range(depth)]
+        self.calls = 0
+
+    def close(self):
+        if self._registered is not None:
+            self._c.lib().tvb_host_unregister(self._registered)
+            self._registered = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def weight_int8pack_mm_group(activations, weights, scales, outs=None, device_index=None, bufs=None, independent=0, host_outs=None):
     """Up to four int8 weight-only decode products of one shape in ONE launch (tvb_qmm8_group / tvb_qmm8_group_gather):
     products that do not depend on each other, such as one decoding step's requests against different weights. Product i is
     activations[i] [m_i, k] (m_i <= 16) times weights[i] [n, k] int8 with scales[i] [n]; n, k and the dtype are shared.
@@ -259,7 +307,9 @@ def weight_int8pack_mm_group(activations, weights, scales, outs=None, device_ind
     finished, and no copy is needed to bring the result down (it is there after synchronize()). Sharded: `outs` are GatheredOutputs
     of one channel, one per product (weights[i] being this rank's rows), `bufs` which buffer of each to write (default: in
     turn); returns the [m_i, N] buffers, valid for the channel's next sharded product at once and for anything else after
-    channel.wait(). `independent`: as for GatheredOutputs.weight_int8pack_mm, counted before the launch's first product."""
+    channel.wait(). `independent`: as for GatheredOutputs.weight_int8pack_mm, counted before the launch's first product.
+    `host_outs` (sharded): one HostGathered per product; the launch also stores every product's columns into its buffer
+    `bufs[i]` in host memory (see HostGathered)."""
     import ctypes
 
     from . import cabi
@@ -288,6 +338,12 @@ def weight_int8pack_mm_group(activations, weights, scales, outs=None, device_ind
         keep.append(ptrs)
         items[i].a, items[i].a_sm, items[i].b, items[i].scales = a.data_ptr(), a.stride(0), w.data_ptr(), s.data_ptr()
         items[i].c_ranks, items[i].m = ctypes.cast(ptrs, ctypes.POINTER(ctypes.c_void_p)), a.shape[0]
+        if host_outs is not None:
+            h = host_outs[i]
+            assert sharded and h.m == a.shape[0] and h.n_total == out.n_total
+            hd = (h.calls % h.depth) if bufs is None else bufs[i]
+            h.calls += 1
+            items[i].c_host = h.dev_ptrs[hd]
         results.append(buf)
     if sharded:
         ch = outs[0].channel
