@@ -1038,8 +1038,14 @@ def main():
 
     # ---- end to end through the C ABI / the ops: A from pinned host memory, C back to the host, every step
     out_pinned = {m: torch.empty(m, N_OUT, dtype=torch.bfloat16).pin_memory() for m in MS}
-    host_gathered = ({m: shard.HostGathered(m, N_OUT, torch.bfloat16, channel) for m in MS}
-                     if fused is not None and "group" in timed and os.environ.get("TVB200_HOST_GATHER", "1") != "0" else None)
+    host_gathered = None
+    if fused is not None and "group" in timed and os.environ.get("TVB200_HOST_GATHER", "1") != "0":
+        try:  # (every rank raises or none does: see HostGathered)
+            host_gathered = {m: shard.HostGathered(m, N_OUT, torch.bfloat16, channel) for m in MS}
+        except RuntimeError as exc:
+            host_gathered = None
+            if rank == 0:
+                print(f"bench.py: no shared host buffer ({exc}); every rank copies the results down", file=sys.stderr)
 
     def e2e_body(g, mode):
         # every product's A goes up from page-locked memory (into the buffers the step reads) and its C comes back into

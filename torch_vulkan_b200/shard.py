@@ -265,28 +265,47 @@ class HostGathered:
         self._c, self.channel, self.m, self.n_total, self.depth = cabi, channel, m, n_total, depth
         esize = torch.empty((), dtype=dtype).element_size()
         each = (m * n_total * esize + 4095) // 4096 * 4096
+        # Every step that can fail is tried locally and the ranks agree on the outcome afterwards, so that a node without
+        # usable shared memory makes every rank raise the same error instead of leaving some of them in a collective.
+        self._file, self._registered, ok, why = None, None, True, ""
         names = [None]
         if channel.rank == 0:
-            names[0] = f"/dev/shm/tvb200_{os.getpid()}_{id(self):x}"
-        dist.broadcast_object_list(names, src=dist.get_global_rank(channel.group, 0) if channel.group is not None else 0, group=channel.group)
+            try:
+                path = f"/dev/shm/tvb200_{os.getpid()}_{id(self):x}"
+                self._file = torch.from_file(path, shared=True, size=each * depth, dtype=torch.uint8)
+                names[0] = path
+            except Exception as exc:  # noqa: BLE001
+                why = str(exc)
+        src = dist.get_global_rank(channel.group, 0) if channel.group is not None else 0
+        dist.broadcast_object_list(names, src=src, group=channel.group)
         self.path = names[0]
-        if channel.rank == 0:
-            self._file = torch.from_file(self.path, shared=True, size=each * depth, dtype=torch.uint8)
-        barrier(channel.group)
+        if self.path is None:
+            raise RuntimeError("HostGathered: rank 0 could not create a shared-memory file " + why)
         if channel.rank != 0:
-            self._file = torch.from_file(self.path, shared=True, size=each * depth, dtype=torch.uint8)
+            try:
+                self._file = torch.from_file(self.path, shared=True, size=each * depth, dtype=torch.uint8)
+            except Exception as exc:  # noqa: BLE001
+                ok, why = False, str(exc)
         barrier(channel.group)
         if channel.rank == 0:
             os.unlink(self.path)  # (the mappings keep the memory)
         dev = ctypes.c_void_p(0)
-        cabi.check(cabi.lib().tvb_host_register(self._file.data_ptr(), each * depth, ctypes.byref(dev)))
-        self._registered = self._file.data_ptr()
+        if ok:
+            if cabi.lib().tvb_host_register(self._file.data_ptr(), each * depth, ctypes.byref(dev)) == 0:
+                self._registered = self._file.data_ptr()
+            else:
+                ok, why = False, cabi.lib().tvb_last_error().decode("utf-8", "replace")
+        flags = [None] * channel.world
+        dist.all_gather_object(flags, (ok, why), group=channel.group)
+        if not all(f[0] for f in flags):
+            self.close()
+            raise RuntimeError("HostGathered: " + "; ".join(f[1] for f in flags if not f[0]))
         self.tensors = [self._file[i * each:i * each + m * n_total * esize].view(dtype).view(m, n_total) for i in range(depth)]
         self.dev_ptrs = [dev.value + i * each for i in range(depth)]
         self.calls = 0
 
     def close(self):
-        if self._registered is not None:
+        if getattr(self, "_registered", None) is not None:
             self._c.lib().tvb_host_unregister(self._registered)
             self._registered = None
 
