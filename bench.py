@@ -1218,6 +1218,7 @@ def main():
                                                   ("a grouped launch holds the step's three products: compare with three times the bytes of a product" if mode == "group"
                                                    else "mean of the M = 1, 4, 16 launches") + "), read from profiles/qmm8_skinny_config2.md")
             line["roofline"]["bytes_per_launch"] = step_bytes if mode != "per_product" else step_bytes / len(MS)
+            line["roofline"]["launch_us"] = avg_launch_ms * 1e3 * (len(MS) if mode != "per_product" else 1)
         if not args.no_cpu and world == 1:
             if torch.get_num_threads() < host_threads():
                 torch.set_num_threads(host_threads())
