@@ -13,12 +13,14 @@
 //    16-row operand, tokens as the 8-column operand), float32 accumulators.
 //    Work is the list of (256-row tile, 128-k chunk) units cut into equal contiguous
 //    ranges, one per CTA, so every SM streams the same number of bytes whatever n is;
-//    a tile shared by several CTAs is finished by the last of them to arrive, which adds
-//    the partial sums in descending CTA order (deterministic), from scratch memory. Nobody
-//    ever waits for another CTA. Two shortcuts keep the consumers streaming: a range that
-//    leaves a shared tile behind hands the arrival to an otherwise idle agent warp and goes
-//    on at once; a CTA whose last tile has already been reached by all its other
-//    contributors fetches their sums under its last chunks and finishes from registers. The scale
+//    a tile shared by several CTAs is finished by the CTA that holds its first k (for which
+//    they are the last units of its range): the others leave their partial sums in scratch and
+//    count themselves in without waiting for an answer; the finisher waits (briefly: all started
+//    together with as many units; bounded) until all are counted and adds their sums in
+//    descending CTA order, its own last, from registers (deterministic). Two shortcuts keep the
+//    consumers streaming: a range that leaves a shared tile behind hands the arrival to an
+//    otherwise idle agent warp and goes on at once; a finisher whose tile has already been
+//    reached by all other contributors fetches their sums under its last chunks. The scale
 //    multiplies the finished sum: (sum a*b) * s instead of sum a*(b*s); both are within
 //    the float32 rounding the reference's tests allow (tests/python/test_quant.py:36-40).
 //  * qmm8_plain_kernel: any shape, stride and dtype (float32 A included), one warp per
@@ -426,61 +428,17 @@ __global__ void __launch_bounds__((NWARPS + 2) * 32, 1)
   }
 
   if (warp == NWARPS + 1) {
-    // ---------------- agent: arrival (and, rarely, completion) of the tile that this CTA's first segment shares
+    // ---------------- agent: arrival at the tile that this CTA's first segment shares
     // A range that starts inside a tile and goes on beyond it leaves that tile's partial sums in scratch and moves on
-    // at once; this warp counts the arrival in the consumers' stead. Should it turn out to be the tile's last arrival
-    // (the other contributors normally come much later), this warp alone completes the tile.
+    // at once; this warp counts the arrival in the consumers' stead.
     const int tile = unit_tile(u0, p.chunks, small), c0 = static_cast<int>(u0 - static_cast<long long>(tile) * p.chunks);
     const int c1 = static_cast<int>(min(static_cast<long long>(p.chunks), c0 + (u1 - u0)));
     const bool left_behind = !(c0 == 0 && c1 == p.chunks) && u0 + (c1 - c0) < u1;
     if (left_behind && ptx::mbar_wait(agent_bar, 0, abort_flag)) {
       ptx::grid_dependency_wait();
-      const long long tile_first_unit = static_cast<long long>(tile) * p.chunks;
-      const int cta_first = range_owner(tile_first_unit, units, grid, small);
-      const int cta_last = range_owner(tile_first_unit + p.chunks - 1, units, grid, small);
-      int last = 0;
       if (lane == 0) {
         __threadfence();  // (cumulative over the consumers' stores, which the barrier ordered before this)
-        last = atomicAdd(&p.counters[tile], 1) == cta_last - cta_first;
-        if (last) atomicExch(&p.counters[tile], 0);
-      }
-      last = __shfl_sync(0xffffffffu, last, 0);
-      if (last) {
-        __threadfence();
-        int product, lt;
-        split(tile, product, lt);
-        const int g = lane >> 2, t = lane & 3, rg = (g >> 1) | ((g & 1) << 2);
-        for (int w = 0; w < NWARPS; w++)  // this warp plays every consumer warp's part in turn
-#pragma unroll
-          for (int rb = 0; rb < RW; rb++)
-#pragma unroll
-            for (int nt = 0; nt < NT; nt++) {
-              float4 sum = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-              for (int cta = cta_last; cta >= cta_first; cta--) {  // the one fixed order of additions
-                const bool cta_first_segment = unit_tile(range_start(cta, units, grid, small), p.chunks, small) == tile;
-                const float4* theirs = reinterpret_cast<const float4*>(
-                    p.partials + (static_cast<size_t>(cta) * 2 + (cta_first_segment ? 0 : 1)) * Cfg::kPartialFloats);
-                const float4 v = __ldcg(&theirs[((w * RW + rb) * NT + nt) * 32 + lane]);
-                sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
-              }
-              const float vals[4] = {sum.x, sum.y, sum.z, sum.w};
-#pragma unroll
-              for (int half = 0; half < 2; half++) {
-                const int col = lt * Cfg::kRowsPerTile + (w * RW + rb) * 16 + rg + 8 * half;
-                if (col >= p.n) continue;
-                const float scale = load_float<DT>(scales_of(product), col);
-#pragma unroll
-                for (int i = 0; i < 2; i++) {
-                  const int token = p.m0 + nt * 8 + 2 * t + i;
-                  if (token >= rows_of(product)) continue;
-                  const float v = vals[2 * half + i] * scale;
-                  uint16_t bits = DT == TVB_BF16 ? f32_to_bf16_bits(v) : f32_to_f16_bits(v);
-                  if constexpr (ADDS) bits = skinny_epilogue<DT>(p, bits, token, col);
-                  const int64_t off = static_cast<int64_t>(token) * p.c_ld + p.c_col0 + col;
-                  for (int r = 0; r < p.ndest; r++) static_cast<uint16_t*>(out_of(product, r))[off] = bits;
-                }
-              }
-            }
+        atomicAdd(&p.counters[tile], 1);  // (this CTA holds the tile's last k: the tile's finisher is another CTA, see below)
       }
     }
     if (p.done != nullptr) {
@@ -659,6 +617,49 @@ __global__ void __launch_bounds__((NWARPS + 2) * 32, 1)
         for (int nt = 0; nt < NT; nt++)
 #pragma unroll
           for (int i = 0; i < 4; i++) acc[rb][nt][i] = pre[rb][nt][i] + acc[rb][nt][i];
+    } else if (!whole_tile && cta_first == static_cast<int>(blockIdx.x)) {
+      // This CTA holds the tile's first k, which are the last units of its range: it finishes the tile. The other
+      // contributors arrive at about the same time (they started together and have as many units), so the wait is
+      // short, and bounded; then their sums are added in descending CTA order and this CTA's own last, from registers.
+      // (With "whoever arrives last finishes", the last arriver paid for a round trip of its own sums through scratch,
+      // an atomic whose answer it had to wait for and a fence before it could fetch anything: 1.3 us more per launch.)
+      int* flag = last_flag + (segment & 1);
+      if (threadIdx.x == 0) {
+        const int want = cta_last - cta_first;
+        int seen = 0, done = 0;
+        const long long start = clock64();
+        for (;;) {
+          asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(seen) : "l"(p.counters + tile) : "memory");
+          if (seen == want) {
+            done = 1;
+            break;
+          }
+          if (*abort_flag != 0 || clock64() - start > ptx::kWaitLimitCycles) break;
+        }
+        if (done) atomicExch(&p.counters[tile], 0);  // zero again for the next launch: nobody else touches it any more
+        else *abort_flag = 1;
+        *flag = done;
+      }
+      ptx::named_bar_sync(1, NWARPS * 32);
+      const bool arrived = *flag != 0;
+      segment++;
+      if (!arrived) {
+        ok = false;
+        break;
+      }
+#pragma unroll
+      for (int rb = 0; rb < RW; rb++)
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+          for (int i = 0; i < 4; i++) pre[rb][nt][i] = 0.0f;
+      add_partials<Cfg, RW, NT>(pre, p.partials, cta_last, cta_first + 1, tile, units, grid, small, p.chunks, warp, lane);
+#pragma unroll
+      for (int rb = 0; rb < RW; rb++)
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+          for (int i = 0; i < 4; i++) acc[rb][nt][i] = pre[rb][nt][i] + acc[rb][nt][i];
     } else if (!whole_tile) {
       float4* mine = reinterpret_cast<float4*>(p.partials + (static_cast<size_t>(blockIdx.x) * 2 + (first_segment ? 0 : 1)) *
                                                                 Cfg::kPartialFloats);
@@ -668,36 +669,18 @@ __global__ void __launch_bounds__((NWARPS + 2) * 32, 1)
         for (int nt = 0; nt < NT; nt++)
           __stcg(&mine[((warp * RW + rb) * NT + nt) * 32 + lane],
                  make_float4(acc[rb][nt][0], acc[rb][nt][1], acc[rb][nt][2], acc[rb][nt][3]));
+      finish = false;
       if (u + (c1 - c0) < u1) {
         // More of the range follows: leave the tile to the agent warp (which counts this arrival) and go on at once.
         __syncwarp();
         if (lane == 0) ptx::mbar_arrive(agent_bar);
-        finish = false;
       } else {
         // All consumer threads have stored their partial sums once they pass the barrier; one thread then publishes
-        // them: its gpu-scope fence is cumulative over what the barrier ordered before it.
+        // them: its gpu-scope fence is cumulative over what the barrier ordered before it. Nobody waits for the answer.
         ptx::named_bar_sync(1, NWARPS * 32);
-        int* flag = last_flag + (segment & 1);  // (alternating slots: no barrier needed before the next segment rewrites it)
         if (threadIdx.x == 0) {
           __threadfence();
-          int arrived = atomicAdd(&p.counters[tile], 1);
-          int last = arrived == cta_last - cta_first;
-          if (last) atomicExch(&p.counters[tile], 0);  // zero again for the next launch
-          *flag = last;
-        }
-        ptx::named_bar_sync(1, NWARPS * 32);
-        finish = *flag != 0;
-        segment++;
-        if (finish) {
-          __threadfence();
-#pragma unroll
-          for (int rb = 0; rb < RW; rb++)
-#pragma unroll
-            for (int nt = 0; nt < NT; nt++)
-#pragma unroll
-              for (int i = 0; i < 4; i++) acc[rb][nt][i] = 0.0f;
-          // fixed order: the sum does not depend on who came last
-          add_partials<Cfg, RW, NT>(acc, p.partials, cta_last, cta_first, tile, units, grid, small, p.chunks, warp, lane);
+          atomicAdd(&p.counters[tile], 1);
         }
       }
     }
