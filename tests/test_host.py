@@ -114,3 +114,25 @@ def test_comm_entry_points_fail_cleanly_without_a_gpu():
         assert lib.tvb_comm_init_rank(0, ident.raw, 1, 0, 100, ctypes.byref(handle)) == -1
         assert len(lib.tvb_last_error()) > 0
     assert lib.tvb_comm_abort(None) == 0 and lib.tvb_comm_destroy(None) == 0
+
+
+def test_grouped_launch_and_host_registration_check_their_arguments():
+    """What tvb_qmm8_group / tvb_qmm8_group_gather / tvb_host_register refuse before they touch a device."""
+    import ctypes
+
+    from torch_vulkan_b200 import cabi
+
+    lib = cabi.lib()
+    items = (cabi.TvbGroupItem * 5)()
+    assert lib.tvb_qmm8_group(0, cabi.BF16, items, 0, 128, 128) == -1 and b"1 to 4 products" in lib.tvb_last_error()
+    assert lib.tvb_qmm8_group(0, cabi.BF16, items, 5, 128, 128) == -1 and b"1 to 4 products" in lib.tvb_last_error()
+    assert lib.tvb_qmm8_group(0, cabi.F32, items, 2, 128, 128) == -1 and b"float16 or bfloat16" in lib.tvb_last_error()
+    assert lib.tvb_qmm8_group(0, cabi.BF16, None, 2, 128, 128) == -1
+    flags = (ctypes.c_void_p * 2)(0, 0)
+    assert lib.tvb_qmm8_group_gather(0, cabi.BF16, items, 2, flags, 9, 0, None, 0, 128, 128) == -1
+    assert b"1 to 8 ranks" in lib.tvb_last_error()
+    assert lib.tvb_qmm8_group_gather(0, cabi.BF16, items, 2, flags, 2, 0, None, 0, 128, 128) == -1
+    assert b"NULL pointer" in lib.tvb_last_error()
+    out = ctypes.c_void_p(0)
+    assert lib.tvb_host_register(None, 4096, ctypes.byref(out)) == -1 and b"tvb_host_register" in lib.tvb_last_error()
+    assert lib.tvb_host_unregister(None) == -1
